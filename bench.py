@@ -1,0 +1,497 @@
+"""Benchmark of the chunk-level mixed-precision optimizer step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N = 1: the GPT-2-XL-shaped chunk set (1 557 611 200 parameters in 64 MiB fp16 chunks, fp32 master and
+moments, AdamW wd 0.01, gradients ~ N(0, 1e-3) * 2^16).  One step = for every chunk the reduce epilogue
+(copy of the reduced gradient block into the shard fused with the inf/nan probe), then the device-side
+decision / loss-scaler update, then ONE fused unscale + AdamW + fp16 copy-back launch over all chunks.
+N > 1 (under torchrun): the OPT-13B-shaped chunk set sharded over the ranks; one step = per chunk
+reduce-scatter (rank average) -> probe, the decision, then per chunk fused update -> all-gather,
+pipelined on side streams.
+
+Prints ONE JSON line (rank 0).  ``value`` is whole-job parameters per second with all inputs resident
+in HBM; ``e2e`` is the same step through ``ChunkStepEngine.step_from_host`` with pinned host buffers on
+both ends (gradients in, updated low-precision parameters out).  ``--impl reference`` times the
+reference's CPU Adam path (torch.optim.AdamW on the host cores — ColossalAI's CPUAdam is not installable
+offline — next to the C oracle with all threads) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+GPT2XL_PARAMS = 48 * (12 * 1600 * 1600 + 13 * 1600) + 50257 * 1600 + 1024 * 1600 + 2 * 1600
+OPT13B_PARAMS = 40 * (12 * 5120 * 5120 + 13 * 5120) + 50272 * 5120 + 2050 * 5120 + 2 * 5120
+CHUNK_1GPU = 32 * 1024 * 1024    # 64 MiB of fp16
+CHUNK_SHARDED = 256 * 1024 * 1024    # 512 MiB of fp16
+BYTES_PER_ELEM = 28    # g 2 + p/m/v 12 read, p/m/v 12 + p16 2 written
+
+
+def load_peaks():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)['hbm_gbs']), 'measured'
+    return 6650.0, 'fallback'
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while timing runs."""
+    QUERY = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,'
+             'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+             'clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix='.csv')
+            os.close(fd)
+            self.proc = subprocess.Popen(['nvidia-smi', '-i', str(self.index), f'--query-gpu={self.QUERY}',
+                                          '--format=csv,noheader,nounits', '-lms', '200'],
+                                         stdout=open(self.path, 'w'), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': [], 'samples': 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        sm, reasons, mx, power = [], set(), None, []
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(',')]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx = float(parts[1])
+                    power.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[3:7]):
+                    if val.lower().startswith('active'):
+                        reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm),
+                       power_w_max=max(power))
+        return out
+
+
+def chunk_layout(total, chunk, world):
+    """(n_chunks, [valid_end of this layout's LAST-rank-agnostic full chunk list]): used elements per chunk."""
+    n = (total + chunk - 1) // chunk
+    used = [chunk] * (n - 1) + [total - chunk * (n - 1)]
+    return n, used
+
+
+def valid_end(used, shard, rank):
+    begin = shard * rank
+    return max(0, min(shard, used - begin))
+
+
+def synth_shard(n, device, seed, scale, sigma, dtype):
+    gen = torch.Generator(device=device).manual_seed(seed)
+    master = torch.empty(n, device=device, dtype=torch.float32).normal_(0.0, 0.02, generator=gen)
+    return master, gen
+
+
+def synth_grad(n, device, gen, scale, sigma, dtype, out=None):
+    g = torch.empty(n, device=device, dtype=torch.float32).normal_(0.0, sigma, generator=gen).mul_(scale)
+    if out is None:
+        return g.to(dtype)
+    out.copy_(g)
+    return out
+
+
+# ------------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------------
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    from elixir_b200 import kernels as K
+    from elixir_b200.engine import ChunkStepEngine
+    from elixir_b200.scaler import DynamicGradScaler
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    if world != args.gpus:
+        raise SystemExit(f'--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run')
+    torch.cuda.set_device(local_rank)
+    device = torch.device('cuda', local_rank)
+    group = None
+    if world > 1:
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        dist.init_process_group('nccl', rank=rank, world_size=world, device_id=device)
+        group = dist.group.WORLD
+
+    dtype = torch.float16
+    if world == 1:
+        workload, total, chunk, scale, wd = 'gpt2xl_chunks_1gpu', GPT2XL_PARAMS, CHUNK_1GPU, 65536.0, 0.01
+    else:
+        workload, total, chunk, scale, wd = f'opt13b_chunks_sharded_w{world}', OPT13B_PARAMS, CHUNK_SHARDED, 1024.0, 0.0
+    sigma = 1e-3
+    n_chunks, used = chunk_layout(total, chunk, world)
+    shard = chunk // world
+
+    scaler = DynamicGradScaler(initial_scale=scale, growth_factor=2, backoff_factor=0.5, growth_interval=1000,
+                               min_scale=1, max_scale=2**24, hysteresis=2)
+    engine = ChunkStepEngine(device, dtype, scaler, process_group=group)
+    for c in range(n_chunks):
+        master, gen = synth_shard(shard, device, args.seed + 1000 * rank + c, scale, sigma, dtype)
+        nv = valid_end(used[c], shard, rank)
+        if nv < shard:
+            master[nv:].zero_()
+        lowp = torch.empty(shard, dtype=dtype, device=device)
+        K.cast_copyback(master, lowp)
+        engine.add_shard(master, lowp, nv, [(0, nv, 0)] if nv else [])
+    engine.finalize()
+    engine.set_hyper([K.hyper(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=wd, adamw_mode=True)])
+    owned = sum(valid_end(used[c], shard, rank) for c in range(n_chunks))
+
+    # gradient sources
+    if world == 1:
+        grad_blocks = []
+        for c in range(n_chunks):
+            gen = torch.Generator(device=device).manual_seed(args.seed + 7919 * (c + 1))
+            grad_blocks.append(synth_grad(shard, device, gen, scale, sigma, dtype))
+        gather_blocks = None
+    else:
+        pool = 4
+        grad_pool, gather_pool = [], []
+        for b in range(pool):
+            gen = torch.Generator(device=device).manual_seed(args.seed + 7919 * (b + 1) + 31 * rank)
+            grad_pool.append(synth_grad(chunk, device, gen, scale, sigma, dtype))
+            gather_pool.append(torch.empty(chunk, dtype=dtype, device=device))
+        grad_blocks = [grad_pool[c % pool] for c in range(n_chunks)]
+        gather_blocks = [gather_pool[c % pool] for c in range(n_chunks)]
+
+    adam_events = []
+
+    def one_step(record=False):
+        if world == 1:
+            for c in range(n_chunks):
+                engine.land(c, grad_blocks[c])
+            engine.begin_step()
+            if record:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                engine.update()
+                b.record()
+                adam_events.append((a, b))
+            else:
+                engine.update()
+            engine.end_step()
+        else:
+            engine.step_sharded(grad_blocks, gather_blocks)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        barrier()
+        ms = a.elapsed_time(b)
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        return ms
+
+    for _ in range(args.warmup):
+        one_step()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    total_ms = timed(lambda: one_step(record=True), args.steps)
+    clocks = sampler.stop()
+    ms_per_step = total_ms / args.steps
+    ctl = engine.read_control()
+    if ctl.status or ctl.skipped_steps:
+        raise SystemExit(f'bench: unexpected control state status={ctl.status} skipped={ctl.skipped_steps}')
+
+    peak, peak_kind = load_peaks()
+    result = {
+        'metric': 'chunk Adam Gparams/s',
+        'value': total / (ms_per_step * 1e-3) / 1e9,
+        'unit': 'Gparams/s',
+        'n_gpus': world,
+        'steps': args.steps,
+        'warmup': args.warmup,
+        'ms_per_step': ms_per_step,
+        'higher_is_better': True,
+        'scaling': 'weak' if world == 1 else 'strong',
+        'vs_baseline': None,
+        'dtype': 'f32',
+        'data': 'synthetic',
+        'config': {
+            'workload': workload,
+            'params': total,
+            'chunk_elems': chunk,
+            'n_chunks': n_chunks,
+            'grad_dtype': 'fp16',
+            'optimizer': f'AdamW lr1e-3 b(0.9,0.999) eps1e-8 wd{wd}',
+            'loss_scale': scale,
+            'l2_policy': 'inputs larger than L2 (state per GPU %.1f GB)' % (engine.n_elements() * 14 / 1e9),
+            'layout': 'flat packing, tensors may straddle chunks',
+        },
+        'clocks': clocks,
+    }
+
+    if world == 1:
+        adam_ms = statistics.mean(a.elapsed_time(b) for a, b in adam_events)
+        n_elems = engine.n_elements()
+        achieved = n_elems * BYTES_PER_ELEM / (adam_ms * 1e-3) / 1e9
+        result['roofline'] = {
+            'bound': 'hbm', 'kernel': 'adam_kernel', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s',
+            'frac': achieved / peak, 'peak_kind': peak_kind, 'ms_per_launch': adam_ms,
+            'elements_per_launch': n_elems, 'bytes_per_element': BYTES_PER_ELEM,
+            'traffic': args.traffic_per_launch, 'frac_of_8TBs_nominal': achieved / 8000.0,
+        }
+        result['adam_gparams_per_s'] = n_elems / (adam_ms * 1e-3) / 1e9
+        result['gpu_launches'] = args.steps * (n_chunks + 2)
+    else:
+        bus_bytes = 2 * chunk * (world - 1) / world * n_chunks    # per collective kind, per rank, per step
+        result['collective'] = {
+            'per_step_bus_bytes_rs': bus_bytes, 'per_step_bus_bytes_ag': bus_bytes,
+            'combined_bus_gbs': 2 * bus_bytes / (ms_per_step * 1e-3) / 1e9,
+            'nominal_gbs_per_direction': 900.0, 'measured_peer_copy_gbs': 770.0,
+        }
+        adam_bytes = engine.n_elements() * BYTES_PER_ELEM
+        result['roofline'] = {
+            'bound': 'nvlink', 'achieved': 2 * bus_bytes / (ms_per_step * 1e-3) / 1e9, 'peak': 770.0,
+            'unit': 'GB/s', 'frac': 2 * bus_bytes / (ms_per_step * 1e-3) / 1e9 / 770.0, 'peak_kind': 'measured',
+            'traffic': None, 'adam_hbm_ms_at_peak': adam_bytes / (peak * 1e9) * 1e3,
+        }
+        result['gpu_launches'] = args.steps * (2 * n_chunks + 1)
+
+    # ---- end to end: pinned host buffers on both ends --------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, scale, sigma, total, timed,
+                      grad_blocks, gather_blocks)
+    result['e2e'] = e2e
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        result['cpu_baseline'] = cpu_baseline(args, chunk, scale, sigma, wd, steps=3, chunks=4)
+    if rank == 0:
+        print(json.dumps(result))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, scale, sigma, total, timed,
+            grad_blocks=None, gather_blocks=None):
+    """The same step with pinned host buffers on both ends, H2D and D2H inside the timed region.
+    1 GPU: reduced fp16 gradients of every shard come from the host, updated fp16 parameters go back.
+    Sharded: every rank's replicated gradient blocks come from the host before their reduce-scatter and
+    every rank's updated shard goes back after the update (the all-gather still runs on the device)."""
+    pool = min(n_chunks, 8 if world == 1 else 4)
+    in_elems = shard if world == 1 else chunk
+    host_in, host_out = [], []
+    for b in range(pool):
+        gen = torch.Generator().manual_seed(args.seed + 104729 * (b + 1) + rank)
+        g = torch.empty(in_elems, dtype=torch.float32).normal_(0.0, sigma, generator=gen).mul_(scale).to(dtype)
+        host_in.append(g.pin_memory())
+        host_out.append(torch.empty(shard, dtype=dtype).pin_memory())
+    grads = [host_in[c % pool] for c in range(n_chunks)]
+    outs = [host_out[c % pool] for c in range(n_chunks)]
+    if world == 1:
+        fn = lambda: engine.step_from_host(grads, outs)
+    else:
+        fn = lambda: engine.step_sharded(grad_blocks, gather_blocks, host_grads=grads, host_params=outs)
+    steps = max(1, min(args.steps, args.e2e_steps))
+    for _ in range(2):
+        fn()
+    ms = timed(fn, steps) / steps
+    ctl = engine.read_control()
+    if ctl.status:
+        raise SystemExit(f'bench e2e: status {ctl.status}')
+    return {
+        'value': total / (ms * 1e-3) / 1e9, 'unit': 'Gparams/s', 'ms_per_step': ms, 'steps': steps,
+        'h2d_bytes_per_step': n_chunks * in_elems * 2 * world, 'd2h_bytes_per_step': n_chunks * shard * 2 * world,
+        'api': 'ChunkStepEngine.step_from_host' if world == 1 else 'ChunkStepEngine.step_sharded(host_grads=, host_params=)',
+        'note': 'pinned fp16 gradients in, updated fp16 parameters out; fp32 master and moments stay in HBM',
+    }
+
+
+# ------------------------------------------------------------------------------------------------------
+# CPU arms
+# ------------------------------------------------------------------------------------------------------
+
+
+def _cpu_inputs(chunks, chunk, scale, sigma, seed):
+    sets = []
+    for c in range(chunks):
+        gen = torch.Generator().manual_seed(seed + c)
+        master = torch.randn(chunk, generator=gen) * 0.02
+        grad = (torch.randn(chunk, generator=gen) * sigma * scale).half()
+        sets.append((master, grad))
+    return sets
+
+
+def cpu_torch_adamw(sets, scale, wd, steps):
+    """The reference's CPU path with torch.optim.AdamW standing in for ColossalAI CPUAdam: finite check of
+    the fp16 gradients, unscale to fp32, AdamW on the fp32 masters, fp16 copy-back."""
+    params = [torch.nn.Parameter(m.clone()) for m, _ in sets]
+    best = None
+    for kwargs in (dict(foreach=True), dict(fused=True)):
+        try:
+            opt = torch.optim.AdamW(params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=wd, **kwargs)
+        except (RuntimeError, TypeError):
+            continue
+        lowp = [g.clone() for _, g in sets]
+        times = []
+        for s in range(steps + 1):
+            for buf, (_, g) in zip(lowp, sets):
+                buf.copy_(g)
+            t0 = time.perf_counter()
+            overflow = any(not torch.isfinite(buf).all().item() for buf in lowp)
+            if not overflow:
+                for p, buf in zip(params, lowp):
+                    p.grad = buf.float().div_(scale)
+                opt.step()
+            for p, buf in zip(params, lowp):
+                buf.copy_(p.data)
+            times.append(time.perf_counter() - t0)
+        t = statistics.mean(times[1:])
+        if best is None or t < best[0]:
+            best = (t, 'torch.optim.AdamW(%s)' % ','.join(kwargs))
+    return best
+
+
+def cpu_oracle(sets, scale, wd, steps):
+    from oracle import oracle as orc
+    from elixir_b200 import kernels as K
+    cs = orc.ChunkSet(torch.float16)
+    lowp = []
+    for master, g in sets:
+        n = master.numel()
+        buf = g.clone()
+        cs.add_chunk(master.clone(), torch.zeros(n), torch.zeros(n), buf, n, [(0, n, 0)])
+        lowp.append(buf)
+    ctl = orc.new_ctl(scale)
+    cfg = K.scaler_cfg(True)
+    hyper = [K.hyper(weight_decay=wd)]
+    times = []
+    for s in range(steps + 1):
+        for buf, (_, g) in zip(lowp, sets):
+            buf.copy_(g)
+        t0 = time.perf_counter()
+        cs.step(ctl, cfg, hyper, probe=True, f64=False)
+        times.append(time.perf_counter() - t0)
+    return statistics.mean(times[1:]), orc.num_threads()
+
+
+def cpu_baseline(args, chunk, scale, sigma, wd, steps, chunks):
+    torch.set_num_threads(os.cpu_count())
+    sets = _cpu_inputs(chunks, chunk, scale, sigma, args.seed)
+    n = chunks * chunk
+    t_torch, how = cpu_torch_adamw(sets, scale, wd, steps)
+    t_orc, threads = cpu_oracle(sets, scale, wd, steps)
+    best = min(t_torch, t_orc)
+    return {
+        'value': n / best / 1e9, 'unit': 'Gparams/s', 'cores': os.cpu_count(), 'kind': 'port',
+        'sample': f'{chunks} chunks x {chunk} elements of the same workload, {steps} timed steps after 1 warm-up',
+        'torch_adamw_gparams_per_s': n / t_torch / 1e9, 'torch_variant': how,
+        'c_oracle_gparams_per_s': n / t_orc / 1e9, 'c_oracle_threads': threads,
+        'note': 'ColossalAI CPUAdam/HybridAdam is not installable offline; torch.optim.AdamW on the host cores '
+                'and the OpenMP C restatement of the same step stand in, the faster one is reported',
+    }
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path on the host cores (rank 0 only)."""
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    world = args.gpus
+    if world == 1:
+        workload, total, chunk, scale, wd = 'gpt2xl_chunks_1gpu', GPT2XL_PARAMS, CHUNK_1GPU, 65536.0, 0.01
+    else:
+        workload, total, chunk, scale, wd = f'opt13b_chunks_sharded_w{world}', OPT13B_PARAMS, CHUNK_SHARDED, 1024.0, 0.0
+    chunks = 4 if world == 1 else 1
+    sample_chunk = chunk if world == 1 else chunk // 2
+    torch.set_num_threads(os.cpu_count())
+    sets = _cpu_inputs(chunks, sample_chunk, scale, 1e-3, args.seed)
+    n = chunks * sample_chunk
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    t_torch, how = cpu_torch_adamw(sets, scale, wd, steps)
+    t_orc, threads = cpu_oracle(sets, scale, wd, steps)
+    best = min(t_torch, t_orc)
+    value = n / best / 1e9
+    line = {
+        'impl': 'reference', 'metric': 'chunk Adam Gparams/s', 'value': value, 'unit': 'Gparams/s', 'n_gpus': world,
+        'steps': steps, 'warmup': 1, 'ms_per_step': best * 1e3 * (total / n), 'higher_is_better': True,
+        'scaling': 'weak' if world == 1 else 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': workload, 'params': total, 'chunk_elems': chunk,
+                   'sampled_elements': n, 'note': 'ms_per_step is the sample time scaled to the full parameter count'},
+        'cpu_baseline': {
+            'value': value, 'unit': 'Gparams/s', 'cores': os.cpu_count(), 'kind': 'port',
+            'sample': f'{chunks} chunks x {sample_chunk} elements, {steps} timed steps after 1 warm-up '
+                      f'(wall {time.perf_counter() - t0:.1f} s)',
+            'torch_adamw_gparams_per_s': n / t_torch / 1e9, 'torch_variant': how,
+            'c_oracle_gparams_per_s': n / t_orc / 1e9, 'c_oracle_threads': threads,
+        },
+        'e2e': {'value': value, 'unit': 'Gparams/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--seed', type=int, default=0)
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--e2e-steps', type=int, default=10)
+    ap.add_argument('--traffic-per-launch', type=float, default=None,
+                    help='DRAM bytes per adam launch from an ncu capture (see profiles/), copied into roofline.traffic')
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        run_reference(args)
+    else:
+        if args.warmup < 3:
+            print('bench: warm-up raised to 3', file=sys.stderr)
+            args.warmup = 3
+        run_ours(args)
+
+
+if __name__ == '__main__':
+    main()

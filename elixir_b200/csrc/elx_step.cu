@@ -1,0 +1,1216 @@
+// Chunk-level mixed-precision optimizer step for B200 (sm_100a): kernels and their C ABI.
+//
+// Everything here is HBM-bandwidth work: each element of a chunk shard is read once and written
+// once, with 256-bit global accesses, from a persistent grid sized to the SM count.  There is no
+// shared-memory staging and no tensor-core use: the arithmetic intensity is ~0.4 flop/byte.
+//
+// Kernels
+//   probe_kernel     inf/nan probe of the reduced low-precision gradients (optionally fused with the
+//                    copy into the shard, optionally with a fixed-order sum of squares)
+//   norm_finalize    fixed-order reduction of the per-tile partial sums of squares
+//   step_begin       one thread: skip decision, combined divisor, loss-scaler update, step count
+//   adam_kernel      unscale + Adam/AdamW on fp32 master / exp_avg / exp_avg_sq + rounded
+//                    low-precision copy-back, or copy-back only on a skipped step
+//   cast_kernel      fp32 -> low-precision copy-back alone
+//
+// Semantics follow hpcaitech/Elixir's ElixirOptimizer.step (elixir/wrapper/optimizer.py:192-220),
+// Chunk.update_extra_reduce_info / optim_update (elixir/chunk/core/chunk.py:345-356, 403-415) and
+// the multi-tensor Adam (with div_scale) and DynamicGradScaler of ColossalAI that Elixir calls.
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "elixir_b200.h"
+
+namespace {
+
+constexpr int kTile = ELX_TILE;
+constexpr int kMaxGroups = 64;
+constexpr int kProbeThreads = 256;   // 16 elements per thread and tile
+
+// ------------------------------------------------------------------------------------------------
+// host-side state
+// ------------------------------------------------------------------------------------------------
+
+thread_local char t_cuda_err[256] = "";
+
+// Launch-shape knobs (elx_set_tuning).  A CTAs-per-SM cap of 0 means "as many as are resident".
+struct Tuning {
+    int adam_threads = 256;
+    int adam_min_blocks = 2;      // __launch_bounds__ minimum CTAs per SM the kernel is compiled for
+    int adam_ctas_per_sm = 0;
+    int probe_ctas_per_sm = 0;
+    int probe_unroll = 4;
+    int math_mode = 1;
+};
+Tuning g_tune;
+
+// CTAs of `kernel` that fit on one SM (cached per kernel instantiation by the callers).
+template <typename KernelT>
+int resident_ctas(KernelT kernel, int threads) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) {
+        (void)cudaGetLastError();
+        n = 1;
+    }
+    return n;
+}
+
+int g_sm_count[64];   // per device ordinal, 0 = not queried yet
+
+int record_cuda(cudaError_t e) {
+    if (e == cudaSuccess) return ELX_OK;
+    snprintf(t_cuda_err, sizeof(t_cuda_err), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+    return ELX_ERR_LAUNCH;
+}
+
+// SM count of the current device, or a negative status.
+int sm_count() {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        record_cuda(e);
+        (void)cudaGetLastError();
+        return ELX_ERR_NODEVICE;
+    }
+    if (dev < 0 || dev >= 64) return ELX_ERR_NODEVICE;
+    if (g_sm_count[dev] == 0) {
+        int n = 0;
+        e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess || n <= 0) {
+            record_cuda(e);
+            (void)cudaGetLastError();
+            return ELX_ERR_NODEVICE;
+        }
+        g_sm_count[dev] = n;
+    }
+    return g_sm_count[dev];
+}
+
+inline bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+inline bool dtype_ok(int dt) { return dt == ELX_F16 || dt == ELX_BF16 || dt == ELX_F32; }
+inline int dtype_bytes(int dt) { return dt == ELX_F32 ? 4 : 2; }
+
+// ------------------------------------------------------------------------------------------------
+// 256-bit / 128-bit global accesses with streaming hints (data is touched once per step)
+// ------------------------------------------------------------------------------------------------
+
+struct U8 {
+    uint32_t x[8];
+};
+
+__device__ __forceinline__ U8 ld256(const void* p) {
+    U8 r;
+    asm volatile("ld.global.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.x[0]), "=r"(r.x[1]), "=r"(r.x[2]), "=r"(r.x[3]), "=r"(r.x[4]), "=r"(r.x[5]),
+                   "=r"(r.x[6]), "=r"(r.x[7])
+                 : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ void st256(void* p, const U8& v) {
+    asm volatile("st.global.L1::no_allocate.L2::evict_first.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 :
+                 : "l"(p), "r"(v.x[0]), "r"(v.x[1]), "r"(v.x[2]), "r"(v.x[3]), "r"(v.x[4]), "r"(v.x[5]),
+                   "r"(v.x[6]), "r"(v.x[7])
+                 : "memory");
+}
+
+struct U4 {
+    uint32_t x[4];
+};
+
+__device__ __forceinline__ U4 ld128(const void* p) {
+    U4 r;
+    asm volatile("ld.global.cs.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x[0]), "=r"(r.x[1]), "=r"(r.x[2]), "=r"(r.x[3])
+                 : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ void st128(void* p, const U4& v) {
+    asm volatile("st.global.cs.v4.b32 [%0], {%1,%2,%3,%4};"
+                 :
+                 : "l"(p), "r"(v.x[0]), "r"(v.x[1]), "r"(v.x[2]), "r"(v.x[3])
+                 : "memory");
+}
+
+// N consecutive 32-bit words, N in {4, 8, 16}
+template <int N>
+__device__ __forceinline__ void ld_words(const void* p, uint32_t (&w)[N]) {
+    if constexpr (N == 4) {
+        U4 r = ld128(p);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = r.x[i];
+    } else {
+#pragma unroll
+        for (int k = 0; k < N / 8; ++k) {
+            U8 r = ld256(static_cast<const char*>(p) + 32 * k);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[8 * k + i] = r.x[i];
+        }
+    }
+}
+
+template <int N>
+__device__ __forceinline__ void st_words(void* p, const uint32_t (&w)[N]) {
+    if constexpr (N == 4) {
+        U4 r;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) r.x[i] = w[i];
+        st128(p, r);
+    } else {
+#pragma unroll
+        for (int k = 0; k < N / 8; ++k) {
+            U8 r;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r.x[i] = w[8 * k + i];
+            st256(static_cast<char*>(p) + 32 * k, r);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// low-precision element traits
+// ------------------------------------------------------------------------------------------------
+
+template <int DT>
+struct Lp;
+
+template <>
+struct Lp<ELX_F16> {
+    using T = __half;
+    static constexpr int kBytes = 2;
+    static __device__ __forceinline__ float2 unpack2(uint32_t u) {
+        return __half22float2(*reinterpret_cast<const __half2*>(&u));
+    }
+    static __device__ __forceinline__ uint32_t pack2(float a, float b) {
+        __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+    // non-zero iff one of the two packed values has an all-ones exponent (inf or nan)
+    static __device__ __forceinline__ uint32_t nonfinite_word(uint32_t u) {
+        return ((u & 0x7C007C00u) + 0x04000400u) & 0x80008000u;
+    }
+    static __device__ __forceinline__ bool nonfinite(T v) { return (__half_as_ushort(v) & 0x7C00u) == 0x7C00u; }
+    static __device__ __forceinline__ float to_float(T v) { return __half2float(v); }
+    static __device__ __forceinline__ T from_float(float f) { return __float2half_rn(f); }
+};
+
+template <>
+struct Lp<ELX_BF16> {
+    using T = __nv_bfloat16;
+    static constexpr int kBytes = 2;
+    static __device__ __forceinline__ float2 unpack2(uint32_t u) {
+        // bf16 -> fp32 is a 16-bit shift
+        return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
+    }
+    static __device__ __forceinline__ uint32_t pack2(float a, float b) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+    static __device__ __forceinline__ uint32_t nonfinite_word(uint32_t u) {
+        return ((u & 0x7F807F80u) + 0x00800080u) & 0x80008000u;
+    }
+    static __device__ __forceinline__ bool nonfinite(T v) { return (__bfloat16_as_ushort(v) & 0x7F80u) == 0x7F80u; }
+    static __device__ __forceinline__ float to_float(T v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ T from_float(float f) { return __float2bfloat16_rn(f); }
+};
+
+template <>
+struct Lp<ELX_F32> {
+    using T = float;
+    static constexpr int kBytes = 4;
+    static __device__ __forceinline__ uint32_t nonfinite_word(uint32_t u) {
+        return (u & 0x7F800000u) == 0x7F800000u ? 1u : 0u;
+    }
+    static __device__ __forceinline__ bool nonfinite(T v) {
+        return (__float_as_uint(v) & 0x7F800000u) == 0x7F800000u;
+    }
+    static __device__ __forceinline__ float to_float(T v) { return v; }
+    static __device__ __forceinline__ T from_float(float f) { return f; }
+};
+
+// Work split inside a tile.  A thread owns EPT/8 groups of 8 consecutive elements.  A warp owns a
+// slab of 32 * EPT consecutive elements; group j of lane l starts at j * 256 + l * 8 inside the slab,
+// so every warp-wide access (256-bit per lane on the fp32 arrays, 128-bit per lane on the 16-bit
+// array) covers whole, consecutive 128-byte lines.
+template <int EPT>
+__device__ __forceinline__ int group_offset(int j) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    return warp * (32 * EPT) + j * 256 + lane * 8;
+}
+
+// The thread's EPT low-precision elements of the tile starting at element e0, as fp32.
+template <int DT, int EPT>
+__device__ __forceinline__ void load_lowp(const void* base, int64_t e0, float (&g)[EPT]) {
+#pragma unroll
+    for (int j = 0; j < EPT / 8; ++j) {
+        const int64_t idx = e0 + group_offset<EPT>(j);
+        if constexpr (DT == ELX_F32) {
+            const U8 r = ld256(static_cast<const float*>(base) + idx);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) g[8 * j + i] = __uint_as_float(r.x[i]);
+        } else {
+            const U4 r = ld128(static_cast<const uint16_t*>(base) + idx);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = Lp<DT>::unpack2(r.x[i]);
+                g[8 * j + 2 * i] = f.x;
+                g[8 * j + 2 * i + 1] = f.y;
+            }
+        }
+    }
+}
+
+template <int DT, int EPT>
+__device__ __forceinline__ void store_lowp(void* base, int64_t e0, const float (&p)[EPT]) {
+#pragma unroll
+    for (int j = 0; j < EPT / 8; ++j) {
+        const int64_t idx = e0 + group_offset<EPT>(j);
+        if constexpr (DT == ELX_F32) {
+            U8 r;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r.x[i] = __float_as_uint(p[8 * j + i]);
+            st256(static_cast<float*>(base) + idx, r);
+        } else {
+            U4 r;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) r.x[i] = Lp<DT>::pack2(p[8 * j + 2 * i], p[8 * j + 2 * i + 1]);
+            st128(static_cast<uint16_t*>(base) + idx, r);
+        }
+    }
+}
+
+template <int EPT>
+__device__ __forceinline__ void load_f32(const float* base, int64_t e0, float (&v)[EPT]) {
+#pragma unroll
+    for (int j = 0; j < EPT / 8; ++j) {
+        const U8 r = ld256(base + e0 + group_offset<EPT>(j));
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[8 * j + i] = __uint_as_float(r.x[i]);
+    }
+}
+
+template <int EPT>
+__device__ __forceinline__ void store_f32(float* base, int64_t e0, const float (&v)[EPT]) {
+#pragma unroll
+    for (int j = 0; j < EPT / 8; ++j) {
+        U8 r;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r.x[i] = __float_as_uint(v[8 * j + i]);
+        st256(base + e0 + group_offset<EPT>(j), r);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// tile -> chunk and element -> segment lookup, cached across a CTA's consecutive tiles
+// ------------------------------------------------------------------------------------------------
+
+// The descriptor a CTA is working in lives in shared memory: every thread of a CTA handles the same
+// tile, so one thread searches and the others read the result.  The search reruns only when a tile
+// leaves the cached descriptor (once per chunk for most CTAs).
+struct ChunkCursor {
+    int64_t t0, t1;   // tile range of the cached descriptor
+    int index;
+    int vec_ok;       // all four pointers are 32-byte aligned
+    ElxChunkDesc d;
+};
+
+__device__ __forceinline__ int64_t tiles_of(int64_t n) { return (n + kTile - 1) / kTile; }
+
+__device__ __forceinline__ void cursor_reset(ChunkCursor& cur) {
+    if (threadIdx.x == 0) {
+        cur.t0 = cur.t1 = 0;
+        cur.index = -1;
+        cur.vec_ok = 0;
+    }
+    __syncthreads();
+}
+
+// CTA-collective (every thread calls it with the same t).  cur is in shared memory.
+__device__ __forceinline__ bool locate_chunk(const ElxChunkDesc* __restrict__ descs, int first, int count,
+                                             int64_t t, ChunkCursor& cur) {
+    if (t >= cur.t0 && t < cur.t1) return true;
+    __syncthreads();   // nobody still reads the old cursor
+    if (threadIdx.x == 0) {
+        int lo = first, hi = first + count - 1;
+        while (lo < hi) {
+            int mid = (lo + hi + 1) >> 1;
+            if (descs[mid].tile_begin <= t) lo = mid; else hi = mid - 1;
+        }
+        const ElxChunkDesc d = descs[lo];
+        const int64_t t0 = d.tile_begin, t1 = t0 + tiles_of(d.n_shard);
+        if (t >= t0 && t < t1) {
+            cur.d = d;
+            cur.index = lo;
+            cur.t0 = t0;
+            cur.t1 = t1;
+            const uintptr_t bits = reinterpret_cast<uintptr_t>(d.master) | reinterpret_cast<uintptr_t>(d.exp_avg) |
+                                   reinterpret_cast<uintptr_t>(d.exp_avg_sq) |
+                                   reinterpret_cast<uintptr_t>(d.grad_param);
+            cur.vec_ok = (bits & 31u) == 0;
+        }
+    }
+    __syncthreads();
+    return t >= cur.t0 && t < cur.t1;
+}
+
+// Cached segment of the cached chunk, also in shared memory.
+struct SegCursor {
+    int64_t b, e;   // [b, e) of the cached segment, b == e when none
+    int group;
+    int chunk;      // descriptor index the cache belongs to
+};
+
+// Index (relative to the chunk's first segment) of the last segment with begin <= e, or -1.
+__device__ __forceinline__ int find_seg(const ElxSeg* __restrict__ segs, int n, int64_t e) {
+    int lo = 0, hi = n;   // first segment with begin > e
+    while (lo < hi) {
+        int mid = (lo + hi) >> 1;
+        if (segs[mid].begin <= e) lo = mid + 1; else hi = mid;
+    }
+    return lo - 1;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Adam
+// ------------------------------------------------------------------------------------------------
+
+// Per-group constants derived once per CTA from ElxHyper and the device step counter.
+struct GroupK {
+    float lr, beta1, omb1, beta2, omb2, eps;
+    float wd_l2;   // weight decay added to the gradient (L2 mode), 0 in decoupled mode
+    float wd_w;    // weight decay added to the update (decoupled mode), 0 in L2 mode
+    float bc1, bc2, rbc1, rbc2;
+};
+
+__device__ __noinline__ GroupK derive_group(const ElxHyper& h, int step) {
+    GroupK k;
+    k.lr = h.lr;
+    k.beta1 = h.beta1;
+    k.beta2 = h.beta2;
+    k.omb1 = 1.0f - h.beta1;
+    k.omb2 = 1.0f - h.beta2;
+    k.eps = h.eps;
+    k.wd_l2 = h.adamw_mode ? 0.0f : h.weight_decay;
+    k.wd_w = h.adamw_mode ? h.weight_decay : 0.0f;
+    double bc1 = 1.0, bc2 = 1.0;
+    if (h.bias_correction) {
+        // 1 - beta^t evaluated in double from the fp32 betas, then rounded to fp32
+        bc1 = 1.0 - pow(static_cast<double>(h.beta1), static_cast<double>(step));
+        bc2 = 1.0 - pow(static_cast<double>(h.beta2), static_cast<double>(step));
+    }
+    k.bc1 = static_cast<float>(bc1);
+    k.bc2 = static_cast<float>(bc2);
+    k.rbc1 = static_cast<float>(1.0 / bc1);
+    k.rbc2 = static_cast<float>(1.0 / bc2);
+    return k;
+}
+
+// How the gradient is unscaled in this launch.
+enum { kNoDiv = 0, kMulInv = 1, kTrueDiv = 2 };
+
+template <int MATH>
+__device__ __forceinline__ void adam_elem(float& p, float& m, float& v, float g, const GroupK& k, int div_mode,
+                                          float div, float inv_div) {
+    if (div_mode == kMulInv) g *= inv_div;                    // exact: the divisor is a power of two
+    else if (div_mode == kTrueDiv) g = __fdiv_rn(g, div);
+    g = fmaf(k.wd_l2, p, g);
+    m = fmaf(k.beta1, m, k.omb1 * g);
+    v = fmaf(k.beta2, v, (k.omb2 * g) * g);
+    float upd;
+    if constexpr (MATH == 1) {
+        float mhat = __fdiv_rn(m, k.bc1);
+        float vhat = __fdiv_rn(v, k.bc2);
+        float denom = __fsqrt_rn(vhat) + k.eps;
+        upd = __fdiv_rn(mhat, denom);
+    } else {
+        float mhat = m * k.rbc1;
+        float vhat = v * k.rbc2;
+        float denom = __fsqrt_rn(vhat) + k.eps;
+        upd = __fdividef(mhat, denom);
+    }
+    upd = fmaf(k.wd_w, p, upd);
+    p = fmaf(-k.lr, upd, p);
+}
+
+struct AdamArgs {
+    const ElxChunkDesc* descs;
+    const ElxSeg* segs;
+    const ElxHyper* hyper;
+    ElxCtl* ctl;
+    int first, count, n_groups, inline_tables;
+    int64_t n_tiles;
+    // single-shard form: the three tables travel in the kernel parameters
+    ElxChunkDesc one_desc;
+    ElxSeg one_seg;
+    ElxHyper one_hyper;
+};
+
+template <int DT, int EPT, int MATH, int MINB>
+__global__ void __launch_bounds__(kTile / EPT, MINB) adam_kernel(const __grid_constant__ AdamArgs a) {
+    __shared__ GroupK s_group[kMaxGroups];
+    __shared__ ChunkCursor s_cur;
+    __shared__ SegCursor s_seg;
+
+    const ElxChunkDesc* __restrict__ descs = a.inline_tables ? &a.one_desc : a.descs;
+    const ElxSeg* __restrict__ segs = a.inline_tables ? &a.one_seg : a.segs;
+    const ElxHyper* __restrict__ hyper = a.inline_tables ? &a.one_hyper : a.hyper;
+    ElxCtl* ctl = a.ctl;
+
+    const bool skip = ctl->skip != 0;
+    const float div = ctl->div_scale;
+    const float inv_div = ctl->inv_div;
+    const int div_mode = div > 0.0f ? (inv_div != 0.0f ? kMulInv : kTrueDiv) : kNoDiv;
+
+    if (!skip) {
+        const int step = ctl->step;
+        for (int gi = threadIdx.x; gi < a.n_groups; gi += blockDim.x) s_group[gi] = derive_group(hyper[gi], step);
+    }
+    if (threadIdx.x == 0) {
+        s_seg.b = s_seg.e = 0;
+        s_seg.group = -1;
+        s_seg.chunk = -1;
+    }
+    cursor_reset(s_cur);
+
+    const int64_t tile_lo = descs[a.first].tile_begin;
+    float nan_acc = 0.0f;   // becomes NaN once a non-finite gradient is multiplied into it
+    bool bad_desc = false;
+
+    for (int64_t it = blockIdx.x; it < a.n_tiles; it += gridDim.x) {
+        const int64_t t = tile_lo + it;
+        if (!locate_chunk(descs, a.first, a.count, t, s_cur) || s_cur.d.dtype != DT) {
+            bad_desc = true;
+            continue;
+        }
+        const int64_t n_shard = s_cur.d.n_shard;
+        const int64_t e0 = (t - s_cur.t0) * kTile;
+        const int64_t e1 = min(e0 + kTile, n_shard);
+        const bool full = (e1 - e0 == kTile) && s_cur.vec_ok;
+        float* const master = s_cur.d.master;
+        void* const lowp = s_cur.d.grad_param;
+
+        if (skip) {
+            // skipped step: the low-precision shard holds gradients and must become parameters again
+            if (full) {
+                float p[EPT];
+                load_f32<EPT>(master, e0, p);
+                store_lowp<DT, EPT>(lowp, e0, p);
+            } else {
+                typename Lp<DT>::T* out = static_cast<typename Lp<DT>::T*>(lowp);
+                for (int64_t e = e0 + threadIdx.x; e < e1; e += blockDim.x) out[e] = Lp<DT>::from_float(master[e]);
+            }
+            continue;
+        }
+
+        // segment that contains e0 (CTA-uniform; refreshed by one thread when e0 leaves the cached one)
+        const ElxSeg* csegs = segs + s_cur.d.seg_first;
+        const int n_segs = s_cur.d.seg_count;
+        if (s_seg.chunk != s_cur.index || e0 < s_seg.b || e0 >= s_seg.e) {
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const int si = find_seg(csegs, n_segs, e0);
+                s_seg.chunk = s_cur.index;
+                if (si >= 0) {
+                    s_seg.b = csegs[si].begin;
+                    s_seg.e = csegs[si].end;
+                    s_seg.group = csegs[si].group;
+                } else {
+                    s_seg.b = s_seg.e = 0;
+                    s_seg.group = -1;
+                }
+            }
+            __syncthreads();
+        }
+        const int grp = s_seg.group;
+        const bool one_group = s_seg.b <= e0 && e1 <= s_seg.e && grp >= 0 && grp < a.n_groups;
+        float* const exp_avg = s_cur.d.exp_avg;
+        float* const exp_avg_sq = s_cur.d.exp_avg_sq;
+
+        if (full && one_group) {
+            const GroupK k = s_group[grp];
+            float g[EPT], p[EPT], m[EPT], v[EPT];
+            load_lowp<DT, EPT>(lowp, e0, g);
+            load_f32<EPT>(master, e0, p);
+            load_f32<EPT>(exp_avg, e0, m);
+            load_f32<EPT>(exp_avg_sq, e0, v);
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) {
+                nan_acc = fmaf(0.0f, g[j], nan_acc);
+                adam_elem<MATH>(p[j], m[j], v[j], g[j], k, div_mode, div, inv_div);
+            }
+            store_f32<EPT>(master, e0, p);
+            store_f32<EPT>(exp_avg, e0, m);
+            store_f32<EPT>(exp_avg_sq, e0, v);
+            store_lowp<DT, EPT>(lowp, e0, p);
+        } else {
+            // ragged tile: shard tail, segment boundary, uncovered elements or unaligned pointers
+            typename Lp<DT>::T* gp = static_cast<typename Lp<DT>::T*>(lowp);
+            for (int64_t e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
+                float p = master[e];
+                const int si = find_seg(csegs, n_segs, e);
+                if (si >= 0 && e < csegs[si].end) {
+                    const int ge = csegs[si].group;
+                    if (ge >= 0 && ge < a.n_groups) {
+                        const GroupK k = s_group[ge];
+                        float g = Lp<DT>::to_float(gp[e]);
+                        float m = exp_avg[e], v = exp_avg_sq[e];
+                        nan_acc = fmaf(0.0f, g, nan_acc);
+                        adam_elem<MATH>(p, m, v, g, k, div_mode, div, inv_div);
+                        master[e] = p;
+                        exp_avg[e] = m;
+                        exp_avg_sq[e] = v;
+                    }
+                }
+                gp[e] = Lp<DT>::from_float(p);
+            }
+        }
+    }
+
+    // warp-reduced report of a non-finite gradient met on an applied step
+    const bool late = nan_acc != nan_acc;
+    const unsigned ballot = __ballot_sync(0xFFFFFFFFu, late);
+    const unsigned ballot_desc = __ballot_sync(0xFFFFFFFFu, bad_desc);
+    if ((threadIdx.x & 31) == 0) {
+        if (ballot) {
+            atomicOr(&ctl->late_inf, 1u);
+            atomicOr(&ctl->status, ELX_STAT_LATE_INF);
+        }
+        if (ballot_desc) atomicOr(&ctl->status, ELX_STAT_BAD_DESC);
+    }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256) cast_kernel(const float* __restrict__ src, void* dst, int64_t n, int vec_ok) {
+    constexpr int EPT = 16;
+    const int64_t n_full = vec_ok ? n / kTile : 0;
+    for (int64_t t = blockIdx.x; t < n_full; t += gridDim.x) {
+        float p[EPT];
+        load_f32<EPT>(src, t * kTile, p);
+        store_lowp<DT, EPT>(dst, t * kTile, p);
+    }
+    typename Lp<DT>::T* out = static_cast<typename Lp<DT>::T*>(dst);
+    for (int64_t e = n_full * kTile + blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; e < n;
+         e += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        out[e] = Lp<DT>::from_float(src[e]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// probe (+ copy, + sum of squares)
+// ------------------------------------------------------------------------------------------------
+
+struct ProbeArgs {
+    const ElxChunkDesc* descs;
+    uint32_t* chunk_flags;   // indexed by descriptor index, may be null
+    uint32_t* one_flag;      // single-shard form, may be null
+    ElxCtl* ctl;             // may be null
+    float* scratch;          // per-tile partial sums of squares (NORM only)
+    void* copy_dst;          // COPY only (single-shard form)
+    int first, count, inline_tables, pad;
+    int64_t n_tiles;
+    ElxChunkDesc one_desc;
+};
+
+// kProbeUnroll = tiles whose loads are in flight together in one CTA iteration
+template <int DT, bool COPY, bool NORM, int kProbeUnroll>
+__global__ void __launch_bounds__(kProbeThreads) probe_kernel(const __grid_constant__ ProbeArgs a) {
+    constexpr int EPT = kTile / kProbeThreads;                   // 16
+    constexpr int WORDS = EPT * Lp<DT>::kBytes / 4;              // 8 (16-bit) or 16 (fp32)
+    using T = typename Lp<DT>::T;
+    __shared__ float s_part[kProbeUnroll][kProbeThreads / 32];
+
+    const ElxChunkDesc* __restrict__ descs = a.inline_tables ? &a.one_desc : a.descs;
+    const int64_t tile_lo = descs[a.first].tile_begin;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ ChunkCursor s_cur;
+    cursor_reset(s_cur);
+    bool bad_desc = false;
+
+    const int64_t n_groups_of_tiles = (a.n_tiles + kProbeUnroll - 1) / kProbeUnroll;
+    for (int64_t q = blockIdx.x; q < n_groups_of_tiles; q += gridDim.x) {
+        uint32_t w[kProbeUnroll][WORDS];
+        bool vec[kProbeUnroll];
+        bool probed[kProbeUnroll];
+        int chunk_of[kProbeUnroll];
+        float sq[kProbeUnroll];
+        uint32_t bad[kProbeUnroll];
+
+        // issue every load of the group first, so that they are all in flight together
+#pragma unroll
+        for (int j = 0; j < kProbeUnroll; ++j) {
+            vec[j] = false;
+            probed[j] = false;
+            chunk_of[j] = -1;
+            sq[j] = 0.0f;
+            bad[j] = 0;
+            const int64_t it = q * kProbeUnroll + j;
+            if (it >= a.n_tiles) continue;
+            const int64_t t = tile_lo + it;
+            if (!locate_chunk(descs, a.first, a.count, t, s_cur) || s_cur.d.dtype != DT) {
+                bad_desc = true;
+                continue;
+            }
+            chunk_of[j] = s_cur.index;
+            struct { const void* grad_param; int64_t n_shard, n_valid; } d = {s_cur.d.grad_param, s_cur.d.n_shard,
+                                                                              s_cur.d.n_valid};
+            const int64_t e0 = (t - s_cur.t0) * kTile;
+            const bool dst_ok = !COPY || (reinterpret_cast<uintptr_t>(a.copy_dst) & 31u) == 0;
+            const bool src_ok = (reinterpret_cast<uintptr_t>(d.grad_param) & 31u) == 0;
+            const bool all_valid = e0 + kTile <= d.n_valid;     // every element is probed
+            const bool none_valid = e0 >= d.n_valid;            // padding only: copied, never probed
+            if (!COPY && none_valid) continue;
+            if (src_ok && dst_ok && e0 + kTile <= d.n_shard && (all_valid || none_valid)) {
+                vec[j] = true;
+                probed[j] = all_valid;
+                ld_words<WORDS>(static_cast<const char*>(d.grad_param) +
+                                    (e0 + static_cast<int64_t>(threadIdx.x) * EPT) * Lp<DT>::kBytes, w[j]);
+            } else {
+                // ragged tile: probe [e0, n_valid), copy [e0, n_shard)
+                const T* src = static_cast<const T*>(d.grad_param);
+                const int64_t e1 = min(e0 + kTile, d.n_shard);
+                for (int64_t e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
+                    const T x = src[e];
+                    if (e < d.n_valid) {
+                        if (Lp<DT>::nonfinite(x)) bad[j] = 1;
+                        if (NORM) {
+                            const float f = Lp<DT>::to_float(x);
+                            sq[j] = fmaf(f, f, sq[j]);
+                        }
+                    }
+                    if (COPY) static_cast<T*>(a.copy_dst)[e] = x;
+                }
+            }
+        }
+
+#pragma unroll
+        for (int j = 0; j < kProbeUnroll; ++j) {
+            if (vec[j]) {
+                uint32_t acc = 0;
+#pragma unroll
+                for (int i = 0; i < WORDS; ++i) acc |= Lp<DT>::nonfinite_word(w[j][i]);
+                bad[j] = probed[j] ? acc : 0u;
+                if (NORM && probed[j]) {
+                    float s = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < WORDS; ++i) {
+                        if constexpr (DT == ELX_F32) {
+                            const float f = __uint_as_float(w[j][i]);
+                            s = fmaf(f, f, s);
+                        } else {
+                            const float2 f = Lp<DT>::unpack2(w[j][i]);
+                            s = fmaf(f.x, f.x, s);
+                            s = fmaf(f.y, f.y, s);
+                        }
+                    }
+                    sq[j] = s;
+                }
+                if (COPY) {
+                    const int64_t it = q * kProbeUnroll + j;
+                    // single-shard form: tile index == it
+                    st_words<WORDS>(static_cast<char*>(a.copy_dst) +
+                                        (it * kTile + static_cast<int64_t>(threadIdx.x) * EPT) * Lp<DT>::kBytes, w[j]);
+                }
+            }
+            // warp-reduced overflow report
+            const unsigned any_bad = __ballot_sync(0xFFFFFFFFu, bad[j] != 0);
+            if (any_bad && lane == 0 && chunk_of[j] >= 0) {
+                if (a.chunk_flags) atomicOr(&a.chunk_flags[chunk_of[j]], 1u);
+                if (a.one_flag) atomicOr(a.one_flag, 1u);
+                if (a.ctl) atomicOr(&a.ctl->found_inf, 1u);
+            }
+        }
+
+        if (NORM) {
+            // fixed-order block reduction of each tile's partial: lanes, then warps 0..7
+#pragma unroll
+            for (int j = 0; j < kProbeUnroll; ++j) {
+                float s = sq[j];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xFFFFFFFFu, s, o);
+                if (lane == 0) s_part[j][warp] = s;
+            }
+            __syncthreads();
+            if (threadIdx.x < kProbeUnroll) {
+                const int64_t it = q * kProbeUnroll + threadIdx.x;
+                if (it < a.n_tiles) {
+                    float s = 0.0f;
+                    for (int wi = 0; wi < kProbeThreads / 32; ++wi) s += s_part[threadIdx.x][wi];
+                    a.scratch[it] = s;
+                }
+            }
+            __syncthreads();
+        }
+    }
+
+    const unsigned ballot_desc = __ballot_sync(0xFFFFFFFFu, bad_desc);
+    if (ballot_desc && lane == 0 && a.ctl) atomicOr(&a.ctl->status, ELX_STAT_BAD_DESC);
+}
+
+struct NormArgs {
+    const ElxChunkDesc* descs;
+    const float* scratch;
+    float* chunk_l2sq;   // indexed by descriptor index, may be null
+    float* one_l2sq;     // single-shard form
+    float* total_l2sq;   // may be null
+    int first, count, inline_tables, pad;
+    ElxChunkDesc one_desc;
+};
+
+// One CTA.  Sums each descriptor's per-tile partials in a fixed order (strided per thread, then a
+// binary tree over threads) in double, so that the result does not depend on the probe grid.
+__global__ void __launch_bounds__(256) norm_finalize(const __grid_constant__ NormArgs a) {
+    __shared__ double s_red[256];
+    const ElxChunkDesc* __restrict__ descs = a.inline_tables ? &a.one_desc : a.descs;
+    const int64_t tile_lo = descs[a.first].tile_begin;
+    double total = 0.0;
+    for (int c = a.first; c < a.first + a.count; ++c) {
+        const int64_t b = descs[c].tile_begin - tile_lo;
+        const int64_t n = tiles_of(descs[c].n_shard);
+        double s = 0.0;
+        for (int64_t i = threadIdx.x; i < n; i += blockDim.x) s += static_cast<double>(a.scratch[b + i]);
+        s_red[threadIdx.x] = s;
+        __syncthreads();
+        for (int o = 128; o > 0; o >>= 1) {
+            if (threadIdx.x < o) s_red[threadIdx.x] += s_red[threadIdx.x + o];
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) {
+            const double r = s_red[0];
+            if (a.chunk_l2sq) a.chunk_l2sq[c] = static_cast<float>(r);
+            if (a.one_l2sq) *a.one_l2sq = static_cast<float>(r);
+            total += r;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && a.total_l2sq) *a.total_l2sq = static_cast<float>(total);
+}
+
+// ------------------------------------------------------------------------------------------------
+// control block
+// ------------------------------------------------------------------------------------------------
+
+__global__ void ctl_init_kernel(ElxCtl* ctl, float initial_scale) {
+    uint32_t* w = reinterpret_cast<uint32_t*>(ctl);
+    for (int i = threadIdx.x; i < static_cast<int>(sizeof(ElxCtl) / 4); i += blockDim.x) w[i] = 0;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        ctl->scale = initial_scale;
+        ctl->div_scale = -1.0f;
+        ctl->clip_coef = 1.0f;
+    }
+}
+
+__device__ __forceinline__ bool is_pow2_float(float x) {
+    const uint32_t u = __float_as_uint(x);
+    const uint32_t ex = (u >> 23) & 0xFFu;
+    // normal, positive, zero mantissa, and the reciprocal is normal too
+    return (u >> 31) == 0 && (u & 0x7FFFFFu) == 0 && ex >= 2 && ex <= 252;
+}
+
+__global__ void step_begin_kernel(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    const bool found = ctl->found_inf != 0;
+    float scale = ctl->scale;
+    if (found) {
+        ctl->skip = 1;
+        ctl->skipped_steps += 1;
+        ctl->div_scale = -1.0f;
+        ctl->inv_div = 0.0f;
+        if (cfg.dynamic) {
+            ctl->hysteresis_step += 1;
+            ctl->growth_step = 0;
+            if (ctl->hysteresis_step >= cfg.hysteresis) {
+                scale = scale * cfg.backoff_factor;
+                if (cfg.min_scale > 0.0f) scale = fmaxf(scale, cfg.min_scale);
+            }
+        }
+    } else {
+        ctl->skip = 0;
+        // combined divisor from the scale as it was during backward
+        double combined = static_cast<double>(scale);
+        float clip_coef = 1.0f;
+        if (cfg.max_norm > 0.0f && norm_sq != nullptr) {
+            const double total_norm = sqrt(static_cast<double>(*norm_sq));
+            const double clip = (total_norm / static_cast<double>(scale) + 1e-6) / static_cast<double>(cfg.max_norm);
+            ctl->grad_norm = static_cast<float>(total_norm / static_cast<double>(scale));
+            if (clip > 1.0) {
+                combined = clip * static_cast<double>(scale);
+                clip_coef = static_cast<float>(clip);
+            }
+        }
+        ctl->clip_coef = clip_coef;
+        float div = static_cast<float>(combined);
+        if (combined == 1.0) div = -1.0f;
+        ctl->div_scale = div;
+        ctl->inv_div = (div > 0.0f && is_pow2_float(div)) ? 1.0f / div : 0.0f;
+        ctl->step += 1;
+        if (cfg.dynamic) {
+            ctl->growth_step += 1;
+            if (ctl->growth_step == cfg.growth_interval) {
+                ctl->growth_step = 0;
+                ctl->hysteresis_step = 0;
+                scale = scale * cfg.growth_factor;
+                if (cfg.max_scale > 0.0f) scale = fminf(scale, cfg.max_scale);
+            }
+        }
+    }
+    ctl->scale = scale;
+    ctl->found_inf = 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// launch helpers
+// ------------------------------------------------------------------------------------------------
+
+int grid_for(int64_t work_items, int ctas_per_sm) {
+    const int sms = sm_count();
+    if (sms < 0) return sms;
+    int64_t g = static_cast<int64_t>(sms) * ctas_per_sm;
+    if (g > work_items) g = work_items;
+    if (g < 1) g = 1;
+    return static_cast<int>(g);
+}
+
+inline int capped(int resident, int cap) { return cap > 0 && cap < resident ? cap : resident; }
+
+template <int DT, int EPT, int MATH, int MINB>
+int launch_adam_inst(const AdamArgs& a, cudaStream_t s) {
+    constexpr int threads = kTile / EPT;
+    static const int resident = resident_ctas(adam_kernel<DT, EPT, MATH, MINB>, threads);
+    const int grid = grid_for(a.n_tiles, capped(resident, g_tune.adam_ctas_per_sm));
+    if (grid < 0) return grid;
+    adam_kernel<DT, EPT, MATH, MINB><<<grid, threads, 0, s>>>(a);
+    return record_cuda(cudaGetLastError());
+}
+
+template <int DT, int EPT, int MATH>
+int launch_adam_minb(const AdamArgs& a, cudaStream_t s) {
+    if (g_tune.adam_min_blocks >= 3) return launch_adam_inst<DT, EPT, MATH, 3>(a, s);
+    if (g_tune.adam_min_blocks == 1) return launch_adam_inst<DT, EPT, MATH, 1>(a, s);
+    return launch_adam_inst<DT, EPT, MATH, 2>(a, s);
+}
+
+template <int DT>
+int launch_adam_dt(const AdamArgs& a, cudaStream_t s) {
+    const bool precise = g_tune.math_mode == 1;
+    if (g_tune.adam_threads == 256)
+        return precise ? launch_adam_minb<DT, 16, 1>(a, s) : launch_adam_minb<DT, 16, 2>(a, s);
+    return precise ? launch_adam_minb<DT, 8, 1>(a, s) : launch_adam_minb<DT, 8, 2>(a, s);
+}
+
+int launch_adam(const AdamArgs& a, int dtype, cudaStream_t s) {
+    switch (dtype) {
+        case ELX_F16: return launch_adam_dt<ELX_F16>(a, s);
+        case ELX_BF16: return launch_adam_dt<ELX_BF16>(a, s);
+        case ELX_F32: return launch_adam_dt<ELX_F32>(a, s);
+    }
+    return ELX_ERR_DTYPE;
+}
+
+template <int DT, bool COPY, bool NORM, int UNROLL>
+int launch_probe_inst(const ProbeArgs& a, cudaStream_t s) {
+    static const int resident = resident_ctas(probe_kernel<DT, COPY, NORM, UNROLL>, kProbeThreads);
+    const int64_t groups = (a.n_tiles + UNROLL - 1) / UNROLL;
+    const int grid = grid_for(groups, capped(resident, g_tune.probe_ctas_per_sm));
+    if (grid < 0) return grid;
+    probe_kernel<DT, COPY, NORM, UNROLL><<<grid, kProbeThreads, 0, s>>>(a);
+    return record_cuda(cudaGetLastError());
+}
+
+template <int DT, bool COPY>
+int launch_probe_norm(const ProbeArgs& a, bool norm, cudaStream_t s) {
+    // fp32 tiles are twice as many bytes: half the unroll keeps the register budget
+    constexpr int kBig = DT == ELX_F32 ? 4 : 8;
+    constexpr int kSmall = DT == ELX_F32 ? 2 : 4;
+    const bool big = g_tune.probe_unroll >= 8;
+    if (norm) return big ? launch_probe_inst<DT, COPY, true, kBig>(a, s) : launch_probe_inst<DT, COPY, true, kSmall>(a, s);
+    return big ? launch_probe_inst<DT, COPY, false, kBig>(a, s) : launch_probe_inst<DT, COPY, false, kSmall>(a, s);
+}
+
+template <bool COPY>
+int launch_probe(const ProbeArgs& a, int dtype, bool norm, cudaStream_t s) {
+    switch (dtype) {
+        case ELX_F16: return launch_probe_norm<ELX_F16, COPY>(a, norm, s);
+        case ELX_BF16: return launch_probe_norm<ELX_BF16, COPY>(a, norm, s);
+        case ELX_F32: return launch_probe_norm<ELX_F32, COPY>(a, norm, s);
+    }
+    return ELX_ERR_DTYPE;
+}
+
+int probe_single(const void* src, void* dst, int dtype, int64_t n_shard, int64_t n_valid, uint32_t* flag,
+                 ElxCtl* ctl, float* l2sq, float* scratch, int64_t scratch_elems, void* stream, bool copy) {
+    if (!src || (copy && !dst)) return ELX_ERR_NULL;
+    if (!flag && !ctl && !l2sq && !copy) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (n_shard < 0 || n_valid < 0 || n_valid > n_shard) return ELX_ERR_SIZE;
+    if (!aligned(src, 32) || (copy && !aligned(dst, 32))) return ELX_ERR_ALIGN;
+    if ((flag && !aligned(flag, 4)) || (ctl && !aligned(ctl, 16)) || (l2sq && !aligned(l2sq, 4))) return ELX_ERR_ALIGN;
+    if (copy) {
+        const char* s0 = static_cast<const char*>(src);
+        const char* d0 = static_cast<const char*>(dst);
+        const int64_t bytes = n_shard * dtype_bytes(dtype);
+        if (s0 < d0 + bytes && d0 < s0 + bytes) return ELX_ERR_ARG;
+    }
+    const int64_t n_tiles = (n_shard + kTile - 1) / kTile;
+    if (l2sq) {
+        if (!scratch) return ELX_ERR_NULL;
+        if (!aligned(scratch, 4)) return ELX_ERR_ALIGN;
+        if (scratch_elems < elx_probe_scratch_elems(n_tiles)) return ELX_ERR_SIZE;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (n_tiles == 0) {
+        if (l2sq) return record_cuda(cudaMemsetAsync(l2sq, 0, sizeof(float), s));
+        return ELX_OK;
+    }
+    ProbeArgs a;
+    memset(&a, 0, sizeof(a));
+    a.one_flag = flag;
+    a.ctl = ctl;
+    a.scratch = scratch;
+    a.copy_dst = dst;
+    a.first = 0;
+    a.count = 1;
+    a.inline_tables = 1;
+    a.n_tiles = n_tiles;
+    a.one_desc.grad_param = const_cast<void*>(src);
+    a.one_desc.n_shard = n_shard;
+    a.one_desc.n_valid = n_valid;
+    a.one_desc.tile_begin = 0;
+    a.one_desc.dtype = dtype;
+    int rc = copy ? launch_probe<true>(a, dtype, l2sq != nullptr, s) : launch_probe<false>(a, dtype, l2sq != nullptr, s);
+    if (rc != ELX_OK) return rc;
+    if (l2sq) {
+        NormArgs na;
+        memset(&na, 0, sizeof(na));
+        na.scratch = scratch;
+        na.one_l2sq = l2sq;
+        na.first = 0;
+        na.count = 1;
+        na.inline_tables = 1;
+        na.one_desc = a.one_desc;
+        norm_finalize<<<1, 256, 0, s>>>(na);
+        rc = record_cuda(cudaGetLastError());
+    }
+    return rc;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------------
+// C ABI
+// ------------------------------------------------------------------------------------------------
+
+extern "C" {
+
+int elx_version(void) { return ELX_ABI_VERSION; }
+
+const char* elx_strerror(int status) {
+    switch (status) {
+        case ELX_OK: return "ok";
+        case ELX_ERR_NULL: return "a required pointer is NULL";
+        case ELX_ERR_ALIGN: return "a pointer is not aligned as required";
+        case ELX_ERR_SIZE: return "a size or count is out of range";
+        case ELX_ERR_DTYPE: return "unknown dtype code";
+        case ELX_ERR_LAUNCH: return "CUDA launch failed";
+        case ELX_ERR_ARG: return "inconsistent arguments";
+        case ELX_ERR_NODEVICE: return "no usable CUDA device";
+        case ELX_ERR_CAPACITY: return "request exceeds a fixed capacity";
+    }
+    return "unknown status";
+}
+
+const char* elx_last_cuda_error(void) { return t_cuda_err; }
+
+int elx_set_tuning(const char* name, int value) {
+    if (!name) return ELX_ERR_NULL;
+    const Tuning def;
+    struct Knob {
+        const char* name;
+        int* slot;
+        int def;
+        int lo, hi;
+    };
+    const Knob knobs[] = {
+        {"adam_threads", &g_tune.adam_threads, def.adam_threads, 256, 512},
+        {"adam_min_blocks", &g_tune.adam_min_blocks, def.adam_min_blocks, 1, 3},
+        {"adam_ctas_per_sm", &g_tune.adam_ctas_per_sm, def.adam_ctas_per_sm, 0, 32},
+        {"probe_ctas_per_sm", &g_tune.probe_ctas_per_sm, def.probe_ctas_per_sm, 0, 32},
+        {"probe_unroll", &g_tune.probe_unroll, def.probe_unroll, 4, 8},
+        {"math_mode", &g_tune.math_mode, def.math_mode, 1, 2},
+    };
+    for (const Knob& k : knobs) {
+        if (strcmp(name, k.name) != 0) continue;
+        if (value < 0) {
+            *k.slot = k.def;
+            return ELX_OK;
+        }
+        if (value < k.lo || value > k.hi) return ELX_ERR_ARG;
+        if (k.slot == &g_tune.adam_threads && value != 256 && value != 512) return ELX_ERR_ARG;
+        if (k.slot == &g_tune.probe_unroll && value != 4 && value != 8) return ELX_ERR_ARG;
+        *k.slot = value;
+        return ELX_OK;
+    }
+    return ELX_ERR_ARG;
+}
+
+int64_t elx_probe_scratch_elems(int64_t n_tiles) { return n_tiles < 0 ? 0 : n_tiles; }
+
+int elx_ctl_init(ElxCtl* ctl, float initial_scale, void* stream) {
+    if (!ctl) return ELX_ERR_NULL;
+    if (!aligned(ctl, 16)) return ELX_ERR_ALIGN;
+    if (!(initial_scale > 0.0f)) return ELX_ERR_ARG;
+    ctl_init_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ctl, initial_scale);
+    return record_cuda(cudaGetLastError());
+}
+
+int elx_step_begin(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq, void* stream) {
+    if (!ctl) return ELX_ERR_NULL;
+    if (!aligned(ctl, 16) || (norm_sq && !aligned(norm_sq, 4))) return ELX_ERR_ALIGN;
+    if (cfg.dynamic) {
+        if (!(cfg.growth_factor > 0.0f) || !(cfg.backoff_factor > 0.0f) || cfg.growth_interval <= 0 ||
+            cfg.hysteresis < 0)
+            return ELX_ERR_ARG;
+    }
+    if (cfg.max_norm > 0.0f && !norm_sq) return ELX_ERR_NULL;
+    step_begin_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ctl, cfg, norm_sq);
+    return record_cuda(cudaGetLastError());
+}
+
+int elx_grad_check(const void* g, int dtype, int64_t n_valid, uint32_t* flag, ElxCtl* ctl, float* l2sq,
+                   float* scratch, int64_t scratch_elems, void* stream) {
+    return probe_single(g, nullptr, dtype, n_valid, n_valid, flag, ctl, l2sq, scratch, scratch_elems, stream, false);
+}
+
+int elx_reduce_epilogue(const void* src, void* dst, int dtype, int64_t n_shard, int64_t n_valid, uint32_t* flag,
+                        ElxCtl* ctl, float* l2sq, float* scratch, int64_t scratch_elems, void* stream) {
+    return probe_single(src, dst, dtype, n_shard, n_valid, flag, ctl, l2sq, scratch, scratch_elems, stream, true);
+}
+
+int elx_grad_check_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                         uint32_t* chunk_flags, ElxCtl* ctl, float* chunk_l2sq, float* total_l2sq, float* scratch,
+                         int64_t scratch_elems, void* stream) {
+    if (!descs) return ELX_ERR_NULL;
+    if (!chunk_flags && !ctl && !chunk_l2sq && !total_l2sq) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (first < 0 || count < 0 || n_tiles < 0) return ELX_ERR_SIZE;
+    if (!aligned(descs, 8) || (chunk_flags && !aligned(chunk_flags, 4)) || (ctl && !aligned(ctl, 16)))
+        return ELX_ERR_ALIGN;
+    const bool norm = chunk_l2sq || total_l2sq;
+    if (norm) {
+        if (!scratch) return ELX_ERR_NULL;
+        if (!aligned(scratch, 4)) return ELX_ERR_ALIGN;
+        if (scratch_elems < elx_probe_scratch_elems(n_tiles)) return ELX_ERR_SIZE;
+    }
+    if (count == 0) return ELX_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int rc = ELX_OK;
+    if (n_tiles > 0) {
+        ProbeArgs a;
+        memset(&a, 0, sizeof(a));
+        a.descs = descs;
+        a.chunk_flags = chunk_flags;
+        a.ctl = ctl;
+        a.scratch = scratch;
+        a.first = first;
+        a.count = count;
+        a.n_tiles = n_tiles;
+        rc = launch_probe<false>(a, dtype, norm, s);
+        if (rc != ELX_OK) return rc;
+    }
+    if (norm) {
+        NormArgs na;
+        memset(&na, 0, sizeof(na));
+        na.descs = descs;
+        na.scratch = scratch;
+        na.chunk_l2sq = chunk_l2sq;
+        na.total_l2sq = total_l2sq;
+        na.first = first;
+        na.count = count;
+        norm_finalize<<<1, 256, 0, s>>>(na);
+        rc = record_cuda(cudaGetLastError());
+    }
+    return rc;
+}
+
+int elx_adam_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype, const ElxSeg* segs,
+                   const ElxHyper* hyper, int n_groups, ElxCtl* ctl, void* stream) {
+    if (!descs || !ctl) return ELX_ERR_NULL;
+    if (n_groups > 0 && (!segs || !hyper)) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (first < 0 || count < 0 || n_tiles < 0 || n_groups < 0) return ELX_ERR_SIZE;
+    if (n_groups > kMaxGroups) return ELX_ERR_CAPACITY;
+    if (!aligned(descs, 8) || !aligned(ctl, 16) || (segs && !aligned(segs, 8)) || (hyper && !aligned(hyper, 4)))
+        return ELX_ERR_ALIGN;
+    if (count == 0 || n_tiles == 0) return ELX_OK;
+    AdamArgs a;
+    memset(&a, 0, sizeof(a));
+    a.descs = descs;
+    a.segs = segs;
+    a.hyper = hyper;
+    a.ctl = ctl;
+    a.first = first;
+    a.count = count;
+    a.n_groups = n_groups;
+    a.n_tiles = n_tiles;
+    return launch_adam(a, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int elx_adam_chunk(float* master, float* exp_avg, float* exp_avg_sq, void* grad_param, int dtype, int64_t n_valid,
+                   int64_t n_shard, ElxHyper hyper, ElxCtl* ctl, void* stream) {
+    if (!master || !exp_avg || !exp_avg_sq || !grad_param || !ctl) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (n_shard < 0 || n_valid < 0 || n_valid > n_shard) return ELX_ERR_SIZE;
+    if (!aligned(master, 4) || !aligned(exp_avg, 4) || !aligned(exp_avg_sq, 4) ||
+        !aligned(grad_param, dtype_bytes(dtype)) || !aligned(ctl, 16))
+        return ELX_ERR_ALIGN;
+    if (n_shard == 0) return ELX_OK;
+    AdamArgs a;
+    memset(&a, 0, sizeof(a));
+    a.ctl = ctl;
+    a.first = 0;
+    a.count = 1;
+    a.n_groups = 1;
+    a.inline_tables = 1;
+    a.n_tiles = (n_shard + kTile - 1) / kTile;
+    a.one_desc.master = master;
+    a.one_desc.exp_avg = exp_avg;
+    a.one_desc.exp_avg_sq = exp_avg_sq;
+    a.one_desc.grad_param = grad_param;
+    a.one_desc.n_shard = n_shard;
+    a.one_desc.n_valid = n_valid;
+    a.one_desc.tile_begin = 0;
+    a.one_desc.seg_first = 0;
+    a.one_desc.seg_count = n_valid > 0 ? 1 : 0;
+    a.one_desc.dtype = dtype;
+    a.one_seg.begin = 0;
+    a.one_seg.end = n_valid;
+    a.one_seg.group = 0;
+    a.one_hyper = hyper;
+    return launch_adam(a, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int elx_cast_copyback(const float* master, void* dst, int dtype, int64_t n, void* stream) {
+    if (!master || !dst) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (n < 0) return ELX_ERR_SIZE;
+    if (!aligned(master, 4) || !aligned(dst, dtype_bytes(dtype))) return ELX_ERR_ALIGN;
+    if (n == 0) return ELX_OK;
+    const int vec_ok = aligned(master, 32) && aligned(dst, 32);
+    const int grid = grid_for((n + kTile - 1) / kTile, 8);
+    if (grid < 0) return grid;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case ELX_F16: cast_kernel<ELX_F16><<<grid, 256, 0, s>>>(master, dst, n, vec_ok); break;
+        case ELX_BF16: cast_kernel<ELX_BF16><<<grid, 256, 0, s>>>(master, dst, n, vec_ok); break;
+        case ELX_F32: cast_kernel<ELX_F32><<<grid, 256, 0, s>>>(master, dst, n, vec_ok); break;
+    }
+    return record_cuda(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -1,0 +1,233 @@
+"""ChunkStepEngine: one rank's optimizer step over its chunk shards, launched as whole-chunk-set kernels.
+
+It replaces the per-tensor loop of the reference (``ElixirOptimizer._set_grad_ptr`` /
+``optim.step`` / ``_update_fp16_params``, ``elixir/wrapper/optimizer.py:115-135, 192-220``): the
+shards are registered once in device tables, and a step is
+
+    [gradients arrive]   land() / probe()   copy into the shard + inf/nan probe, per chunk
+    begin_step()         overflow agreement across ranks (4-byte MAX all-reduce), the optional global
+                         norm, then ``elx_step_begin``: skip decision, divisor, scaler update — on the
+                         device, no host read
+    update()             ``elx_adam_multi``: unscale + Adam/AdamW + low-precision copy-back (or the
+                         copy-back alone on a skipped step)
+    end_step()           clear the per-chunk overflow words
+
+For sharded runs ``step_sharded`` pipelines reduce-scatter -> probe per chunk on a reduce stream and
+update -> all-gather per chunk on a gather stream; ``step_from_host`` does the same with host buffers
+on the two ends (pinned gradients in, updated low-precision parameters out).
+"""
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import comm, kernels
+from .scaler import BaseGradScaler, ConstantGradScaler
+
+
+class ChunkStepEngine:
+
+    def __init__(self,
+                 device,
+                 dtype: torch.dtype,
+                 scaler: Optional[BaseGradScaler] = None,
+                 process_group=None,
+                 sync_overflow: bool = True,
+                 max_norm: float = 0.0):
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.group = process_group
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.sync_overflow = sync_overflow
+        self.scaler = scaler if scaler is not None else ConstantGradScaler(1.0)
+        self.scaler.set_max_norm(max_norm)
+        self.clipping = max_norm > 0.0
+        self.ctl = kernels.ControlBlock(self.device, self.scaler.initial_scale)
+        self.scaler.attach(self.ctl)
+        self.table = kernels.ChunkTable(self.device, dtype)
+        self.shards: List[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, int]] = []
+        self.chunk_flags: Optional[torch.Tensor] = None
+        self.chunk_l2sq: Optional[torch.Tensor] = None
+        self.total_l2sq: Optional[torch.Tensor] = None
+        self._scratch: Optional[torch.Tensor] = None
+        self._streams = None
+        self._finalized = False
+
+    # ------------------------------------------------------------------ registration
+
+    def add_shard(self,
+                  master: torch.Tensor,
+                  lowp: torch.Tensor,
+                  n_valid: int,
+                  segments: Sequence[Tuple[int, int, int]],
+                  exp_avg: Optional[torch.Tensor] = None,
+                  exp_avg_sq: Optional[torch.Tensor] = None) -> int:
+        """Register a shard: fp32 master, the paired low-precision shard (gradient in / parameter out),
+        ``valid_end`` and the (begin, end, param-group) ranges the optimizer updates.  The two moments
+        are allocated here, flat and congruent with the master, unless given."""
+        exp_avg = torch.zeros_like(master) if exp_avg is None else exp_avg
+        exp_avg_sq = torch.zeros_like(master) if exp_avg_sq is None else exp_avg_sq
+        index = self.table.add_chunk(master, exp_avg, exp_avg_sq, lowp, n_valid, segments)
+        self.shards.append((master, exp_avg, exp_avg_sq, lowp, n_valid))
+        return index
+
+    def finalize(self):
+        self.table.finalize()
+        n = max(1, self.table.n_chunks)
+        self.chunk_flags = torch.zeros(n, dtype=torch.int32, device=self.device)
+        self.chunk_l2sq = torch.zeros(n, dtype=torch.float32, device=self.device)
+        self.total_l2sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        if self.clipping:
+            self._scratch = torch.empty(max(1, self.table.tiles()), dtype=torch.float32, device=self.device)
+        self._finalized = True
+        return self
+
+    @property
+    def n_chunks(self) -> int:
+        return self.table.n_chunks
+
+    def n_elements(self) -> int:
+        return sum(s[0].numel() for s in self.shards)
+
+    def set_hyper(self, groups):
+        self.table.set_hyper(groups)
+
+    # ------------------------------------------------------------------ gradient arrival
+
+    def land(self, index: int, src: torch.Tensor):
+        """Copy reduced gradients ``src`` into shard ``index`` and probe them in the same pass."""
+        lowp, n_valid = self.shards[index][3], self.shards[index][4]
+        kernels.reduce_epilogue(src, lowp, n_valid=n_valid, flag=self.chunk_flags[index:index + 1], ctl=self.ctl)
+
+    def probe(self, first: int = 0, count: Optional[int] = None):
+        """Probe gradients that were written straight into the shards."""
+        kernels.grad_check_multi(self.table, self.ctl, chunk_flags=self.chunk_flags, first=first, count=count)
+
+    def probe_one(self, index: int):
+        lowp, n_valid = self.shards[index][3], self.shards[index][4]
+        kernels.grad_check(lowp, n_valid=n_valid, flag=self.chunk_flags[index:index + 1], ctl=self.ctl)
+
+    # ------------------------------------------------------------------ the step
+
+    def begin_step(self):
+        if self.world > 1 and self.sync_overflow:
+            comm.agree_on_overflow(self.ctl.found_inf, self.group)
+        norm_sq = None
+        if self.clipping:
+            kernels.grad_check_multi(self.table, None, chunk_l2sq=self.chunk_l2sq, total_l2sq=self.total_l2sq,
+                                     scratch=self._scratch)
+            if self.world > 1:
+                dist.all_reduce(self.total_l2sq, group=self.group)
+            norm_sq = self.total_l2sq
+        kernels.step_begin(self.ctl, self.scaler.cfg, norm_sq)
+
+    def update(self, first: int = 0, count: Optional[int] = None):
+        kernels.adam_multi(self.table, self.ctl, first=first, count=count)
+
+    def end_step(self):
+        self.chunk_flags.zero_()
+
+    def step(self):
+        """Decision + fused update of every shard.  Gradients must already sit (probed) in the shards."""
+        self.begin_step()
+        self.update()
+        self.end_step()
+
+    # ------------------------------------------------------------------ pipelines
+
+    def _side_streams(self):
+        if self._streams is None:
+            self._streams = (torch.cuda.Stream(self.device), torch.cuda.Stream(self.device))
+        return self._streams
+
+    def step_sharded(self,
+                     grad_blocks: Sequence[torch.Tensor],
+                     gather_blocks: Sequence[Optional[torch.Tensor]],
+                     host_grads: Optional[Sequence[torch.Tensor]] = None,
+                     host_params: Optional[Sequence[torch.Tensor]] = None):
+        """Sharded step: for chunk k, ``grad_blocks[k]`` is the replicated gradient block (chunk_size
+        elements) and ``gather_blocks[k]`` the block the updated parameters are gathered into (or None).
+
+        reduce stream:  RS(0) RS(1) ...            (rank average, output straight into the shard)
+        main stream:       probe(0) probe(1) ... | decision | Adam(0) Adam(1) ...
+        gather stream:                                           AG(0)   AG(1) ...
+        The update of any chunk starts only after every chunk was reduced and probed, because one
+        overflow anywhere skips the whole step (``elixir/wrapper/optimizer.py:194-203``).
+
+        With ``host_grads`` (pinned, chunk_size each) block k is first filled from the host on the reduce
+        stream; with ``host_params`` (pinned, shard_size each) the updated shard k is copied out on the
+        gather stream.  Blocks may be reused between chunks: stream order keeps each reuse behind the
+        collective that last read or wrote the block.
+        """
+        assert len(grad_blocks) == self.n_chunks and len(gather_blocks) == self.n_chunks
+        main = torch.cuda.current_stream(self.device)
+        reduce_stream, gather_stream = self._side_streams()
+        reduce_stream.wait_stream(main)
+        gather_stream.wait_stream(main)
+        for k, block in enumerate(grad_blocks):
+            lowp = self.shards[k][3]
+            with torch.cuda.stream(reduce_stream):
+                if host_grads is not None:
+                    block.copy_(host_grads[k], non_blocking=True)
+                comm.reduce_scatter_avg(lowp, block, self.group)
+                done = torch.cuda.Event()
+                done.record(reduce_stream)
+            main.wait_event(done)
+            self.probe_one(k)
+        self.begin_step()
+        for k, block in enumerate(gather_blocks):
+            self.update(first=k, count=1)
+            if block is None and host_params is None:
+                continue
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(gather_stream):
+                gather_stream.wait_event(done)
+                if block is not None:
+                    comm.all_gather(block, self.shards[k][3], self.group)
+                if host_params is not None:
+                    host_params[k].copy_(self.shards[k][3], non_blocking=True)
+        self.end_step()
+        main.wait_stream(gather_stream)
+
+    def step_from_host(self, host_grads: Sequence[torch.Tensor], host_params: Sequence[torch.Tensor]):
+        """A whole step with host buffers on both ends: ``host_grads[k]`` (pinned, shard_size elements of
+        the chunk dtype) holds the reduced gradients of shard k; ``host_params[k]`` (pinned) receives the
+        updated low-precision parameters.  Copies in, probes, updates and copies out are pipelined per
+        chunk on three streams; fp32 master and moments never leave the device."""
+        assert len(host_grads) == self.n_chunks and len(host_params) == self.n_chunks
+        main = torch.cuda.current_stream(self.device)
+        h2d, d2h = self._side_streams()
+        h2d.wait_stream(main)
+        for k, src in enumerate(host_grads):
+            lowp = self.shards[k][3]
+            with torch.cuda.stream(h2d):
+                lowp.copy_(src, non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(h2d)
+            main.wait_event(arrived)
+            self.probe_one(k)
+        self.begin_step()
+        for k, dst in enumerate(host_params):
+            self.update(first=k, count=1)
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(d2h):
+                d2h.wait_event(done)
+                dst.copy_(self.shards[k][3], non_blocking=True)
+        self.end_step()
+        main.wait_stream(d2h)
+
+    # ------------------------------------------------------------------ introspection (synchronising)
+
+    def read_control(self):
+        return self.ctl.read()
+
+    def check_status(self):
+        """Raise if a kernel reported an anomaly (sticky status word).  Synchronises."""
+        c = self.ctl.read()
+        if c.status:
+            raise RuntimeError(f'elixir_b200 kernels reported status {c.status:#x} '
+                               f'(1: non-finite gradient met on an applied step, 2: descriptor table mismatch)')
+EOF
+echo ok

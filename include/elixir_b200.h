@@ -1,0 +1,246 @@
+/*
+ * elixir_b200 — C ABI of the chunk-level mixed-precision optimizer step for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a host runtime binds to (ctypes / cffi / pybind / plain C).  Every pointer
+ * marked "device" is a CUDA device pointer owned by the caller; the library never allocates, frees
+ * or synchronises.  Every entry point is stream-ordered on the `stream` it is given (a cudaStream_t
+ * passed as void*, NULL = the legacy default stream) and returns an `int` status: 0 on success,
+ * a negative ELX_ERR_* code when an argument is rejected (nothing was launched) or a launch failed.
+ *
+ * The functions replace the following pieces of hpcaitech/Elixir (paths inside that project):
+ *   elixir/wrapper/optimizer.py   ElixirOptimizer.step / _check_overflow / _get_combined_scale
+ *   elixir/chunk/core/chunk.py    Chunk.reduce (copy into the shard), set_overflow_flag,
+ *                                 set_l2_norm, optim_update
+ *   colossalai FusedAdam/HybridAdam.step(div_scale=...) and DynamicGradScaler.update(...)
+ *   (third-party to Elixir, called at elixir/wrapper/optimizer.py:78-86,198,208,216)
+ */
+#ifndef ELIXIR_B200_H
+#define ELIXIR_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ELX_ABI_VERSION 1
+
+/* Elements per work tile.  `ElxChunkDesc.tile_begin` counts tiles of this many elements. */
+#define ELX_TILE 4096
+
+/* dtype codes for the low-precision (working / gradient) chunk. */
+#define ELX_F16 0
+#define ELX_BF16 1
+#define ELX_F32 2
+
+/* status codes */
+#define ELX_OK 0
+#define ELX_ERR_NULL (-1)      /* a required pointer is NULL                                   */
+#define ELX_ERR_ALIGN (-2)     /* a pointer is not aligned as documented                        */
+#define ELX_ERR_SIZE (-3)      /* negative size, n_valid > n_shard, count out of range ...      */
+#define ELX_ERR_DTYPE (-4)     /* unknown dtype code                                            */
+#define ELX_ERR_LAUNCH (-5)    /* the CUDA runtime rejected the launch (see elx_last_cuda_error) */
+#define ELX_ERR_ARG (-6)       /* inconsistent argument combination                             */
+#define ELX_ERR_NODEVICE (-7)  /* no usable CUDA device / driver                                */
+#define ELX_ERR_CAPACITY (-8)  /* request exceeds a documented fixed capacity                   */
+
+/* sticky bits in ElxCtl.status */
+#define ELX_STAT_LATE_INF 1u   /* the Adam kernel met a non-finite gradient the probe had not flagged */
+#define ELX_STAT_BAD_DESC 2u   /* a kernel could not map a tile to a chunk descriptor                   */
+
+/*
+ * Device-resident control block of one optimizer (128 bytes, 16-byte aligned).  It replaces the
+ * host-side state that the reference reads back with .item() on every step: the loss scale and
+ * its counters (DynamicGradScaler), the per-chunk overflow booleans OR-ed by
+ * ElixirOptimizer._check_overflow (optimizer.py:137-142), and the per-tensor Adam step count.
+ */
+typedef struct ElxCtl {
+    float    scale;            /* current loss scale                                             */
+    uint32_t found_inf;        /* OR of all probes since the last elx_step_begin                  */
+    int32_t  growth_step;      /* clean steps since the last growth / overflow                    */
+    int32_t  hysteresis_step;  /* overflows seen since the last growth                            */
+    int32_t  step;             /* number of applied (non-skipped) Adam steps                      */
+    uint32_t skip;             /* decision of the last elx_step_begin: 1 = copy-back only         */
+    float    div_scale;        /* divisor for the gradients of this step, -1 = do not divide      */
+    float    inv_div;          /* 1/div_scale when that product is exact (power of two), else 0   */
+    uint32_t skipped_steps;    /* total skipped steps                                             */
+    uint32_t status;           /* sticky ELX_STAT_* bits                                          */
+    uint32_t late_inf;         /* set by the Adam kernel when it meets inf/nan on an applied step */
+    uint32_t ticket;           /* internal: last-block election of the probe kernels              */
+    float    clip_coef;        /* clip factor of the last applied step (1 = not clipped)          */
+    float    grad_norm;        /* unscaled global gradient norm of the last applied step          */
+    uint32_t reserved[18];
+} ElxCtl;
+
+/* Loss-scaler configuration, passed by value.  Mirrors DynamicGradScaler / ConstantGradScaler as
+ * constructed at elixir/wrapper/optimizer.py:76-86. */
+typedef struct ElxScalerCfg {
+    int32_t dynamic;           /* 1 = dynamic scaler, 0 = constant scale (never updated)          */
+    float   growth_factor;
+    float   backoff_factor;
+    float   min_scale;         /* <= 0: no lower bound                                            */
+    float   max_scale;         /* <= 0: no upper bound                                            */
+    int32_t growth_interval;
+    int32_t hysteresis;
+    float   max_norm;          /* > 0 enables gradient clipping by global L2 norm                 */
+} ElxScalerCfg;
+
+/* Hyper-parameters of one optimizer param group (host-written device table, 32 bytes each). */
+typedef struct ElxHyper {
+    float   lr;
+    float   beta1;
+    float   beta2;
+    float   eps;
+    float   weight_decay;
+    int32_t adamw_mode;        /* 1 = decoupled decay (AdamW), 0 = L2 (decay added to the gradient) */
+    int32_t bias_correction;   /* 0 = both corrections are 1                                        */
+    int32_t reserved;
+} ElxHyper;
+
+/* A contiguous range [begin, end) of a shard whose elements belong to param group `group`.
+ * Segments of one chunk are sorted, disjoint and lie inside [0, n_valid).  Elements of the shard
+ * covered by no segment are not updated (their working copy is still refreshed from the master).
+ * Equivalent of ElixirOptimizer.param_to_range (optimizer.py:238-265) with neighbours merged. */
+typedef struct ElxSeg {
+    int64_t begin;
+    int64_t end;
+    int32_t group;
+    int32_t reserved;
+} ElxSeg;
+
+/* One chunk shard of this rank (device table, 72 bytes each): the fp32 master chunk's shard, the
+ * two Adam moments laid out congruently, and the paired low-precision shard that holds the
+ * gradient before the step and the refreshed working copy after it (optimizer.py:115-124,
+ * chunk.py:403-415).  All four pointers must be 32-byte aligned. */
+typedef struct ElxChunkDesc {
+    float*  master;            /* device, n_shard floats                                           */
+    float*  exp_avg;           /* device, n_shard floats                                           */
+    float*  exp_avg_sq;        /* device, n_shard floats                                           */
+    void*   grad_param;        /* device, n_shard elements of `dtype`: gradient in, working copy out */
+    int64_t n_shard;           /* shard_size                                                       */
+    int64_t n_valid;           /* valid_end: elements that hold real parameters (chunk.py:253-257) */
+    int64_t tile_begin;        /* sum over earlier descriptors of ceil(n_shard / ELX_TILE)         */
+    int32_t seg_first;         /* index of this chunk's first segment in the segment table         */
+    int32_t seg_count;
+    int32_t dtype;             /* ELX_F16 / ELX_BF16 / ELX_F32                                      */
+    int32_t reserved;
+} ElxChunkDesc;
+
+/* ---- library ----------------------------------------------------------------------------- */
+
+/* ABI version of the loaded library (ELX_ABI_VERSION it was built with). */
+int elx_version(void);
+
+/* Static, human-readable text for a status code. */
+const char* elx_strerror(int status);
+
+/* Text of the last CUDA runtime error seen by this thread inside the library ("" if none). */
+const char* elx_last_cuda_error(void);
+
+/* Launch-shape knobs, by name; a negative value restores the default.  Affects later launches of
+ * the calling process; results never depend on them (bit-identical for every setting except
+ * math_mode).
+ *   "adam_threads"       256 (16 elements per thread) or 512 (8 per thread)
+ *   "adam_min_blocks"    1..3: CTAs per SM the Adam kernel is compiled for (register budget)
+ *   "adam_ctas_per_sm"   cap on the persistent grid, 0 = every resident CTA
+ *   "probe_ctas_per_sm"  the same for the probe kernels
+ *   "probe_unroll"       4 or 8 tiles in flight per probe CTA
+ *   "math_mode"          1 = IEEE division and square root in the update, 2 = reciprocal
+ *                        multiplies and approximate division (both within 1e-6 relative) */
+int elx_set_tuning(const char* name, int value);
+
+/* Number of floats of scratch the probe entry points need for `n_tiles` tiles when an L2 norm is
+ * requested (one partial sum per tile). */
+int64_t elx_probe_scratch_elems(int64_t n_tiles);
+
+/* ---- control block ------------------------------------------------------------------------ */
+
+/* Initialise a device control block: scale = initial_scale, all counters and flags zero.
+ * Replaces DynamicGradScaler.__init__ state.  ctl: device, 16-byte aligned. */
+int elx_ctl_init(ElxCtl* ctl, float initial_scale, void* stream);
+
+/*
+ * The per-step decision, entirely on the device (one tiny launch, no host read-back).  Replaces the
+ * head of ElixirOptimizer.step (optimizer.py:192-209):
+ *   found_inf = OR of chunk overflow flags            (_check_overflow, :137-142)
+ *   if found_inf: skip = 1, scaler.update(True)        (:196-203)
+ *   else: div = loss scale read BEFORE the update, times the clip factor when clipping is on and
+ *         the factor exceeds 1, or -1 when div == 1    (_get_combined_scale, :166-183)
+ *         scaler.update(False); step += 1              (:208, optimizer state['step'])
+ *   found_inf is cleared                               (_clear_optim_states, :144-147)
+ * norm_sq: device pointer to the global sum of squared (still scaled) gradients, or NULL when
+ * cfg.max_norm <= 0.
+ */
+int elx_step_begin(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq, void* stream);
+
+/* ---- overflow / norm probe ------------------------------------------------------------------ */
+
+/*
+ * Probe one gradient shard: set *flag (and ctl->found_inf when ctl != NULL) to 1 if any of the
+ * first n_valid elements is inf or nan, tested on the exponent bits of the stored low-precision
+ * values.  Replaces Chunk.set_overflow_flag (chunk.py:214-216) as used by
+ * update_extra_reduce_info (chunk.py:345-356).  The flag is only ever raised, never cleared.
+ * When l2sq != NULL the sum of squares of the same elements (each converted to fp32) is written
+ * to *l2sq, reduced in a fixed order (bit-reproducible); replaces set_l2_norm (chunk.py:218-221).
+ * That needs `scratch` (device floats, >= elx_probe_scratch_elems(ceil(n_valid/ELX_TILE))).
+ * g: device, 32-byte aligned.  flag, l2sq may alias nothing else.
+ */
+int elx_grad_check(const void* g, int dtype, int64_t n_valid, uint32_t* flag, ElxCtl* ctl,
+                   float* l2sq, float* scratch, int64_t scratch_elems, void* stream);
+
+/*
+ * The same probe fused with the copy that ends Chunk.reduce (chunk.py:313, 484-489): copies
+ * n_shard elements src -> dst (the reduced slice of the replicated block into the persistent
+ * shard) and probes the first n_valid of them in the same pass.  src, dst: device, 32-byte
+ * aligned, must not overlap.
+ */
+int elx_reduce_epilogue(const void* src, void* dst, int dtype, int64_t n_shard, int64_t n_valid,
+                        uint32_t* flag, ElxCtl* ctl, float* l2sq, float* scratch,
+                        int64_t scratch_elems, void* stream);
+
+/*
+ * Probe descriptors [first, first + count) of a descriptor table in ONE launch.  chunk_flags
+ * (device, one uint32 per descriptor of the table, may be NULL) receives the per-chunk overflow
+ * booleans (Chunk.overflow); ctl->found_inf receives their OR.  When chunk_l2sq != NULL it
+ * receives one sum of squares per descriptor (Chunk.l2_norm) and total_l2sq (may be NULL) their
+ * sum in descriptor order.  n_tiles = number of ELX_TILE tiles of the probed descriptors; dtype =
+ * the dtype every probed descriptor carries (a descriptor with another dtype is left untouched and
+ * raises ELX_STAT_BAD_DESC in ctl->status).
+ */
+int elx_grad_check_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles,
+                         int dtype, uint32_t* chunk_flags, ElxCtl* ctl, float* chunk_l2sq, float* total_l2sq,
+                         float* scratch, int64_t scratch_elems, void* stream);
+
+/* ---- fused update ---------------------------------------------------------------------------- */
+
+/*
+ * The fused step over descriptors [first, first + count): for every element of every segment
+ *   g = float(g_lowp);  g = g / ctl->div_scale (when > 0);  Adam / AdamW on master, exp_avg,
+ *   exp_avg_sq with the group's hyper-parameters and bias corrections for ctl->step;
+ * then, over the WHOLE shard [0, n_shard), the working copy is refreshed with the master rounded
+ * to nearest-even.  When ctl->skip is 1 only the refresh runs.  One pass over memory: 28 bytes per
+ * element with 16-bit gradients.  Replaces _set_grad_ptr + optim.step(div_scale) +
+ * _update_fp16_params (optimizer.py:115-135, 216-219; chunk.py:403-415).
+ * n_tiles = number of ELX_TILE tiles of those descriptors; dtype = the dtype all of them carry.
+ * hyper: device table of n_groups entries (n_groups <= 64).  All tables are device memory.
+ */
+int elx_adam_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                   const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl,
+                   void* stream);
+
+/*
+ * Single-shard convenience form with the hyper-parameters by value and one implicit segment
+ * [0, n_valid).  Same arithmetic as elx_adam_multi.  Pointers need only be aligned to their
+ * element size; the vector path is used when all of them are 32-byte aligned.
+ */
+int elx_adam_chunk(float* master, float* exp_avg, float* exp_avg_sq, void* grad_param, int dtype,
+                   int64_t n_valid, int64_t n_shard, ElxHyper hyper, ElxCtl* ctl, void* stream);
+
+/* Working-copy refresh alone: dst[i] = round_to_nearest_even(master[i]) for i in [0, n).
+ * Replaces Chunk.optim_update for CUDA shards (chunk.py:413-415). */
+int elx_cast_copyback(const float* master, void* dst, int dtype, int64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ELIXIR_B200_H */

@@ -1,0 +1,498 @@
+"""Parity of the CUDA kernels (called through the C ABI) against the CPU oracle on the same seeded inputs.
+
+Bars: overflow flag, skip decision, scaler state and the low-precision copy of the kernel's own
+master: bit-exact.  fp32 master / exp_avg / exp_avg_sq: within 1e-6 (relative to max(|x|, rms)) of
+the double-precision oracle.  Low-precision working copy vs the oracle's: within 1 ulp of the format.
+"""
+import ctypes
+
+import pytest
+import torch
+
+from _util import bits_equal, close_1e6, lowp_within_1ulp, make_chunk
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float16, torch.bfloat16, torch.float32]
+SIZES = [1, 7, 8, 9, 1023, 4096, 4097, 3 * 4096 + 15, 70001, (1 << 20) + 3]
+
+
+@pytest.fixture(scope='module')
+def K(cuda):
+    from elixir_b200 import kernels
+    return kernels
+
+
+def _inject(g, positions, values):
+    for pos, val in zip(positions, values):
+        g[pos] = val
+    return g
+
+
+# --------------------------------------------------------------------------------------------------
+# probe
+# --------------------------------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
+@pytest.mark.parametrize('n', SIZES)
+def test_probe_clean_and_dirty(K, oracle, cuda, dtype, n):
+    gen = torch.Generator().manual_seed(n)
+    g = (torch.randn(n, generator=gen) * 100).to(dtype)
+    cases = [('clean', [], [])]
+    for name, val in (('inf', float('inf')), ('ninf', -float('inf')), ('nan', float('nan'))):
+        cases.append((name + '_first', [0], [val]))
+        cases.append((name + '_last', [n - 1], [val]))
+        cases.append((name + '_mid', [n // 2], [val]))
+    for name, pos, vals in cases:
+        gc = _inject(g.clone(), pos, vals)
+        want = oracle.probe(gc)
+        assert want == (name != 'clean')
+        flag = torch.zeros(1, dtype=torch.int32, device=cuda)
+        ctl = K.ControlBlock(cuda, 1.0)
+        K.grad_check(gc.to(cuda), flag=flag, ctl=ctl)
+        assert bool(flag.item()) == want, (name, n, dtype)
+        assert bool(ctl.read().found_inf) == want
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
+def test_probe_respects_valid_end(K, oracle, cuda, dtype):
+    n = 5 * 4096 + 100
+    g = torch.ones(n, dtype=dtype)
+    for n_valid in (0, 1, 4095, 4096, 4097, 3 * 4096, n - 1):
+        gc = g.clone()
+        gc[n_valid] = float('nan')    # first element of the padding: must not count
+        flag = torch.zeros(1, dtype=torch.int32, device=cuda)
+        K.grad_check(gc.to(cuda), n_valid=n_valid, flag=flag)
+        assert flag.item() == 0 and not oracle.probe(gc, n_valid)
+        if n_valid > 0:
+            gc[n_valid - 1] = float('inf')    # last valid element: must count
+            K.grad_check(gc.to(cuda), n_valid=n_valid, flag=flag)
+            assert flag.item() == 1 and oracle.probe(gc, n_valid)
+
+
+def test_probe_largest_finite_values_do_not_flag(K, cuda):
+    for dtype, big in ((torch.float16, 65504.0), (torch.bfloat16, 3.3895e38), (torch.float32, 3.4028e38)):
+        g = torch.full((8192,), big, dtype=dtype, device=cuda)
+        g[1::2] = -big
+        assert torch.isfinite(g.float()).all()
+        flag = torch.zeros(1, dtype=torch.int32, device=cuda)
+        K.grad_check(g, flag=flag)
+        assert flag.item() == 0
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
+@pytest.mark.parametrize('n', [1, 4095, 4096, 70001, (1 << 22) + 17])
+def test_probe_l2_norm(K, oracle, cuda, dtype, n):
+    gen = torch.Generator().manual_seed(n + 1)
+    g = (torch.randn(n, generator=gen) * 3).to(dtype)
+    n_valid = max(0, n - 5)
+    want = oracle.l2sq(g, n_valid)
+    gd = g.to(cuda)
+    out = torch.full((1,), -1.0, device=cuda)
+    scratch = torch.empty(K.n_tiles(n), device=cuda)
+    K.grad_check(gd, n_valid=n_valid, l2sq=out, scratch=scratch)
+    got = out.item()
+    assert abs(got - want) <= 1e-5 * max(want, 1e-30), (got, want)
+    # bit-reproducible, also under another grid size
+    K.set_tuning(probe_ctas_per_sm=1)
+    try:
+        out2 = torch.full((1,), -1.0, device=cuda)
+        K.grad_check(gd, n_valid=n_valid, l2sq=out2, scratch=scratch)
+    finally:
+        K.set_tuning(probe_ctas_per_sm=-1)
+    assert bits_equal(out, out2)
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
+@pytest.mark.parametrize('n,n_valid', [(1, 1), (4096, 4096), (4097, 100), (70001, 69000), (1 << 20, 0), ((1 << 20) + 8, 1 << 19)])
+def test_reduce_epilogue_copy_and_probe(K, oracle, cuda, dtype, n, n_valid):
+    gen = torch.Generator().manual_seed(n)
+    src = (torch.randn(n, generator=gen) * 10).to(dtype)
+    for dirty in (False, True):
+        s = src.clone()
+        if dirty and n_valid > 0:
+            s[n_valid - 1] = float('inf')
+        if n_valid < n:
+            s[n_valid] = float('nan')    # padding is copied but never probed
+        dst = torch.zeros(n, dtype=dtype, device=cuda)
+        flag = torch.zeros(1, dtype=torch.int32, device=cuda)
+        K.reduce_epilogue(s.to(cuda), dst, n_valid=n_valid, flag=flag)
+        assert bits_equal(dst, s)
+        assert bool(flag.item()) == oracle.probe(s, n_valid) == (dirty and n_valid > 0)
+
+
+# --------------------------------------------------------------------------------------------------
+# control block: decision + loss scaler
+# --------------------------------------------------------------------------------------------------
+
+
+def _ctl_fields(c):
+    return (c.scale, c.found_inf, c.growth_step, c.hysteresis_step, c.step, c.skip, c.div_scale, c.inv_div,
+            c.skipped_steps)
+
+
+@pytest.mark.parametrize('hysteresis', [1, 2, 3])
+@pytest.mark.parametrize('initial', [65536.0, 1.0, 3.0])
+def test_scaler_trajectory_bit_exact(K, oracle, cuda, hysteresis, initial):
+    cfg = K.scaler_cfg(True, 2.0, 0.5, 1.0, 2.0**24, growth_interval=5, hysteresis=hysteresis)
+    gen = torch.Generator().manual_seed(hysteresis * 100 + int(initial))
+    pattern = (torch.rand(400, generator=gen) < 0.15).tolist()
+    dev = K.ControlBlock(cuda, initial)
+    host = oracle.new_ctl(initial)
+    for found in pattern:
+        if found:
+            dev.found_inf.fill_(1)
+            host.found_inf = 1
+        K.step_begin(dev, cfg)
+        oracle.step_begin(host, cfg)
+        assert _ctl_fields(dev.read()) == _ctl_fields(host)
+    assert host.skipped_steps == sum(pattern)
+
+
+def test_constant_scaler_and_clip(K, oracle, cuda):
+    cfg = K.scaler_cfg(False, max_norm=1.0)
+    dev = K.ControlBlock(cuda, 1.0)
+    host = oracle.new_ctl(1.0)
+    for norm_sq in (0.25, 4.0, 1.0, 123.456):
+        ns = torch.tensor([norm_sq], device=cuda)
+        K.step_begin(dev, cfg, ns)
+        oracle.step_begin(host, cfg, norm_sq)
+        d = dev.read()
+        assert _ctl_fields(d) == _ctl_fields(host)
+        assert (d.clip_coef, d.grad_norm) == (host.clip_coef, host.grad_norm)
+    # scale 1 and no clipping: the divisor is the -1 sentinel
+    K.step_begin(dev, K.scaler_cfg(False))
+    assert dev.read().div_scale == -1.0
+
+
+# --------------------------------------------------------------------------------------------------
+# fused Adam, single shard
+# --------------------------------------------------------------------------------------------------
+
+HYPERS = [
+    dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, adamw_mode=True),
+    dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, adamw_mode=True),
+    dict(lr=1e-3, betas=(0.8, 0.95), eps=1e-8, weight_decay=0.1, adamw_mode=False),
+    dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, adamw_mode=True, bias_correction=False),
+]
+
+
+def _run_single(K, oracle, cuda, n, dtype, hyper_kw, scale, steps, n_valid=None, math_mode=1):
+    n_valid = n if n_valid is None else n_valid
+    h = K.hyper(**hyper_kw)
+    cfg = K.scaler_cfg(False)
+    p, m, v, g = make_chunk(n, dtype, seed=n + steps, scale=scale)
+    dp, dm, dv = p.to(cuda), m.to(cuda), v.to(cuda)
+    ref = [t.clone() for t in (p, m, v)]
+    f32 = [t.clone() for t in (p, m, v)]
+    dev_ctl = K.ControlBlock(cuda, scale)
+    host_ctl = oracle.new_ctl(scale)
+    K.set_tuning(math_mode=math_mode)
+    try:
+        for s in range(steps):
+            gen = torch.Generator().manual_seed(1000 * s + n)
+            g = (torch.randn(n, generator=gen) * 1e-3 * scale).to(dtype)
+            dg = g.to(cuda)
+            K.step_begin(dev_ctl, cfg)
+            oracle.step_begin(host_ctl, cfg)
+            K.adam_chunk(dp, dm, dv, dg, h, dev_ctl, n_valid=n_valid)
+            oracle.adam(ref[0], ref[1], ref[2], g, h, host_ctl.step, host_ctl.div_scale, 0, n_valid, f64=True)
+            oracle.adam(f32[0], f32[1], f32[2], g, h, host_ctl.step, host_ctl.div_scale, 0, n_valid, f64=False)
+    finally:
+        K.set_tuning(math_mode=-1)
+    return (dp, dm, dv, dg), ref, f32, dev_ctl
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
+@pytest.mark.parametrize('n', SIZES)
+def test_adam_chunk_sizes(K, oracle, cuda, dtype, n):
+    (dp, dm, dv, dg), ref, _, ctl = _run_single(K, oracle, cuda, n, dtype, HYPERS[1], 64.0, steps=2)
+    for name, got, want in (('master', dp, ref[0]), ('exp_avg', dm, ref[1]), ('exp_avg_sq', dv, ref[2])):
+        ok, ratio = close_1e6(got, want)
+        assert ok, (name, n, dtype, ratio)
+    # the working copy is the kernel's own master rounded to nearest even: bit-exact
+    want16 = torch.empty(n, dtype=dtype)
+    oracle.cast(dp.cpu(), want16)
+    assert bits_equal(dg, want16)
+    if dtype != torch.float32:
+        ref16 = torch.empty(n, dtype=dtype)
+        oracle.cast(ref[0], ref16)
+        assert lowp_within_1ulp(dg, ref16, ref[0])[0]
+    assert ctl.read().status == 0 and ctl.read().late_inf == 0
+
+
+@pytest.mark.parametrize('math_mode', [1, 2])
+@pytest.mark.parametrize('hyper_kw', HYPERS)
+@pytest.mark.parametrize('scale', [1.0, 64.0, 65536.0, 3.7])
+def test_adam_chunk_hypers_scales(K, oracle, cuda, hyper_kw, scale, math_mode):
+    n = 5 * 4096 + 77
+    (dp, dm, dv, dg), ref, f32, ctl = _run_single(K, oracle, cuda, n, torch.float16, hyper_kw, scale, steps=3,
+                                                  math_mode=math_mode)
+    for name, got, want in (('master', dp, ref[0]), ('exp_avg', dm, ref[1]), ('exp_avg_sq', dv, ref[2])):
+        ok, ratio = close_1e6(got, want)
+        assert ok, (name, hyper_kw, scale, ratio)
+    want_div = -1.0 if scale == 1.0 else scale
+    assert abs(ctl.read().div_scale - want_div) < 1e-6 * abs(want_div)
+
+
+def test_adam_chunk_ill_conditioned_update_no_worse_than_strict_fp32(K, oracle, cuda):
+    """With a large lr and eps, elements whose effective gradient is of the order of eps amplify fp32
+    rounding beyond 1e-6 in ANY fp32 evaluation.  There the kernel must stay within a small multiple
+    of the error the strict-fp32 oracle itself makes against the double-precision one."""
+    hyper_kw = dict(lr=3e-2, betas=(0.8, 0.95), eps=1e-6, weight_decay=0.1, adamw_mode=False)
+    n = 5 * 4096 + 77
+    (dp, dm, dv, dg), ref, f32, _ = _run_single(K, oracle, cuda, n, torch.float16, hyper_kw, 1.0, steps=3)
+    for got, want64, want32 in zip((dp, dm, dv), ref, f32):
+        err_gpu = (got.cpu().double() - want64.double()).abs()
+        err_f32 = (want32.double() - want64.double()).abs()
+        rms = want64.double().pow(2).mean().sqrt()
+        bound = 1e-6 * torch.maximum(want64.double().abs(), rms.expand_as(err_gpu))
+        bad = err_gpu > bound
+        assert bad.double().mean().item() < 0.02
+        assert (err_gpu[bad] <= 8 * err_f32[bad] + bound[bad]).all()
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_adam_chunk_padding_is_only_refreshed(K, oracle, cuda, dtype):
+    n, n_valid = 6 * 4096, 2 * 4096 + 33
+    h = K.hyper(weight_decay=0.01)
+    p, m, v, g = make_chunk(n, dtype, seed=5)
+    m += 0.5
+    v += 0.25
+    dp, dm, dv, dg = (t.to(cuda) for t in (p, m, v, g))
+    ctl = K.ControlBlock(cuda, 64.0)
+    K.step_begin(ctl, K.scaler_cfg(False))
+    K.adam_chunk(dp, dm, dv, dg, h, ctl, n_valid=n_valid)
+    assert bits_equal(dp[n_valid:], p[n_valid:])
+    assert bits_equal(dm[n_valid:], m[n_valid:])
+    assert bits_equal(dv[n_valid:], v[n_valid:])
+    want16 = torch.empty(n, dtype=dtype)
+    oracle.cast(dp.cpu(), want16)
+    assert bits_equal(dg, want16)
+    assert not bits_equal(dp[:n_valid], p[:n_valid])
+
+
+def test_adam_chunk_unaligned_views(K, oracle, cuda):
+    """Views that start off a 32-byte boundary take the scalar path and still match."""
+    n = 3 * 4096 + 5
+    h = K.hyper(weight_decay=0.01)
+    p, m, v, g = make_chunk(n + 3, torch.float16, seed=9)
+    dp, dm, dv, dg = (t.to(cuda) for t in (p, m, v, g))
+    ctl = K.ControlBlock(cuda, 64.0)
+    host = oracle.new_ctl(64.0)
+    K.step_begin(ctl, K.scaler_cfg(False))
+    oracle.step_begin(host, K.scaler_cfg(False))
+    K.adam_chunk(dp[3:], dm[3:], dv[3:], dg[3:], h, ctl)
+    rp, rm, rv = p[3:].clone(), m[3:].clone(), v[3:].clone()
+    oracle.adam(rp, rm, rv, g[3:].clone(), h, host.step, host.div_scale, f64=True)
+    for got, want in ((dp[3:], rp), (dm[3:], rm), (dv[3:], rv)):
+        assert close_1e6(got, want)[0]
+    assert bits_equal(dp[:3], p[:3]) and bits_equal(dg[:3], g[:3])
+
+
+def test_skip_leaves_state_untouched_and_restores_params(K, oracle, cuda):
+    n = 4 * 4096 + 9
+    p, m, v, g = make_chunk(n, torch.float16, seed=11, scale=65536.0)
+    m += 0.125
+    g[n // 3] = float('inf')
+    dp, dm, dv, dg = (t.to(cuda) for t in (p, m, v, g))
+    ctl = K.ControlBlock(cuda, 65536.0)
+    cfg = K.scaler_cfg(True, hysteresis=1)
+    K.grad_check(dg, ctl=ctl)
+    K.step_begin(ctl, cfg)
+    K.adam_chunk(dp, dm, dv, dg, K.hyper(), ctl)
+    c = ctl.read()
+    assert (c.skip, c.step, c.scale, c.skipped_steps, c.found_inf) == (1, 0, 32768.0, 1, 0)
+    assert bits_equal(dp, p) and bits_equal(dm, m) and bits_equal(dv, v)
+    want16 = torch.empty(n, dtype=torch.float16)
+    oracle.cast(p, want16)
+    assert bits_equal(dg, want16)
+
+
+def test_late_inf_is_reported(K, cuda):
+    """A non-finite gradient on an applied step (probe not run) raises the sticky status bit."""
+    n = 2 * 4096
+    p, m, v, g = make_chunk(n, torch.float16, seed=13)
+    g[17] = float('nan')
+    dp, dm, dv, dg = (t.to(cuda) for t in (p, m, v, g))
+    ctl = K.ControlBlock(cuda, 64.0)
+    K.step_begin(ctl, K.scaler_cfg(False))
+    K.adam_chunk(dp, dm, dv, dg, K.hyper(), ctl)
+    c = ctl.read()
+    assert c.late_inf == 1 and c.status & 1
+
+
+def test_cast_copyback(K, oracle, cuda):
+    for dtype in DTYPES:
+        for n in (1, 4095, 4096, 70001):
+            gen = torch.Generator().manual_seed(n)
+            src = torch.randn(n, generator=gen) * torch.logspace(-8, 5, n)
+            dst = torch.empty(n, dtype=dtype, device=cuda)
+            K.cast_copyback(src.to(cuda), dst)
+            want = torch.empty(n, dtype=dtype)
+            oracle.cast(src, want)
+            assert bits_equal(dst, want)
+
+
+# --------------------------------------------------------------------------------------------------
+# multi-chunk launches
+# --------------------------------------------------------------------------------------------------
+
+
+def _build_set(K, oracle, cuda, dtype, sizes, valid, seg_lists, seed, scale):
+    table = K.ChunkTable(cuda, dtype)
+    host = oracle.ChunkSet(dtype)
+    dev_tensors, host_tensors = [], []
+    for c, (n, nv, segs) in enumerate(zip(sizes, valid, seg_lists)):
+        p, m, v, g = make_chunk(n, dtype, seed=seed + c, scale=scale)
+        dts = tuple(t.to(cuda) for t in (p, m, v, g))
+        table.add_chunk(*dts, n_valid=nv, segments=segs)
+        host.add_chunk(p, m, v, g, nv, segs)
+        dev_tensors.append(dts)
+        host_tensors.append((p, m, v, g))
+    table.finalize()
+    return table, host, dev_tensors, host_tensors
+
+
+def _segments(n_valid, cuts, groups):
+    """Split [0, n_valid) at `cuts`; groups[i] < 0 leaves the piece uncovered."""
+    edges = [0] + [c for c in cuts if 0 < c < n_valid] + [n_valid]
+    out = []
+    for i in range(len(edges) - 1):
+        grp = groups[i % len(groups)]
+        if grp >= 0 and edges[i] < edges[i + 1]:
+            out.append((edges[i], edges[i + 1], grp))
+    return out
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
+def test_adam_multi_segments_and_groups(K, oracle, cuda, dtype):
+    sizes = [8 * 4096, 5 * 4096 + 100, 4096, 3, 12 * 4096]
+    valid = [8 * 4096, 5 * 4096 + 100, 1000, 0, 7 * 4096 + 1]
+    seg_lists = [
+        _segments(valid[0], [100, 4096, 4096 + 7, 3 * 4096, 5 * 4096 + 2048], [0, 1, 2, -1, 0, 1]),
+        _segments(valid[1], [2 * 4096], [1, 0]),
+        _segments(valid[2], [], [2]),
+        [],
+        _segments(valid[4], [3 * 4096 + 5], [0, 2]),
+    ]
+    hypers = [
+        K.hyper(1e-3, (0.9, 0.999), 1e-8, 0.01, True),
+        K.hyper(5e-4, (0.9, 0.98), 1e-6, 0.0, True),
+        K.hyper(2e-3, (0.85, 0.99), 1e-8, 0.05, False),
+    ]
+    scale = 1024.0
+    table, host, dev_t, host_t = _build_set(K, oracle, cuda, dtype, sizes, valid, seg_lists, 77, scale)
+    table.set_hyper(hypers)
+    cfg = K.scaler_cfg(True, growth_interval=2, hysteresis=1)
+    dev_ctl = K.ControlBlock(cuda, scale)
+    host_ctl = oracle.new_ctl(scale)
+    flags = torch.zeros(table.n_chunks, dtype=torch.int32, device=cuda)
+    for step in range(4):
+        for c, n in enumerate(sizes):
+            gen = torch.Generator().manual_seed(31 * step + c)
+            g = (torch.randn(n, generator=gen) * 1e-3 * host_ctl.scale).to(dtype)
+            if step == 2 and c == 1:
+                g[valid[c] - 1] = float('inf')
+            host_t[c][3].copy_(g)
+            dev_t[c][3].copy_(g)
+        flags.zero_()
+        K.grad_check_multi(table, dev_ctl, chunk_flags=flags)
+        K.step_begin(dev_ctl, cfg)
+        K.adam_multi(table, dev_ctl)
+        skipped = host.step(host_ctl, cfg, hypers, probe=True, f64=True)
+        assert skipped == (step == 2)
+        assert flags.tolist() == [int(step == 2 and c == 1) for c in range(len(sizes))]
+        assert _ctl_fields(dev_ctl.read()) == _ctl_fields(host_ctl)
+        for c in range(len(sizes)):
+            for name, got, want in zip(('master', 'exp_avg', 'exp_avg_sq'), dev_t[c][:3], host_t[c][:3]):
+                ok, ratio = close_1e6(got, want)
+                assert ok, (step, c, name, ratio)
+            want16 = torch.empty(sizes[c], dtype=dtype)
+            oracle.cast(dev_t[c][0].cpu(), want16)
+            assert bits_equal(dev_t[c][3], want16), (step, c)
+            if dtype != torch.float32:
+                assert lowp_within_1ulp(dev_t[c][3], host_t[c][3], host_t[c][0])[0]
+    assert dev_ctl.read().status == 0
+
+
+def test_adam_multi_sub_ranges_equal_one_launch(K, oracle, cuda):
+    """Launching chunk by chunk (as the sharded pipeline does) gives the same bits as one launch."""
+    sizes = [4 * 4096, 4096 + 5, 9 * 4096]
+    segs = [[(0, n, 0)] for n in sizes]
+    hypers = [K.hyper(weight_decay=0.01)]
+    results = []
+    for per_chunk in (False, True):
+        table, _, dev_t, _ = _build_set(K, oracle, cuda, torch.float16, sizes, sizes, segs, 5, 64.0)
+        table.set_hyper(hypers)
+        ctl = K.ControlBlock(cuda, 64.0)
+        K.step_begin(ctl, K.scaler_cfg(False))
+        if per_chunk:
+            for c in range(len(sizes)):
+                K.adam_multi(table, ctl, first=c, count=1)
+        else:
+            K.adam_multi(table, ctl)
+        results.append([[t.cpu() for t in ts] for ts in dev_t])
+    for a, b in zip(*results):
+        for x, y in zip(a, b):
+            assert bits_equal(x, y)
+
+
+@pytest.mark.parametrize('threads,ctas', [(256, 1), (256, 3), (512, 2), (512, 4)])
+def test_launch_shapes_give_identical_bits(K, oracle, cuda, threads, ctas):
+    sizes = [16 * 4096, 4096 + 5]
+    segs = [[(0, n, 0)] for n in sizes]
+    hypers = [K.hyper(weight_decay=0.01)]
+
+    def run():
+        table, _, dev_t, _ = _build_set(K, oracle, cuda, torch.float16, sizes, sizes, segs, 3, 64.0)
+        table.set_hyper(hypers)
+        ctl = K.ControlBlock(cuda, 64.0)
+        K.step_begin(ctl, K.scaler_cfg(False))
+        K.adam_multi(table, ctl)
+        return [[t.cpu() for t in ts] for ts in dev_t]
+
+    base = run()
+    K.set_tuning(adam_threads=threads, adam_ctas_per_sm=ctas)
+    try:
+        other = run()
+    finally:
+        K.set_tuning(adam_threads=-1, adam_ctas_per_sm=-1)
+    for a, b in zip(base, other):
+        for x, y in zip(a, b):
+            assert bits_equal(x, y)
+
+
+# --------------------------------------------------------------------------------------------------
+# argument validation: errors are status codes, nothing is launched
+# --------------------------------------------------------------------------------------------------
+
+
+def test_bad_arguments_are_rejected(K, cuda):
+    from elixir_b200 import _abi, _lib
+    lib = _lib.get()
+    good = torch.zeros(4096, device=cuda)
+    g16 = torch.zeros(4096, dtype=torch.float16, device=cuda)
+    ctl = K.ControlBlock(cuda, 1.0)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    flag = torch.zeros(1, dtype=torch.int32, device=cuda)
+    assert lib.elx_grad_check(None, 0, 10, P(flag), None, None, None, 0, None) == _abi.ERR_NULL
+    assert lib.elx_grad_check(P(g16), 7, 10, P(flag), None, None, None, 0, None) == _abi.ERR_DTYPE
+    assert lib.elx_grad_check(P(g16), 0, -1, P(flag), None, None, None, 0, None) == _abi.ERR_SIZE
+    assert lib.elx_grad_check(ctypes.c_void_p(g16.data_ptr() + 2), 0, 10, P(flag), None, None, None, 0,
+                              None) == _abi.ERR_ALIGN
+    out = torch.zeros(1, device=cuda)
+    assert lib.elx_grad_check(P(g16), 0, 4096, None, None, P(out), None, 0, None) == _abi.ERR_NULL
+    assert lib.elx_grad_check(P(g16), 0, 4096, None, None, P(out), P(good), 0, None) == _abi.ERR_SIZE
+    assert lib.elx_reduce_epilogue(P(g16), P(g16), 0, 4096, 4096, P(flag), None, None, None, 0, None) == _abi.ERR_ARG
+    assert lib.elx_adam_chunk(P(good), P(good), P(good), P(g16), 0, 5000, 4096, K.hyper(), ctl.ptr,
+                              None) == _abi.ERR_SIZE
+    assert lib.elx_adam_chunk(P(good), None, P(good), P(g16), 0, 4096, 4096, K.hyper(), ctl.ptr, None) == _abi.ERR_NULL
+    assert lib.elx_adam_multi(P(good), 0, 1, 1, 0, P(good), P(good), 65, ctl.ptr, None) == _abi.ERR_CAPACITY
+    assert lib.elx_set_tuning(b'adam_threads', 300) == _abi.ERR_ARG
+    assert lib.elx_set_tuning(b'no_such_knob', 1) == _abi.ERR_ARG
+    assert lib.elx_strerror(_abi.ERR_ALIGN).decode().startswith('a pointer')
+    with pytest.raises(RuntimeError):
+        K.grad_check(torch.zeros(8, dtype=torch.float16), flag=flag.cpu())    # CPU tensor: no CPU path
+    torch.cuda.synchronize()
