@@ -47,8 +47,9 @@ def load_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while timing runs."""
-    QUERY = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,'
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 20 ms from before the warm-up;
+    only samples whose timestamp falls inside the timed region are summarised."""
+    QUERY = ('timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,'
              'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
              'clocks_event_reasons.sw_power_cap')
 
@@ -56,46 +57,67 @@ class ClockSampler:
         self.index = index
         self.proc = None
         self.path = None
+        self.t0 = self.t1 = None
 
     def start(self):
         try:
             fd, self.path = tempfile.mkstemp(suffix='.csv')
             os.close(fd)
             self.proc = subprocess.Popen(['nvidia-smi', '-i', str(self.index), f'--query-gpu={self.QUERY}',
-                                          '--format=csv,noheader,nounits', '-lms', '200'],
+                                          '--format=csv,noheader,nounits', '-lms', '20'],
                                          stdout=open(self.path, 'w'), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
+
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
+
+    @staticmethod
+    def _stamp(text):
+        import datetime
+        try:
+            return datetime.datetime.strptime(text, '%Y/%m/%d %H:%M:%S.%f').timestamp()
+        except ValueError:
+            return None
 
     def stop(self):
         out = {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': [], 'samples': 0}
         if self.proc is None:
             return out
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
         names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
-        sm, reasons, mx, power = [], set(), None, []
+        rows = []
         with open(self.path) as f:
             for line in f:
                 parts = [p.strip() for p in line.split(',')]
-                if len(parts) < 7:
+                if len(parts) < 8:
                     continue
                 try:
-                    sm.append(float(parts[0]))
-                    mx = float(parts[1])
-                    power.append(float(parts[2]))
+                    rows.append((self._stamp(parts[0]), float(parts[1]), float(parts[2]), float(parts[3]), parts[4:8]))
                 except ValueError:
                     continue
-                for name, val in zip(names, parts[3:7]):
+        os.unlink(self.path)
+        inside = [r for r in rows if r[0] is not None and self.t0 is not None and self.t0 <= r[0] <= self.t1]
+        scope = 'timed region'
+        if len(inside) < 3:
+            inside, scope = rows, 'whole run (timed region shorter than the sampling period)'
+        if inside:
+            reasons = set()
+            for r in inside:
+                for name, val in zip(names, r[4]):
                     if val.lower().startswith('active'):
                         reasons.add(name)
-        os.unlink(self.path)
-        if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm),
-                       power_w_max=max(power))
+            out.update(sm_mhz=statistics.median(r[1] for r in inside), sm_max_mhz=inside[0][2],
+                       reasons=sorted(reasons), samples=len(inside), power_w_max=max(r[3] for r in inside),
+                       scope=scope)
         return out
 
 
@@ -229,11 +251,14 @@ def run_ours(args):
             ms = t.item()
         return ms
 
-    for _ in range(args.warmup):
-        one_step()
     sampler = ClockSampler(local_rank)
     sampler.start()
+    for _ in range(args.warmup):
+        one_step()
+    torch.cuda.synchronize()
+    sampler.mark_begin()
     total_ms = timed(lambda: one_step(record=True), args.steps)
+    sampler.mark_end()
     clocks = sampler.stop()
     ms_per_step = total_ms / args.steps
     ctl = engine.read_control()
@@ -474,8 +499,8 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
-    ap.add_argument('--steps', type=int, default=20)
-    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--steps', type=int, default=50)
+    ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--seed', type=int, default=0)
     ap.add_argument('--no-cpu-baseline', action='store_true')

@@ -229,5 +229,3 @@ class ChunkStepEngine:
         if c.status:
             raise RuntimeError(f'elixir_b200 kernels reported status {c.status:#x} '
                                f'(1: non-finite gradient met on an applied step, 2: descriptor table mismatch)')
-EOF
-echo ok
