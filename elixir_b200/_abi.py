@@ -113,6 +113,8 @@ PROTOTYPES = {
     'elx_ctl_init': (_i, [_p, _f, _p]),
     'elx_step_begin': (_i, [_p, ElxScalerCfg, _p, _p]),
     'elx_grad_check': (_i, [_p, _i, _i64, _p, _p, _p, _p, _i64, _p]),
+    'elx_grad_check_static': (_i, [_p, _i, _i64, _p, _p, _p, _p]),
+    'elx_grad_check_static_max_elems': (_i64, []),
     'elx_reduce_epilogue': (_i, [_p, _p, _i, _i64, _i64, _p, _p, _p, _p, _i64, _p]),
     'elx_grad_check_multi': (_i, [_p, _i, _i, _i64, _i, _p, _p, _p, _p, _p, _i64, _p]),
     'elx_adam_multi': (_i, [_p, _i, _i, _i64, _i, _p, _p, _i, _p, _p]),

@@ -1000,6 +1000,42 @@ int probe_single(const void* src, void* dst, int dtype, int64_t n_shard, int64_t
     return rc;
 }
 
+// ------------------------------------------------------------------------------------------------
+// built-in scratch for callers that cannot allocate
+// ------------------------------------------------------------------------------------------------
+
+// One partial sum per tile, so the largest shard elx_grad_check_static accepts has this many tiles
+// (16384 tiles x 4096 elements = 67 108 864 elements).  64 KiB on every GPU that loads the library.
+constexpr int64_t kStaticScratchTiles = 16384;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchTiles];
+
+// Device address of g_static_scratch per device ordinal.  In host code the array's name is only a
+// handle for the runtime, not something a kernel may dereference; the address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+float* g_static_scratch_addr[64];
+
+int static_scratch(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        if (e != cudaSuccess) record_cuda(e);
+        (void)cudaGetLastError();
+        return ELX_ERR_NODEVICE;
+    }
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void* addr = nullptr;
+        e = cudaGetSymbolAddress(&addr, g_static_scratch);
+        if (e != cudaSuccess || addr == nullptr) {
+            record_cuda(e);
+            (void)cudaGetLastError();
+            return e == cudaSuccess ? ELX_ERR_NODEVICE : ELX_ERR_LAUNCH;
+        }
+        g_static_scratch_addr[dev] = static_cast<float*>(addr);
+    }
+    *out = g_static_scratch_addr[dev];
+    return ELX_OK;
+}
+
 }  // namespace
 
 // ------------------------------------------------------------------------------------------------
@@ -1085,6 +1121,20 @@ int elx_step_begin(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq, void* st
 int elx_grad_check(const void* g, int dtype, int64_t n_valid, uint32_t* flag, ElxCtl* ctl, float* l2sq,
                    float* scratch, int64_t scratch_elems, void* stream) {
     return probe_single(g, nullptr, dtype, n_valid, n_valid, flag, ctl, l2sq, scratch, scratch_elems, stream, false);
+}
+
+int64_t elx_grad_check_static_max_elems(void) { return kStaticScratchTiles * kTile; }
+
+int elx_grad_check_static(const void* g, int dtype, int64_t n_valid, uint32_t* flag, ElxCtl* ctl, float* l2sq,
+                          void* stream) {
+    if (n_valid > kStaticScratchTiles * kTile) return ELX_ERR_CAPACITY;
+    float* scratch = nullptr;
+    if (l2sq) {
+        const int rc = static_scratch(&scratch);
+        if (rc != ELX_OK) return rc;
+    }
+    return probe_single(g, nullptr, dtype, n_valid, n_valid, flag, ctl, l2sq, scratch, kStaticScratchTiles, stream,
+                        false);
 }
 
 int elx_reduce_epilogue(const void* src, void* dst, int dtype, int64_t n_shard, int64_t n_valid, uint32_t* flag,

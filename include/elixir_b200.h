@@ -189,6 +189,29 @@ int elx_grad_check(const void* g, int dtype, int64_t n_valid, uint32_t* flag, El
                    float* l2sq, float* scratch, int64_t scratch_elems, void* stream);
 
 /*
+ * elx_grad_check without a scratch argument, for callers that have no way to hand the library device
+ * memory of their own: a host runtime that binds only this C ABI and owns no allocator, or code that
+ * runs where cudaMalloc is off limits (inside a library callback, on a thread that must not block
+ * on the allocator's lock, in a process whose memory pool is already carved up).  It has no
+ * counterpart in the reference, whose norm goes through torch temporaries.
+ *
+ * The per-tile partial sums go to a 64 KiB array that is part of the library image on every GPU that
+ * loads it, so n_valid is limited to elx_grad_check_static_max_elems() (67 108 864) elements; a larger
+ * request returns ELX_ERR_CAPACITY and launches nothing.  The call allocates and frees nothing.
+ * The first call on each device (with l2sq != NULL) looks up the array's device address once and
+ * caches it; make that first call outside any stream capture, with the device current.
+ * All calls on a device share the array and every call overwrites the slots it uses (nothing has to
+ * start at zero), so two calls whose kernels can overlap on the GPU (different streams without an
+ * ordering between them) race on it: keep calls on one device ordered.
+ * Results are bit-identical to elx_grad_check given the same inputs.
+ */
+int elx_grad_check_static(const void* g, int dtype, int64_t n_valid, uint32_t* flag, ElxCtl* ctl,
+                          float* l2sq, void* stream);
+
+/* Largest n_valid elx_grad_check_static accepts. */
+int64_t elx_grad_check_static_max_elems(void);
+
+/*
  * The same probe fused with the copy that ends Chunk.reduce (chunk.py:313, 484-489): copies
  * n_shard elements src -> dst (the reduced slice of the replicated block into the persistent
  * shard) and probes the first n_valid of them in the same pass.  src, dst: device, 32-byte
