@@ -1,9 +1,10 @@
 from .chunk import Chunk, ChunkFullError, TensorInfo
+from .fetcher import ChunkFetcher
 from .group import ChunkGroup
 from .memory_pool import BlockRequire, MemoryPool, PrivateBlock, PublicBlock, TensorBlock
 from .states import TensorState, ts_update_sanity_check
 
 __all__ = [
-    'BlockRequire', 'Chunk', 'ChunkFullError', 'ChunkGroup', 'MemoryPool', 'PrivateBlock', 'PublicBlock',
+    'BlockRequire', 'Chunk', 'ChunkFetcher', 'ChunkFullError', 'ChunkGroup', 'MemoryPool', 'PrivateBlock', 'PublicBlock',
     'TensorBlock', 'TensorInfo', 'TensorState', 'ts_update_sanity_check'
 ]

@@ -1,0 +1,212 @@
+"""ElixirOptimizer: the mixed-precision optimizer step over a module's chunks.
+
+Same constructor, methods and attributes as ``elixir/wrapper/optimizer.py`` (``ElixirOptimizer``,
+``:27-265``).  What changed is where the step runs: the per-rank shards are registered once with a
+``ChunkStepEngine`` and ``step()`` issues — without reading anything back from the device —
+
+    1. (W > 1) a 4-byte MAX all-reduce of the overflow word, so every rank takes the same decision
+       (the reference decides per rank, ``:137-142``);
+    2. ``elx_step_begin``: skip decision, combined divisor (loss scale as it was during backward, times
+       the clip factor), loss-scaler update, step count (``:192-209``, ``:166-183``);
+    3. ``elx_adam_multi``: unscale + Adam/AdamW + low-precision copy-back, or the copy-back alone when
+       the step is skipped (``:216-219``, ``_update_fp16_params`` ``:126-135``).
+"""
+from enum import Enum
+from typing import Dict, List, Set, Tuple
+
+import torch
+import torch.distributed as dist
+from torch.nn import Parameter
+
+from .. import kernels
+from ..chunk import Chunk
+from ..engine import ChunkStepEngine
+from ..optim import FusedAdam, HybridAdam
+from ..scaler import BaseGradScaler, ConstantGradScaler, DynamicGradScaler
+from .module import ElixirModule
+
+_AVAIL_OPTIM_LIST = {FusedAdam, HybridAdam}
+
+
+class OptimState(Enum):
+    SCALED = 0
+    UNSCALED = 1
+
+
+class ElixirOptimizer:
+
+    def __init__(self,
+                 module: ElixirModule,
+                 optimizer: torch.optim.Optimizer,
+                 initial_scale: float = 32768,
+                 min_scale: float = 1,
+                 growth_factor: float = 2,
+                 backoff_factor: float = 0.5,
+                 growth_interval: int = 1000,
+                 hysteresis: int = 2,
+                 max_scale: float = 2**24,
+                 max_norm: float = 0.0,
+                 norm_type: float = 2.0,
+                 init_step: bool = False,
+                 sync_overflow: bool = True):
+        assert isinstance(module, ElixirModule)
+        if type(optimizer) not in _AVAIL_OPTIM_LIST:
+            raise TypeError(f'You should use an optimizer in the available list:\n{_AVAIL_OPTIM_LIST}')
+        self.optim = optimizer
+        self.scaled_optimizer = True
+        self.module = module
+        self.param_chunk_group = module.param_chunk_group
+        self.optim_chunk_group = module.optim_chunk_group
+        self.optim_state = OptimState.UNSCALED
+        self.param_to_range: Dict[Parameter, Tuple[int, int]] = dict()
+        self.param_to_optim_chunk: Dict[Parameter, Chunk] = dict()
+        self.param_chunk_set: Set[Chunk] = self.param_chunk_group.fused_chunks.union(
+            self.param_chunk_group.float_chunks)
+
+        self.clipping_flag = max_norm > 0.0
+        self.max_norm = max_norm
+        if self.clipping_flag:
+            assert norm_type == 2.0, 'ElixirOptimizer only supports L2 norm now'
+
+        if module.use_amp:
+            self.grad_scaler: BaseGradScaler = DynamicGradScaler(initial_scale=initial_scale, min_scale=min_scale,
+                                                                 growth_factor=growth_factor,
+                                                                 backoff_factor=backoff_factor,
+                                                                 growth_interval=growth_interval,
+                                                                 hysteresis=hysteresis, max_scale=max_scale)
+        else:
+            self.grad_scaler = ConstantGradScaler(1.0, verbose=False)
+
+        segments = self._init_optimizer()
+        self._init_engine(segments, sync_overflow)
+        if init_step:
+            self._zero_step()
+
+    # ------------------------------------------------------------------ construction
+
+    def _init_optimizer(self) -> Dict[Chunk, List[Tuple[int, int, int]]]:
+        """Replace every real parameter of the wrapped optimizer by an empty stand-in and remember its range
+        inside this rank's shard (``__init__optimizer``, ``:238-265``)."""
+        segments: Dict[Chunk, List[Tuple[int, int, int]]] = {c: [] for c in self.param_chunk_set}
+        for group_index, group in enumerate(self.optim.param_groups):
+            fake_params = []
+            for param in group['params']:
+                if not param.requires_grad:
+                    continue
+                param_chunk = self.module.fetcher.get_one_chunk(param)
+                info = param_chunk.tensors_info[param]
+                begin = max(0, info.offset - param_chunk.shard_begin)
+                end = min(param_chunk.shard_size, info.end - param_chunk.shard_begin)
+                if begin >= end:
+                    continue
+                fake = Parameter(torch.empty([0], device=param_chunk.shard.device))
+                self.param_to_optim_chunk[fake] = param_chunk.paired_chunk
+                self.param_to_range[fake] = (begin, end)
+                segments[param_chunk].append((begin, end, group_index))
+                fake_params.append(fake)
+            group['params'] = fake_params
+        for segs in segments.values():
+            segs.sort()
+        return segments
+
+    def _init_engine(self, segments, sync_overflow: bool):
+        chunks = sorted(self.param_chunk_set, key=lambda c: c.chunk_id)
+        self._chunks = chunks
+        device = chunks[0].shard.device if chunks else torch.device('cuda', torch.cuda.current_device())
+        dtype = self.module.dtype
+        group = self.module.process_group
+        self.engine = ChunkStepEngine(device, dtype, self.grad_scaler, process_group=group,
+                                      sync_overflow=sync_overflow, max_norm=self.max_norm)
+        for chunk in chunks:
+            self.engine.add_shard(chunk.paired_chunk.shard, chunk.shard, chunk.valid_end, segments[chunk])
+        self.engine.finalize()
+        for index, chunk in enumerate(chunks):
+            chunk.bind_control(self.engine.ctl, self.engine.chunk_flags[index:index + 1])
+        self.optim.bind_engine(self.engine)
+        self.engine.set_hyper(self.optim.hyper_table())
+        # per-parameter views of the flat moments, under the keys the reference's optimizers use
+        index_of = {chunk.paired_chunk: i for i, chunk in enumerate(chunks)}
+        for fake, (begin, end) in self.param_to_range.items():
+            _, exp_avg, exp_avg_sq, _, _ = self.engine.shards[index_of[self.param_to_optim_chunk[fake]]]
+            self.optim.state[fake] = dict(step=0, exp_avg=exp_avg[begin:end], exp_avg_sq=exp_avg_sq[begin:end])
+
+    def _zero_step(self):
+        """One step with zero gradients before training (``__zero_step``, ``:94-113``).  The reference uses
+        it to allocate optimizer state early; its side effects — the step count becomes 1 and decoupled
+        weight decay is applied once — are reproduced."""
+        for _, _, _, lowp, _ in self.engine.shards:
+            lowp.zero_()
+        ctl = self.engine.read_control()
+        ctl.skip, ctl.div_scale, ctl.inv_div = 0, -1.0, 0.0
+        ctl.step += 1
+        self.engine.ctl.write(ctl)
+        self.optim.step()
+        self.zero_grad()
+
+    # ------------------------------------------------------------------ optimizer protocol
+
+    @property
+    def param_groups(self):
+        return self.optim.param_groups
+
+    @property
+    def state(self):
+        return self.optim.state
+
+    @property
+    def defaults(self):
+        return self.optim.defaults
+
+    def zero_grad(self, *args, **kwargs):
+        return self.optim.zero_grad(set_to_none=True)
+
+    @property
+    def loss_scale(self) -> float:
+        """Current loss scale as a Python float.  Synchronises (the reference does too, ``:185-187``);
+        ``backward`` does not use it."""
+        return float(self.grad_scaler.scale.item())
+
+    def _check_overflow(self) -> bool:
+        """Whether any chunk of this rank flagged inf/nan.  Synchronises; the step itself does not call it."""
+        return bool(self.engine.chunk_flags.any().item())
+
+    def step(self, *args, **kwargs):
+        self.optim_state = OptimState.UNSCALED
+        self.engine.begin_step()
+        ret = self.optim.step(*args, **kwargs)
+        self.engine.end_step()
+        for chunk in self._chunks:
+            chunk._l2_valid = False
+        self.zero_grad()
+        return ret
+
+    def clip_grad_norm(self, model: torch.nn.Module, max_norm: float, norm_type: float = 2.0):
+        raise NotImplementedError
+
+    def backward(self, loss: torch.Tensor):
+        # fp32 product with the device-resident scale: no host read, and 2^16 does not overflow a half loss
+        loss = loss.float() * self.grad_scaler.scale
+        self.optim_state = OptimState.SCALED
+        self.module.backward(loss)
+
+    def backward_by_grad(self, tensor: torch.Tensor, grad: torch.Tensor):
+        self.optim_state = OptimState.SCALED
+        self.module.backward_by_grad(tensor, grad)
+
+    # ------------------------------------------------------------------ checkpoint
+
+    def state_dict(self):
+        """This rank's flat optimizer state: one (exp_avg, exp_avg_sq) pair per chunk shard plus the control
+        block fields.  The reference saves none of this (its scaler state is lost on restart)."""
+        return dict(scaler=self.grad_scaler.state_dict(),
+                    shards=[dict(exp_avg=s[1].detach().cpu(), exp_avg_sq=s[2].detach().cpu())
+                            for s in self.engine.shards],
+                    param_groups=[{k: v for k, v in g.items() if k != 'params'} for g in self.optim.param_groups])
+
+    def load_state_dict(self, state):
+        self.grad_scaler.load_state_dict(state['scaler'])
+        for shard, saved in zip(self.engine.shards, state['shards']):
+            shard[1].copy_(saved['exp_avg'])
+            shard[2].copy_(saved['exp_avg_sq'])
+        for group, saved in zip(self.optim.param_groups, state['param_groups']):
+            group.update(saved)

@@ -1,0 +1,169 @@
+/*
+ * TEST INFRASTRUCTURE — the elx_* C ABI implemented on HOST memory with the CPU oracle.
+ *
+ * The test-suite loads this in place of libelixir_b200.so (tests/conftest.py) to run the host-side
+ * logic of the package — chunk geometry, collectives over gloo, the ElixirOptimizer state machine —
+ * on machines without a GPU.  The product never loads it.  Pointers are host pointers, the stream
+ * argument is ignored, every call completes before it returns.  Arithmetic: elx_oracle.c (double
+ * precision evaluation of the update, rounded to fp32).
+ */
+#include <stdint.h>
+#include <string.h>
+
+#include "elixir_b200.h"
+
+int orc_probe(const void* g, int dtype, int64_t n_valid);
+double orc_l2sq(const void* g, int dtype, int64_t n_valid);
+void orc_cast(const float* src, void* dst, int dtype, int64_t n);
+void orc_ctl_init(ElxCtl* ctl, float initial_scale);
+void orc_step_begin(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq);
+void orc_adam_f64(float* p, float* m, float* v, const void* g, int dtype, int64_t begin, int64_t end, ElxHyper h,
+                  int step, float div_scale);
+
+static int dtype_ok(int dt) { return dt == ELX_F16 || dt == ELX_BF16 || dt == ELX_F32; }
+static int dtype_bytes(int dt) { return dt == ELX_F32 ? 4 : 2; }
+
+int elx_version(void) { return ELX_ABI_VERSION; }
+const char* elx_strerror(int status) { return status == ELX_OK ? "ok" : "host shim: argument rejected"; }
+const char* elx_last_cuda_error(void) { return ""; }
+int elx_set_tuning(const char* name, int value) {
+    (void)value;
+    return name ? ELX_OK : ELX_ERR_NULL;
+}
+int64_t elx_probe_scratch_elems(int64_t n_tiles) { return n_tiles < 0 ? 0 : n_tiles; }
+int64_t elx_grad_check_static_max_elems(void) { return (int64_t)16384 * ELX_TILE; }
+
+int elx_ctl_init(ElxCtl* ctl, float initial_scale, void* stream) {
+    (void)stream;
+    if (!ctl) return ELX_ERR_NULL;
+    orc_ctl_init(ctl, initial_scale);
+    return ELX_OK;
+}
+
+int elx_step_begin(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq, void* stream) {
+    (void)stream;
+    if (!ctl) return ELX_ERR_NULL;
+    if (cfg.max_norm > 0.0f && !norm_sq) return ELX_ERR_NULL;
+    orc_step_begin(ctl, cfg, norm_sq);
+    return ELX_OK;
+}
+
+static int probe_common(const void* g, int dtype, int64_t n_valid, uint32_t* flag, ElxCtl* ctl, float* l2sq) {
+    if (!g) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (n_valid < 0) return ELX_ERR_SIZE;
+    if (orc_probe(g, dtype, n_valid)) {
+        if (flag) *flag = 1;
+        if (ctl) ctl->found_inf = 1;
+    }
+    if (l2sq) *l2sq = (float)orc_l2sq(g, dtype, n_valid);
+    return ELX_OK;
+}
+
+int elx_grad_check(const void* g, int dtype, int64_t n_valid, uint32_t* flag, ElxCtl* ctl, float* l2sq, float* scratch,
+                   int64_t scratch_elems, void* stream) {
+    (void)scratch;
+    (void)scratch_elems;
+    (void)stream;
+    return probe_common(g, dtype, n_valid, flag, ctl, l2sq);
+}
+
+int elx_grad_check_static(const void* g, int dtype, int64_t n_valid, uint32_t* flag, ElxCtl* ctl, float* l2sq,
+                          void* stream) {
+    (void)stream;
+    if (n_valid > elx_grad_check_static_max_elems()) return ELX_ERR_CAPACITY;
+    return probe_common(g, dtype, n_valid, flag, ctl, l2sq);
+}
+
+int elx_reduce_epilogue(const void* src, void* dst, int dtype, int64_t n_shard, int64_t n_valid, uint32_t* flag,
+                        ElxCtl* ctl, float* l2sq, float* scratch, int64_t scratch_elems, void* stream) {
+    (void)scratch;
+    (void)scratch_elems;
+    (void)stream;
+    if (!src || !dst) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (n_shard < 0 || n_valid < 0 || n_valid > n_shard) return ELX_ERR_SIZE;
+    memmove(dst, src, (size_t)n_shard * dtype_bytes(dtype));
+    return probe_common(src, dtype, n_valid, flag, ctl, l2sq);
+}
+
+int elx_grad_check_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                         uint32_t* chunk_flags, ElxCtl* ctl, float* chunk_l2sq, float* total_l2sq, float* scratch,
+                         int64_t scratch_elems, void* stream) {
+    (void)n_tiles;
+    (void)scratch;
+    (void)scratch_elems;
+    (void)stream;
+    if (!descs) return ELX_ERR_NULL;
+    double total = 0.0;
+    for (int c = first; c < first + count; ++c) {
+        if (descs[c].dtype != dtype) {
+            if (ctl) ctl->status |= ELX_STAT_BAD_DESC;
+            continue;
+        }
+        float l2 = 0.0f;
+        int rc = probe_common(descs[c].grad_param, dtype, descs[c].n_valid, chunk_flags ? &chunk_flags[c] : 0, ctl,
+                              (chunk_l2sq || total_l2sq) ? &l2 : 0);
+        if (rc != ELX_OK) return rc;
+        if (chunk_l2sq) chunk_l2sq[c] = l2;
+        total += l2;
+    }
+    if (total_l2sq) *total_l2sq = (float)total;
+    return ELX_OK;
+}
+
+static void step_one(const ElxChunkDesc* d, const ElxSeg* segs, const ElxHyper* hyper, int n_groups,
+                     const ElxCtl* ctl) {
+    if (!ctl->skip) {
+        for (int s = d->seg_first; s < d->seg_first + d->seg_count; ++s) {
+            if (segs[s].group < 0 || segs[s].group >= n_groups) continue;
+            orc_adam_f64(d->master, d->exp_avg, d->exp_avg_sq, d->grad_param, d->dtype, segs[s].begin, segs[s].end,
+                         hyper[segs[s].group], ctl->step, ctl->div_scale);
+        }
+    }
+    orc_cast(d->master, d->grad_param, d->dtype, d->n_shard);
+}
+
+int elx_adam_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype, const ElxSeg* segs,
+                   const ElxHyper* hyper, int n_groups, ElxCtl* ctl, void* stream) {
+    (void)n_tiles;
+    (void)stream;
+    if (!descs || !ctl) return ELX_ERR_NULL;
+    if (n_groups > 64) return ELX_ERR_CAPACITY;
+    for (int c = first; c < first + count; ++c) {
+        if (descs[c].dtype != dtype) {
+            ctl->status |= ELX_STAT_BAD_DESC;
+            continue;
+        }
+        step_one(&descs[c], segs, hyper, n_groups, ctl);
+    }
+    return ELX_OK;
+}
+
+int elx_adam_chunk(float* master, float* exp_avg, float* exp_avg_sq, void* grad_param, int dtype, int64_t n_valid,
+                   int64_t n_shard, ElxHyper hyper, ElxCtl* ctl, void* stream) {
+    (void)stream;
+    if (!master || !exp_avg || !exp_avg_sq || !grad_param || !ctl) return ELX_ERR_NULL;
+    if (n_valid < 0 || n_valid > n_shard) return ELX_ERR_SIZE;
+    ElxChunkDesc d;
+    memset(&d, 0, sizeof(d));
+    d.master = master;
+    d.exp_avg = exp_avg;
+    d.exp_avg_sq = exp_avg_sq;
+    d.grad_param = grad_param;
+    d.n_shard = n_shard;
+    d.n_valid = n_valid;
+    d.seg_count = n_valid > 0 ? 1 : 0;
+    d.dtype = dtype;
+    ElxSeg seg = {0, n_valid, 0, 0};
+    step_one(&d, &seg, &hyper, 1, ctl);
+    return ELX_OK;
+}
+
+int elx_cast_copyback(const float* master, void* dst, int dtype, int64_t n, void* stream) {
+    (void)stream;
+    if (!master || !dst) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    orc_cast(master, dst, dtype, n);
+    return ELX_OK;
+}

@@ -32,6 +32,15 @@ def build(force=False):
     return so
 
 
+def build_host_shim(force=False):
+    """oracle/libelx_hostshim.so: the elx_* ABI on host memory (CPU-only tests of the host logic)."""
+    so = os.path.join(_HERE, 'libelx_hostshim.so')
+    srcs = [os.path.join(_HERE, 'elx_host_shim.c'), os.path.join(_HERE, 'elx_oracle.c')]
+    if force or not os.path.exists(so) or os.path.getmtime(so) < max(os.path.getmtime(s) for s in srcs):
+        subprocess.run(['make', '-C', _HERE, '-B', 'libelx_hostshim.so'], check=True, capture_output=True)
+    return so
+
+
 def lib():
     global _LIB
     if _LIB is None:

@@ -1,0 +1,223 @@
+"""Generate the golden fixtures of this directory by running hpcaitech/Elixir's OWN Python code on CPU.
+
+    python tests/golden/make_golden.py [/path/to/Elixir]        (default /root/reference)
+
+Needs the reference checkout; the fixtures it writes (`chunk_w*.pt`, `optim_w*.pt`) are committed, so
+the test-suite does not.  What runs is the reference's `elixir.chunk.Chunk` / `ChunkGroup` /
+`MemoryPool` and `elixir.wrapper.ElixirModule` / `ElixirOptimizer`, unmodified, with:
+  * gloo process groups of 1, 2 and 4 CPU ranks;
+  * `gpu_device()` pointed at the CPU and `torch.cuda.Stream` replaced by a dummy (there is no GPU);
+  * the `colossalai` stub beside this file (ColossalAI is not installable offline): its Adam delegates
+    to torch.optim.Adam/AdamW, its scaler restates DynamicGradScaler.
+Gradients are injected straight into the chunks (the reference's forward hooks do not run under
+current PyTorch), through the same calls its autograd hook makes (`_gradient_handler`).
+
+Fixture contents
+  chunk_w{W}.pt  per rank: shard after close, valid_end, gathered payload, reduced shard and overflow
+                 flag for a clean and for an inf-carrying gradient set (elixir/chunk/core/chunk.py)
+  optim_w{W}.pt  per rank and step: overflow decision, loss scale after the step, fp32 master shards
+                 (elixir/wrapper/optimizer.py:192-220)
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+import torch.nn as nn
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get('ELIXIR_REFERENCE', '/root/reference')    # overridden by the command-line argument in main()
+
+CHUNK_SHAPES = [(2, 64), (2, 2, 128), (128,), (4, 32)]    # 896 of 1024 elements used, as test/chunk/test_chunk.py
+CHUNK_SIZE = 1024
+
+
+def _patch_reference_for_cpu():
+    sys.path.insert(0, os.path.join(HERE, 'colossalai_stub'))
+    sys.path.insert(0, REF)
+    cpu = torch.device('cpu')
+    import elixir.cuda
+    elixir.cuda.gpu_device = lambda: cpu
+
+    class _DummyStream:
+
+        def wait_stream(self, other):
+            pass
+
+    torch.cuda.Stream = _DummyStream
+    torch.cuda.current_stream = lambda *a, **k: _DummyStream()
+    import elixir.chunk.core.chunk as ref_chunk
+    ref_chunk.gpu_device = lambda: cpu
+    import elixir.hook.storage as ref_storage
+    ref_storage.gpu_device = lambda: cpu
+    orig_init = ref_storage.BufferStore.__init__
+
+    def cpu_init(self, buffer_size, buffer_dtype, device_str='cpu'):
+        orig_init(self, buffer_size, buffer_dtype, 'cpu')
+
+    ref_storage.BufferStore.__init__ = cpu_init
+    import elixir.wrapper.module as ref_module
+    import elixir.wrapper.optimizer as ref_optimizer
+    ref_module.gpu_device = lambda: cpu
+    ref_optimizer.gpu_device = lambda: cpu
+    orig_pool_init = ref_module.MemoryPool.__init__
+
+    def cpu_pool_init(self, device_type):
+        orig_pool_init(self, 'cpu')
+
+    ref_module.MemoryPool.__init__ = cpu_pool_init
+
+
+def chunk_inputs(world):
+    gen = torch.Generator().manual_seed(2261)
+    tensors = [torch.randn(shape, generator=gen).half() for shape in CHUNK_SHAPES]
+    grads = [[(torch.randn(shape, generator=gen) * 8).half() for shape in CHUNK_SHAPES] for _ in range(world)]
+    return tensors, grads
+
+
+def run_chunk(rank, world):
+    from elixir.chunk import Chunk, MemoryPool, TensorState
+    cpu = torch.device('cpu')
+    tensors, grads = chunk_inputs(world)
+    out = {}
+    for case in ('clean', 'inf'):
+        pool = MemoryPool('cpu')
+        pool.allocate(public_dtype=torch.float16, public_block_size=CHUNK_SIZE, public_block_number=1)
+        chunk = Chunk(pool, CHUNK_SIZE, torch.float16, dist.GroupMember.WORLD, temp_device=cpu, shard_device=cpu)
+        held = [t.clone() for t in tensors]
+        for t in held:
+            chunk.append_tensor(t)
+        chunk.close_chunk()
+        rec = dict(shard_after_close=chunk.shard.clone(), valid_end=chunk.valid_end, shard_begin=chunk.shard_begin,
+                   shard_size=chunk.shard_size)
+        block = pool.get_public_block()
+        chunk.access_chunk(block)
+        rec['payload_after_access'] = block.payload.clone()
+        for t, g in zip(held, grads[rank]):
+            g = g.clone()
+            if case == 'inf' and rank == world - 1 and t is held[0]:
+                g.view(-1)[3] = float('inf')
+            for state in (TensorState.COMPUTE, TensorState.HOLD_AFTER_BWD, TensorState.READY_FOR_REDUCE):
+                chunk.tensor_trans_state(t, state)
+            chunk.copy_tensor_to_chunk_slice(t, g)
+        assert chunk.reduce_check
+        chunk.reduce_chunk()
+        rec['shard_after_reduce'] = chunk.shard.clone()
+        rec['overflow'] = bool(chunk.overflow)
+        out[case] = rec
+    return out
+
+
+class TinyNet(nn.Module):
+    """Two linear layers and a LayerNorm: enough tensors to straddle shard boundaries."""
+
+    def __init__(self):
+        super().__init__()
+        self.fc1 = nn.Linear(24, 40)
+        self.norm = nn.LayerNorm(40)
+        self.fc2 = nn.Linear(40, 10)
+
+
+def optim_inputs(world, steps):
+    torch.manual_seed(7)
+    model = TinyNet()
+    gen = torch.Generator().manual_seed(99)
+    grads = []
+    for s in range(steps):
+        per_rank = []
+        for r in range(world):
+            per_rank.append({n: torch.randn(p.shape, generator=gen) * 1e-3 for n, p in model.named_parameters()})
+        grads.append(per_rank)
+    return model, grads
+
+
+OPTIM_STEPS = 6
+OPTIM_CFG = dict(initial_scale=64.0, min_scale=1, growth_factor=2, backoff_factor=0.5, growth_interval=2, hysteresis=1,
+                 max_scale=2**24)
+OPTIM_HYPER = dict(lr=0.0009765625, betas=(0.875, 0.99609375), eps=1e-8, weight_decay=0.0078125)
+OPTIM_CHUNK = 1024    # two public chunks for the 1490 parameters (the second one 48% used); divisible by 1, 2, 4
+INF_STEP = 2
+
+
+def run_optim(rank, world):
+    from colossalai.nn.optimizer import HybridAdam
+    from elixir.chunk import ChunkGroup, MemoryPool, TensorState
+    from elixir.search.result import ChunkPlan, SearchResult
+    from elixir.wrapper import ElixirModule, ElixirOptimizer
+    from elixir.wrapper.optimizer import OptimState
+    cpu = torch.device('cpu')
+    model, grads = optim_inputs(world, OPTIM_STEPS)
+    names = [n for n, _ in model.named_parameters()]
+    plans, cur, room = [], [], 0
+    sizes = {n: p.numel() for n, p in model.named_parameters()}
+    for n in names:
+        if sizes[n] > room:
+            cur = []
+            plans.append(ChunkPlan(name_list=cur, chunk_size=OPTIM_CHUNK, chunk_dtype=torch.float16,
+                                   kwargs=dict(shard_device=cpu, temp_device=cpu)))
+            room = OPTIM_CHUNK
+        cur.append(n)
+        room -= sizes[n]
+    pool = MemoryPool('cpu')
+    pool.allocate(public_dtype=torch.float16, public_block_size=OPTIM_CHUNK, public_block_number=len(plans))
+    sr = SearchResult(ChunkGroup(pool), plans)
+    inner = HybridAdam(model.parameters(), adamw_mode=True, **OPTIM_HYPER)
+    emodel = ElixirModule(model, sr, dist.GroupMember.WORLD, dtype=torch.float16)
+    eoptim = ElixirOptimizer(emodel, inner, **OPTIM_CFG)
+    group = emodel.param_chunk_group
+    chunks = sorted(group.float_chunks | group.fused_chunks, key=lambda c: c.chunk_id)
+    out = dict(plans=[list(p.name_list) for p in plans], steps=[],
+               init_master=[c.paired_chunk.shard.clone() for c in chunks],
+               valid_end=[c.valid_end for c in chunks])
+    params = dict(emodel.module.named_parameters())
+    for s in range(OPTIM_STEPS):
+        scale = eoptim.loss_scale
+        for c in chunks:
+            group.access_chunk(c)
+        for n in names:
+            p = params[n]
+            g = (grads[s][rank][n] * scale).half()
+            if s == INF_STEP and rank == world - 1 and n == 'fc2.weight':
+                g.view(-1)[5] = float('inf')
+            group.tensor_trans_state(p, TensorState.COMPUTE)
+            group.tensor_trans_state(p, TensorState.HOLD_AFTER_BWD)
+            emodel._gradient_handler(g, p)
+        flags = [bool(c.overflow) for c in chunks]
+        grad_shards = [c.shard.clone() for c in chunks]
+        eoptim.optim_state = OptimState.SCALED
+        eoptim.step()
+        out['steps'].append(dict(scale_before=scale, scale_after=eoptim.loss_scale, chunk_overflow=flags,
+                                 grad_shards=grad_shards,
+                                 master=[c.paired_chunk.shard.clone() for c in chunks]))
+    return out
+
+
+def worker(rank, world, port, result_dir):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
+                      MASTER_PORT=str(port))
+    _patch_reference_for_cpu()
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    torch.save(run_chunk(rank, world), os.path.join(result_dir, f'chunk_{rank}.pt'))
+    torch.save(run_optim(rank, world), os.path.join(result_dir, f'optim_{rank}.pt'))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def main():
+    import tempfile
+    global REF
+    if len(sys.argv) > 1:
+        REF = sys.argv[1]
+    os.environ['ELIXIR_REFERENCE'] = REF    # spawned workers re-import this module
+    for i, world in enumerate((1, 2, 4)):
+        with tempfile.TemporaryDirectory() as tmp:
+            mp.spawn(worker, args=(world, 29600 + i, tmp), nprocs=world)
+            for kind in ('chunk', 'optim'):
+                per_rank = [torch.load(os.path.join(tmp, f'{kind}_{r}.pt')) for r in range(world)]
+                torch.save(dict(world=world, ranks=per_rank), os.path.join(HERE, f'{kind}_w{world}.pt'))
+        print(f'world {world}: fixtures written')
+
+
+if __name__ == '__main__':
+    main()
