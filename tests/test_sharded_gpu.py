@@ -1,0 +1,98 @@
+"""Sharded step over NCCL on 2+ GPUs of one box (skipped when fewer are visible): pre-multiplied-sum
+reduce-scatter, probe, overflow agreement, fused update and all-gather, against the CPU oracle."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE='0')
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, 'tests'))
+    import torch.distributed as dist
+    from _util import bits_equal, close_1e6
+    from elixir_b200 import kernels as K
+    from elixir_b200.engine import ChunkStepEngine
+    from elixir_b200.scaler import DynamicGradScaler
+    from oracle import oracle as orc
+    torch.cuda.set_device(rank)
+    dev = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    dtype, scale = torch.float16, 256.0
+    chunk_sizes = [world * 4096 * 3, world * (4096 + 8), world * 4096 * 5]
+    used = [chunk_sizes[0], chunk_sizes[1], chunk_sizes[2] // 2 + 7]
+    engine = ChunkStepEngine(dev, dtype, DynamicGradScaler(initial_scale=scale, hysteresis=1, growth_interval=3),
+                             process_group=dist.group.WORLD)
+    host = orc.ChunkSet(dtype)
+    host_ctl = orc.new_ctl(scale)
+    hypers = [K.hyper(weight_decay=0.01)]
+    host_state, full_masters = [], []
+    for c, (C, u) in enumerate(zip(chunk_sizes, used)):
+        S = C // world
+        gen = torch.Generator().manual_seed(c)
+        full = torch.randn(C, generator=gen) * 0.02
+        full[u:] = 0
+        full_masters.append(full)
+        mine = full[rank * S:(rank + 1) * S].clone()
+        nv = max(0, min(S, u - rank * S))
+        lowp = torch.zeros(S, dtype=dtype)
+        host.add_chunk(mine, torch.zeros(S), torch.zeros(S), lowp, nv, [(0, nv, 0)] if nv else [])
+        host_state.append((mine, lowp, nv))
+        engine.add_shard(mine.to(dev), torch.zeros(S, dtype=dtype, device=dev), nv, [(0, nv, 0)] if nv else [])
+    engine.finalize()
+    engine.set_hyper(hypers)
+    gather = [torch.empty(C, dtype=dtype, device=dev) for C in chunk_sizes]
+    for step in range(5):
+        blocks, per_rank = [], []
+        for c, C in enumerate(chunk_sizes):
+            rank_grads = []
+            for r in range(world):
+                gen = torch.Generator().manual_seed(1000 * step + 10 * c + r)
+                g = (torch.randn(C, generator=gen) * 1e-3 * host_ctl.scale).to(dtype)
+                if step == 2 and c == 1 and r == world - 1:
+                    g[5] = float('inf')    # lands in rank 0's shard only
+                rank_grads.append(g)
+            per_rank.append(rank_grads)
+            blocks.append(rank_grads[rank].to(dev))
+        engine.step_sharded(blocks, gather)
+        torch.cuda.synchronize()
+        # oracle: the reference's average (divide in fp16, then sum) of every rank's block, this rank's slice
+        for c, C in enumerate(chunk_sizes):
+            S = C // world
+            avg = orc.reduce_avg([g[rank * S:(rank + 1) * S].contiguous() for g in per_rank[c]])
+            host_state[c][1].copy_(avg)
+        any_inf = step == 2
+        if any_inf:
+            host_ctl.found_inf = 1    # agreement: every rank skips, also those whose shards are clean
+        skipped = host.step(host_ctl, engine.scaler.cfg, hypers, probe=True, f64=True)
+        ctl = engine.read_control()
+        assert bool(ctl.skip) == skipped == any_inf, (step, rank)
+        assert (ctl.scale, ctl.step) == (host_ctl.scale, host_ctl.step)
+        for c, C in enumerate(chunk_sizes):
+            S = C // world
+            ok, ratio = close_1e6(engine.shards[c][0], host_state[c][0].double(), rtol=2e-6)
+            assert ok, (step, rank, c, ratio)
+            # the gathered block holds every rank's refreshed shard
+            mine16 = engine.shards[c][3]
+            assert bits_equal(gather[c][rank * S:(rank + 1) * S], mine16)
+            others = [torch.empty_like(mine16) for _ in range(world)]
+            dist.all_gather(others, mine16)
+            assert bits_equal(gather[c], torch.cat(others))
+    assert engine.read_control().status == 0
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('world', [2, 4])
+def test_sharded_step_nccl(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f'needs {world} GPUs')
+    mp.spawn(_worker, args=(world, 29800 + world), nprocs=world)

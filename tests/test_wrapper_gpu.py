@@ -1,0 +1,166 @@
+"""ElixirModule + ElixirOptimizer on a GPU, driven by a real forward / backward (world size 1)."""
+import copy
+
+import pytest
+import torch
+import torch.nn as nn
+
+from _util import bits_equal, close_1e6
+
+pytestmark = pytest.mark.gpu
+
+
+class TiedNet(nn.Module):
+    """Embedding tied to the output projection (a parameter used twice gets a private chunk)."""
+
+    def __init__(self, vocab=64, hidden=32):
+        super().__init__()
+        self.embed = nn.Embedding(vocab, hidden)
+        self.fc = nn.Linear(hidden, hidden)
+        self.norm = nn.LayerNorm(hidden)
+        self.head = nn.Linear(hidden, vocab, bias=False)
+        self.head.weight = self.embed.weight
+
+    def forward(self, ids):
+        h = self.norm(torch.relu(self.fc(self.embed(ids))))
+        return self.head(h).float().logsumexp(-1).mean()
+
+
+class Mlp(nn.Module):
+
+    def __init__(self):
+        super().__init__()
+        self.net = nn.Sequential(nn.Linear(48, 96), nn.GELU(), nn.Linear(96, 96), nn.GELU(), nn.Linear(96, 8))
+
+    def forward(self, x):
+        return self.net(x).float().pow(2).mean()
+
+
+@pytest.fixture(scope='module')
+def single_group(cuda):
+    import torch.distributed as dist
+    if not dist.is_initialized():
+        dist.init_process_group('gloo', init_method='tcp://127.0.0.1:29791', rank=0, world_size=1)
+    yield dist.GroupMember.WORLD
+
+
+def _wrap(model, group, dtype, **opt_kwargs):
+    from elixir_b200.optim import HybridAdam
+    from elixir_b200.wrapper import ElixirModule, ElixirOptimizer, simple_plan
+    sr = simple_plan(model, 1, split_number=3, unified_dtype=dtype)
+    inner = HybridAdam(model.parameters(), lr=opt_kwargs.pop('lr', 1e-3), weight_decay=opt_kwargs.pop('wd', 0.01))
+    emodel = ElixirModule(model, sr, group, dtype=dtype)
+    return emodel, ElixirOptimizer(emodel, inner, **opt_kwargs)
+
+
+def test_fp32_mode_matches_plain_torch_training(cuda, single_group):
+    """The reference's own acceptance test in spirit (test/wrapper/test_optimizer.py): one optimizer on a
+    plain model, the same optimizer behind ElixirModule/ElixirOptimizer, fp32, a few steps, full state
+    compared with rtol 2e-6 / atol 2e-5."""
+    torch.manual_seed(0)
+    plain = Mlp().to(cuda)
+    wrapped_model = copy.deepcopy(plain)
+    opt = torch.optim.AdamW(plain.parameters(), lr=1e-2, betas=(0.875, 0.99609375), weight_decay=0.0)
+    emodel, eopt = _wrap(wrapped_model, single_group, torch.float, lr=1e-2, wd=0.0)
+    for g in eopt.param_groups:
+        g['betas'] = (0.875, 0.99609375)
+    for step in range(3):
+        x = torch.randn(16, 48, device=cuda)
+        opt.zero_grad()
+        loss_a = plain(x)
+        loss_a.backward()
+        opt.step()
+        eopt.zero_grad()
+        loss_b = emodel(x)
+        eopt.backward(loss_b)
+        eopt.step()
+        torch.testing.assert_close(loss_a, loss_b)
+    got = emodel.state_dict()
+    for name, ref in plain.state_dict().items():
+        torch.testing.assert_close(got[name].to(cuda), ref, rtol=2e-6, atol=2e-5)
+    assert eopt.engine.read_control().status == 0
+
+
+@pytest.mark.parametrize('model_cls', [Mlp, TiedNet])
+def test_fp16_step_matches_oracle_on_the_gradients_autograd_produced(cuda, oracle, single_group, model_cls):
+    from elixir_b200 import kernels as K
+    torch.manual_seed(1)
+    model = model_cls().to(cuda)
+    emodel, eopt = _wrap(model, single_group, torch.float16, initial_scale=128.0, hysteresis=1, growth_interval=2)
+    chunks = emodel.param_chunks
+    assert any(c.rcache_fused for c in chunks) == (model_cls is TiedNet)
+    host_ctl = oracle.new_ctl(128.0)
+    hyper = [K.hyper(lr=1e-3, weight_decay=0.01)]
+    for step in range(4):
+        if model_cls is Mlp:
+            batch = torch.randn(8, 48, device=cuda)
+        else:
+            batch = torch.randint(0, 64, (8, 12), device=cuda)
+        eopt.zero_grad()
+        loss = emodel(batch)
+        eopt.backward(loss)
+        if step == 2:    # poison one reduced gradient: the whole step must be skipped
+            chunks[0].shard[3] = float('inf')
+            chunks[0].overflow = True
+            eopt.engine.ctl.found_inf.fill_(1)
+        # CPU replay on what is in the shards right now
+        cs = oracle.ChunkSet(torch.float16)
+        masters = []
+        for i, c in enumerate(chunks):
+            m, e1, e2, lowp, nv = (t.cpu().clone() if torch.is_tensor(t) else t for t in eopt.engine.shards[i])
+            cs.add_chunk(m, e1, e2, lowp, nv, [(0, nv, 0)] if nv else [])
+            masters.append((m, e1, e2))
+        eopt.step()
+        skipped = cs.step(host_ctl, eopt.grad_scaler.cfg, hyper, probe=True, f64=True)
+        ctl = eopt.engine.read_control()
+        assert bool(ctl.skip) == skipped == (step == 2)
+        assert (ctl.scale, ctl.step, ctl.growth_step) == (host_ctl.scale, host_ctl.step, host_ctl.growth_step)
+        for i, c in enumerate(chunks):
+            for got, want in zip(eopt.engine.shards[i][:3], masters[i]):
+                ok, ratio = close_1e6(got, want.double())
+                assert ok, (step, i, ratio)
+            want16 = torch.empty(c.shard_size, dtype=torch.float16)
+            oracle.cast(c.paired_chunk.shard.cpu(), want16)
+            assert bits_equal(c.shard, want16)
+    assert eopt.engine.read_control().status == 0
+    assert all(p.grad is None for p in model.parameters())
+
+
+def test_training_reduces_the_loss_and_state_dict_round_trips(cuda, single_group):
+    torch.manual_seed(2)
+    model = Mlp().to(cuda)
+    emodel, eopt = _wrap(model, single_group, torch.float16, lr=3e-3, wd=0.0, initial_scale=1024.0)
+    x = torch.randn(64, 48, device=cuda)
+    losses = []
+    for _ in range(30):
+        eopt.zero_grad()
+        loss = emodel(x)
+        eopt.backward(loss)
+        eopt.step()
+        losses.append(loss.item())
+    assert losses[-1] < 0.5 * losses[0]
+    state = emodel.state_dict()
+    ostate = eopt.state_dict()
+    assert ostate['scaler']['step'] == 30 - ostate['scaler']['skipped_steps']
+    zeros = {k: torch.zeros_like(v) for k, v in state.items()}
+    emodel.load_state_dict(zeros)
+    assert all(float(v.abs().max()) == 0.0 for v in emodel.state_dict().values())
+    emodel.load_state_dict(state)
+    again = emodel.state_dict()
+    for k in state:
+        assert bits_equal(again[k], state[k])
+    with torch.no_grad():
+        assert abs(emodel(x).item() - emodel(x).item()) == 0.0
+
+
+def test_init_step_reproduces_the_reference_side_effects(cuda, single_group):
+    """init_step=True takes one step with zero gradients: the step count becomes 1 and decoupled weight decay
+    shrinks every weight once (elixir/wrapper/optimizer.py:94-113)."""
+    torch.manual_seed(3)
+    model = Mlp().to(cuda)
+    before = {n: p.detach().clone().float() for n, p in model.named_parameters()}
+    emodel, eopt = _wrap(model, single_group, torch.float16, lr=1e-2, wd=0.1, init_step=True)
+    assert eopt.engine.read_control().step == 1
+    after = emodel.state_dict()
+    for n, ref in before.items():
+        torch.testing.assert_close(after[n].to(cuda), ref * (1 - 1e-2 * 0.1), rtol=1e-6, atol=1e-9)
