@@ -36,6 +36,10 @@ OPT13B_PARAMS = 40 * (12 * 5120 * 5120 + 13 * 5120) + 50272 * 5120 + 2050 * 5120
 CHUNK_1GPU = 32 * 1024 * 1024    # 64 MiB of fp16
 CHUNK_SHARDED = 256 * 1024 * 1024    # 512 MiB of fp16
 BYTES_PER_ELEM = 28    # g 2 + p/m/v 12 read, p/m/v 12 + p16 2 written
+# dram__bytes_read.sum + dram__bytes_write.sum of one adam_tma_kernel launch over 67 108 864 elements,
+# from the ncu capture summarised in profiles/adam_tma_kernel_small_case_ncu.md; traffic grows in
+# proportion to the elements, so roofline.traffic scales it to the launch measured here.
+NCU_TRAFFIC_BYTES_PER_ELEM = 1819.3e6 / 67108864
 
 
 def load_peaks():
@@ -298,10 +302,11 @@ def run_ours(args):
         n_elems = engine.n_elements()
         achieved = n_elems * BYTES_PER_ELEM / (adam_ms * 1e-3) / 1e9
         result['roofline'] = {
-            'bound': 'hbm', 'kernel': 'adam_kernel', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s',
+            'bound': 'hbm', 'kernel': 'adam_tma_kernel', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s',
             'frac': achieved / peak, 'peak_kind': peak_kind, 'ms_per_launch': adam_ms,
             'elements_per_launch': n_elems, 'bytes_per_element': BYTES_PER_ELEM,
-            'traffic': args.traffic_per_launch, 'frac_of_8TBs_nominal': achieved / 8000.0,
+            'traffic': NCU_TRAFFIC_BYTES_PER_ELEM * n_elems, 'traffic_note': 'ncu capture of a 67M-element launch scaled by elements',
+            'frac_of_8TBs_nominal': achieved / 8000.0,
         }
         result['adam_gparams_per_s'] = n_elems / (adam_ms * 1e-3) / 1e9
         result['gpu_launches'] = args.steps * (n_chunks + 2)
@@ -319,6 +324,12 @@ def run_ours(args):
             'traffic': None, 'adam_hbm_ms_at_peak': adam_bytes / (peak * 1e9) * 1e3,
         }
         result['gpu_launches'] = args.steps * (2 * n_chunks + 1)
+        # one more, untimed, step with phase timestamps: where the step time goes
+        engine.profile = True
+        one_step()
+        torch.cuda.synchronize()
+        result['phases_ms'] = engine.phase_ms()
+        engine.profile = False
 
     # ---- end to end: pinned host buffers on both ends --------------------------------------------
     e2e = None
@@ -506,8 +517,6 @@ def main():
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--e2e-steps', type=int, default=10)
-    ap.add_argument('--traffic-per-launch', type=float, default=None,
-                    help='DRAM bytes per adam launch from an ncu capture (see profiles/), copied into roofline.traffic')
     args = ap.parse_args()
     if args.impl == 'reference':
         run_reference(args)

@@ -135,6 +135,28 @@ class ChunkStepEngine:
 
     # ------------------------------------------------------------------ pipelines
 
+    def _phase_marks(self, stream):
+        """When ``self.profile`` is set, timestamp the phases of a pipelined step with CUDA events on the
+        main stream; ``phase_ms()`` reads them back (after a synchronize)."""
+        if not getattr(self, 'profile', False):
+            return lambda name: None
+        events = [('start', torch.cuda.Event(enable_timing=True))]
+        events[0][1].record(stream)
+        self._last_marks = events
+
+        def mark(name):
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(stream)
+            events.append((name, ev))
+
+        return mark
+
+    def phase_ms(self):
+        marks = getattr(self, '_last_marks', None)
+        if not marks:
+            return {}
+        return {b[0]: a[1].elapsed_time(b[1]) for a, b in zip(marks, marks[1:])}
+
     def _side_streams(self):
         if self._streams is None:
             self._streams = (torch.cuda.Stream(self.device), torch.cuda.Stream(self.device))
@@ -164,6 +186,7 @@ class ChunkStepEngine:
         reduce_stream, gather_stream = self._side_streams()
         reduce_stream.wait_stream(main)
         gather_stream.wait_stream(main)
+        marks = self._phase_marks(main)
         for k, block in enumerate(grad_blocks):
             lowp = self.shards[k][3]
             with torch.cuda.stream(reduce_stream):
@@ -174,7 +197,9 @@ class ChunkStepEngine:
                 done.record(reduce_stream)
             main.wait_event(done)
             self.probe_one(k)
+        marks('reduced')
         self.begin_step()
+        marks('decided')
         for k, block in enumerate(gather_blocks):
             self.update(first=k, count=1)
             if block is None and host_params is None:
@@ -188,7 +213,9 @@ class ChunkStepEngine:
                 if host_params is not None:
                     host_params[k].copy_(self.shards[k][3], non_blocking=True)
         self.end_step()
+        marks('updated')
         main.wait_stream(gather_stream)
+        marks('gathered')
 
     def step_from_host(self, host_grads: Sequence[torch.Tensor], host_params: Sequence[torch.Tensor]):
         """A whole step with host buffers on both ends: ``host_grads[k]`` (pinned, shard_size elements of

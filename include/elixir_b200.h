@@ -47,6 +47,7 @@ extern "C" {
 /* sticky bits in ElxCtl.status */
 #define ELX_STAT_LATE_INF 1u   /* the Adam kernel met a non-finite gradient the probe had not flagged */
 #define ELX_STAT_BAD_DESC 2u   /* a kernel could not map a tile to a chunk descriptor                   */
+#define ELX_STAT_TIMEOUT 4u    /* a bounded wait on an on-chip barrier expired; the kernel gave up        */
 
 /*
  * Device-resident control block of one optimizer (128 bytes, 16-byte aligned).  It replaces the
@@ -145,6 +146,8 @@ const char* elx_last_cuda_error(void);
  *   "adam_ctas_per_sm"   cap on the persistent grid, 0 = every resident CTA
  *   "probe_ctas_per_sm"  the same for the probe kernels
  *   "probe_unroll"       4 or 8 tiles in flight per probe CTA
+ *   "adam_variant"       0 = direct 256-bit global accesses, 1 = bulk-copy (TMA) pipeline through
+ *                        shared memory
  *   "math_mode"          1 = IEEE division and square root in the update, 2 = reciprocal
  *                        multiplies and approximate division (both within 1e-6 relative) */
 int elx_set_tuning(const char* name, int value);

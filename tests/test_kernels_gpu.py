@@ -454,12 +454,52 @@ def test_launch_shapes_give_identical_bits(K, oracle, cuda, threads, ctas):
         return [[t.cpu() for t in ts] for ts in dev_t]
 
     base = run()
-    K.set_tuning(adam_threads=threads, adam_ctas_per_sm=ctas)
+    K.set_tuning(adam_variant=0, adam_threads=threads, adam_ctas_per_sm=ctas)
     try:
         other = run()
     finally:
-        K.set_tuning(adam_threads=-1, adam_ctas_per_sm=-1)
+        K.set_tuning(adam_variant=-1, adam_threads=-1, adam_ctas_per_sm=-1)
     for a, b in zip(base, other):
+        for x, y in zip(a, b):
+            assert bits_equal(x, y)
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
+def test_bulk_copy_pipeline_variant_is_bit_identical_to_direct(K, oracle, cuda, dtype):
+    """adam_variant=1 stages tiles through shared memory with cp.async.bulk; the arithmetic is shared, so
+    applied and skipped steps must give the same bits, over many tiles per CTA, ragged tiles and groups."""
+    sizes = [700 * 4096, 5 * 4096 + 100, 4096, 3, 12 * 4096]
+    valid = [700 * 4096 - 5, 5 * 4096 + 100, 1000, 0, 7 * 4096 + 1]
+    seg_lists = [
+        _segments(valid[0], [100, 4096, 4096 + 7, 300 * 4096, 500 * 4096 + 2048], [0, 1, 2, -1, 0, 1]),
+        _segments(valid[1], [2 * 4096], [1, 0]),
+        _segments(valid[2], [], [2]),
+        [],
+        _segments(valid[4], [3 * 4096 + 5], [0, 2]),
+    ]
+    hypers = [K.hyper(1e-3, (0.9, 0.999), 1e-8, 0.01, True), K.hyper(5e-4, (0.9, 0.98), 1e-6, 0.0, True),
+              K.hyper(2e-3, (0.85, 0.99), 1e-8, 0.05, False)]
+    outs = []
+    for variant in (0, 1):
+        K.set_tuning(adam_variant=variant)
+        try:
+            table, _, dev_t, _ = _build_set(K, oracle, cuda, dtype, sizes, valid, seg_lists, 21, 512.0)
+            table.set_hyper(hypers)
+            ctl = K.ControlBlock(cuda, 512.0)
+            cfg = K.scaler_cfg(True, hysteresis=1)
+            for step in range(3):
+                if step == 1:
+                    ctl.found_inf.fill_(1)    # a skipped step in the middle
+                K.step_begin(ctl, cfg)
+                K.adam_multi(table, ctl)
+                for ts in dev_t:    # next step's "gradients": something deterministic and finite
+                    ts[3].copy_((ts[0] * 37.0).to(dtype))
+            torch.cuda.synchronize()
+            assert ctl.read().status == 0
+            outs.append([[t.cpu() for t in ts] for ts in dev_t])
+        finally:
+            K.set_tuning(adam_variant=-1)
+    for a, b in zip(*outs):
         for x, y in zip(a, b):
             assert bits_equal(x, y)
 
