@@ -1,0 +1,171 @@
+"""The BASELINE configurations as parity cases (the single-GPU ones; sharded ones: test_sharded_gpu.py).
+
+config 1  4 chunks x 4 194 304 elements, fp16 gradients N(0,1e-3)*64, Adam lr 1e-3 b(0.9,0.999) eps 1e-8 wd 0,
+          10 steps, seed 0 — full size, every step against the CPU oracle.
+config 4  overflow path: fp16 chunk set, inf/nan injected at rate 1e-6 in a random 1 of 20 steps, dynamic scale
+          2^16 / backoff 0.5 / growth 2 every 1000 steps.  Full size (1 G parameters) through size-independent
+          properties (bit patterns of master and moments untouched on the skipped step, working copy restored,
+          decision and scale trajectory equal to the oracle's); a 16 M-parameter instance element by element,
+          with hysteresis 1 and 2, and with growth interval 5 so that growth is exercised too.
+"""
+import pytest
+import torch
+
+from _util import bits_equal, close_1e6, lowp_within_1ulp
+
+pytestmark = pytest.mark.gpu
+
+
+def _ctl_tuple(c):
+    return (c.scale, c.found_inf, c.growth_step, c.hysteresis_step, c.step, c.skip, c.div_scale, c.skipped_steps)
+
+
+def test_config1_ten_steps_full_size(cuda, oracle):
+    from elixir_b200 import kernels as K
+    from elixir_b200.engine import ChunkStepEngine
+    from elixir_b200.scaler import DynamicGradScaler
+    n_chunks, n, scale = 4, 4194304, 64.0
+    hyper = [K.hyper(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)]
+    engine = ChunkStepEngine(cuda, torch.float16, DynamicGradScaler(initial_scale=scale))
+    host = oracle.ChunkSet(torch.float16)
+    host_ctl = oracle.new_ctl(scale)
+    gen = torch.Generator().manual_seed(0)
+    hs = []
+    for c in range(n_chunks):
+        master = torch.randn(n, generator=gen) * 0.02
+        lowp = torch.zeros(n, dtype=torch.float16)
+        hm = (master.clone(), torch.zeros(n), torch.zeros(n), lowp)
+        host.add_chunk(*hm, n, [(0, n, 0)])
+        hs.append(hm)
+        engine.add_shard(master.to(cuda), torch.zeros(n, dtype=torch.float16, device=cuda), n, [(0, n, 0)])
+    engine.finalize()
+    engine.set_hyper(hyper)
+    for step in range(10):
+        for c in range(n_chunks):
+            g = (torch.randn(n, generator=gen) * 1e-3 * scale).half()
+            hs[c][3].copy_(g)
+            engine.land(c, g.to(cuda))
+        engine.step()
+        assert not host.step(host_ctl, engine.scaler.cfg, hyper, probe=True, f64=True)
+        assert _ctl_tuple(engine.read_control()) == _ctl_tuple(host_ctl)
+        for c in range(n_chunks):
+            for name, got, want in zip(('master', 'exp_avg', 'exp_avg_sq'), engine.shards[c][:3], hs[c][:3]):
+                ok, ratio = close_1e6(got, want.double())
+                assert ok, (step, c, name, ratio)
+            want16 = torch.empty(n, dtype=torch.float16)
+            oracle.cast(engine.shards[c][0].cpu(), want16)
+            assert bits_equal(engine.shards[c][3], want16)
+            assert lowp_within_1ulp(engine.shards[c][3], hs[c][3], hs[c][0])[0]
+    assert engine.read_control().status == 0 and engine.read_control().step == 10
+
+
+def _inject(g, gen, rate):
+    """Replace elements by +inf / -inf / nan with probability `rate` (Bernoulli mask from `gen`)."""
+    mask = torch.rand(g.numel(), generator=gen, device=g.device) < rate
+    kinds = torch.randint(0, 3, (g.numel(),), generator=gen, device=g.device)
+    vals = torch.tensor([float('inf'), -float('inf'), float('nan')], device=g.device)[kinds].to(g.dtype)
+    out = torch.where(mask, vals, g)
+    return out, int(mask.sum().item())
+
+
+@pytest.mark.parametrize('hysteresis,growth_interval', [(1, 1000), (2, 1000), (1, 5), (2, 5)])
+def test_config4_overflow_trajectory_16m_elementwise(cuda, oracle, hysteresis, growth_interval):
+    from elixir_b200 import kernels as K
+    from elixir_b200.engine import ChunkStepEngine
+    from elixir_b200.scaler import DynamicGradScaler
+    n_chunks, n = 4, 4194304
+    hyper = [K.hyper(lr=1e-3, weight_decay=0.0)]
+    scaler = DynamicGradScaler(initial_scale=2.0**16, backoff_factor=0.5, growth_factor=2, growth_interval=growth_interval,
+                               min_scale=1, max_scale=2**24, hysteresis=hysteresis)
+    engine = ChunkStepEngine(cuda, torch.float16, scaler)
+    host = oracle.ChunkSet(torch.float16)
+    host_ctl = oracle.new_ctl(2.0**16)
+    gen = torch.Generator().manual_seed(4)
+    bad_steps = {int(torch.randint(0, 20, (1,), generator=gen)), 11, 12}    # the drawn one plus two in a row
+    hs = []
+    for c in range(n_chunks):
+        master = torch.randn(n, generator=gen) * 0.02
+        hm = (master.clone(), torch.zeros(n), torch.zeros(n), torch.zeros(n, dtype=torch.float16))
+        host.add_chunk(*hm, n, [(0, n, 0)])
+        hs.append(hm)
+        engine.add_shard(master.to(cuda), torch.zeros(n, dtype=torch.float16, device=cuda), n, [(0, n, 0)])
+    engine.finalize()
+    engine.set_hyper(hyper)
+    skipped_steps = []
+    for step in range(20):
+        for c in range(n_chunks):
+            g = (torch.randn(n, generator=gen) * 1e-3 * host_ctl.scale).half()
+            if step in bad_steps:
+                g, count = _inject(g, gen, 1e-6 if c else 2e-6)
+            hs[c][3].copy_(g)
+            engine.land(c, g.to(cuda))
+        flags = engine.chunk_flags.tolist()
+        assert flags == [int(oracle.probe(hs[c][3])) for c in range(n_chunks)]
+        engine.step()
+        skipped = host.step(host_ctl, engine.scaler.cfg, hyper, probe=True, f64=True)
+        assert _ctl_tuple(engine.read_control()) == _ctl_tuple(host_ctl), step
+        if skipped:
+            skipped_steps.append(step)
+        if step % 5 == 4 or skipped:
+            for c in range(n_chunks):
+                for got, want in zip(engine.shards[c][:3], hs[c][:3]):
+                    assert close_1e6(got, want.double())[0], (step, c)
+    assert set(skipped_steps) <= bad_steps and len(skipped_steps) >= 1
+    assert engine.read_control().status == 0
+
+
+def _bit_checksum(t):
+    return int(t.view(torch.int32).to(torch.int64).sum().item())
+
+
+def test_config4_overflow_trajectory_full_size_properties(cuda, oracle):
+    from elixir_b200 import kernels as K
+    from elixir_b200.engine import ChunkStepEngine
+    from elixir_b200.scaler import DynamicGradScaler
+    free, _ = torch.cuda.mem_get_info(cuda)
+    n_chunks, n = 32, 33554432    # 1 073 741 824 parameters
+    if free < n_chunks * n * 20:
+        pytest.skip('not enough free device memory for the 1 G-parameter instance')
+    hyper = [K.hyper(lr=1e-3, weight_decay=0.0)]
+    scaler = DynamicGradScaler(initial_scale=2.0**16, backoff_factor=0.5, growth_factor=2, growth_interval=1000,
+                               min_scale=1, max_scale=2**24, hysteresis=2)
+    engine = ChunkStepEngine(cuda, torch.float16, scaler)
+    host_ctl = oracle.new_ctl(2.0**16)
+    dgen = torch.Generator(device=cuda).manual_seed(44)
+    for c in range(n_chunks):
+        master = torch.empty(n, device=cuda).normal_(0.0, 0.02, generator=dgen)
+        engine.add_shard(master, torch.zeros(n, dtype=torch.float16, device=cuda), n, [(0, n, 0)])
+    engine.finalize()
+    engine.set_hyper(hyper)
+    bad_step = int(torch.randint(0, 20, (1,), generator=torch.Generator().manual_seed(44)))
+    block = torch.empty(n, dtype=torch.float16, device=cuda)
+    tmp = torch.empty(n, device=cuda)
+    for step in range(20):
+        before = None
+        if step == bad_step:
+            before = [[_bit_checksum(t) for t in engine.shards[c][:3]] for c in range(n_chunks)]
+        injected = 0
+        for c in range(n_chunks):
+            block.copy_(tmp.normal_(0.0, 1e-3, generator=dgen).mul_(host_ctl.scale))
+            if step == bad_step:
+                dirty, count = _inject(block, dgen, 1e-6)
+                block.copy_(dirty)
+                injected += count
+            engine.land(c, block)
+        if step == bad_step:
+            assert injected > 0
+            host_ctl.found_inf = 1
+        assert bool(engine.read_control().found_inf) == (step == bad_step)
+        engine.step()
+        oracle.step_begin(host_ctl, engine.scaler.cfg)
+        assert _ctl_tuple(engine.read_control()) == _ctl_tuple(host_ctl), step
+        if step == bad_step:
+            after = [[_bit_checksum(t) for t in engine.shards[c][:3]] for c in range(n_chunks)]
+            assert after == before    # master and both moments untouched, bit for bit
+        # the working copy is the rounded master after every step, skipped or not (checked with torch's cast,
+        # which the oracle's cast is pinned to bit for bit)
+        c = step % n_chunks
+        assert torch.equal(engine.shards[c][3].view(torch.int16), engine.shards[c][0].half().view(torch.int16))
+    ctl = engine.read_control()
+    assert (ctl.skipped_steps, ctl.step, ctl.status) == (1, 19, 0)
+    assert ctl.scale == 2.0**16    # hysteresis 2: a single overflow does not back off
