@@ -206,6 +206,18 @@ def run_ours(args):
             gen = torch.Generator(device=device).manual_seed(args.seed + 7919 * (c + 1))
             grad_blocks.append(synth_grad(shard, device, gen, scale, sigma, dtype))
         gather_blocks = None
+    elif args.collective == 'p2p':
+        # NVLink path: every chunk owns a block in the peer-mapped gradient and gather slabs
+        engine.enable_p2p([chunk] * n_chunks)
+        seeds = 4
+        for c in range(n_chunks):
+            if c < seeds:
+                gen = torch.Generator(device=device).manual_seed(args.seed + 7919 * (c + 1) + 31 * rank)
+                synth_grad(chunk, device, gen, scale, sigma, dtype, out=engine.grad_block(c))
+            else:
+                engine.grad_block(c).copy_(engine.grad_block(c % seeds))
+        grad_blocks = [engine.grad_block(c) for c in range(n_chunks)]
+        gather_blocks = [engine.gather_block(c) for c in range(n_chunks)]
     else:
         pool = 4
         grad_pool, gather_pool = [], []
@@ -232,6 +244,8 @@ def run_ours(args):
             else:
                 engine.update()
             engine.end_step()
+        elif args.collective == 'p2p':
+            engine.step_sharded_p2p()
         else:
             engine.step_sharded(grad_blocks, gather_blocks)
 
@@ -293,6 +307,10 @@ def run_ours(args):
             'loss_scale': scale,
             'l2_policy': 'inputs larger than L2 (state per GPU %.1f GB)' % (engine.n_elements() * 14 / 1e9),
             'layout': 'flat packing, tensors may straddle chunks',
+            'collectives': 'none (1 GPU)' if world == 1 else
+                           ('fused into the kernels over peer-mapped NVLink memory (pull reduce-scatter + probe, '
+                            'Adam + push all-gather)' if args.collective == 'p2p' else
+                            'NCCL reduce-scatter (pre-multiplied sum) and all-gather per chunk on side streams'),
         },
         'clocks': clocks,
     }
@@ -323,13 +341,17 @@ def run_ours(args):
             'unit': 'GB/s', 'frac': 2 * bus_bytes / (ms_per_step * 1e-3) / 1e9 / 770.0, 'peak_kind': 'measured',
             'traffic': None, 'adam_hbm_ms_at_peak': adam_bytes / (peak * 1e9) * 1e3,
         }
-        result['gpu_launches'] = args.steps * (2 * n_chunks + 1)
-        # one more, untimed, step with phase timestamps: where the step time goes
-        engine.profile = True
-        one_step()
-        torch.cuda.synchronize()
-        result['phases_ms'] = engine.phase_ms()
-        engine.profile = False
+        if args.collective == 'p2p':
+            result['gpu_launches'] = args.steps * 6
+            result['phases_ms'] = p2p_phases(engine)
+        else:
+            result['gpu_launches'] = args.steps * (2 * n_chunks + 1)
+            # one more, untimed, step with phase timestamps: where the step time goes
+            engine.profile = True
+            one_step()
+            torch.cuda.synchronize()
+            result['phases_ms'] = engine.phase_ms()
+            engine.profile = False
 
     # ---- end to end: pinned host buffers on both ends --------------------------------------------
     e2e = None
@@ -345,6 +367,25 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def p2p_phases(engine):
+    """CUDA-event time of the two fused kernels of one (untimed) NVLink step, barriers included in neither."""
+    from elixir_b200 import kernels as K
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    engine.peer_barrier(engine.ctl)
+    ev[0].record()
+    K.pull_reduce_multi(engine.table, engine.grad_slab.table, engine.block_off, engine.ctl, chunk_flags=engine.chunk_flags)
+    ev[1].record()
+    engine.peer_barrier(engine.ctl, exchange_overflow=True)
+    K.step_begin(engine.ctl, engine.scaler.cfg)
+    ev[2].record()
+    K.adam_multi_push(engine.table, engine.ctl, engine.gather_slab.table, engine.block_off)
+    ev[3].record()
+    engine.end_step()
+    engine.peer_barrier(engine.ctl)
+    torch.cuda.synchronize()
+    return {'pull_reduce_probe': ev[0].elapsed_time(ev[1]), 'adam_push_gather': ev[2].elapsed_time(ev[3])}
 
 
 def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, scale, sigma, total, timed,
@@ -365,6 +406,13 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
     outs = [host_out[c % pool] for c in range(n_chunks)]
     if world == 1:
         fn = lambda: engine.step_from_host(grads, outs)
+    elif args.collective == 'p2p':
+        def fn():
+            for k in range(n_chunks):
+                grad_blocks[k].copy_(grads[k], non_blocking=True)
+            engine.step_sharded_p2p()
+            for k in range(n_chunks):
+                outs[k].copy_(engine.shards[k][3], non_blocking=True)
     else:
         fn = lambda: engine.step_sharded(grad_blocks, gather_blocks, host_grads=grads, host_params=outs)
     steps = max(1, min(args.steps, args.e2e_steps))
@@ -377,7 +425,9 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
     return {
         'value': total / (ms * 1e-3) / 1e9, 'unit': 'Gparams/s', 'ms_per_step': ms, 'steps': steps,
         'h2d_bytes_per_step': n_chunks * in_elems * 2 * world, 'd2h_bytes_per_step': n_chunks * shard * 2 * world,
-        'api': 'ChunkStepEngine.step_from_host' if world == 1 else 'ChunkStepEngine.step_sharded(host_grads=, host_params=)',
+        'api': 'ChunkStepEngine.step_from_host' if world == 1 else
+               ('H2D into the gradient slab + ChunkStepEngine.step_sharded_p2p + D2H of the shards' if args.collective == 'p2p'
+                else 'ChunkStepEngine.step_sharded(host_grads=, host_params=)'),
         'note': 'pinned fp16 gradients in, updated fp16 parameters out; fp32 master and moments stay in HBM',
     }
 
@@ -514,6 +564,8 @@ def main():
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--seed', type=int, default=0)
+    ap.add_argument('--collective', default='p2p', choices=['p2p', 'nccl'],
+                    help='N > 1: collectives fused into the kernels over peer-mapped NVLink memory, or NCCL')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--e2e-steps', type=int, default=10)

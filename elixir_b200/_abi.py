@@ -16,6 +16,7 @@ ERR_NULL, ERR_ALIGN, ERR_SIZE, ERR_DTYPE, ERR_LAUNCH, ERR_ARG, ERR_NODEVICE, ERR
 
 STAT_LATE_INF = 1
 STAT_BAD_DESC = 2
+STAT_TIMEOUT = 4
 
 MAX_GROUPS = 64
 
@@ -92,6 +93,18 @@ class ElxChunkDesc(C.Structure):
     ]
 
 
+MAX_PEERS = 16
+
+
+class ElxPeerTable(C.Structure):
+    _fields_ = [
+        ('base', C.c_void_p * MAX_PEERS),
+        ('rank', C.c_int32),
+        ('world', C.c_int32),
+    ]
+
+
+assert C.sizeof(ElxPeerTable) == 8 * MAX_PEERS + 8
 assert C.sizeof(ElxCtl) == 128
 assert C.sizeof(ElxScalerCfg) == 32
 assert C.sizeof(ElxHyper) == 32
@@ -118,6 +131,15 @@ PROTOTYPES = {
     'elx_reduce_epilogue': (_i, [_p, _p, _i, _i64, _i64, _p, _p, _p, _p, _i64, _p]),
     'elx_grad_check_multi': (_i, [_p, _i, _i, _i64, _i, _p, _p, _p, _p, _p, _i64, _p]),
     'elx_adam_multi': (_i, [_p, _i, _i, _i64, _i, _p, _p, _i, _p, _p]),
+    'elx_enable_peer_access': (_i, [_i]),
+    'elx_peer_alloc': (_i, [_i64, C.POINTER(C.c_void_p), _p]),
+    'elx_peer_free': (_i, [_p]),
+    'elx_ipc_open': (_i, [_p, C.POINTER(C.c_void_p)]),
+    'elx_ipc_close': (_i, [_p]),
+    'elx_peek_u32': (_i, [_p, C.POINTER(C.c_uint32)]),
+    'elx_peer_barrier': (_i, [ElxPeerTable, C.c_uint32, _p, _i, _i, _p]),
+    'elx_pull_reduce_multi': (_i, [_p, _i, _i, _i64, _i, ElxPeerTable, _p, _p, _p, _p]),
+    'elx_adam_multi_push': (_i, [_p, _i, _i, _i64, _i, _p, _p, _i, _p, ElxPeerTable, _p, _p]),
     'elx_adam_chunk': (_i, [_p, _p, _p, _p, _i, _i64, _i64, ElxHyper, _p, _p]),
     'elx_cast_copyback': (_i, [_p, _p, _i, _i64, _p]),
 }

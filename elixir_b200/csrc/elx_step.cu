@@ -47,6 +47,7 @@ struct Tuning {
     int probe_unroll = 4;
     int math_mode = 1;
     int adam_variant = 1;         // 0 = direct global accesses, 1 = bulk-copy (TMA) pipeline
+    int pull_ctas_per_sm = 0;
 };
 Tuning g_tune;
 
@@ -447,11 +448,19 @@ struct AdamArgs {
     ElxCtl* ctl;
     int first, count, n_groups, inline_tables;
     int64_t n_tiles;
+    // push all-gather: the refreshed working copy also goes to every rank's gather block (world > 0)
+    ElxPeerTable push;
+    const int64_t* push_off;   // per descriptor: element offset of the chunk's block inside the slabs
     // single-shard form: the three tables travel in the kernel parameters
     ElxChunkDesc one_desc;
     ElxSeg one_seg;
     ElxHyper one_hyper;
 };
+
+// Push all-gather: element offset of this rank's shard of descriptor `c` inside every rank's gather slab.
+__device__ __forceinline__ int64_t push_base_elem(const AdamArgs& a, int c, int64_t n_shard) {
+    return a.push_off[c] + static_cast<int64_t>(a.push.rank) * n_shard;
+}
 
 // Skipped step: the low-precision shard holds gradients and must become parameters again.
 // CTA-collective; s_cur is a shared-memory cursor that cursor_reset() has initialised.
@@ -470,13 +479,20 @@ __device__ __forceinline__ bool copyback_tiles(const AdamArgs& a, const ElxChunk
         const int64_t e1 = min(e0 + kTile, s_cur.d.n_shard);
         float* const master = s_cur.d.master;
         void* const lowp = s_cur.d.grad_param;
-        if ((e1 - e0 == kTile) && s_cur.vec_ok) {
+        const int world = a.push.world;
+        const int64_t pb = world > 0 ? push_base_elem(a, s_cur.index, s_cur.d.n_shard) : 0;
+        if ((e1 - e0 == kTile) && s_cur.vec_ok && (pb & 15) == 0) {
             float p[EPT];
             load_f32<EPT>(master, e0, p);
             store_lowp<DT, EPT>(lowp, e0, p);
+            for (int j = 0; j < world; ++j) store_lowp<DT, EPT>(a.push.base[j], pb + e0, p);
         } else {
             typename Lp<DT>::T* out = static_cast<typename Lp<DT>::T*>(lowp);
-            for (int64_t e = e0 + threadIdx.x; e < e1; e += blockDim.x) out[e] = Lp<DT>::from_float(master[e]);
+            for (int64_t e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
+                const typename Lp<DT>::T val = Lp<DT>::from_float(master[e]);
+                out[e] = val;
+                for (int j = 0; j < world; ++j) static_cast<typename Lp<DT>::T*>(a.push.base[j])[pb + e] = val;
+            }
         }
     }
     return bad_desc;
@@ -690,6 +706,7 @@ struct TileSlot {
     void* lowp;
     const ElxSeg* segs;
     int64_t e0, e1;
+    int64_t push_elem;   // element offset of this tile inside every rank's gather slab (push all-gather)
     int n_segs;
     int group;
     int kind;
@@ -762,7 +779,9 @@ __device__ __forceinline__ void classify_tile(const AdamArgs& a, const ElxChunkD
     out.e0 = e0;
     out.e1 = e1;
     out.group = pc.seg_group;
-    out.kind = (e1 - e0 == kTile && pc.vec_ok && one_group) ? kTileBulk : kTileRagged;
+    out.push_elem = a.push.world > 0 ? push_base_elem(a, pc.index, pc.d.n_shard) + e0 : 0;
+    const bool push_ok = a.push.world == 0 || (out.push_elem & 15) == 0;   // bulk copies need 16-byte alignment
+    out.kind = (e1 - e0 == kTile && pc.vec_ok && one_group && push_ok) ? kTileBulk : kTileRagged;
 }
 
 template <int DT, int MATH>
@@ -898,7 +917,10 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                         slot.exp_avg_sq[e] = v;
                     }
                 }
-                gp[e] = Lp<DT>::from_float(p);
+                const typename Lp<DT>::T val = Lp<DT>::from_float(p);
+                gp[e] = val;
+                for (int j = 0; j < a.push.world; ++j)
+                    static_cast<typename Lp<DT>::T*>(a.push.base[j])[slot.push_elem + (e - slot.e0)] = val;
             }
         } else if (slot.kind == kTileBad) {
             bad_desc = true;
@@ -911,6 +933,11 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                 bulk_s2g(slot.master + slot.e0, base + Stage::kLowpBytes, Stage::kF32Bytes);
                 bulk_s2g(slot.exp_avg + slot.e0, base + Stage::kLowpBytes + Stage::kF32Bytes, Stage::kF32Bytes);
                 bulk_s2g(slot.exp_avg_sq + slot.e0, base + Stage::kLowpBytes + 2 * Stage::kF32Bytes, Stage::kF32Bytes);
+                // push all-gather: the same 8 KB of refreshed parameters to every rank's gather block,
+                // plain (non-multicast) bulk stores, W - 1 of them crossing NVLink
+                for (int j = 0; j < a.push.world; ++j)
+                    bulk_s2g(static_cast<char*>(a.push.base[j]) + slot.push_elem * Lp<DT>::kBytes, base,
+                             Stage::kLowpBytes);
             }
             bulk_commit();
             if (k + kTmaStages - 1 < my_tiles) {
@@ -1148,6 +1175,143 @@ __global__ void __launch_bounds__(256) norm_finalize(const __grid_constant__ Nor
 }
 
 // ------------------------------------------------------------------------------------------------
+// NVLink: pull reduce-scatter fused with the probe, and the cross-rank barrier
+// ------------------------------------------------------------------------------------------------
+//
+// Every rank keeps its replicated gradient blocks in a slab that all ranks of the box can address
+// (peer-mapped memory).  Rank r produces its shard of a chunk by READING the r-th slice of that
+// chunk's block from every rank with ordinary loads (its own slice from local HBM, W - 1 slices over
+// NVLink), summing float(x) * (1/W) in rank order in fp32, rounding once to the chunk dtype, storing
+// the shard and probing the rounded result for inf/nan in the same pass.  No TMA, no multicast.
+
+struct PullArgs {
+    const ElxChunkDesc* descs;
+    uint32_t* chunk_flags;
+    ElxCtl* ctl;
+    ElxPeerTable grads;
+    const int64_t* block_off;   // per descriptor: element offset of the chunk's block inside the slabs
+    int first, count;
+    int64_t n_tiles;
+};
+
+template <int DT>
+__global__ void __launch_bounds__(256) pull_reduce_kernel(const __grid_constant__ PullArgs a) {
+    constexpr int EPT = 16;
+    using T = typename Lp<DT>::T;
+    __shared__ ChunkCursor s_cur;
+    cursor_reset(s_cur);
+    const ElxChunkDesc* __restrict__ descs = a.descs;
+    const int64_t tile_lo = descs[a.first].tile_begin;
+    const int world = a.grads.world, rank = a.grads.rank;
+    const float inv_w = 1.0f / static_cast<float>(world);
+    const int lane = threadIdx.x & 31;
+    bool bad_desc = false;
+
+    for (int64_t it = blockIdx.x; it < a.n_tiles; it += gridDim.x) {
+        const int64_t t = tile_lo + it;
+        if (!locate_chunk(descs, a.first, a.count, t, s_cur) || s_cur.d.dtype != DT) {
+            bad_desc = true;
+            continue;
+        }
+        const int64_t n_shard = s_cur.d.n_shard, n_valid = s_cur.d.n_valid;
+        const int64_t e0 = (t - s_cur.t0) * kTile;
+        const int64_t e1 = min(e0 + kTile, n_shard);
+        const int64_t src0 = a.block_off[s_cur.index] + static_cast<int64_t>(rank) * n_shard;   // element offset
+        void* const dst = s_cur.d.grad_param;
+        const bool all_valid = e0 + kTile <= n_valid, none_valid = e0 >= n_valid;
+        uint32_t bad = 0;
+        if ((e1 - e0 == kTile) && (all_valid || none_valid) && (src0 & 15) == 0 &&
+            (reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
+            float acc[EPT];
+#pragma unroll
+            for (int i = 0; i < EPT; ++i) acc[i] = 0.0f;
+            for (int j = 0; j < world; ++j) {
+                float g[EPT];
+                load_lowp<DT, EPT>(a.grads.base[j], src0 + e0, g);
+#pragma unroll
+                for (int i = 0; i < EPT; ++i) acc[i] = fmaf(g[i], inv_w, acc[i]);
+            }
+            store_lowp<DT, EPT>(dst, e0, acc);
+            if (all_valid) {
+                if constexpr (DT == ELX_F32) {
+#pragma unroll
+                    for (int i = 0; i < EPT; ++i) bad |= Lp<DT>::nonfinite_word(__float_as_uint(acc[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < EPT / 2; ++i) bad |= Lp<DT>::nonfinite_word(Lp<DT>::pack2(acc[2 * i], acc[2 * i + 1]));
+                }
+            }
+        } else {
+            T* out = static_cast<T*>(dst);
+            for (int64_t e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
+                float acc = 0.0f;
+                for (int j = 0; j < world; ++j)
+                    acc = fmaf(Lp<DT>::to_float(static_cast<const T*>(a.grads.base[j])[src0 + e]), inv_w, acc);
+                const T val = Lp<DT>::from_float(acc);
+                out[e] = val;
+                if (e < n_valid && Lp<DT>::nonfinite(val)) bad = 1;
+            }
+        }
+        const unsigned any_bad = __ballot_sync(0xFFFFFFFFu, bad != 0);
+        if (any_bad && lane == 0) {
+            if (a.chunk_flags) atomicOr(&a.chunk_flags[s_cur.index], 1u);
+            if (a.ctl) atomicOr(&a.ctl->found_inf, 1u);
+        }
+    }
+    const unsigned ballot_desc = __ballot_sync(0xFFFFFFFFu, bad_desc);
+    if (ballot_desc && lane == 0 && a.ctl) atomicOr(&a.ctl->status, ELX_STAT_BAD_DESC);
+}
+
+// Flag region of one rank (peer-mapped): for each parity of the epoch and each sender, {epoch, word}.
+// A rank can run at most one barrier ahead of a peer, so two parities are enough.
+__device__ __forceinline__ uint32_t* flag_slot(void* region, uint32_t epoch, int sender) {
+    return static_cast<uint32_t*>(region) + ((epoch & 1u) * ELX_MAX_PEERS + sender) * 2;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// One warp.  Lane j tells rank j "rank `rank` reached barrier `epoch`" (with this rank's overflow word
+// riding along), then waits — for at most timeout_ns — until rank j has told this rank the same.
+// On expiry the sticky ELX_STAT_TIMEOUT bit is raised and the kernel returns; it never traps.
+__global__ void peer_barrier_kernel(ElxPeerTable flags, uint32_t epoch, ElxCtl* ctl, int exchange_overflow,
+                                    uint64_t timeout_ns) {
+    const int j = threadIdx.x;
+    const int world = flags.world, rank = flags.rank;
+    uint32_t seen_inf = 0;
+    bool expired = false;
+    if (j < world) {
+        const uint32_t mine = (exchange_overflow && ctl) ? ctl->found_inf : 0u;
+        __threadfence_system();   // everything this rank wrote before the barrier is visible to the peers first
+        uint32_t* out = flag_slot(flags.base[j], epoch, rank);
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(out + 1), "r"(mine) : "memory");
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(out), "r"(epoch) : "memory");
+        const uint32_t* in = flag_slot(flags.base[rank], epoch, j);
+        const uint64_t t_start = global_timer_ns();
+        for (;;) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(in) : "memory");
+            if (v == epoch) break;
+            if (global_timer_ns() - t_start > timeout_ns) {
+                expired = true;
+                break;
+            }
+            __nanosleep(200);
+        }
+        if (!expired) asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(seen_inf) : "l"(in + 1) : "memory");
+    }
+    const unsigned any_inf = __ballot_sync(0xFFFFFFFFu, seen_inf != 0);
+    const unsigned any_expired = __ballot_sync(0xFFFFFFFFu, expired);
+    if (j == 0 && ctl) {
+        if (exchange_overflow && any_inf) atomicOr(&ctl->found_inf, 1u);
+        if (any_expired) atomicOr(&ctl->status, ELX_STAT_TIMEOUT);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // control block
 // ------------------------------------------------------------------------------------------------
 
@@ -1265,7 +1429,7 @@ int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
 template <int DT>
 int launch_adam_dt(const AdamArgs& a, cudaStream_t s) {
     const bool precise = g_tune.math_mode == 1;
-    if (g_tune.adam_variant == 1)
+    if (g_tune.adam_variant == 1 || a.push.world > 0)
         return precise ? launch_adam_tma<DT, 1>(a, s) : launch_adam_tma<DT, 2>(a, s);
     if (g_tune.adam_threads == 256)
         return precise ? launch_adam_minb<DT, 16, 1>(a, s) : launch_adam_minb<DT, 16, 2>(a, s);
@@ -1448,6 +1612,7 @@ int elx_set_tuning(const char* name, int value) {
         {"probe_unroll", &g_tune.probe_unroll, def.probe_unroll, 4, 8},
         {"math_mode", &g_tune.math_mode, def.math_mode, 1, 2},
         {"adam_variant", &g_tune.adam_variant, def.adam_variant, 0, 1},
+        {"pull_ctas_per_sm", &g_tune.pull_ctas_per_sm, def.pull_ctas_per_sm, 0, 32},
     };
     for (const Knob& k : knobs) {
         if (strcmp(name, k.name) != 0) continue;
@@ -1577,6 +1742,211 @@ int elx_adam_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_ti
     a.count = count;
     a.n_groups = n_groups;
     a.n_tiles = n_tiles;
+    return launch_adam(a, dtype, static_cast<cudaStream_t>(stream));
+}
+
+static int peer_table_ok(const ElxPeerTable& t) {
+    if (t.world < 1 || t.world > ELX_MAX_PEERS || t.rank < 0 || t.rank >= t.world) return ELX_ERR_SIZE;
+    for (int j = 0; j < t.world; ++j) {
+        if (!t.base[j]) return ELX_ERR_NULL;
+        if (!aligned(t.base[j], 32)) return ELX_ERR_ALIGN;
+    }
+    return ELX_OK;
+}
+
+int elx_enable_peer_access(int peer_device) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        record_cuda(e);
+        (void)cudaGetLastError();
+        return ELX_ERR_NODEVICE;
+    }
+    if (peer_device == dev) return ELX_OK;
+    int can = 0;
+    e = cudaDeviceCanAccessPeer(&can, dev, peer_device);
+    if (e != cudaSuccess || !can) {
+        if (e != cudaSuccess) record_cuda(e);
+        (void)cudaGetLastError();
+        return ELX_ERR_ARG;
+    }
+    e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        (void)cudaGetLastError();
+        return ELX_OK;
+    }
+    return record_cuda(e);
+}
+
+int elx_peer_alloc(int64_t bytes, void** ptr, void* handle) {
+    if (!ptr || !handle) return ELX_ERR_NULL;
+    if (bytes <= 0) return ELX_ERR_SIZE;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, static_cast<size_t>(bytes));
+    if (e != cudaSuccess) {
+        const int rc = record_cuda(e);
+        (void)cudaGetLastError();
+        return rc;
+    }
+    cudaIpcMemHandle_t h;
+    e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        const int rc = record_cuda(e);
+        (void)cudaGetLastError();
+        (void)cudaFree(p);
+        return rc;
+    }
+    memcpy(handle, &h, sizeof(h));
+    *ptr = p;
+    return ELX_OK;
+}
+
+int elx_peer_free(void* ptr) {
+    if (!ptr) return ELX_ERR_NULL;
+    const cudaError_t e = cudaFree(ptr);
+    if (e != cudaSuccess) {
+        const int rc = record_cuda(e);
+        (void)cudaGetLastError();
+        return rc;
+    }
+    return ELX_OK;
+}
+
+int elx_ipc_open(const void* handle, void** base) {
+    if (!handle || !base) return ELX_ERR_NULL;
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(h) == 64, "cudaIpcMemHandle_t is 64 bytes");
+    memcpy(&h, handle, sizeof(h));
+    void* ptr = nullptr;
+    // opened with the ACCESSING device current: the driver maps the exporter's memory for this device and
+    // turns peer access on as needed
+    const cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+        const int rc = record_cuda(e);
+        (void)cudaGetLastError();
+        return rc;
+    }
+    *base = ptr;
+    return ELX_OK;
+}
+
+int elx_peek_u32(const void* device_ptr, uint32_t* value) {
+    if (!device_ptr || !value) return ELX_ERR_NULL;
+    cudaPointerAttributes attr;
+    cudaError_t e = cudaPointerGetAttributes(&attr, device_ptr);
+    if (e != cudaSuccess || attr.type != cudaMemoryTypeDevice) {
+        if (e != cudaSuccess) record_cuda(e);
+        (void)cudaGetLastError();
+        return ELX_ERR_ARG;
+    }
+    e = cudaMemcpy(value, device_ptr, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        const int rc = record_cuda(e);
+        (void)cudaGetLastError();
+        return rc;
+    }
+    return ELX_OK;
+}
+
+int elx_ipc_close(void* base) {
+    if (!base) return ELX_ERR_NULL;
+    const cudaError_t e = cudaIpcCloseMemHandle(base);
+    if (e != cudaSuccess) {
+        const int rc = record_cuda(e);
+        (void)cudaGetLastError();
+        return rc;
+    }
+    return ELX_OK;
+}
+
+int elx_peer_barrier(ElxPeerTable flags, uint32_t epoch, ElxCtl* ctl, int exchange_overflow, int timeout_ms,
+                     void* stream) {
+    const int rc = peer_table_ok(flags);
+    if (rc != ELX_OK) return rc;
+    if (ctl && !aligned(ctl, 16)) return ELX_ERR_ALIGN;
+    if (exchange_overflow && !ctl) return ELX_ERR_NULL;
+    if (timeout_ms <= 0 || epoch == 0) return ELX_ERR_ARG;
+    peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, epoch, ctl, exchange_overflow,
+                                                                      static_cast<uint64_t>(timeout_ms) * 1000000ull);
+    return record_cuda(cudaGetLastError());
+}
+
+int elx_pull_reduce_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                          ElxPeerTable grads, const int64_t* block_off, uint32_t* chunk_flags, ElxCtl* ctl,
+                          void* stream) {
+    if (!descs || !block_off) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (first < 0 || count < 0 || n_tiles < 0) return ELX_ERR_SIZE;
+    const int rc = peer_table_ok(grads);
+    if (rc != ELX_OK) return rc;
+    if (!aligned(descs, 8) || !aligned(block_off, 8) || (chunk_flags && !aligned(chunk_flags, 4)) ||
+        (ctl && !aligned(ctl, 16)))
+        return ELX_ERR_ALIGN;
+    if (count == 0 || n_tiles == 0) return ELX_OK;
+    PullArgs a;
+    memset(&a, 0, sizeof(a));
+    a.descs = descs;
+    a.chunk_flags = chunk_flags;
+    a.ctl = ctl;
+    a.grads = grads;
+    a.block_off = block_off;
+    a.first = first;
+    a.count = count;
+    a.n_tiles = n_tiles;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int grid = 0;
+    switch (dtype) {
+        case ELX_F16: {
+            static const int resident = resident_ctas(pull_reduce_kernel<ELX_F16>, 256);
+            grid = grid_for(n_tiles, capped(resident, g_tune.pull_ctas_per_sm));
+            if (grid < 0) return grid;
+            pull_reduce_kernel<ELX_F16><<<grid, 256, 0, s>>>(a);
+            break;
+        }
+        case ELX_BF16: {
+            static const int resident = resident_ctas(pull_reduce_kernel<ELX_BF16>, 256);
+            grid = grid_for(n_tiles, capped(resident, g_tune.pull_ctas_per_sm));
+            if (grid < 0) return grid;
+            pull_reduce_kernel<ELX_BF16><<<grid, 256, 0, s>>>(a);
+            break;
+        }
+        case ELX_F32: {
+            static const int resident = resident_ctas(pull_reduce_kernel<ELX_F32>, 256);
+            grid = grid_for(n_tiles, capped(resident, g_tune.pull_ctas_per_sm));
+            if (grid < 0) return grid;
+            pull_reduce_kernel<ELX_F32><<<grid, 256, 0, s>>>(a);
+            break;
+        }
+    }
+    return record_cuda(cudaGetLastError());
+}
+
+int elx_adam_multi_push(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                        const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl, ElxPeerTable gather,
+                        const int64_t* block_off, void* stream) {
+    if (!descs || !ctl || !block_off) return ELX_ERR_NULL;
+    if (n_groups > 0 && (!segs || !hyper)) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (first < 0 || count < 0 || n_tiles < 0 || n_groups < 0) return ELX_ERR_SIZE;
+    if (n_groups > kMaxGroups) return ELX_ERR_CAPACITY;
+    const int rc = peer_table_ok(gather);
+    if (rc != ELX_OK) return rc;
+    if (!aligned(descs, 8) || !aligned(ctl, 16) || !aligned(block_off, 8) || (segs && !aligned(segs, 8)) ||
+        (hyper && !aligned(hyper, 4)))
+        return ELX_ERR_ALIGN;
+    if (count == 0 || n_tiles == 0) return ELX_OK;
+    AdamArgs a;
+    memset(&a, 0, sizeof(a));
+    a.descs = descs;
+    a.segs = segs;
+    a.hyper = hyper;
+    a.ctl = ctl;
+    a.first = first;
+    a.count = count;
+    a.n_groups = n_groups;
+    a.n_tiles = n_tiles;
+    a.push = gather;
+    a.push_off = block_off;
     return launch_adam(a, dtype, static_cast<cudaStream_t>(stream));
 }
 

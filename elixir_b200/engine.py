@@ -217,6 +217,60 @@ class ChunkStepEngine:
         main.wait_stream(gather_stream)
         marks('gathered')
 
+    # ------------------------------------------------------------------ NVLink path
+
+    def enable_p2p(self, chunk_sizes: Sequence[int], timeout_ms: int = 20000):
+        """Allocate the peer-mapped slabs of the NVLink path: one gradient slab and one gather slab per rank,
+        each holding a block of ``chunk_sizes[k]`` elements for every registered chunk k, plus the barrier
+        flags.  ``grad_block(k)`` / ``gather_block(k)`` are this rank's blocks."""
+        from .peer import PeerBarrier, PeerBuffer
+        assert len(chunk_sizes) == self.n_chunks
+        offsets, total = [], 0
+        for k, size in enumerate(chunk_sizes):
+            if size != self.shards[k][0].numel() * self.world:
+                raise ValueError(f'chunk {k}: chunk size {size} is not world x shard size')
+            offsets.append(total)
+            total += (size + 15) // 16 * 16
+        self._p2p_sizes = list(chunk_sizes)
+        self._p2p_offsets = offsets
+        self.block_off = torch.tensor(offsets, dtype=torch.int64, device=self.device)
+        self.grad_slab = PeerBuffer(total, self.dtype, self.device, self.group)
+        self.gather_slab = PeerBuffer(total, self.dtype, self.device, self.group)
+        self.peer_barrier = PeerBarrier(self.device, self.group, timeout_ms)
+        return self
+
+    def grad_block(self, k: int) -> torch.Tensor:
+        return self.grad_slab.local[self._p2p_offsets[k]:self._p2p_offsets[k] + self._p2p_sizes[k]]
+
+    def gather_block(self, k: int) -> torch.Tensor:
+        return self.gather_slab.local[self._p2p_offsets[k]:self._p2p_offsets[k] + self._p2p_sizes[k]]
+
+    def step_sharded_p2p(self):
+        """Sharded step with both collectives fused into the kernels, over peer-mapped memory:
+
+            barrier            every rank's gradient blocks are written
+            pull reduce        one launch: rank average of this rank's slices, read from all ranks, + probe
+            barrier + agree    every rank is done reading (blocks may be rewritten); overflow word OR-ed
+            decision           elx_step_begin
+            update + push      one launch: fused Adam, refreshed parameters stored into every rank's gather block
+            barrier            every rank's pushes have landed: the gather blocks are complete
+
+        Six launches per step, no NCCL call, no host synchronisation."""
+        self.peer_barrier(self.ctl)
+        kernels.pull_reduce_multi(self.table, self.grad_slab.table, self.block_off, self.ctl,
+                                  chunk_flags=self.chunk_flags)
+        self.peer_barrier(self.ctl, exchange_overflow=self.sync_overflow)
+        norm_sq = None
+        if self.clipping:
+            kernels.grad_check_multi(self.table, None, chunk_l2sq=self.chunk_l2sq, total_l2sq=self.total_l2sq,
+                                     scratch=self._scratch)
+            dist.all_reduce(self.total_l2sq, group=self.group)
+            norm_sq = self.total_l2sq
+        kernels.step_begin(self.ctl, self.scaler.cfg, norm_sq)
+        kernels.adam_multi_push(self.table, self.ctl, self.gather_slab.table, self.block_off)
+        self.end_step()
+        self.peer_barrier(self.ctl)
+
     def step_from_host(self, host_grads: Sequence[torch.Tensor], host_params: Sequence[torch.Tensor]):
         """A whole step with host buffers on both ends: ``host_grads[k]`` (pinned, shard_size elements of
         the chunk dtype) holds the reduced gradients of shard k; ``host_params[k]`` (pinned) receives the

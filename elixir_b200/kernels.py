@@ -385,3 +385,38 @@ def adam_multi(table: ChunkTable, ctl: ControlBlock, first: int = 0, count: Opti
             _lib.get().elx_adam_multi(_ptr(table.descs_dev), first, count, table.tiles(first, count), table.code,
                                       _ptr(table.segs_dev), _ptr(table.hyper_dev), table.n_groups, ctl.ptr,
                                       _stream(table.descs_dev)), 'elx_adam_multi')
+
+
+def pull_reduce_multi(table: ChunkTable, grads_table, block_off: torch.Tensor, ctl: Optional[ControlBlock],
+                      chunk_flags: Optional[torch.Tensor] = None, first: int = 0, count: Optional[int] = None):
+    """NVLink pull reduce-scatter fused with the probe (``elx_pull_reduce_multi``).  ``grads_table`` is the
+    ``ElxPeerTable`` of the ranks' gradient slabs, ``block_off`` (int64, device) the element offset of each
+    chunk's block inside a slab."""
+    count = table.n_chunks - first if count is None else count
+    _check_tensor(block_off, 'block_off', torch.int64)
+    if block_off.numel() < table.n_chunks:
+        raise ValueError('block_off is shorter than the table')
+    if chunk_flags is not None:
+        _check_tensor(chunk_flags, 'chunk_flags', torch.int32)
+    with _DeviceGuard(table.descs_dev):
+        _lib.check(
+            _lib.get().elx_pull_reduce_multi(_ptr(table.descs_dev), first, count, table.tiles(first, count), table.code,
+                                             grads_table, _ptr(block_off), _ptr(chunk_flags),
+                                             ctl.ptr if ctl else None, _stream(table.descs_dev)),
+            'elx_pull_reduce_multi')
+
+
+def adam_multi_push(table: ChunkTable, ctl: ControlBlock, gather_table, block_off: torch.Tensor, first: int = 0,
+                    count: Optional[int] = None):
+    """Fused update whose refreshed low-precision tiles are also stored into every rank's gather slab
+    (``elx_adam_multi_push``)."""
+    count = table.n_chunks - first if count is None else count
+    _check_tensor(block_off, 'block_off', torch.int64)
+    if block_off.numel() < table.n_chunks:
+        raise ValueError('block_off is shorter than the table')
+    with _DeviceGuard(table.descs_dev):
+        _lib.check(
+            _lib.get().elx_adam_multi_push(_ptr(table.descs_dev), first, count, table.tiles(first, count), table.code,
+                                           _ptr(table.segs_dev), _ptr(table.hyper_dev), table.n_groups, ctl.ptr,
+                                           gather_table, _ptr(block_off), _stream(table.descs_dev)),
+            'elx_adam_multi_push')

@@ -127,6 +127,16 @@ typedef struct ElxChunkDesc {
     int32_t reserved;
 } ElxChunkDesc;
 
+/* Device addresses of one buffer per rank of a single-node group, as seen from THIS process: entry j
+ * is rank j's buffer mapped into this process (peer-mapped / IPC memory; entry `rank` is the local
+ * one).  All are 32-byte aligned. */
+#define ELX_MAX_PEERS 16
+typedef struct ElxPeerTable {
+    void*   base[ELX_MAX_PEERS];
+    int32_t rank;
+    int32_t world;
+} ElxPeerTable;
+
 /* ---- library ----------------------------------------------------------------------------- */
 
 /* ABI version of the loaded library (ELX_ABI_VERSION it was built with). */
@@ -148,6 +158,7 @@ const char* elx_last_cuda_error(void);
  *   "probe_unroll"       4 or 8 tiles in flight per probe CTA
  *   "adam_variant"       0 = direct 256-bit global accesses, 1 = bulk-copy (TMA) pipeline through
  *                        shared memory
+ *   "pull_ctas_per_sm"   cap on the grid of the pull reduce-scatter kernel, 0 = every resident CTA
  *   "math_mode"          1 = IEEE division and square root in the update, 2 = reciprocal
  *                        multiplies and approximate division (both within 1e-6 relative) */
 int elx_set_tuning(const char* name, int value);
@@ -253,6 +264,66 @@ int elx_grad_check_multi(const ElxChunkDesc* descs, int first, int count, int64_
 int elx_adam_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
                    const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl,
                    void* stream);
+
+/* ---- NVLink paths (single node, peer-mapped memory) -------------------------------------------- */
+
+/* Enable access from the current device to memory of `peer_device` (cudaDeviceEnablePeerAccess;
+ * "already enabled" is success). */
+int elx_enable_peer_access(int peer_device);
+
+/* The one place where the library allocates: a buffer of `bytes` on the current device that other
+ * processes of the box can map (cudaMalloc + cudaIpcGetMemHandle).  `handle` receives the 64-byte
+ * cudaIpcMemHandle_t to send to the peers.  Set-up time only; elx_peer_free releases the buffer. */
+int elx_peer_alloc(int64_t bytes, void** ptr, void* handle);
+int elx_peer_free(void* ptr);
+
+/* Map a buffer another process exported (a 64-byte cudaIpcMemHandle_t) for access from the CURRENT device
+ * of the calling process; *base receives the address of the exporter's allocation.  Open each handle
+ * once per process.  elx_ipc_close unmaps it. */
+int elx_ipc_open(const void* handle, void** base);
+int elx_ipc_close(void* base);
+
+/* Set-up check of a mapping: confirm that device_ptr is device memory known to this process and read one
+ * word from it with a blocking copy.  Synchronises; not for the step path. */
+int elx_peek_u32(const void* device_ptr, uint32_t* value);
+
+/*
+ * Barrier across the ranks of a box, on the device: rank r writes `epoch` into its slot of every
+ * rank's flag region (flags.base[j], 256 zero-initialised uint32 each) and waits until every rank
+ * has written `epoch` into r's region.  Everything a rank wrote to its peer-visible buffers before
+ * the barrier is visible to every rank after it.  With exchange_overflow != 0 each rank's
+ * ctl->found_inf rides along and ctl->found_inf becomes the OR over all ranks — the agreement the
+ * reference lacks (elixir/wrapper/optimizer.py:137-142 decides per rank).  Epochs must increase by 1
+ * per call, starting at 1, identically on all ranks.  The wait is bounded: after timeout_ms the kernel
+ * raises ELX_STAT_TIMEOUT in ctl->status and returns.
+ */
+int elx_peer_barrier(ElxPeerTable flags, uint32_t epoch, ElxCtl* ctl, int exchange_overflow, int timeout_ms,
+                     void* stream);
+
+/*
+ * Reduce-scatter by pulling, fused with the probe: for every descriptor c in [first, first + count)
+ * this rank's shard (descs[c].grad_param, n_shard elements) becomes the rank average of slice
+ * [rank * n_shard, (rank + 1) * n_shard) of chunk c's gradient block, read from every rank's slab
+ * (grads.base[j] + block_off[c] elements): sum over j in rank order of float(x_j) * (1/W) in fp32, rounded
+ * once to the chunk dtype; the first n_valid results are probed for inf/nan (chunk_flags[c],
+ * ctl->found_inf).  Replaces Chunk.reduce + update_extra_reduce_info (elixir/chunk/core/chunk.py:282-315,
+ * 345-356) for a group inside one NVLink domain; the reference's `x / W` then SUM differs from it
+ * only in where the roundings fall.  Call it between two elx_peer_barrier calls: one after every rank
+ * wrote its blocks, one before any rank overwrites them.
+ */
+int elx_pull_reduce_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                          ElxPeerTable grads, const int64_t* block_off, uint32_t* chunk_flags, ElxCtl* ctl,
+                          void* stream);
+
+/*
+ * elx_adam_multi fused with the parameter all-gather: every refreshed low-precision tile is also
+ * stored into every rank's gather slab at gather.base[j] + block_off[c] + rank * n_shard (elements),
+ * so that after the next elx_peer_barrier each rank holds the whole updated chunk
+ * (Chunk.__update_replica, chunk.py:475-482) without a separate all-gather pass.
+ */
+int elx_adam_multi_push(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                        const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl,
+                        ElxPeerTable gather, const int64_t* block_off, void* stream);
 
 /*
  * Single-shard convenience form with the hyper-parameters by value and one implicit segment

@@ -167,3 +167,49 @@ int elx_cast_copyback(const float* master, void* dst, int dtype, int64_t n, void
     orc_cast(master, dst, dtype, n);
     return ELX_OK;
 }
+
+/* The NVLink entry points have no host-memory form: they need peer-mapped device memory. */
+int elx_enable_peer_access(int peer_device) {
+    (void)peer_device;
+    return ELX_ERR_NODEVICE;
+}
+int elx_peer_barrier(ElxPeerTable flags, uint32_t epoch, ElxCtl* ctl, int exchange_overflow, int timeout_ms,
+                     void* stream) {
+    (void)flags; (void)epoch; (void)ctl; (void)exchange_overflow; (void)timeout_ms; (void)stream;
+    return ELX_ERR_NODEVICE;
+}
+int elx_pull_reduce_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                          ElxPeerTable grads, const int64_t* block_off, uint32_t* chunk_flags, ElxCtl* ctl,
+                          void* stream) {
+    (void)descs; (void)first; (void)count; (void)n_tiles; (void)dtype; (void)grads; (void)block_off;
+    (void)chunk_flags; (void)ctl; (void)stream;
+    return ELX_ERR_NODEVICE;
+}
+int elx_adam_multi_push(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                        const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl, ElxPeerTable gather,
+                        const int64_t* block_off, void* stream) {
+    (void)descs; (void)first; (void)count; (void)n_tiles; (void)dtype; (void)segs; (void)hyper; (void)n_groups;
+    (void)ctl; (void)gather; (void)block_off; (void)stream;
+    return ELX_ERR_NODEVICE;
+}
+int elx_ipc_open(const void* handle, void** base) {
+    (void)handle; (void)base;
+    return ELX_ERR_NODEVICE;
+}
+int elx_ipc_close(void* base) {
+    (void)base;
+    return ELX_ERR_NODEVICE;
+}
+int elx_peek_u32(const void* device_ptr, uint32_t* value) {
+    if (!device_ptr || !value) return ELX_ERR_NULL;
+    *value = *(const uint32_t*)device_ptr;
+    return ELX_OK;
+}
+int elx_peer_alloc(int64_t bytes, void** ptr, void* handle) {
+    (void)bytes; (void)ptr; (void)handle;
+    return ELX_ERR_NODEVICE;
+}
+int elx_peer_free(void* ptr) {
+    (void)ptr;
+    return ELX_ERR_NODEVICE;
+}

@@ -173,6 +173,18 @@ void orc_reduce_avg(const void* const* ranks, int world, int dtype, int64_t n, v
     }
 }
 
+/* The pull reduce-scatter of the NVLink path: sum over ranks, in rank order, of float(x_r) * (1/W) in
+ * fp32, rounded once to the chunk dtype (elx_pull_reduce_multi). */
+void orc_reduce_avg_f32acc(const void* const* ranks, int world, int dtype, int64_t n, void* out) {
+    const float inv_w = 1.0f / (float)world;
+#pragma omp parallel for
+    for (int64_t i = 0; i < n; ++i) {
+        float acc = 0.0f;
+        for (int r = 0; r < world; ++r) acc = fmaf(lowp_get(ranks[r], dtype, i), inv_w, acc);
+        lowp_set(out, dtype, i, acc);
+    }
+}
+
 /* ---- step decision + loss scaler (host copy of the control block) --------------------------- */
 
 void orc_ctl_init(ElxCtl* ctl, float initial_scale) {

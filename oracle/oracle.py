@@ -50,6 +50,7 @@ def lib():
         L.orc_l2sq.restype, L.orc_l2sq.argtypes = C.c_double, [p, i, i64]
         L.orc_cast.restype, L.orc_cast.argtypes = None, [p, p, i, i64]
         L.orc_reduce_avg.restype, L.orc_reduce_avg.argtypes = None, [p, i, i, i64, p]
+        L.orc_reduce_avg_f32acc.restype, L.orc_reduce_avg_f32acc.argtypes = None, [p, i, i, i64, p]
         L.orc_ctl_init.restype, L.orc_ctl_init.argtypes = None, [p, f]
         L.orc_step_begin.restype, L.orc_step_begin.argtypes = None, [p, ElxScalerCfg, p]
         for name in ('orc_adam_f32', 'orc_adam_f64'):
@@ -94,6 +95,14 @@ def reduce_avg(rank_tensors):
     out = torch.empty_like(rank_tensors[0])
     arr = (C.c_void_p * len(rank_tensors))(*[t.data_ptr() for t in rank_tensors])
     lib().orc_reduce_avg(arr, len(rank_tensors), _CODES[out.dtype], out.numel(), _cpu(out))
+    return out
+
+
+def reduce_avg_f32acc(rank_tensors):
+    """The NVLink pull reduce: fp32 accumulation of x_r * (1/W) in rank order, one rounding."""
+    out = torch.empty_like(rank_tensors[0])
+    arr = (C.c_void_p * len(rank_tensors))(*[t.data_ptr() for t in rank_tensors])
+    lib().orc_reduce_avg_f32acc(arr, len(rank_tensors), _CODES[out.dtype], out.numel(), _cpu(out))
     return out
 
 

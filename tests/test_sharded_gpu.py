@@ -91,6 +91,108 @@ def _worker(rank, world, port):
     dist.destroy_process_group()
 
 
+def _p2p_worker(rank, world, port):
+    """The NVLink path: pull reduce-scatter + probe, overflow agreement inside the barrier, fused update with
+    push all-gather — no NCCL collective in the step."""
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE='0')
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, 'tests'))
+    import torch.distributed as dist
+    from _util import bits_equal, close_1e6
+    from elixir_b200 import kernels as K
+    from elixir_b200.engine import ChunkStepEngine
+    from elixir_b200.scaler import DynamicGradScaler
+    from oracle import oracle as orc
+    torch.cuda.set_device(rank)
+    dev = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    dtype, scale = torch.float16, 256.0
+    chunk_sizes = [world * 4096 * 40, world * (4096 + 16), world * 4096 * 5, world * 24]
+    used = [chunk_sizes[0], chunk_sizes[1], chunk_sizes[2] // 2 + 7, 9]
+    engine = ChunkStepEngine(dev, dtype, DynamicGradScaler(initial_scale=scale, hysteresis=1, growth_interval=3),
+                             process_group=dist.group.WORLD)
+    host = orc.ChunkSet(dtype)
+    host_ctl = orc.new_ctl(scale)
+    hypers = [K.hyper(weight_decay=0.01)]
+    host_state = []
+    for c, (C, u) in enumerate(zip(chunk_sizes, used)):
+        S = C // world
+        gen = torch.Generator().manual_seed(c)
+        full = torch.randn(C, generator=gen) * 0.02
+        full[u:] = 0
+        mine = full[rank * S:(rank + 1) * S].clone()
+        nv = max(0, min(S, u - rank * S))
+        lowp = torch.zeros(S, dtype=dtype)
+        host.add_chunk(mine, torch.zeros(S), torch.zeros(S), lowp, nv, [(0, nv, 0)] if nv else [])
+        host_state.append((mine, lowp, nv))
+        engine.add_shard(mine.to(dev), torch.zeros(S, dtype=dtype, device=dev), nv, [(0, nv, 0)] if nv else [])
+    engine.finalize()
+    engine.set_hyper(hypers)
+    engine.enable_p2p(chunk_sizes, timeout_ms=5000)
+
+    def fill(step):
+        per_rank = []
+        for c, C in enumerate(chunk_sizes):
+            rank_grads = []
+            for r in range(world):
+                gen = torch.Generator().manual_seed(1000 * step + 10 * c + r)
+                g = (torch.randn(C, generator=gen) * 1e-3 * host_ctl.scale).to(dtype)
+                if step == 2 and c == 1 and r == world - 1:
+                    g[5] = float('inf')    # lands in rank 0's shard only
+                rank_grads.append(g)
+            per_rank.append(rank_grads)
+            engine.grad_block(c).copy_(rank_grads[rank])
+        return per_rank
+
+    # the pull alone: bit-exact against the oracle's fp32-accumulated average
+    per_rank = fill(0)
+    engine.peer_barrier(engine.ctl)
+    K.pull_reduce_multi(engine.table, engine.grad_slab.table, engine.block_off, engine.ctl,
+                        chunk_flags=engine.chunk_flags)
+    engine.peer_barrier(engine.ctl)
+    torch.cuda.synchronize()
+    for c, C in enumerate(chunk_sizes):
+        S = C // world
+        want = orc.reduce_avg_f32acc([g[rank * S:(rank + 1) * S].contiguous() for g in per_rank[c]])
+        assert bits_equal(engine.shards[c][3], want), (rank, c)
+    assert engine.chunk_flags.sum().item() == 0
+
+    for step in range(5):
+        per_rank = fill(step)
+        engine.step_sharded_p2p()
+        torch.cuda.synchronize()
+        for c, C in enumerate(chunk_sizes):
+            S = C // world
+            host_state[c][1].copy_(orc.reduce_avg_f32acc([g[rank * S:(rank + 1) * S].contiguous()
+                                                          for g in per_rank[c]]))
+        any_inf = step == 2
+        if any_inf:
+            host_ctl.found_inf = 1    # agreement: every rank skips
+        skipped = host.step(host_ctl, engine.scaler.cfg, hypers, probe=True, f64=True)
+        ctl = engine.read_control()
+        assert ctl.status == 0, (step, rank, ctl.status)
+        assert bool(ctl.skip) == skipped == any_inf, (step, rank)
+        assert (ctl.scale, ctl.step) == (host_ctl.scale, host_ctl.step)
+        for c, C in enumerate(chunk_sizes):
+            S = C // world
+            ok, ratio = close_1e6(engine.shards[c][0], host_state[c][0].double(), rtol=2e-6)
+            assert ok, (step, rank, c, ratio)
+            mine16 = engine.shards[c][3]
+            others = [torch.empty_like(mine16) for _ in range(world)]
+            dist.all_gather(others, mine16)
+            assert bits_equal(engine.gather_block(c), torch.cat(others)), (step, rank, c)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('world', [2, 4])
+def test_sharded_step_p2p_kernels(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f'needs {world} GPUs')
+    mp.spawn(_p2p_worker, args=(world, 29820 + world), nprocs=world)
+
+
 @pytest.mark.parametrize('world', [2, 4])
 def test_sharded_step_nccl(world):
     if torch.cuda.device_count() < world:
