@@ -19,6 +19,7 @@ def _worker(rank, world, port):
     sys.path.insert(0, os.path.join(ROOT, 'tests'))
     import torch.distributed as dist
     from _util import bits_equal, close_1e6
+    from elixir_b200 import comm
     from elixir_b200 import kernels as K
     from elixir_b200.engine import ChunkStepEngine
     from elixir_b200.scaler import DynamicGradScaler
@@ -62,13 +63,24 @@ def _worker(rank, world, port):
                 rank_grads.append(g)
             per_rank.append(rank_grads)
             blocks.append(rank_grads[rank].to(dev))
-        engine.step_sharded(blocks, gather)
-        torch.cuda.synchronize()
-        # oracle: the reference's average (divide in fp16, then sum) of every rank's block, this rank's slice
+        # NCCL's fp16 summation order is its own, so parity of the step is defined GIVEN the reduced gradients:
+        # capture them with the same collective first, then run the pipelined step on the same inputs
+        reduced = []
         for c, C in enumerate(chunk_sizes):
             S = C // world
-            avg = orc.reduce_avg([g[rank * S:(rank + 1) * S].contiguous() for g in per_rank[c]])
-            host_state[c][1].copy_(avg)
+            out = torch.empty(S, dtype=dtype, device=dev)
+            comm.reduce_scatter_avg(out, blocks[c].clone(), dist.group.WORLD)
+            reduced.append(out.cpu())
+            # ... and they agree with the reference's divide-then-sum to fp16 rounding
+            want = orc.reduce_avg([g[rank * S:(rank + 1) * S].contiguous() for g in per_rank[c]])
+            finite = torch.isfinite(want.float()) & torch.isfinite(reduced[c].float())
+            assert torch.equal(torch.isfinite(want.float()), torch.isfinite(reduced[c].float()))
+            err = (reduced[c].float() - want.float()).abs()[finite]
+            assert float(err.max()) <= 2 * 2.0**-10 * float(want.float().abs()[finite].max())
+        engine.step_sharded(blocks, gather)
+        torch.cuda.synchronize()
+        for c in range(len(chunk_sizes)):
+            host_state[c][1].copy_(reduced[c])
         any_inf = step == 2
         if any_inf:
             host_ctl.found_inf = 1    # agreement: every rank skips, also those whose shards are clean
@@ -186,7 +198,7 @@ def _p2p_worker(rank, world, port):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize('world', [2, 4])
+@pytest.mark.parametrize('world', [2, 4, 8])
 def test_sharded_step_p2p_kernels(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f'needs {world} GPUs')
