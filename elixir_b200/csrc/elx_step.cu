@@ -1194,15 +1194,19 @@ struct PullArgs {
     int64_t n_tiles;
 };
 
-template <int DT>
+// kWorld > 0: the group size is a compile-time constant, so the loads from all ranks are issued back to
+// back before the first one is consumed (kWorld x 32 bytes in flight per thread); 0 = any group size.
+template <int DT, int kWorld>
 __global__ void __launch_bounds__(256) pull_reduce_kernel(const __grid_constant__ PullArgs a) {
-    constexpr int EPT = 16;
+    constexpr int EPT = 16;                                      // consecutive elements per thread
+    constexpr int WORDS = EPT * Lp<DT>::kBytes / 4;              // 8 (16-bit) or 16 (fp32)
     using T = typename Lp<DT>::T;
     __shared__ ChunkCursor s_cur;
     cursor_reset(s_cur);
     const ElxChunkDesc* __restrict__ descs = a.descs;
     const int64_t tile_lo = descs[a.first].tile_begin;
-    const int world = a.grads.world, rank = a.grads.rank;
+    const int world = kWorld > 0 ? kWorld : a.grads.world;
+    const int rank = a.grads.rank;
     const float inv_w = 1.0f / static_cast<float>(world);
     const int lane = threadIdx.x & 31;
     bool bad_desc = false;
@@ -1222,24 +1226,59 @@ __global__ void __launch_bounds__(256) pull_reduce_kernel(const __grid_constant_
         uint32_t bad = 0;
         if ((e1 - e0 == kTile) && (all_valid || none_valid) && (src0 & 15) == 0 &&
             (reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
+            const int64_t mine = e0 + static_cast<int64_t>(threadIdx.x) * EPT;
             float acc[EPT];
 #pragma unroll
             for (int i = 0; i < EPT; ++i) acc[i] = 0.0f;
-            for (int j = 0; j < world; ++j) {
-                float g[EPT];
-                load_lowp<DT, EPT>(a.grads.base[j], src0 + e0, g);
-#pragma unroll
-                for (int i = 0; i < EPT; ++i) acc[i] = fmaf(g[i], inv_w, acc[i]);
-            }
-            store_lowp<DT, EPT>(dst, e0, acc);
-            if (all_valid) {
+            auto accumulate = [&](const uint32_t (&w)[WORDS]) {
                 if constexpr (DT == ELX_F32) {
 #pragma unroll
-                    for (int i = 0; i < EPT; ++i) bad |= Lp<DT>::nonfinite_word(__float_as_uint(acc[i]));
+                    for (int i = 0; i < WORDS; ++i) acc[i] = fmaf(__uint_as_float(w[i]), inv_w, acc[i]);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < EPT / 2; ++i) bad |= Lp<DT>::nonfinite_word(Lp<DT>::pack2(acc[2 * i], acc[2 * i + 1]));
+                    for (int i = 0; i < WORDS; ++i) {
+                        const float2 f = Lp<DT>::unpack2(w[i]);
+                        acc[2 * i] = fmaf(f.x, inv_w, acc[2 * i]);
+                        acc[2 * i + 1] = fmaf(f.y, inv_w, acc[2 * i + 1]);
+                    }
                 }
+            };
+            if constexpr (kWorld > 0) {
+                uint32_t raw[kWorld][WORDS];
+#pragma unroll
+                for (int j = 0; j < kWorld; ++j)
+                    ld_words<WORDS>(static_cast<const char*>(a.grads.base[j]) + (src0 + mine) * Lp<DT>::kBytes, raw[j]);
+                // keep every rank's words live until all loads are issued: the empty asm statements are ordered
+                // after the (volatile) loads, so the compiler cannot fold a load into its first use
+#pragma unroll
+                for (int j = 0; j < kWorld; ++j) {
+#pragma unroll
+                    for (int i = 0; i < WORDS; i += 8)
+                        asm volatile(""
+                                     : "+r"(raw[j][i]), "+r"(raw[j][i + 1]), "+r"(raw[j][i + 2]), "+r"(raw[j][i + 3]),
+                                       "+r"(raw[j][i + 4]), "+r"(raw[j][i + 5]), "+r"(raw[j][i + 6]), "+r"(raw[j][i + 7]));
+                }
+#pragma unroll
+                for (int j = 0; j < kWorld; ++j) accumulate(raw[j]);    // rank order
+            } else {
+                for (int j = 0; j < world; ++j) {
+                    uint32_t raw[WORDS];
+                    ld_words<WORDS>(static_cast<const char*>(a.grads.base[j]) + (src0 + mine) * Lp<DT>::kBytes, raw);
+                    accumulate(raw);
+                }
+            }
+            uint32_t out[WORDS];
+            if constexpr (DT == ELX_F32) {
+#pragma unroll
+                for (int i = 0; i < WORDS; ++i) out[i] = __float_as_uint(acc[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < WORDS; ++i) out[i] = Lp<DT>::pack2(acc[2 * i], acc[2 * i + 1]);
+            }
+            st_words<WORDS>(static_cast<char*>(dst) + mine * Lp<DT>::kBytes, out);
+            if (all_valid) {
+#pragma unroll
+                for (int i = 0; i < WORDS; ++i) bad |= Lp<DT>::nonfinite_word(out[i]);
             }
         } else {
             T* out = static_cast<T*>(dst);
@@ -1260,6 +1299,28 @@ __global__ void __launch_bounds__(256) pull_reduce_kernel(const __grid_constant_
     }
     const unsigned ballot_desc = __ballot_sync(0xFFFFFFFFu, bad_desc);
     if (ballot_desc && lane == 0 && a.ctl) atomicOr(&a.ctl->status, ELX_STAT_BAD_DESC);
+}
+
+int grid_for(int64_t work_items, int ctas_per_sm);
+int capped(int resident, int cap);
+
+template <int DT, int kWorld>
+int launch_pull_inst(const PullArgs& a, cudaStream_t s) {
+    static const int resident = resident_ctas(pull_reduce_kernel<DT, kWorld>, 256);
+    const int grid = grid_for(a.n_tiles, capped(resident, g_tune.pull_ctas_per_sm));
+    if (grid < 0) return grid;
+    pull_reduce_kernel<DT, kWorld><<<grid, 256, 0, s>>>(a);
+    return record_cuda(cudaGetLastError());
+}
+
+template <int DT>
+int launch_pull(const PullArgs& a, cudaStream_t s) {
+    switch (a.grads.world) {
+        case 2: return launch_pull_inst<DT, 2>(a, s);
+        case 4: return launch_pull_inst<DT, 4>(a, s);
+        case 8: return launch_pull_inst<DT, 8>(a, s);
+    }
+    return launch_pull_inst<DT, 0>(a, s);
 }
 
 // Flag region of one rank (peer-mapped): for each parity of the epoch and each sender, {epoch, word}.
@@ -1397,7 +1458,7 @@ int grid_for(int64_t work_items, int ctas_per_sm) {
     return static_cast<int>(g);
 }
 
-inline int capped(int resident, int cap) { return cap > 0 && cap < resident ? cap : resident; }
+int capped(int resident, int cap) { return cap > 0 && cap < resident ? cap : resident; }
 
 template <int DT, int EPT, int MATH, int MINB>
 int launch_adam_inst(const AdamArgs& a, cudaStream_t s) {
@@ -1894,31 +1955,12 @@ int elx_pull_reduce_multi(const ElxChunkDesc* descs, int first, int count, int64
     a.count = count;
     a.n_tiles = n_tiles;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    int grid = 0;
     switch (dtype) {
-        case ELX_F16: {
-            static const int resident = resident_ctas(pull_reduce_kernel<ELX_F16>, 256);
-            grid = grid_for(n_tiles, capped(resident, g_tune.pull_ctas_per_sm));
-            if (grid < 0) return grid;
-            pull_reduce_kernel<ELX_F16><<<grid, 256, 0, s>>>(a);
-            break;
-        }
-        case ELX_BF16: {
-            static const int resident = resident_ctas(pull_reduce_kernel<ELX_BF16>, 256);
-            grid = grid_for(n_tiles, capped(resident, g_tune.pull_ctas_per_sm));
-            if (grid < 0) return grid;
-            pull_reduce_kernel<ELX_BF16><<<grid, 256, 0, s>>>(a);
-            break;
-        }
-        case ELX_F32: {
-            static const int resident = resident_ctas(pull_reduce_kernel<ELX_F32>, 256);
-            grid = grid_for(n_tiles, capped(resident, g_tune.pull_ctas_per_sm));
-            if (grid < 0) return grid;
-            pull_reduce_kernel<ELX_F32><<<grid, 256, 0, s>>>(a);
-            break;
-        }
+        case ELX_F16: return launch_pull<ELX_F16>(a, s);
+        case ELX_BF16: return launch_pull<ELX_BF16>(a, s);
+        case ELX_F32: return launch_pull<ELX_F32>(a, s);
     }
-    return record_cuda(cudaGetLastError());
+    return ELX_ERR_DTYPE;
 }
 
 int elx_adam_multi_push(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,

@@ -103,7 +103,7 @@ def _worker(rank, world, port):
     dist.destroy_process_group()
 
 
-def _p2p_worker(rank, world, port):
+def _p2p_worker(rank, world, port, dtype_name='float16'):
     """The NVLink path: pull reduce-scatter + probe, overflow agreement inside the barrier, fused update with
     push all-gather — no NCCL collective in the step."""
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
@@ -119,7 +119,7 @@ def _p2p_worker(rank, world, port):
     torch.cuda.set_device(rank)
     dev = torch.device('cuda', rank)
     dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
-    dtype, scale = torch.float16, 256.0
+    dtype, scale = getattr(torch, dtype_name), 256.0
     chunk_sizes = [world * 4096 * 40, world * (4096 + 16), world * 4096 * 5, world * 24]
     used = [chunk_sizes[0], chunk_sizes[1], chunk_sizes[2] // 2 + 7, 9]
     engine = ChunkStepEngine(dev, dtype, DynamicGradScaler(initial_scale=scale, hysteresis=1, growth_interval=3),
@@ -203,6 +203,13 @@ def test_sharded_step_p2p_kernels(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f'needs {world} GPUs')
     mp.spawn(_p2p_worker, args=(world, 29820 + world), nprocs=world)
+
+
+def test_sharded_step_p2p_kernels_bf16():
+    """The OPT-66B configuration's dtype (bf16 chunks) through the same NVLink path, on two ranks."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    mp.spawn(_p2p_worker, args=(2, 29830, 'bfloat16'), nprocs=2)
 
 
 @pytest.mark.parametrize('world', [2, 4])
