@@ -308,6 +308,11 @@ class ChunkTable:
         self.tile_begin.append(self.tile_begin[-1] + n_tiles(n))
         return len(self._descs) - 1
 
+    def _segs_of(self, index: int):
+        """(begin, end, group) of descriptor ``index`` as registered (neighbours merged)."""
+        d = self._descs[index]
+        return [(s.begin, s.end, s.group) for s in self._segs[d.seg_first:d.seg_first + d.seg_count]]
+
     def finalize(self):
         self.descs_dev = _struct_array_to_tensor((ElxChunkDesc * len(self._descs))(*self._descs), self.device)
         self.segs_dev = _struct_array_to_tensor((ElxSeg * len(self._segs))(*self._segs), self.device)

@@ -205,6 +205,56 @@ def test_sharded_step_p2p_kernels(world):
     mp.spawn(_p2p_worker, args=(world, 29820 + world), nprocs=world)
 
 
+def _wrapper_worker(rank, world, port):
+    """ElixirModule + ElixirOptimizer over NCCL with a real forward / backward, against plain data-parallel
+    training (gradients averaged by hand, torch.optim.AdamW): the reference's test/wrapper/test_optimizer.py
+    in spirit, tolerance included."""
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE='0')
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, 'tests'))
+    import copy
+    import torch.distributed as dist
+    import torch.nn as nn
+    from elixir_b200.optim import HybridAdam
+    from elixir_b200.wrapper import ElixirModule, ElixirOptimizer, simple_plan
+    torch.cuda.set_device(rank)
+    dev = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    torch.manual_seed(0)
+    plain = nn.Sequential(nn.Linear(40, 72), nn.GELU(), nn.Linear(72, 72), nn.GELU(), nn.Linear(72, 6)).to(dev)
+    wrapped = copy.deepcopy(plain)
+    opt = torch.optim.AdamW(plain.parameters(), lr=1e-2, betas=(0.875, 0.99609375), weight_decay=0.0)
+    sr = simple_plan(wrapped, world, split_number=3, unified_dtype=torch.float)
+    inner = HybridAdam(wrapped.parameters(), lr=1e-2, betas=(0.875, 0.99609375), weight_decay=0.0)
+    emodel = ElixirModule(wrapped, sr, dist.group.WORLD, dtype=torch.float)
+    eopt = ElixirOptimizer(emodel, inner)
+    for step in range(3):
+        torch.manual_seed(100 * step + rank)    # every rank its own batch
+        x = torch.randn(16, 40, device=dev)
+        opt.zero_grad()
+        plain(x).pow(2).mean().backward()
+        for p in plain.parameters():
+            dist.all_reduce(p.grad)
+            p.grad /= world
+        opt.step()
+        eopt.zero_grad()
+        eopt.backward(emodel(x).pow(2).mean())
+        eopt.step()
+    got = emodel.state_dict()
+    for name, ref in plain.state_dict().items():
+        torch.testing.assert_close(got[name].to(dev), ref, rtol=2e-6, atol=2e-5)
+    assert eopt.engine.read_control().status == 0
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_wrapper_data_parallel_training_matches_plain_ddp():
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    mp.spawn(_wrapper_worker, args=(2, 29840), nprocs=2)
+
+
 def test_sharded_step_p2p_kernels_bf16():
     """The OPT-66B configuration's dtype (bf16 chunks) through the same NVLink path, on two ranks."""
     if torch.cuda.device_count() < 2:

@@ -164,3 +164,42 @@ def test_init_step_reproduces_the_reference_side_effects(cuda, single_group):
     after = emodel.state_dict()
     for n, ref in before.items():
         torch.testing.assert_close(after[n].to(cuda), ref * (1 - 1e-2 * 0.1), rtol=1e-6, atol=1e-9)
+
+
+def test_lr_schedule_and_param_groups_are_picked_up_every_step(cuda, oracle, single_group):
+    """Hyper-parameters are re-read from param_groups on every step (lr schedulers mutate them) and groups with
+    different settings update their own ranges of the same chunks."""
+    from elixir_b200 import kernels as K
+    from elixir_b200.optim import HybridAdam
+    from elixir_b200.wrapper import ElixirModule, ElixirOptimizer, simple_plan
+    torch.manual_seed(5)
+    model = Mlp().to(cuda)
+    decay = [p for n, p in model.named_parameters() if n.endswith('weight')]
+    no_decay = [p for n, p in model.named_parameters() if n.endswith('bias')]
+    inner = HybridAdam([dict(params=decay, weight_decay=0.05), dict(params=no_decay, weight_decay=0.0, lr=2e-3)], lr=1e-3)
+    sr = simple_plan(model, 1, split_number=2, unified_dtype=torch.float16)
+    emodel = ElixirModule(model, sr, single_group, dtype=torch.float16)
+    eopt = ElixirOptimizer(emodel, inner, initial_scale=256.0)
+    sched = torch.optim.lr_scheduler.LambdaLR(inner, lambda step: 1.0 / (1 + step))
+    host_ctl = oracle.new_ctl(256.0)
+    chunks = emodel.param_chunks
+    seg_lists = [[(b, e, g) for b, e, g in eopt.engine.table._segs_of(i)] for i in range(len(chunks))]
+    assert any(len({g for _, _, g in segs}) == 2 for segs in seg_lists)    # both groups inside one chunk
+    for step in range(3):
+        x = torch.randn(8, 48, device=cuda)
+        eopt.zero_grad()
+        eopt.backward(emodel(x))
+        hypers = [K.hyper(lr=g['lr'], weight_decay=g['weight_decay']) for g in inner.param_groups]
+        cs = oracle.ChunkSet(torch.float16)
+        masters = []
+        for i in range(len(chunks)):
+            m, e1, e2, lowp, nv = (t.cpu().clone() if torch.is_tensor(t) else t for t in eopt.engine.shards[i])
+            cs.add_chunk(m, e1, e2, lowp, nv, seg_lists[i])
+            masters.append(m)
+        eopt.step()
+        sched.step()
+        cs.step(host_ctl, eopt.grad_scaler.cfg, hypers, probe=True, f64=True)
+        for i in range(len(chunks)):
+            ok, ratio = close_1e6(eopt.engine.shards[i][0], masters[i].double())
+            assert ok, (step, i, ratio)
+    assert inner.param_groups[0]['lr'] < 1e-3
