@@ -232,8 +232,7 @@ def run_ours(args):
 
     def one_step(record=False):
         if world == 1:
-            for c in range(n_chunks):
-                engine.land(c, grad_blocks[c])
+            engine.land_all(grad_blocks, streams=args.land_streams)
             engine.begin_step()
             if record:
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -566,6 +565,8 @@ def main():
     ap.add_argument('--seed', type=int, default=0)
     ap.add_argument('--collective', default='p2p', choices=['p2p', 'nccl'],
                     help='N > 1: collectives fused into the kernels over peer-mapped NVLink memory, or NCCL')
+    ap.add_argument('--land-streams', type=int, default=2,
+                    help='N = 1: side streams the per-chunk landing launches alternate on')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--e2e-steps', type=int, default=10)

@@ -76,10 +76,11 @@ class Chunk:
         self._my_block = rcache.get_private_block(chunk_size, chunk_dtype) if rcache_fused else None
         self.is_replica = True
 
-        default_device = rcache.device_type if rcache.device_type != 'cuda' or not torch.cuda.is_available() else \
-            torch.device('cuda', torch.cuda.current_device())
-        temp_device = torch.device(temp_device) if temp_device is not None else torch.device(default_device)
-        shard_device = torch.device(shard_device) if shard_device is not None else torch.device(default_device)
+        default_device = torch.device(rcache.device_type)
+        if default_device.type == 'cuda' and default_device.index is None:
+            default_device = torch.device('cuda', torch.cuda.current_device())
+        temp_device = torch.device(temp_device) if temp_device is not None else default_device
+        shard_device = torch.device(shard_device) if shard_device is not None else default_device
         if rcache_fused:
             self.chunk_temp = self._my_block.payload
             self.chunk_temp.zero_()
@@ -324,6 +325,13 @@ class Chunk:
                                     **self._norm_args())
         self._probed = True
         self.is_replica = False
+
+    def defer_reduce(self):
+        """NVLink step: all gradients of the chunk are in its replicated block; leave them there (the
+        optimizer pulls every rank's slice at step time) and keep the block."""
+        assert not self.is_init and self.is_replica and self.reduce_check
+        self._update_tensors_state(TensorState.HOLD)
+        self._probed = True
 
     def reduce_chunk(self, always_fp32: bool = False, sync: bool = True) -> Optional[TensorBlock]:
         assert not self.is_init

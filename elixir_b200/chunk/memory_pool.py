@@ -20,10 +20,12 @@ class TensorBlock:
     total_count: int = 0
     block_type = 'block'
 
-    def __init__(self, numel: int, dtype: torch.dtype, device_type, payload: torch.Tensor = None) -> None:
+    def __init__(self, numel: int, dtype: torch.dtype, device_type, payload: torch.Tensor = None,
+                 slab_offset: int = None) -> None:
         self.block_id = TensorBlock.total_count
         TensorBlock.total_count += 1
         self.device_type = device_type
+        self.slab_offset = slab_offset    # element offset inside the pool's slab, when the pool has one
         self.payload = payload if payload is not None else torch.empty((numel,), dtype=dtype, device=device_type)
         assert self.payload.numel() == numel and self.payload.dtype == dtype
         self.memo_occ = numel * self.payload.element_size()
@@ -61,8 +63,13 @@ class PrivateBlock(TensorBlock):
 
 class MemoryPool:
 
-    def __init__(self, device_type) -> None:
+    def __init__(self, device_type, slab_factory=None) -> None:
+        """``slab_factory(numel, dtype)``, when given, returns an object with a ``local`` tensor out of which
+        EVERY block (public and private) is carved — used to place the replica cache in peer-mapped memory
+        (``elixir_b200.peer.PeerBuffer``) for the NVLink step."""
         self.device_type = device_type
+        self.slab_factory = slab_factory
+        self.slab = None
         self.public_space = 0
         self.public_block_size = 0
         self.public_dtype = None
@@ -87,14 +94,27 @@ class MemoryPool:
         self.public_block_size = public_block_size
         self.public_free_blocks = []
         self.public_used_blocks = set()
+        private_block_list = list(private_block_list)
+        pad = lambda n: (n + 15) // 16 * 16
+        cursor = 0
+        if self.slab_factory is not None:
+            assert all(r.dtype == public_dtype for r in private_block_list), 'one dtype per slab'
+            total = public_block_number * pad(public_block_size) + sum(pad(r.numel) for r in private_block_list)
+            self.slab = self.slab_factory(max(total, 16), public_dtype)
         if public_block_number > 0:
-            self._public_slab = torch.empty(public_block_number * public_block_size,
-                                            dtype=public_dtype,
-                                            device=self.device_type)
+            if self.slab is not None:
+                self._public_slab = self.slab.local
+                stride = pad(public_block_size)
+            else:
+                self._public_slab = torch.empty(public_block_number * public_block_size, dtype=public_dtype,
+                                                device=self.device_type)
+                stride = public_block_size
             for i in range(public_block_number):
-                view = self._public_slab[i * public_block_size:(i + 1) * public_block_size]
-                self.public_free_blocks.append(PublicBlock(public_block_size, public_dtype, self.device_type, view))
-            self.public_space = self._public_slab.numel() * self._public_slab.element_size()
+                view = self._public_slab[i * stride:i * stride + public_block_size]
+                self.public_free_blocks.append(
+                    PublicBlock(public_block_size, public_dtype, self.device_type, view, slab_offset=i * stride))
+            cursor = public_block_number * stride
+            self.public_space = public_block_number * public_block_size * self._public_slab.element_size()
         self.public_free_cnt = public_block_number
         self.public_used_cnt = 0
 
@@ -102,7 +122,12 @@ class MemoryPool:
         self.private_lookup_dict = defaultdict(list)
         self.private_space = 0
         for require in private_block_list:
-            block = PrivateBlock(require.numel, require.dtype, self.device_type)
+            if self.slab is not None:
+                view = self.slab.local[cursor:cursor + require.numel]
+                block = PrivateBlock(require.numel, require.dtype, self.device_type, view, slab_offset=cursor)
+                cursor += pad(require.numel)
+            else:
+                block = PrivateBlock(require.numel, require.dtype, self.device_type)
             self.private_space += block.memo_occ
             self.private_blocks.append(block)
             self.private_lookup_dict[require].append(block)

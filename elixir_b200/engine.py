@@ -99,6 +99,26 @@ class ChunkStepEngine:
         lowp, n_valid = self.shards[index][3], self.shards[index][4]
         kernels.reduce_epilogue(src, lowp, n_valid=n_valid, flag=self.chunk_flags[index:index + 1], ctl=self.ctl)
 
+    def land_all(self, srcs: Sequence[torch.Tensor], streams: int = 2):
+        """``land`` for every shard, issued round-robin on ``streams`` side streams so that the tail of one
+        launch overlaps the ramp-up of the next (the launches are independent: different shards, and the flag
+        words are only ever raised).  The current stream waits for all of them."""
+        assert len(srcs) == self.n_chunks
+        main = torch.cuda.current_stream(self.device)
+        if streams <= 1 or self.device.type != 'cuda':
+            for k, src in enumerate(srcs):
+                self.land(k, src)
+            return
+        if getattr(self, '_land_streams', None) is None or len(self._land_streams) != streams:
+            self._land_streams = [torch.cuda.Stream(self.device) for _ in range(streams)]
+        for st in self._land_streams:
+            st.wait_stream(main)
+        for k, src in enumerate(srcs):
+            with torch.cuda.stream(self._land_streams[k % streams]):
+                self.land(k, src)
+        for st in self._land_streams:
+            main.wait_stream(st)
+
     def probe(self, first: int = 0, count: Optional[int] = None):
         """Probe gradients that were written straight into the shards."""
         kernels.grad_check_multi(self.table, self.ctl, chunk_flags=self.chunk_flags, first=first, count=count)
@@ -236,6 +256,20 @@ class ChunkStepEngine:
         self.block_off = torch.tensor(offsets, dtype=torch.int64, device=self.device)
         self.grad_slab = PeerBuffer(total, self.dtype, self.device, self.group)
         self.gather_slab = PeerBuffer(total, self.dtype, self.device, self.group)
+        self.peer_barrier = PeerBarrier(self.device, self.group, timeout_ms)
+        return self
+
+    def attach_p2p(self, slab, block_offsets: Sequence[int], timeout_ms: int = 20000):
+        """NVLink path over ONE existing peer-mapped slab (a replica cache): block k of every rank, at element
+        offset ``block_offsets[k]``, holds that rank's gradients of chunk k before the step and receives the
+        gathered parameters after it.  Rank r only ever reads and writes slice r of the other ranks' blocks, so
+        sharing the slab between the two directions needs no extra ordering."""
+        from .peer import PeerBarrier
+        assert len(block_offsets) == self.n_chunks
+        self._p2p_sizes = [self.shards[k][0].numel() * self.world for k in range(self.n_chunks)]
+        self._p2p_offsets = list(block_offsets)
+        self.block_off = torch.tensor(self._p2p_offsets, dtype=torch.int64, device=self.device)
+        self.grad_slab = self.gather_slab = slab
         self.peer_barrier = PeerBarrier(self.device, self.group, timeout_ms)
         return self
 

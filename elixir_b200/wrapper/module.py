@@ -59,6 +59,11 @@ class ElixirModule(nn.Module):
         self.no_grad_state_dict: Dict[str, torch.Tensor] = dict()
         self.grad_state_dict: Dict[str, torch.Tensor] = dict()
         self._init_chunk_group(search_result)
+        pool = search_result.chunk_group.rcache
+        # replica cache in peer-mapped memory and more than one rank: the optimizer step does the collectives
+        self.nvlink_step = getattr(pool, 'slab', None) is not None and dist.get_world_size(process_group) > 1
+        if self.nvlink_step and reduce_always_fp32:
+            raise ValueError('the NVLink step always accumulates in fp32; drop reduce_always_fp32')
         self.fetcher = ChunkFetcher(self.param_chunk_group, overlap=prefetch, reduce_always_fp32=reduce_always_fp32)
 
         for name, param in module.named_parameters():
@@ -136,7 +141,11 @@ class ElixirModule(nn.Module):
             raise RuntimeError('a gradient arrived for a parameter that is not waiting for one')
         self.param_chunk_group.tensor_trans_state(param, TensorState.READY_FOR_REDUCE)
         chunk.copy_tensor_to_chunk_slice(param, grad)
-        self.fetcher.reduce_chunk(chunk)
+        if self.nvlink_step:
+            if chunk.reduce_check:
+                chunk.defer_reduce()
+        else:
+            self.fetcher.reduce_chunk(chunk)
 
     def inject_gradients(self, grads: Dict[str, torch.Tensor]):
         """Drive the backward tail without running a model: gather the chunks, hand every parameter its

@@ -170,8 +170,29 @@ class ElixirOptimizer:
         """Whether any chunk of this rank flagged inf/nan.  Synchronises; the step itself does not call it."""
         return bool(self.engine.chunk_flags.any().item())
 
+    def _attach_nvlink(self):
+        """First NVLink step: every chunk sits in a block of the peer-mapped replica cache by now; remember
+        where, and from here on the chunks keep their blocks (the step leaves them gathered)."""
+        offsets = []
+        for chunk in self._chunks:
+            assert chunk.is_replica and chunk.rcb is not None and chunk.rcb.slab_offset is not None, \
+                'NVLink step: run forward/backward (or inject_gradients) before the first step'
+            offsets.append(chunk.rcb.slab_offset)
+        self.engine.attach_p2p(self.param_chunk_group.rcache.slab, offsets)
+        self._nvlink_offsets = offsets
+
     def step(self, *args, **kwargs):
         self.optim_state = OptimState.UNSCALED
+        if self.module.nvlink_step:
+            if getattr(self, '_nvlink_offsets', None) is None:
+                self._attach_nvlink()
+            assert [c.rcb.slab_offset for c in self._chunks] == self._nvlink_offsets
+            self.engine.set_hyper(self.optim.hyper_table())
+            self.engine.step_sharded_p2p()
+            for chunk in self._chunks:
+                chunk._l2_valid = False
+            self.zero_grad()
+            return None
         self.engine.begin_step()
         ret = self.optim.step(*args, **kwargs)
         self.engine.end_step()

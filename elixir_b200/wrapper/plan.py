@@ -55,9 +55,12 @@ def simple_plan(m: nn.Module,
                 prefetch: bool = False,
                 verbose: bool = False,
                 chunk_size: Optional[int] = None,
-                rcache_device=None) -> SearchResult:
+                rcache_device=None,
+                peer_group=None) -> SearchResult:
     """Plan chunks for the parameters of ``m`` that require gradients.  ``chunk_size`` (elements) overrides
-    the size derived from ``split_number``; parameters are then packed greedily in order."""
+    the size derived from ``split_number``; parameters are then packed greedily in order.  ``peer_group`` (a
+    single-node process group) places the replica cache in memory every rank of the group can address, which
+    lets ``ElixirOptimizer`` run reduce-scatter and all-gather inside its kernels over NVLink."""
     names = {p: n for n, p in m.named_parameters()}
     params = [p for p in m.parameters() if p.requires_grad]
     private = get_multi_used_params(m)
@@ -100,7 +103,13 @@ def simple_plan(m: nn.Module,
             plan.kwargs['temp_device'] = rcache_device
 
     device_type = rcache_device if rcache_device is not None else 'cuda'
-    pool = MemoryPool(device_type)
+    slab_factory = None
+    if peer_group is not None:
+        # replica cache in peer-mapped memory: the optimizer step then runs its collectives inside the kernels
+        from ..peer import PeerBuffer
+        device = torch.device('cuda', torch.cuda.current_device())
+        slab_factory = lambda numel, dtype: PeerBuffer(numel, dtype, device, peer_group)    # noqa: E731
+    pool = MemoryPool(device_type, slab_factory=slab_factory)
     pool.allocate(public_dtype=unified_dtype,
                   public_block_size=max(public_size, 1),
                   public_block_number=max(len(groups), math.ceil(len(groups) * allocate_factor)),

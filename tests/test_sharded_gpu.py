@@ -205,7 +205,7 @@ def test_sharded_step_p2p_kernels(world):
     mp.spawn(_p2p_worker, args=(world, 29820 + world), nprocs=world)
 
 
-def _wrapper_worker(rank, world, port):
+def _wrapper_worker(rank, world, port, nvlink=False):
     """ElixirModule + ElixirOptimizer over NCCL with a real forward / backward, against plain data-parallel
     training (gradients averaged by hand, torch.optim.AdamW): the reference's test/wrapper/test_optimizer.py
     in spirit, tolerance included."""
@@ -225,10 +225,12 @@ def _wrapper_worker(rank, world, port):
     plain = nn.Sequential(nn.Linear(40, 72), nn.GELU(), nn.Linear(72, 72), nn.GELU(), nn.Linear(72, 6)).to(dev)
     wrapped = copy.deepcopy(plain)
     opt = torch.optim.AdamW(plain.parameters(), lr=1e-2, betas=(0.875, 0.99609375), weight_decay=0.0)
-    sr = simple_plan(wrapped, world, split_number=3, unified_dtype=torch.float)
+    sr = simple_plan(wrapped, world, split_number=3, unified_dtype=torch.float,
+                     peer_group=dist.group.WORLD if nvlink else None)
     inner = HybridAdam(wrapped.parameters(), lr=1e-2, betas=(0.875, 0.99609375), weight_decay=0.0)
     emodel = ElixirModule(wrapped, sr, dist.group.WORLD, dtype=torch.float)
     eopt = ElixirOptimizer(emodel, inner)
+    assert emodel.nvlink_step == nvlink
     for step in range(3):
         torch.manual_seed(100 * step + rank)    # every rank its own batch
         x = torch.randn(16, 40, device=dev)
@@ -253,6 +255,14 @@ def test_wrapper_data_parallel_training_matches_plain_ddp():
     if torch.cuda.device_count() < 2:
         pytest.skip('needs 2 GPUs')
     mp.spawn(_wrapper_worker, args=(2, 29840), nprocs=2)
+
+
+def test_wrapper_training_with_the_nvlink_step_matches_plain_ddp():
+    """The same training with the replica cache in peer-mapped memory: no NCCL collective after the first
+    gather; reduce-scatter and all-gather happen inside the optimizer's kernels."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    mp.spawn(_wrapper_worker, args=(2, 29850, True), nprocs=2)
 
 
 def test_sharded_step_p2p_kernels_bf16():
