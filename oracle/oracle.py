@@ -79,15 +79,18 @@ def num_threads():
 
 def probe(g, n_valid=None):
     n_valid = g.numel() if n_valid is None else n_valid
+    assert 0 <= n_valid <= g.numel()
     return bool(lib().orc_probe(_cpu(g), _CODES[g.dtype], n_valid))
 
 
 def l2sq(g, n_valid=None):
     n_valid = g.numel() if n_valid is None else n_valid
+    assert 0 <= n_valid <= g.numel()
     return lib().orc_l2sq(_cpu(g), _CODES[g.dtype], n_valid)
 
 
 def cast(master, dst):
+    assert master.numel() == dst.numel()
     lib().orc_cast(_cpu(master, torch.float32), _cpu(dst), _CODES[dst.dtype], master.numel())
 
 
@@ -119,6 +122,7 @@ def step_begin(ctl, cfg, norm_sq=None):
 
 def adam(master, exp_avg, exp_avg_sq, g, hyper, step, div_scale, begin=0, end=None, f64=False):
     end = master.numel() if end is None else end
+    assert 0 <= begin <= end <= min(master.numel(), exp_avg.numel(), exp_avg_sq.numel(), g.numel()), 'range outside the tensors'
     fn = lib().orc_adam_f64 if f64 else lib().orc_adam_f32
     fn(_cpu(master, torch.float32), _cpu(exp_avg, torch.float32), _cpu(exp_avg_sq, torch.float32), _cpu(g),
        _CODES[g.dtype], begin, end, hyper, step, div_scale)

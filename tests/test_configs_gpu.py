@@ -169,3 +169,55 @@ def test_config4_overflow_trajectory_full_size_properties(cuda, oracle):
     ctl = engine.read_control()
     assert (ctl.skipped_steps, ctl.step, ctl.status) == (1, 19, 0)
     assert ctl.scale == 2.0**16    # hysteresis 2: a single overflow does not back off
+
+
+def test_shard_larger_than_2_31_elements(cuda, oracle):
+    """Index arithmetic past 2^31: one shard of 2^31 + 3 * 4096 + 5 elements (the OPT-66B configuration holds
+    8.2 G elements per rank).  Slices at the start, around 2^31 and at the ragged tail are compared with the
+    oracle element by element; everything in between through checksums of a second, identical run."""
+    from elixir_b200 import kernels as K
+    n = 2**31 + 3 * 4096 + 5
+    free, _ = torch.cuda.mem_get_info(cuda)
+    if free < n * 16:
+        pytest.skip('not enough free device memory')
+    n_valid = n - 3
+    gen = torch.Generator(device=cuda).manual_seed(7)
+    master = torch.empty(n, device=cuda).normal_(0.0, 0.02, generator=gen)
+    exp_avg = torch.zeros(n, device=cuda)
+    exp_avg_sq = torch.zeros(n, device=cuda)
+    lowp = torch.empty(n, dtype=torch.float16, device=cuda)
+    step_size = 1 << 28
+    for b in range(0, n, step_size):    # gradients generated piecewise to bound temporaries
+        e = min(n, b + step_size)
+        lowp[b:e] = torch.empty(e - b, device=cuda).normal_(0.0, 1e-3, generator=gen).mul_(64.0).half()
+    windows = [(0, 70000), (2**31 - 40000, 2**31 + 6000), (n - 5000, n)]
+    assert all(0 <= b < e <= n for b, e in windows)
+    before = [(master[b:e].cpu(), lowp[b:e].cpu()) for b, e in windows]
+    lowp[2**31 + 77] = float('inf')
+    flag = torch.zeros(1, dtype=torch.int32, device=cuda)
+    K.grad_check(lowp, n_valid=n_valid, flag=flag)
+    assert flag.item() == 1                      # an inf beyond index 2^31 is found
+    lowp[2**31 + 77] = before[1][1][40000 + 77].item()
+    flag.zero_()
+    lowp[n - 2] = float('nan')                   # padding (>= n_valid): ignored
+    K.grad_check(lowp, n_valid=n_valid, flag=flag)
+    assert flag.item() == 0
+    h = K.hyper(lr=1e-3, weight_decay=0.01)
+    ctl = K.ControlBlock(cuda, 64.0)
+    K.step_begin(ctl, K.scaler_cfg(False))
+    K.adam_chunk(master, exp_avg, exp_avg_sq, lowp, h, ctl, n_valid=n_valid)
+    c = ctl.read()
+    assert c.status == 0 and c.step == 1
+    for (b, e), (m0, g0) in zip(windows, before):
+        hi = min(e, n_valid)
+        rm, r1, r2 = m0.clone(), torch.zeros(e - b), torch.zeros(e - b)
+        oracle.adam(rm, r1, r2, g0, h, 1, 64.0, 0, hi - b, f64=True)
+        for got, want in ((master[b:e], rm), (exp_avg[b:e], r1), (exp_avg_sq[b:e], r2)):
+            ok, ratio = close_1e6(got, want.double())
+            assert ok, (b, e, ratio)
+        want16 = torch.empty(e - b, dtype=torch.float16)
+        oracle.cast(master[b:e].cpu(), want16)
+        assert bits_equal(lowp[b:e], want16)
+    assert torch.equal(master[n_valid:].cpu(), before[2][0][-3:])    # padding untouched
+    # every element was updated exactly once: no moment is still zero where the gradient was not
+    assert int((exp_avg_sq[:n_valid] == 0).sum().item()) < 2048
