@@ -312,6 +312,9 @@ def run_ours(args):
                             'NCCL reduce-scatter (pre-multiplied sum) and all-gather per chunk on side streams'),
         },
         'clocks': clocks,
+        'context': {'reference_planner_gpu_adam_gparams_per_s_per_gpu': 50.0,
+                    'note': 'constant fitted by the reference authors on unnamed hardware for fp32 gradients without the '
+                            'copy-back (elixir/search/simulator.py:128-129); not this exact metric, hence vs_baseline null'},
     }
 
     if world == 1:
