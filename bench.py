@@ -33,6 +33,7 @@ sys.path.insert(0, ROOT)
 
 GPT2XL_PARAMS = 48 * (12 * 1600 * 1600 + 13 * 1600) + 50257 * 1600 + 1024 * 1600 + 2 * 1600
 OPT13B_PARAMS = 40 * (12 * 5120 * 5120 + 13 * 5120) + 50272 * 5120 + 2050 * 5120 + 2 * 5120
+OPT66B_PARAMS = 64 * (12 * 9216 * 9216 + 13 * 9216) + 50272 * 9216 + 2050 * 9216 + 2 * 9216
 CHUNK_1GPU = 32 * 1024 * 1024    # 64 MiB of fp16
 CHUNK_SHARDED = 256 * 1024 * 1024    # 512 MiB of fp16
 BYTES_PER_ELEM = 28    # g 2 + p/m/v 12 read, p/m/v 12 + p16 2 written
@@ -175,17 +176,29 @@ def run_ours(args):
         dist.init_process_group('nccl', rank=rank, world_size=world, device_id=device)
         group = dist.group.WORLD
 
-    dtype = torch.float16
+    dtype, sigma = torch.float16, 1e-3
     if world == 1:
         workload, total, chunk, scale, wd = 'gpt2xl_chunks_1gpu', GPT2XL_PARAMS, CHUNK_1GPU, 65536.0, 0.01
+    elif args.workload == 'opt66b_bf16':
+        # BASELINE config 5: bf16 chunks, constant scale 1, AdamW, ~8.2 G elements of state per rank at W = 8.
+        # The replicated blocks cannot all be resident next to 115 GB of state, so they come from a small pool,
+        # as in training, and the step runs chunk by chunk.
+        workload, total, chunk, scale, wd = f'opt66b_bf16_chunks_sharded_w{world}', OPT66B_PARAMS, CHUNK_SHARDED, 1.0, 0.01
+        dtype, sigma = torch.bfloat16, 1e-4
+        args.pool = args.pool or 4
     else:
         workload, total, chunk, scale, wd = f'opt13b_chunks_sharded_w{world}', OPT13B_PARAMS, CHUNK_SHARDED, 1024.0, 0.0
-    sigma = 1e-3
+    if args.params:
+        total, workload = args.params, workload + f'_params{args.params}'
     n_chunks, used = chunk_layout(total, chunk, world)
     shard = chunk // world
 
-    scaler = DynamicGradScaler(initial_scale=scale, growth_factor=2, backoff_factor=0.5, growth_interval=1000,
-                               min_scale=1, max_scale=2**24, hysteresis=2)
+    if dtype == torch.bfloat16:
+        from elixir_b200.scaler import ConstantGradScaler
+        scaler = ConstantGradScaler(1.0)
+    else:
+        scaler = DynamicGradScaler(initial_scale=scale, growth_factor=2, backoff_factor=0.5, growth_interval=1000,
+                                   min_scale=1, max_scale=2**24, hysteresis=2)
     engine = ChunkStepEngine(device, dtype, scaler, process_group=group)
     for c in range(n_chunks):
         master, gen = synth_shard(shard, device, args.seed + 1000 * rank + c, scale, sigma, dtype)
@@ -208,9 +221,9 @@ def run_ours(args):
         gather_blocks = None
     elif args.collective == 'p2p':
         # NVLink path: every chunk owns a block in the peer-mapped gradient and gather slabs
-        engine.enable_p2p([chunk] * n_chunks)
+        engine.enable_p2p([chunk] * n_chunks, pool=args.pool or None)
         seeds = 4
-        for c in range(n_chunks):
+        for c in range(min(n_chunks, args.pool) if args.pool else n_chunks):
             if c < seeds:
                 gen = torch.Generator(device=device).manual_seed(args.seed + 7919 * (c + 1) + 31 * rank)
                 synth_grad(chunk, device, gen, scale, sigma, dtype, out=engine.grad_block(c))
@@ -301,11 +314,12 @@ def run_ours(args):
             'params': total,
             'chunk_elems': chunk,
             'n_chunks': n_chunks,
-            'grad_dtype': 'fp16',
+            'grad_dtype': 'bf16' if dtype == torch.bfloat16 else 'fp16',
             'optimizer': f'AdamW lr1e-3 b(0.9,0.999) eps1e-8 wd{wd}',
             'loss_scale': scale,
             'l2_policy': 'inputs larger than L2 (state per GPU %.1f GB)' % (engine.n_elements() * 14 / 1e9),
             'layout': 'flat packing, tensors may straddle chunks',
+            'block_pool': args.pool or n_chunks,
             'collectives': 'none (1 GPU)' if world == 1 else
                            ('fused into the kernels over peer-mapped NVLink memory (pull reduce-scatter + probe, '
                             'Adam + push all-gather)' if args.collective == 'p2p' else
@@ -343,7 +357,9 @@ def run_ours(args):
             'unit': 'GB/s', 'frac': 2 * bus_bytes / (ms_per_step * 1e-3) / 1e9 / 770.0, 'peak_kind': 'measured',
             'traffic': None, 'adam_hbm_ms_at_peak': adam_bytes / (peak * 1e9) * 1e3,
         }
-        if args.collective == 'p2p':
+        if args.collective == 'p2p' and args.pool:
+            result['gpu_launches'] = args.steps * (3 * n_chunks + 3)
+        elif args.collective == 'p2p':
             result['gpu_launches'] = args.steps * 6
             result['phases_ms'] = p2p_phases(engine)
         else:
@@ -568,6 +584,11 @@ def main():
     ap.add_argument('--seed', type=int, default=0)
     ap.add_argument('--collective', default='p2p', choices=['p2p', 'nccl'],
                     help='N > 1: collectives fused into the kernels over peer-mapped NVLink memory, or NCCL')
+    ap.add_argument('--workload', default='auto', choices=['auto', 'opt66b_bf16'],
+                    help='N > 1: auto = OPT-13B-shaped fp16 chunk set; opt66b_bf16 = OPT-66B-shaped bf16 chunk set (8 GPUs)')
+    ap.add_argument('--params', type=int, default=0, help='override the parameter count (smoke runs of a workload)')
+    ap.add_argument('--pool', type=int, default=0,
+                    help='N > 1: number of replicated blocks per slab (0 = one per chunk); chunk k uses block k %% pool')
     ap.add_argument('--land-streams', type=int, default=2,
                     help='N = 1: side streams the per-chunk landing launches alternate on')
     ap.add_argument('--no-cpu-baseline', action='store_true')

@@ -239,18 +239,29 @@ class ChunkStepEngine:
 
     # ------------------------------------------------------------------ NVLink path
 
-    def enable_p2p(self, chunk_sizes: Sequence[int], timeout_ms: int = 20000):
-        """Allocate the peer-mapped slabs of the NVLink path: one gradient slab and one gather slab per rank,
-        each holding a block of ``chunk_sizes[k]`` elements for every registered chunk k, plus the barrier
-        flags.  ``grad_block(k)`` / ``gather_block(k)`` are this rank's blocks."""
+    def enable_p2p(self, chunk_sizes: Sequence[int], timeout_ms: int = 20000, pool: Optional[int] = None):
+        """Allocate the peer-mapped slabs of the NVLink path: one gradient slab and one gather slab per rank, plus
+        the barrier flags.  By default each slab holds a block of ``chunk_sizes[k]`` elements for every
+        registered chunk k.  With ``pool`` = P the slabs hold only P blocks (of the largest chunk size) and chunk
+        k uses block ``k % P`` — the regime of models whose replicated blocks cannot all be resident; the step
+        then runs chunk by chunk (``step_sharded_p2p``).  ``grad_block(k)`` / ``gather_block(k)`` are this rank's
+        blocks."""
         from .peer import PeerBarrier, PeerBuffer
         assert len(chunk_sizes) == self.n_chunks
-        offsets, total = [], 0
         for k, size in enumerate(chunk_sizes):
             if size != self.shards[k][0].numel() * self.world:
                 raise ValueError(f'chunk {k}: chunk size {size} is not world x shard size')
-            offsets.append(total)
-            total += (size + 15) // 16 * 16
+        pad = lambda n: (n + 15) // 16 * 16
+        if pool:
+            stride = pad(max(chunk_sizes))
+            offsets = [(k % pool) * stride for k in range(self.n_chunks)]
+            total = min(pool, self.n_chunks) * stride
+        else:
+            offsets, total = [], 0
+            for size in chunk_sizes:
+                offsets.append(total)
+                total += pad(size)
+        self._p2p_pool = pool or 0
         self._p2p_sizes = list(chunk_sizes)
         self._p2p_offsets = offsets
         self.block_off = torch.tensor(offsets, dtype=torch.int64, device=self.device)
@@ -266,6 +277,7 @@ class ChunkStepEngine:
         sharing the slab between the two directions needs no extra ordering."""
         from .peer import PeerBarrier
         assert len(block_offsets) == self.n_chunks
+        self._p2p_pool = 0
         self._p2p_sizes = [self.shards[k][0].numel() * self.world for k in range(self.n_chunks)]
         self._p2p_offsets = list(block_offsets)
         self.block_off = torch.tensor(self._p2p_offsets, dtype=torch.int64, device=self.device)
@@ -289,10 +301,21 @@ class ChunkStepEngine:
             update + push      one launch: fused Adam, refreshed parameters stored into every rank's gather block
             barrier            every rank's pushes have landed: the gather blocks are complete
 
-        Six launches per step, no NCCL call, no host synchronisation."""
-        self.peer_barrier(self.ctl)
-        kernels.pull_reduce_multi(self.table, self.grad_slab.table, self.block_off, self.ctl,
-                                  chunk_flags=self.chunk_flags)
+        Six launches per step, no NCCL call, no host synchronisation.
+
+        With pooled blocks (``enable_p2p(pool=P)``) the two fused kernels are launched chunk by chunk, with a
+        barrier before each pull (chunk k's gradients are in block ``k % P`` on every rank) — the order in which
+        a backward pass produces them; the decision still waits for the last chunk."""
+        pooled = getattr(self, '_p2p_pool', 0)
+        if pooled:
+            for k in range(self.n_chunks):
+                self.peer_barrier(self.ctl)
+                kernels.pull_reduce_multi(self.table, self.grad_slab.table, self.block_off, self.ctl,
+                                          chunk_flags=self.chunk_flags, first=k, count=1)
+        else:
+            self.peer_barrier(self.ctl)
+            kernels.pull_reduce_multi(self.table, self.grad_slab.table, self.block_off, self.ctl,
+                                      chunk_flags=self.chunk_flags)
         self.peer_barrier(self.ctl, exchange_overflow=self.sync_overflow)
         norm_sq = None
         if self.clipping:
@@ -301,7 +324,11 @@ class ChunkStepEngine:
             dist.all_reduce(self.total_l2sq, group=self.group)
             norm_sq = self.total_l2sq
         kernels.step_begin(self.ctl, self.scaler.cfg, norm_sq)
-        kernels.adam_multi_push(self.table, self.ctl, self.gather_slab.table, self.block_off)
+        if pooled:
+            for k in range(self.n_chunks):
+                kernels.adam_multi_push(self.table, self.ctl, self.gather_slab.table, self.block_off, first=k, count=1)
+        else:
+            kernels.adam_multi_push(self.table, self.ctl, self.gather_slab.table, self.block_off)
         self.end_step()
         self.peer_barrier(self.ctl)
 

@@ -103,7 +103,7 @@ def _worker(rank, world, port):
     dist.destroy_process_group()
 
 
-def _p2p_worker(rank, world, port, dtype_name='float16'):
+def _p2p_worker(rank, world, port, dtype_name='float16', pool=None):
     """The NVLink path: pull reduce-scatter + probe, overflow agreement inside the barrier, fused update with
     push all-gather — no NCCL collective in the step."""
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
@@ -122,6 +122,10 @@ def _p2p_worker(rank, world, port, dtype_name='float16'):
     dtype, scale = getattr(torch, dtype_name), 256.0
     chunk_sizes = [world * 4096 * 40, world * (4096 + 16), world * 4096 * 5, world * 24]
     used = [chunk_sizes[0], chunk_sizes[1], chunk_sizes[2] // 2 + 7, 9]
+    if pool:
+        # pooled blocks: equal-sized chunks, chunk k lives in block k % pool
+        chunk_sizes = [world * (4096 * 6 + 32)] * 5
+        used = [chunk_sizes[0], chunk_sizes[0], chunk_sizes[0] // 2 + 7, chunk_sizes[0], 9]
     engine = ChunkStepEngine(dev, dtype, DynamicGradScaler(initial_scale=scale, hysteresis=1, growth_interval=3),
                              process_group=dist.group.WORLD)
     host = orc.ChunkSet(dtype)
@@ -141,12 +145,16 @@ def _p2p_worker(rank, world, port, dtype_name='float16'):
         engine.add_shard(mine.to(dev), torch.zeros(S, dtype=dtype, device=dev), nv, [(0, nv, 0)] if nv else [])
     engine.finalize()
     engine.set_hyper(hypers)
-    engine.enable_p2p(chunk_sizes, timeout_ms=5000)
+    engine.enable_p2p(chunk_sizes, timeout_ms=5000, pool=pool)
 
     def fill(step):
         per_rank = []
         for c, C in enumerate(chunk_sizes):
             rank_grads = []
+            if pool and c >= pool:
+                # the block is shared with chunk c - pool: same gradients (the engine reads what is in the block)
+                per_rank.append(per_rank[c - pool])
+                continue
             for r in range(world):
                 gen = torch.Generator().manual_seed(1000 * step + 10 * c + r)
                 g = (torch.randn(C, generator=gen) * 1e-3 * host_ctl.scale).to(dtype)
@@ -193,9 +201,17 @@ def _p2p_worker(rank, world, port, dtype_name='float16'):
             mine16 = engine.shards[c][3]
             others = [torch.empty_like(mine16) for _ in range(world)]
             dist.all_gather(others, mine16)
-            assert bits_equal(engine.gather_block(c), torch.cat(others)), (step, rank, c)
+            if not pool or c + pool >= len(chunk_sizes):    # a pooled gather block holds its LAST chunk
+                assert bits_equal(engine.gather_block(c), torch.cat(others)), (step, rank, c)
     dist.barrier()
     dist.destroy_process_group()
+
+
+def test_sharded_step_p2p_pooled_blocks():
+    """Chunk-by-chunk NVLink step over a pool of 2 replicated blocks for 5 chunks."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    mp.spawn(_p2p_worker, args=(2, 29860, 'float16', 2), nprocs=2)
 
 
 @pytest.mark.parametrize('world', [2, 4, 8])
