@@ -1478,9 +1478,23 @@ int launch_adam_minb(const AdamArgs& a, cudaStream_t s) {
 template <int DT, int MATH>
 int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
     constexpr int smem = kTmaStages * TmaStage<DT>::kBytes;
-    static const cudaError_t attr =
-        cudaFuncSetAttribute(adam_tma_kernel<DT, MATH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (attr != cudaSuccess) return record_cuda(attr);
+    // the opt-in to more than 48 KB of dynamic shared memory is per device: once for each ordinal
+    static bool opted_in[64];
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        (void)cudaGetLastError();
+        return ELX_ERR_NODEVICE;
+    }
+    if (!opted_in[dev]) {
+        const cudaError_t attr =
+            cudaFuncSetAttribute(adam_tma_kernel<DT, MATH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (attr != cudaSuccess) {
+            const int rc = record_cuda(attr);
+            (void)cudaGetLastError();
+            return rc;
+        }
+        opted_in[dev] = true;
+    }
     const int grid = grid_for(a.n_tiles, 1);
     if (grid < 0) return grid;
     adam_tma_kernel<DT, MATH><<<grid, kTmaThreads, smem, s>>>(a);
