@@ -9,8 +9,8 @@ import sys
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 ROOT_DIR = os.path.dirname(PKG_DIR)
-SOURCES = [os.path.join(PKG_DIR, 'csrc', 'elx_step.cu')]
-HEADER = os.path.join(ROOT_DIR, 'include', 'elixir_b200.h')
+SOURCES = [os.path.join(PKG_DIR, 'csrc', name) for name in ('elx_control.cu', 'elx_adam.cu', 'elx_probe.cu', 'elx_peer.cu')]
+HEADERS = [os.path.join(ROOT_DIR, 'include', 'elixir_b200.h'), os.path.join(PKG_DIR, 'csrc', 'elx_common.cuh')]
 LIB_PATH = os.path.join(PKG_DIR, 'libelixir_b200.so')
 
 NVCC_FLAGS = [
@@ -29,14 +29,14 @@ def needs_build():
     if not os.path.exists(LIB_PATH):
         return True
     built = os.path.getmtime(LIB_PATH)
-    return any(os.path.getmtime(src) > built for src in SOURCES + [HEADER])
+    return any(os.path.getmtime(src) > built for src in SOURCES + HEADERS)
 
 
 def build(force=False, verbose=False):
     """Compile the library if it is missing or older than its sources.  Returns its path."""
     if not force and not needs_build():
         return LIB_PATH
-    cmd = [_nvcc()] + NVCC_FLAGS + ['-I', os.path.join(ROOT_DIR, 'include'), '-o', LIB_PATH] + SOURCES
+    cmd = [_nvcc()] + NVCC_FLAGS + ['--threads', '4', '-I', os.path.join(ROOT_DIR, 'include'), '-o', LIB_PATH] + SOURCES
     if verbose:
         cmd.insert(1, '-Xptxas')
         cmd.insert(2, '-v')

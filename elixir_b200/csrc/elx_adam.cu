@@ -1,0 +1,782 @@
+// Part of the elixir_b200 CUDA library (C ABI: include/elixir_b200.h).  See elx_common.cuh for the
+// overview of the kernels and of how the sources are divided.
+#include "elx_common.cuh"
+
+using namespace elx;
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// Adam
+// ------------------------------------------------------------------------------------------------
+
+// Per-group constants derived once per CTA from ElxHyper and the device step counter.
+struct GroupK {
+    float lr, beta1, omb1, beta2, omb2, eps;
+    float wd_l2;   // weight decay added to the gradient (L2 mode), 0 in decoupled mode
+    float wd_w;    // weight decay added to the update (decoupled mode), 0 in L2 mode
+    float bc1, bc2, rbc1, rbc2;
+};
+
+__device__ __noinline__ GroupK derive_group(const ElxHyper& h, int step) {
+    GroupK k;
+    k.lr = h.lr;
+    k.beta1 = h.beta1;
+    k.beta2 = h.beta2;
+    k.omb1 = 1.0f - h.beta1;
+    k.omb2 = 1.0f - h.beta2;
+    k.eps = h.eps;
+    k.wd_l2 = h.adamw_mode ? 0.0f : h.weight_decay;
+    k.wd_w = h.adamw_mode ? h.weight_decay : 0.0f;
+    double bc1 = 1.0, bc2 = 1.0;
+    if (h.bias_correction) {
+        // 1 - beta^t evaluated in double from the fp32 betas, then rounded to fp32
+        bc1 = 1.0 - pow(static_cast<double>(h.beta1), static_cast<double>(step));
+        bc2 = 1.0 - pow(static_cast<double>(h.beta2), static_cast<double>(step));
+    }
+    k.bc1 = static_cast<float>(bc1);
+    k.bc2 = static_cast<float>(bc2);
+    k.rbc1 = static_cast<float>(1.0 / bc1);
+    k.rbc2 = static_cast<float>(1.0 / bc2);
+    return k;
+}
+
+// How the gradient is unscaled in this launch.
+enum { kNoDiv = 0, kMulInv = 1, kTrueDiv = 2 };
+
+template <int MATH>
+__device__ __forceinline__ void adam_elem(float& p, float& m, float& v, float g, const GroupK& k, int div_mode,
+                                          float div, float inv_div) {
+    if (div_mode == kMulInv) g *= inv_div;                    // exact: the divisor is a power of two
+    else if (div_mode == kTrueDiv) g = __fdiv_rn(g, div);
+    g = fmaf(k.wd_l2, p, g);
+    m = fmaf(k.beta1, m, k.omb1 * g);
+    v = fmaf(k.beta2, v, (k.omb2 * g) * g);
+    float upd;
+    if constexpr (MATH == 1) {
+        float mhat = __fdiv_rn(m, k.bc1);
+        float vhat = __fdiv_rn(v, k.bc2);
+        float denom = __fsqrt_rn(vhat) + k.eps;
+        upd = __fdiv_rn(mhat, denom);
+    } else {
+        float mhat = m * k.rbc1;
+        float vhat = v * k.rbc2;
+        float denom = __fsqrt_rn(vhat) + k.eps;
+        upd = __fdividef(mhat, denom);
+    }
+    upd = fmaf(k.wd_w, p, upd);
+    p = fmaf(-k.lr, upd, p);
+}
+
+struct AdamArgs {
+    const ElxChunkDesc* descs;
+    const ElxSeg* segs;
+    const ElxHyper* hyper;
+    ElxCtl* ctl;
+    int first, count, n_groups, inline_tables;
+    int64_t n_tiles;
+    // push all-gather: the refreshed working copy also goes to every rank's gather block (world > 0)
+    ElxPeerTable push;
+    const int64_t* push_off;   // per descriptor: element offset of the chunk's block inside the slabs
+    // single-shard form: the three tables travel in the kernel parameters
+    ElxChunkDesc one_desc;
+    ElxSeg one_seg;
+    ElxHyper one_hyper;
+};
+
+// Push all-gather: element offset of this rank's shard of descriptor `c` inside every rank's gather slab.
+__device__ __forceinline__ int64_t push_base_elem(const AdamArgs& a, int c, int64_t n_shard) {
+    return a.push_off[c] + static_cast<int64_t>(a.push.rank) * n_shard;
+}
+
+// Skipped step: the low-precision shard holds gradients and must become parameters again.
+// CTA-collective; s_cur is a shared-memory cursor that cursor_reset() has initialised.
+template <int DT, int EPT>
+__device__ __forceinline__ bool copyback_tiles(const AdamArgs& a, const ElxChunkDesc* __restrict__ descs,
+                                               ChunkCursor& s_cur) {
+    bool bad_desc = false;
+    const int64_t tile_lo = descs[a.first].tile_begin;
+    for (int64_t it = blockIdx.x; it < a.n_tiles; it += gridDim.x) {
+        const int64_t t = tile_lo + it;
+        if (!locate_chunk(descs, a.first, a.count, t, s_cur) || s_cur.d.dtype != DT) {
+            bad_desc = true;
+            continue;
+        }
+        const int64_t e0 = (t - s_cur.t0) * kTile;
+        const int64_t e1 = min(e0 + kTile, s_cur.d.n_shard);
+        float* const master = s_cur.d.master;
+        void* const lowp = s_cur.d.grad_param;
+        const int world = a.push.world;
+        const int64_t pb = world > 0 ? push_base_elem(a, s_cur.index, s_cur.d.n_shard) : 0;
+        if ((e1 - e0 == kTile) && s_cur.vec_ok && (pb & 15) == 0) {
+            float p[EPT];
+            load_f32<EPT>(master, e0, p);
+            store_lowp<DT, EPT>(lowp, e0, p);
+            for (int j = 0; j < world; ++j) store_lowp<DT, EPT>(a.push.base[j], pb + e0, p);
+        } else {
+            typename Lp<DT>::T* out = static_cast<typename Lp<DT>::T*>(lowp);
+            for (int64_t e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
+                const typename Lp<DT>::T val = Lp<DT>::from_float(master[e]);
+                out[e] = val;
+                for (int j = 0; j < world; ++j) static_cast<typename Lp<DT>::T*>(a.push.base[j])[pb + e] = val;
+            }
+        }
+    }
+    return bad_desc;
+}
+
+template <int DT, int EPT, int MATH, int MINB>
+__global__ void __launch_bounds__(kTile / EPT, MINB) adam_kernel(const __grid_constant__ AdamArgs a) {
+    __shared__ GroupK s_group[kMaxGroups];
+    __shared__ ChunkCursor s_cur;
+    __shared__ SegCursor s_seg;
+
+    const ElxChunkDesc* __restrict__ descs = a.inline_tables ? &a.one_desc : a.descs;
+    const ElxSeg* __restrict__ segs = a.inline_tables ? &a.one_seg : a.segs;
+    const ElxHyper* __restrict__ hyper = a.inline_tables ? &a.one_hyper : a.hyper;
+    ElxCtl* ctl = a.ctl;
+
+    const bool skip = ctl->skip != 0;
+    const float div = ctl->div_scale;
+    const float inv_div = ctl->inv_div;
+    const int div_mode = div > 0.0f ? (inv_div != 0.0f ? kMulInv : kTrueDiv) : kNoDiv;
+
+    if (!skip) {
+        const int step = ctl->step;
+        for (int gi = threadIdx.x; gi < a.n_groups; gi += blockDim.x) s_group[gi] = derive_group(hyper[gi], step);
+    }
+    if (threadIdx.x == 0) {
+        s_seg.b = s_seg.e = 0;
+        s_seg.group = -1;
+        s_seg.chunk = -1;
+    }
+    cursor_reset(s_cur);
+
+    const int64_t tile_lo = descs[a.first].tile_begin;
+    float nan_acc = 0.0f;   // becomes NaN once a non-finite gradient is multiplied into it
+    bool bad_desc = false;
+
+    if (skip) {
+        bad_desc = copyback_tiles<DT, EPT>(a, descs, s_cur);
+        if (__ballot_sync(0xFFFFFFFFu, bad_desc) && (threadIdx.x & 31) == 0) atomicOr(&ctl->status, ELX_STAT_BAD_DESC);
+        return;
+    }
+
+    for (int64_t it = blockIdx.x; it < a.n_tiles; it += gridDim.x) {
+        const int64_t t = tile_lo + it;
+        if (!locate_chunk(descs, a.first, a.count, t, s_cur) || s_cur.d.dtype != DT) {
+            bad_desc = true;
+            continue;
+        }
+        const int64_t n_shard = s_cur.d.n_shard;
+        const int64_t e0 = (t - s_cur.t0) * kTile;
+        const int64_t e1 = min(e0 + kTile, n_shard);
+        const bool full = (e1 - e0 == kTile) && s_cur.vec_ok;
+        float* const master = s_cur.d.master;
+        void* const lowp = s_cur.d.grad_param;
+
+        // segment that contains e0 (CTA-uniform; refreshed by one thread when e0 leaves the cached one)
+        const ElxSeg* csegs = segs + s_cur.d.seg_first;
+        const int n_segs = s_cur.d.seg_count;
+        if (s_seg.chunk != s_cur.index || e0 < s_seg.b || e0 >= s_seg.e) {
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const int si = find_seg(csegs, n_segs, e0);
+                s_seg.chunk = s_cur.index;
+                if (si >= 0) {
+                    s_seg.b = csegs[si].begin;
+                    s_seg.e = csegs[si].end;
+                    s_seg.group = csegs[si].group;
+                } else {
+                    s_seg.b = s_seg.e = 0;
+                    s_seg.group = -1;
+                }
+            }
+            __syncthreads();
+        }
+        const int grp = s_seg.group;
+        const bool one_group = s_seg.b <= e0 && e1 <= s_seg.e && grp >= 0 && grp < a.n_groups;
+        float* const exp_avg = s_cur.d.exp_avg;
+        float* const exp_avg_sq = s_cur.d.exp_avg_sq;
+
+        if (full && one_group) {
+            const GroupK k = s_group[grp];
+            float g[EPT], p[EPT], m[EPT], v[EPT];
+            load_lowp<DT, EPT>(lowp, e0, g);
+            load_f32<EPT>(master, e0, p);
+            load_f32<EPT>(exp_avg, e0, m);
+            load_f32<EPT>(exp_avg_sq, e0, v);
+#pragma unroll
+            for (int j = 0; j < EPT; ++j) {
+                nan_acc = fmaf(0.0f, g[j], nan_acc);
+                adam_elem<MATH>(p[j], m[j], v[j], g[j], k, div_mode, div, inv_div);
+            }
+            store_f32<EPT>(master, e0, p);
+            store_f32<EPT>(exp_avg, e0, m);
+            store_f32<EPT>(exp_avg_sq, e0, v);
+            store_lowp<DT, EPT>(lowp, e0, p);
+        } else {
+            // ragged tile: shard tail, segment boundary, uncovered elements or unaligned pointers
+            typename Lp<DT>::T* gp = static_cast<typename Lp<DT>::T*>(lowp);
+            for (int64_t e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
+                float p = master[e];
+                const int si = find_seg(csegs, n_segs, e);
+                if (si >= 0 && e < csegs[si].end) {
+                    const int ge = csegs[si].group;
+                    if (ge >= 0 && ge < a.n_groups) {
+                        const GroupK k = s_group[ge];
+                        float g = Lp<DT>::to_float(gp[e]);
+                        float m = exp_avg[e], v = exp_avg_sq[e];
+                        nan_acc = fmaf(0.0f, g, nan_acc);
+                        adam_elem<MATH>(p, m, v, g, k, div_mode, div, inv_div);
+                        master[e] = p;
+                        exp_avg[e] = m;
+                        exp_avg_sq[e] = v;
+                    }
+                }
+                gp[e] = Lp<DT>::from_float(p);
+            }
+        }
+    }
+
+    // warp-reduced report of a non-finite gradient met on an applied step
+    const bool late = nan_acc != nan_acc;
+    const unsigned ballot = __ballot_sync(0xFFFFFFFFu, late);
+    const unsigned ballot_desc = __ballot_sync(0xFFFFFFFFu, bad_desc);
+    if ((threadIdx.x & 31) == 0) {
+        if (ballot) {
+            atomicOr(&ctl->late_inf, 1u);
+            atomicOr(&ctl->status, ELX_STAT_LATE_INF);
+        }
+        if (ballot_desc) atomicOr(&ctl->status, ELX_STAT_BAD_DESC);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Adam, bulk-copy pipelined variant
+// ------------------------------------------------------------------------------------------------
+//
+// Same arithmetic, different data movement: one elected thread streams whole tiles between HBM and
+// shared memory with cp.async.bulk (the TMA unit's untiled form), completion tracked by mbarriers,
+// so loads of the next two tiles and stores of the previous one are in flight while the CTA's warps
+// compute on the current one out of shared memory.  One CTA per SM, kTmaStages stages of one tile
+// each (16-bit gradients: 8 KB + 3 x 16 KB = 56 KB per stage).
+//
+//   iteration k (stage s = k % 3):
+//     all threads   wait full[s]; read g,p,m,v from the stage; update; write p,m,v,p16 back in place
+//                   fence.proxy.async; __syncthreads
+//     thread 0      4 bulk stores stage s -> HBM, commit; wait until the stores of iteration k-1 have
+//                   read their stage; arm full[(k+2) % 3] and issue the 4 bulk loads of tile k+2 into it
+//
+// Ragged tiles (shard tail, segment boundary, unaligned pointers) bypass the pipeline and are updated
+// in place in global memory by the same scalar path as the direct kernel.  Every mbarrier wait is
+// bounded: on expiry the CTA raises ELX_STAT_TIMEOUT, stops issuing copies, drains and returns.
+
+constexpr int kTmaStages = 3;
+constexpr int kTmaThreads = 512;
+constexpr uint32_t kTmaSpinLimit = 1u << 22;   // polls of at most ~1 us each: a few seconds, then give up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)   // give up this poll after about a microsecond
+        : "memory");
+    return done != 0;
+}
+// false = gave up
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kTmaSpinLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+enum { kTileNone = 0, kTileBulk = 1, kTileRagged = 2, kTileBad = 3 };
+
+// What the producer thread decided about one tile, published to the CTA through shared memory.
+struct TileSlot {
+    float* master;
+    float* exp_avg;
+    float* exp_avg_sq;
+    void* lowp;
+    const ElxSeg* segs;
+    int64_t e0, e1;
+    int64_t push_elem;   // element offset of this tile inside every rank's gather slab (push all-gather)
+    int n_segs;
+    int group;
+    int kind;
+    int pad;
+};
+
+template <int DT>
+struct TmaStage {
+    static constexpr int kLowpBytes = kTile * Lp<DT>::kBytes;
+    static constexpr int kF32Bytes = kTile * 4;
+    static constexpr int kBytes = kLowpBytes + 3 * kF32Bytes;
+};
+
+// Producer-side (one thread) chunk and segment lookup with its own register cursors.
+struct ProducerCursor {
+    int64_t t0 = 0, t1 = 0;
+    int index = -1;
+    bool vec_ok = false;
+    ElxChunkDesc d;
+    int64_t seg_b = 0, seg_e = 0;
+    int seg_group = -1;
+    int seg_chunk = -1;
+};
+
+template <int DT>
+__device__ __forceinline__ void classify_tile(const AdamArgs& a, const ElxChunkDesc* __restrict__ descs,
+                                              const ElxSeg* __restrict__ segs, int64_t t, ProducerCursor& pc,
+                                              TileSlot& out) {
+    if (!(t >= pc.t0 && t < pc.t1)) {
+        int lo = a.first, hi = a.first + a.count - 1;
+        while (lo < hi) {
+            int mid = (lo + hi + 1) >> 1;
+            if (descs[mid].tile_begin <= t) lo = mid; else hi = mid - 1;
+        }
+        pc.d = descs[lo];
+        pc.index = lo;
+        pc.t0 = pc.d.tile_begin;
+        pc.t1 = pc.t0 + tiles_of(pc.d.n_shard);
+        const uintptr_t bits = reinterpret_cast<uintptr_t>(pc.d.master) | reinterpret_cast<uintptr_t>(pc.d.exp_avg) |
+                               reinterpret_cast<uintptr_t>(pc.d.exp_avg_sq) |
+                               reinterpret_cast<uintptr_t>(pc.d.grad_param);
+        pc.vec_ok = (bits & 31u) == 0;
+    }
+    if (!(t >= pc.t0 && t < pc.t1) || pc.d.dtype != DT) {
+        out.kind = kTileBad;
+        return;
+    }
+    const int64_t e0 = (t - pc.t0) * kTile;
+    const int64_t e1 = min(e0 + kTile, pc.d.n_shard);
+    const ElxSeg* csegs = segs + pc.d.seg_first;
+    if (pc.seg_chunk != pc.index || e0 < pc.seg_b || e0 >= pc.seg_e) {
+        pc.seg_chunk = pc.index;
+        const int si = find_seg(csegs, pc.d.seg_count, e0);
+        if (si >= 0) {
+            pc.seg_b = csegs[si].begin;
+            pc.seg_e = csegs[si].end;
+            pc.seg_group = csegs[si].group;
+        } else {
+            pc.seg_b = pc.seg_e = 0;
+            pc.seg_group = -1;
+        }
+    }
+    const bool one_group = pc.seg_b <= e0 && e1 <= pc.seg_e && pc.seg_group >= 0 && pc.seg_group < a.n_groups;
+    out.master = pc.d.master;
+    out.exp_avg = pc.d.exp_avg;
+    out.exp_avg_sq = pc.d.exp_avg_sq;
+    out.lowp = pc.d.grad_param;
+    out.segs = csegs;
+    out.n_segs = pc.d.seg_count;
+    out.e0 = e0;
+    out.e1 = e1;
+    out.group = pc.seg_group;
+    out.push_elem = a.push.world > 0 ? push_base_elem(a, pc.index, pc.d.n_shard) + e0 : 0;
+    const bool push_ok = a.push.world == 0 || (out.push_elem & 15) == 0;   // bulk copies need 16-byte alignment
+    out.kind = (e1 - e0 == kTile && pc.vec_ok && one_group && push_ok) ? kTileBulk : kTileRagged;
+}
+
+template <int DT, int MATH>
+__global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_constant__ AdamArgs a) {
+    using Stage = TmaStage<DT>;
+    extern __shared__ __align__(128) unsigned char s_dyn[];
+    __shared__ GroupK s_group[kMaxGroups];
+    __shared__ TileSlot s_slot[kTmaStages];
+    __shared__ __align__(8) uint64_t s_full[kTmaStages];
+    __shared__ int s_abort;
+
+    const ElxChunkDesc* __restrict__ descs = a.inline_tables ? &a.one_desc : a.descs;
+    const ElxSeg* __restrict__ segs = a.inline_tables ? &a.one_seg : a.segs;
+    const ElxHyper* __restrict__ hyper = a.inline_tables ? &a.one_hyper : a.hyper;
+    ElxCtl* ctl = a.ctl;
+
+    if (ctl->skip != 0) {
+        // skipped step: copy-back only, with direct accesses (6 bytes per element, no staging needed)
+        __shared__ ChunkCursor s_cur;
+        cursor_reset(s_cur);
+        const bool bad = copyback_tiles<DT, kTile / kTmaThreads>(a, descs, s_cur);
+        if (__ballot_sync(0xFFFFFFFFu, bad) && (threadIdx.x & 31) == 0) atomicOr(&ctl->status, ELX_STAT_BAD_DESC);
+        return;
+    }
+
+    const float div = ctl->div_scale;
+    const float inv_div = ctl->inv_div;
+    const int div_mode = div > 0.0f ? (inv_div != 0.0f ? kMulInv : kTrueDiv) : kNoDiv;
+    const int step = ctl->step;
+    for (int gi = threadIdx.x; gi < a.n_groups; gi += blockDim.x) s_group[gi] = derive_group(hyper[gi], step);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTmaStages; ++s) mbar_init(&s_full[s], 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int64_t tile_lo = descs[a.first].tile_begin;
+    const int64_t my_tiles = blockIdx.x < a.n_tiles ? (a.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    ProducerCursor pc;
+    float nan_acc = 0.0f;
+    bool bad_desc = false;
+
+    // producer: classify tile k of this CTA, publish it in its stage's slot, start its loads
+    auto produce = [&](int64_t k) {
+        const int s = static_cast<int>(k % kTmaStages);
+        TileSlot slot;
+        slot.kind = kTileNone;
+        classify_tile<DT>(a, descs, segs, tile_lo + blockIdx.x + k * gridDim.x, pc, slot);
+        s_slot[s] = slot;
+        if (slot.kind == kTileBulk) {
+            unsigned char* base = s_dyn + static_cast<size_t>(s) * Stage::kBytes;
+            mbar_arrive_expect_tx(&s_full[s], Stage::kBytes);
+            bulk_g2s(base, static_cast<const char*>(slot.lowp) + slot.e0 * Lp<DT>::kBytes, Stage::kLowpBytes, &s_full[s]);
+            bulk_g2s(base + Stage::kLowpBytes, slot.master + slot.e0, Stage::kF32Bytes, &s_full[s]);
+            bulk_g2s(base + Stage::kLowpBytes + Stage::kF32Bytes, slot.exp_avg + slot.e0, Stage::kF32Bytes, &s_full[s]);
+            bulk_g2s(base + Stage::kLowpBytes + 2 * Stage::kF32Bytes, slot.exp_avg_sq + slot.e0, Stage::kF32Bytes,
+                     &s_full[s]);
+        } else {
+            mbar_arrive(&s_full[s]);   // nothing to load: the phase completes at once and publishes the slot
+        }
+    };
+
+    if (threadIdx.x == 0) {
+        for (int64_t k = 0; k < my_tiles && k < kTmaStages - 1; ++k) produce(k);
+    }
+
+    int64_t k = 0;
+    for (; k < my_tiles; ++k) {
+        const int s = static_cast<int>(k % kTmaStages);
+        const uint32_t parity = static_cast<uint32_t>((k / kTmaStages) & 1);
+        if (!mbar_wait_bounded(&s_full[s], parity)) s_abort = 1;
+        __syncthreads();
+        if (s_abort) break;
+        const TileSlot slot = s_slot[s];
+        unsigned char* base = s_dyn + static_cast<size_t>(s) * Stage::kBytes;
+
+        if (slot.kind == kTileBulk) {
+            const GroupK k_ = s_group[slot.group];
+            float* sp = reinterpret_cast<float*>(base + Stage::kLowpBytes);
+            float* sm = sp + kTile;
+            float* sv = sm + kTile;
+            // a thread owns 2 x 4 consecutive elements, 2048 apart: conflict-free 128-bit shared accesses
+#pragma unroll
+            for (int h = 0; h < kTile / (kTmaThreads * 4); ++h) {
+                const int e = h * (kTmaThreads * 4) + threadIdx.x * 4;
+                float4 p = *reinterpret_cast<float4*>(sp + e);
+                float4 m = *reinterpret_cast<float4*>(sm + e);
+                float4 v = *reinterpret_cast<float4*>(sv + e);
+                float g[4];
+                if constexpr (DT == ELX_F32) {
+                    const float4 gg = *reinterpret_cast<const float4*>(base + static_cast<size_t>(e) * 4);
+                    g[0] = gg.x; g[1] = gg.y; g[2] = gg.z; g[3] = gg.w;
+                } else {
+                    const uint2 gg = *reinterpret_cast<const uint2*>(base + static_cast<size_t>(e) * 2);
+                    const float2 a0 = Lp<DT>::unpack2(gg.x), a1 = Lp<DT>::unpack2(gg.y);
+                    g[0] = a0.x; g[1] = a0.y; g[2] = a1.x; g[3] = a1.y;
+                }
+                float pp[4] = {p.x, p.y, p.z, p.w}, mm[4] = {m.x, m.y, m.z, m.w}, vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    nan_acc = fmaf(0.0f, g[j], nan_acc);
+                    adam_elem<MATH>(pp[j], mm[j], vv[j], g[j], k_, div_mode, div, inv_div);
+                }
+                *reinterpret_cast<float4*>(sp + e) = make_float4(pp[0], pp[1], pp[2], pp[3]);
+                *reinterpret_cast<float4*>(sm + e) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+                *reinterpret_cast<float4*>(sv + e) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+                if constexpr (DT == ELX_F32) {
+                    *reinterpret_cast<float4*>(base + static_cast<size_t>(e) * 4) = make_float4(pp[0], pp[1], pp[2], pp[3]);
+                } else {
+                    uint2 out;
+                    out.x = Lp<DT>::pack2(pp[0], pp[1]);
+                    out.y = Lp<DT>::pack2(pp[2], pp[3]);
+                    *reinterpret_cast<uint2*>(base + static_cast<size_t>(e) * 2) = out;
+                }
+            }
+            fence_async_smem();   // the bulk stores below read what the threads just wrote
+        } else if (slot.kind == kTileRagged) {
+            typename Lp<DT>::T* gp = static_cast<typename Lp<DT>::T*>(slot.lowp);
+            for (int64_t e = slot.e0 + threadIdx.x; e < slot.e1; e += blockDim.x) {
+                float p = slot.master[e];
+                const int si = find_seg(slot.segs, slot.n_segs, e);
+                if (si >= 0 && e < slot.segs[si].end) {
+                    const int ge = slot.segs[si].group;
+                    if (ge >= 0 && ge < a.n_groups) {
+                        const GroupK k_ = s_group[ge];
+                        float g = Lp<DT>::to_float(gp[e]);
+                        float m = slot.exp_avg[e], v = slot.exp_avg_sq[e];
+                        nan_acc = fmaf(0.0f, g, nan_acc);
+                        adam_elem<MATH>(p, m, v, g, k_, div_mode, div, inv_div);
+                        slot.master[e] = p;
+                        slot.exp_avg[e] = m;
+                        slot.exp_avg_sq[e] = v;
+                    }
+                }
+                const typename Lp<DT>::T val = Lp<DT>::from_float(p);
+                gp[e] = val;
+                for (int j = 0; j < a.push.world; ++j)
+                    static_cast<typename Lp<DT>::T*>(a.push.base[j])[slot.push_elem + (e - slot.e0)] = val;
+            }
+        } else if (slot.kind == kTileBad) {
+            bad_desc = true;
+        }
+        __syncthreads();   // the stage is fully written (bulk) / fully consumed
+
+        if (threadIdx.x == 0) {
+            if (slot.kind == kTileBulk) {
+                bulk_s2g(static_cast<char*>(slot.lowp) + slot.e0 * Lp<DT>::kBytes, base, Stage::kLowpBytes);
+                bulk_s2g(slot.master + slot.e0, base + Stage::kLowpBytes, Stage::kF32Bytes);
+                bulk_s2g(slot.exp_avg + slot.e0, base + Stage::kLowpBytes + Stage::kF32Bytes, Stage::kF32Bytes);
+                bulk_s2g(slot.exp_avg_sq + slot.e0, base + Stage::kLowpBytes + 2 * Stage::kF32Bytes, Stage::kF32Bytes);
+                // push all-gather: the same 8 KB of refreshed parameters to every rank's gather block,
+                // plain (non-multicast) bulk stores, W - 1 of them crossing NVLink
+                for (int j = 0; j < a.push.world; ++j)
+                    bulk_s2g(static_cast<char*>(a.push.base[j]) + slot.push_elem * Lp<DT>::kBytes, base,
+                             Stage::kLowpBytes);
+            }
+            bulk_commit();
+            if (k + kTmaStages - 1 < my_tiles) {
+                bulk_wait_read<1>();   // the stage of tile k-1 has been read out by its stores
+                produce(k + kTmaStages - 1);
+            }
+        }
+    }
+    if (threadIdx.x == 0) {
+        if (s_abort) {
+            // gave up on tile k: the loads already issued for the tiles after it still target this CTA's
+            // shared memory, so wait (bounded again) for them before the CTA may exit
+            for (int64_t j = k; j < my_tiles && j < k + kTmaStages - 1; ++j)
+                (void)mbar_wait_bounded(&s_full[j % kTmaStages], static_cast<uint32_t>((j / kTmaStages) & 1));
+            atomicOr(&ctl->status, ELX_STAT_TIMEOUT);
+        }
+        bulk_wait_all();
+    }
+
+    const bool late = nan_acc != nan_acc;
+    const unsigned ballot = __ballot_sync(0xFFFFFFFFu, late);
+    const unsigned ballot_desc = __ballot_sync(0xFFFFFFFFu, bad_desc);
+    if ((threadIdx.x & 31) == 0) {
+        if (ballot) {
+            atomicOr(&ctl->late_inf, 1u);
+            atomicOr(&ctl->status, ELX_STAT_LATE_INF);
+        }
+        if (ballot_desc) atomicOr(&ctl->status, ELX_STAT_BAD_DESC);
+    }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256) cast_kernel(const float* __restrict__ src, void* dst, int64_t n, int vec_ok) {
+    constexpr int EPT = 16;
+    const int64_t n_full = vec_ok ? n / kTile : 0;
+    for (int64_t t = blockIdx.x; t < n_full; t += gridDim.x) {
+        float p[EPT];
+        load_f32<EPT>(src, t * kTile, p);
+        store_lowp<DT, EPT>(dst, t * kTile, p);
+    }
+    typename Lp<DT>::T* out = static_cast<typename Lp<DT>::T*>(dst);
+    for (int64_t e = n_full * kTile + blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; e < n;
+         e += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        out[e] = Lp<DT>::from_float(src[e]);
+}
+
+template <int DT, int EPT, int MATH, int MINB>
+int launch_adam_inst(const AdamArgs& a, cudaStream_t s) {
+    constexpr int threads = kTile / EPT;
+    static const int resident = resident_ctas(adam_kernel<DT, EPT, MATH, MINB>, threads);
+    const int grid = grid_for(a.n_tiles, capped(resident, g_tune.adam_ctas_per_sm));
+    if (grid < 0) return grid;
+    adam_kernel<DT, EPT, MATH, MINB><<<grid, threads, 0, s>>>(a);
+    return record_cuda(cudaGetLastError());
+}
+
+template <int DT, int EPT, int MATH>
+int launch_adam_minb(const AdamArgs& a, cudaStream_t s) {
+    return launch_adam_inst<DT, EPT, MATH, 2>(a, s);
+}
+
+template <int DT, int MATH>
+int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
+    constexpr int smem = kTmaStages * TmaStage<DT>::kBytes;
+    // the opt-in to more than 48 KB of dynamic shared memory is per device: once for each ordinal
+    static bool opted_in[64];
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        (void)cudaGetLastError();
+        return ELX_ERR_NODEVICE;
+    }
+    if (!opted_in[dev]) {
+        const cudaError_t attr =
+            cudaFuncSetAttribute(adam_tma_kernel<DT, MATH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (attr != cudaSuccess) {
+            const int rc = record_cuda(attr);
+            (void)cudaGetLastError();
+            return rc;
+        }
+        opted_in[dev] = true;
+    }
+    const int grid = grid_for(a.n_tiles, 1);
+    if (grid < 0) return grid;
+    adam_tma_kernel<DT, MATH><<<grid, kTmaThreads, smem, s>>>(a);
+    return record_cuda(cudaGetLastError());
+}
+
+template <int DT>
+int launch_adam_dt(const AdamArgs& a, cudaStream_t s) {
+    const bool precise = g_tune.math_mode == 1;
+    if (g_tune.adam_variant == 1 || a.push.world > 0)
+        return precise ? launch_adam_tma<DT, 1>(a, s) : launch_adam_tma<DT, 2>(a, s);
+    if (g_tune.adam_threads == 256)
+        return precise ? launch_adam_minb<DT, 16, 1>(a, s) : launch_adam_minb<DT, 16, 2>(a, s);
+    return precise ? launch_adam_minb<DT, 8, 1>(a, s) : launch_adam_minb<DT, 8, 2>(a, s);
+}
+
+int launch_adam(const AdamArgs& a, int dtype, cudaStream_t s) {
+    switch (dtype) {
+        case ELX_F16: return launch_adam_dt<ELX_F16>(a, s);
+        case ELX_BF16: return launch_adam_dt<ELX_BF16>(a, s);
+        case ELX_F32: return launch_adam_dt<ELX_F32>(a, s);
+    }
+    return ELX_ERR_DTYPE;
+}
+
+}  // namespace
+
+extern "C" {
+
+int elx_adam_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype, const ElxSeg* segs,
+                   const ElxHyper* hyper, int n_groups, ElxCtl* ctl, void* stream) {
+    if (!descs || !ctl) return ELX_ERR_NULL;
+    if (n_groups > 0 && (!segs || !hyper)) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (first < 0 || count < 0 || n_tiles < 0 || n_groups < 0) return ELX_ERR_SIZE;
+    if (n_groups > kMaxGroups) return ELX_ERR_CAPACITY;
+    if (!aligned(descs, 8) || !aligned(ctl, 16) || (segs && !aligned(segs, 8)) || (hyper && !aligned(hyper, 4)))
+        return ELX_ERR_ALIGN;
+    if (count == 0 || n_tiles == 0) return ELX_OK;
+    AdamArgs a;
+    memset(&a, 0, sizeof(a));
+    a.descs = descs;
+    a.segs = segs;
+    a.hyper = hyper;
+    a.ctl = ctl;
+    a.first = first;
+    a.count = count;
+    a.n_groups = n_groups;
+    a.n_tiles = n_tiles;
+    return launch_adam(a, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int elx_adam_multi_push(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                        const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl, ElxPeerTable gather,
+                        const int64_t* block_off, void* stream) {
+    if (!descs || !ctl || !block_off) return ELX_ERR_NULL;
+    if (n_groups > 0 && (!segs || !hyper)) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (first < 0 || count < 0 || n_tiles < 0 || n_groups < 0) return ELX_ERR_SIZE;
+    if (n_groups > kMaxGroups) return ELX_ERR_CAPACITY;
+    const int rc = peer_table_ok(gather);
+    if (rc != ELX_OK) return rc;
+    if (!aligned(descs, 8) || !aligned(ctl, 16) || !aligned(block_off, 8) || (segs && !aligned(segs, 8)) ||
+        (hyper && !aligned(hyper, 4)))
+        return ELX_ERR_ALIGN;
+    if (count == 0 || n_tiles == 0) return ELX_OK;
+    AdamArgs a;
+    memset(&a, 0, sizeof(a));
+    a.descs = descs;
+    a.segs = segs;
+    a.hyper = hyper;
+    a.ctl = ctl;
+    a.first = first;
+    a.count = count;
+    a.n_groups = n_groups;
+    a.n_tiles = n_tiles;
+    a.push = gather;
+    a.push_off = block_off;
+    return launch_adam(a, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int elx_adam_chunk(float* master, float* exp_avg, float* exp_avg_sq, void* grad_param, int dtype, int64_t n_valid,
+                   int64_t n_shard, ElxHyper hyper, ElxCtl* ctl, void* stream) {
+    if (!master || !exp_avg || !exp_avg_sq || !grad_param || !ctl) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (n_shard < 0 || n_valid < 0 || n_valid > n_shard) return ELX_ERR_SIZE;
+    if (!aligned(master, 4) || !aligned(exp_avg, 4) || !aligned(exp_avg_sq, 4) ||
+        !aligned(grad_param, dtype_bytes(dtype)) || !aligned(ctl, 16))
+        return ELX_ERR_ALIGN;
+    if (n_shard == 0) return ELX_OK;
+    AdamArgs a;
+    memset(&a, 0, sizeof(a));
+    a.ctl = ctl;
+    a.first = 0;
+    a.count = 1;
+    a.n_groups = 1;
+    a.inline_tables = 1;
+    a.n_tiles = (n_shard + kTile - 1) / kTile;
+    a.one_desc.master = master;
+    a.one_desc.exp_avg = exp_avg;
+    a.one_desc.exp_avg_sq = exp_avg_sq;
+    a.one_desc.grad_param = grad_param;
+    a.one_desc.n_shard = n_shard;
+    a.one_desc.n_valid = n_valid;
+    a.one_desc.tile_begin = 0;
+    a.one_desc.seg_first = 0;
+    a.one_desc.seg_count = n_valid > 0 ? 1 : 0;
+    a.one_desc.dtype = dtype;
+    a.one_seg.begin = 0;
+    a.one_seg.end = n_valid;
+    a.one_seg.group = 0;
+    a.one_hyper = hyper;
+    return launch_adam(a, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int elx_cast_copyback(const float* master, void* dst, int dtype, int64_t n, void* stream) {
+    if (!master || !dst) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (n < 0) return ELX_ERR_SIZE;
+    if (!aligned(master, 4) || !aligned(dst, dtype_bytes(dtype))) return ELX_ERR_ALIGN;
+    if (n == 0) return ELX_OK;
+    const int vec_ok = aligned(master, 32) && aligned(dst, 32);
+    const int grid = grid_for((n + kTile - 1) / kTile, 8);
+    if (grid < 0) return grid;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case ELX_F16: cast_kernel<ELX_F16><<<grid, 256, 0, s>>>(master, dst, n, vec_ok); break;
+        case ELX_BF16: cast_kernel<ELX_BF16><<<grid, 256, 0, s>>>(master, dst, n, vec_ok); break;
+        case ELX_F32: cast_kernel<ELX_F32><<<grid, 256, 0, s>>>(master, dst, n, vec_ok); break;
+    }
+    return record_cuda(cudaGetLastError());
+}
+
+}  // extern "C"

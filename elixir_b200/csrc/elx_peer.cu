@@ -1,0 +1,356 @@
+// Part of the elixir_b200 CUDA library (C ABI: include/elixir_b200.h).  See elx_common.cuh for the
+// overview of the kernels and of how the sources are divided.
+#include "elx_common.cuh"
+
+using namespace elx;
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// NVLink: pull reduce-scatter fused with the probe, and the cross-rank barrier
+// ------------------------------------------------------------------------------------------------
+//
+// Every rank keeps its replicated gradient blocks in a slab that all ranks of the box can address
+// (peer-mapped memory).  Rank r produces its shard of a chunk by READING the r-th slice of that
+// chunk's block from every rank with ordinary loads (its own slice from local HBM, W - 1 slices over
+// NVLink), summing float(x) * (1/W) in rank order in fp32, rounding once to the chunk dtype, storing
+// the shard and probing the rounded result for inf/nan in the same pass.  No TMA, no multicast.
+
+struct PullArgs {
+    const ElxChunkDesc* descs;
+    uint32_t* chunk_flags;
+    ElxCtl* ctl;
+    ElxPeerTable grads;
+    const int64_t* block_off;   // per descriptor: element offset of the chunk's block inside the slabs
+    int first, count;
+    int64_t n_tiles;
+};
+
+// kWorld > 0: the group size is a compile-time constant, so the loads from all ranks are issued back to
+// back before the first one is consumed (kWorld x 32 bytes in flight per thread); 0 = any group size.
+template <int DT, int kWorld>
+__global__ void __launch_bounds__(256) pull_reduce_kernel(const __grid_constant__ PullArgs a) {
+    constexpr int EPT = 16;                                      // consecutive elements per thread
+    constexpr int WORDS = EPT * Lp<DT>::kBytes / 4;              // 8 (16-bit) or 16 (fp32)
+    using T = typename Lp<DT>::T;
+    __shared__ ChunkCursor s_cur;
+    cursor_reset(s_cur);
+    const ElxChunkDesc* __restrict__ descs = a.descs;
+    const int64_t tile_lo = descs[a.first].tile_begin;
+    const int world = kWorld > 0 ? kWorld : a.grads.world;
+    const int rank = a.grads.rank;
+    const float inv_w = 1.0f / static_cast<float>(world);
+    const int lane = threadIdx.x & 31;
+    bool bad_desc = false;
+
+    for (int64_t it = blockIdx.x; it < a.n_tiles; it += gridDim.x) {
+        const int64_t t = tile_lo + it;
+        if (!locate_chunk(descs, a.first, a.count, t, s_cur) || s_cur.d.dtype != DT) {
+            bad_desc = true;
+            continue;
+        }
+        const int64_t n_shard = s_cur.d.n_shard, n_valid = s_cur.d.n_valid;
+        const int64_t e0 = (t - s_cur.t0) * kTile;
+        const int64_t e1 = min(e0 + kTile, n_shard);
+        const int64_t src0 = a.block_off[s_cur.index] + static_cast<int64_t>(rank) * n_shard;   // element offset
+        void* const dst = s_cur.d.grad_param;
+        const bool all_valid = e0 + kTile <= n_valid, none_valid = e0 >= n_valid;
+        uint32_t bad = 0;
+        if ((e1 - e0 == kTile) && (all_valid || none_valid) && (src0 & 15) == 0 &&
+            (reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
+            const int64_t mine = e0 + static_cast<int64_t>(threadIdx.x) * EPT;
+            float acc[EPT];
+#pragma unroll
+            for (int i = 0; i < EPT; ++i) acc[i] = 0.0f;
+            auto accumulate = [&](const uint32_t (&w)[WORDS]) {
+                if constexpr (DT == ELX_F32) {
+#pragma unroll
+                    for (int i = 0; i < WORDS; ++i) acc[i] = fmaf(__uint_as_float(w[i]), inv_w, acc[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < WORDS; ++i) {
+                        const float2 f = Lp<DT>::unpack2(w[i]);
+                        acc[2 * i] = fmaf(f.x, inv_w, acc[2 * i]);
+                        acc[2 * i + 1] = fmaf(f.y, inv_w, acc[2 * i + 1]);
+                    }
+                }
+            };
+            if constexpr (kWorld > 0) {
+                uint32_t raw[kWorld][WORDS];
+#pragma unroll
+                for (int j = 0; j < kWorld; ++j)
+                    ld_words<WORDS>(static_cast<const char*>(a.grads.base[j]) + (src0 + mine) * Lp<DT>::kBytes, raw[j]);
+                // keep every rank's words live until all loads are issued: the empty asm statements are ordered
+                // after the (volatile) loads, so the compiler cannot fold a load into its first use
+#pragma unroll
+                for (int j = 0; j < kWorld; ++j) {
+#pragma unroll
+                    for (int i = 0; i < WORDS; i += 8)
+                        asm volatile(""
+                                     : "+r"(raw[j][i]), "+r"(raw[j][i + 1]), "+r"(raw[j][i + 2]), "+r"(raw[j][i + 3]),
+                                       "+r"(raw[j][i + 4]), "+r"(raw[j][i + 5]), "+r"(raw[j][i + 6]), "+r"(raw[j][i + 7]));
+                }
+#pragma unroll
+                for (int j = 0; j < kWorld; ++j) accumulate(raw[j]);    // rank order
+            } else {
+                for (int j = 0; j < world; ++j) {
+                    uint32_t raw[WORDS];
+                    ld_words<WORDS>(static_cast<const char*>(a.grads.base[j]) + (src0 + mine) * Lp<DT>::kBytes, raw);
+                    accumulate(raw);
+                }
+            }
+            uint32_t out[WORDS];
+            if constexpr (DT == ELX_F32) {
+#pragma unroll
+                for (int i = 0; i < WORDS; ++i) out[i] = __float_as_uint(acc[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < WORDS; ++i) out[i] = Lp<DT>::pack2(acc[2 * i], acc[2 * i + 1]);
+            }
+            st_words<WORDS>(static_cast<char*>(dst) + mine * Lp<DT>::kBytes, out);
+            if (all_valid) {
+#pragma unroll
+                for (int i = 0; i < WORDS; ++i) bad |= Lp<DT>::nonfinite_word(out[i]);
+            }
+        } else {
+            T* out = static_cast<T*>(dst);
+            for (int64_t e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
+                float acc = 0.0f;
+                for (int j = 0; j < world; ++j)
+                    acc = fmaf(Lp<DT>::to_float(static_cast<const T*>(a.grads.base[j])[src0 + e]), inv_w, acc);
+                const T val = Lp<DT>::from_float(acc);
+                out[e] = val;
+                if (e < n_valid && Lp<DT>::nonfinite(val)) bad = 1;
+            }
+        }
+        const unsigned any_bad = __ballot_sync(0xFFFFFFFFu, bad != 0);
+        if (any_bad && lane == 0) {
+            if (a.chunk_flags) atomicOr(&a.chunk_flags[s_cur.index], 1u);
+            if (a.ctl) atomicOr(&a.ctl->found_inf, 1u);
+        }
+    }
+    const unsigned ballot_desc = __ballot_sync(0xFFFFFFFFu, bad_desc);
+    if (ballot_desc && lane == 0 && a.ctl) atomicOr(&a.ctl->status, ELX_STAT_BAD_DESC);
+}
+
+template <int DT, int kWorld>
+int launch_pull_inst(const PullArgs& a, cudaStream_t s) {
+    static const int resident = resident_ctas(pull_reduce_kernel<DT, kWorld>, 256);
+    const int grid = grid_for(a.n_tiles, capped(resident, g_tune.pull_ctas_per_sm));
+    if (grid < 0) return grid;
+    pull_reduce_kernel<DT, kWorld><<<grid, 256, 0, s>>>(a);
+    return record_cuda(cudaGetLastError());
+}
+
+template <int DT>
+int launch_pull(const PullArgs& a, cudaStream_t s) {
+    switch (a.grads.world) {
+        case 2: return launch_pull_inst<DT, 2>(a, s);
+        case 4: return launch_pull_inst<DT, 4>(a, s);
+        case 8: return launch_pull_inst<DT, 8>(a, s);
+    }
+    return launch_pull_inst<DT, 0>(a, s);
+}
+
+// Flag region of one rank (peer-mapped): for each parity of the epoch and each sender, {epoch, word}.
+// A rank can run at most one barrier ahead of a peer, so two parities are enough.
+__device__ __forceinline__ uint32_t* flag_slot(void* region, uint32_t epoch, int sender) {
+    return static_cast<uint32_t*>(region) + ((epoch & 1u) * ELX_MAX_PEERS + sender) * 2;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// One warp.  Lane j tells rank j "rank `rank` reached barrier `epoch`" (with this rank's overflow word
+// riding along), then waits — for at most timeout_ns — until rank j has told this rank the same.
+// On expiry the sticky ELX_STAT_TIMEOUT bit is raised and the kernel returns; it never traps.
+__global__ void peer_barrier_kernel(ElxPeerTable flags, uint32_t epoch, ElxCtl* ctl, int exchange_overflow,
+                                    uint64_t timeout_ns) {
+    const int j = threadIdx.x;
+    const int world = flags.world, rank = flags.rank;
+    uint32_t seen_inf = 0;
+    bool expired = false;
+    if (j < world) {
+        const uint32_t mine = (exchange_overflow && ctl) ? ctl->found_inf : 0u;
+        __threadfence_system();   // everything this rank wrote before the barrier is visible to the peers first
+        uint32_t* out = flag_slot(flags.base[j], epoch, rank);
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(out + 1), "r"(mine) : "memory");
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(out), "r"(epoch) : "memory");
+        const uint32_t* in = flag_slot(flags.base[rank], epoch, j);
+        const uint64_t t_start = global_timer_ns();
+        for (;;) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(in) : "memory");
+            if (v == epoch) break;
+            if (global_timer_ns() - t_start > timeout_ns) {
+                expired = true;
+                break;
+            }
+            __nanosleep(200);
+        }
+        if (!expired) asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(seen_inf) : "l"(in + 1) : "memory");
+    }
+    const unsigned any_inf = __ballot_sync(0xFFFFFFFFu, seen_inf != 0);
+    const unsigned any_expired = __ballot_sync(0xFFFFFFFFu, expired);
+    if (j == 0 && ctl) {
+        if (exchange_overflow && any_inf) atomicOr(&ctl->found_inf, 1u);
+        if (any_expired) atomicOr(&ctl->status, ELX_STAT_TIMEOUT);
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int elx_enable_peer_access(int peer_device) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        record_cuda(e);
+        (void)cudaGetLastError();
+        return ELX_ERR_NODEVICE;
+    }
+    if (peer_device == dev) return ELX_OK;
+    int can = 0;
+    e = cudaDeviceCanAccessPeer(&can, dev, peer_device);
+    if (e != cudaSuccess || !can) {
+        if (e != cudaSuccess) record_cuda(e);
+        (void)cudaGetLastError();
+        return ELX_ERR_ARG;
+    }
+    e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        (void)cudaGetLastError();
+        return ELX_OK;
+    }
+    return record_cuda(e);
+}
+
+int elx_peer_alloc(int64_t bytes, void** ptr, void* handle) {
+    if (!ptr || !handle) return ELX_ERR_NULL;
+    if (bytes <= 0) return ELX_ERR_SIZE;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, static_cast<size_t>(bytes));
+    if (e != cudaSuccess) {
+        const int rc = record_cuda(e);
+        (void)cudaGetLastError();
+        return rc;
+    }
+    cudaIpcMemHandle_t h;
+    e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        const int rc = record_cuda(e);
+        (void)cudaGetLastError();
+        (void)cudaFree(p);
+        return rc;
+    }
+    memcpy(handle, &h, sizeof(h));
+    *ptr = p;
+    return ELX_OK;
+}
+
+int elx_peer_free(void* ptr) {
+    if (!ptr) return ELX_ERR_NULL;
+    const cudaError_t e = cudaFree(ptr);
+    if (e != cudaSuccess) {
+        const int rc = record_cuda(e);
+        (void)cudaGetLastError();
+        return rc;
+    }
+    return ELX_OK;
+}
+
+int elx_ipc_open(const void* handle, void** base) {
+    if (!handle || !base) return ELX_ERR_NULL;
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(h) == 64, "cudaIpcMemHandle_t is 64 bytes");
+    memcpy(&h, handle, sizeof(h));
+    void* ptr = nullptr;
+    // opened with the ACCESSING device current: the driver maps the exporter's memory for this device and
+    // turns peer access on as needed
+    const cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+        const int rc = record_cuda(e);
+        (void)cudaGetLastError();
+        return rc;
+    }
+    *base = ptr;
+    return ELX_OK;
+}
+
+int elx_peek_u32(const void* device_ptr, uint32_t* value) {
+    if (!device_ptr || !value) return ELX_ERR_NULL;
+    cudaPointerAttributes attr;
+    cudaError_t e = cudaPointerGetAttributes(&attr, device_ptr);
+    if (e != cudaSuccess || attr.type != cudaMemoryTypeDevice) {
+        if (e != cudaSuccess) record_cuda(e);
+        (void)cudaGetLastError();
+        return ELX_ERR_ARG;
+    }
+    e = cudaMemcpy(value, device_ptr, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        const int rc = record_cuda(e);
+        (void)cudaGetLastError();
+        return rc;
+    }
+    return ELX_OK;
+}
+
+int elx_ipc_close(void* base) {
+    if (!base) return ELX_ERR_NULL;
+    const cudaError_t e = cudaIpcCloseMemHandle(base);
+    if (e != cudaSuccess) {
+        const int rc = record_cuda(e);
+        (void)cudaGetLastError();
+        return rc;
+    }
+    return ELX_OK;
+}
+
+int elx_peer_barrier(ElxPeerTable flags, uint32_t epoch, ElxCtl* ctl, int exchange_overflow, int timeout_ms,
+                     void* stream) {
+    const int rc = peer_table_ok(flags);
+    if (rc != ELX_OK) return rc;
+    if (ctl && !aligned(ctl, 16)) return ELX_ERR_ALIGN;
+    if (exchange_overflow && !ctl) return ELX_ERR_NULL;
+    if (timeout_ms <= 0 || epoch == 0) return ELX_ERR_ARG;
+    peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, epoch, ctl, exchange_overflow,
+                                                                      static_cast<uint64_t>(timeout_ms) * 1000000ull);
+    return record_cuda(cudaGetLastError());
+}
+
+int elx_pull_reduce_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                          ElxPeerTable grads, const int64_t* block_off, uint32_t* chunk_flags, ElxCtl* ctl,
+                          void* stream) {
+    if (!descs || !block_off) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (first < 0 || count < 0 || n_tiles < 0) return ELX_ERR_SIZE;
+    const int rc = peer_table_ok(grads);
+    if (rc != ELX_OK) return rc;
+    if (!aligned(descs, 8) || !aligned(block_off, 8) || (chunk_flags && !aligned(chunk_flags, 4)) ||
+        (ctl && !aligned(ctl, 16)))
+        return ELX_ERR_ALIGN;
+    if (count == 0 || n_tiles == 0) return ELX_OK;
+    PullArgs a;
+    memset(&a, 0, sizeof(a));
+    a.descs = descs;
+    a.chunk_flags = chunk_flags;
+    a.ctl = ctl;
+    a.grads = grads;
+    a.block_off = block_off;
+    a.first = first;
+    a.count = count;
+    a.n_tiles = n_tiles;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case ELX_F16: return launch_pull<ELX_F16>(a, s);
+        case ELX_BF16: return launch_pull<ELX_BF16>(a, s);
+        case ELX_F32: return launch_pull<ELX_F32>(a, s);
+    }
+    return ELX_ERR_DTYPE;
+}
+
+}  // extern "C"

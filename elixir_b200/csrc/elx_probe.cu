@@ -1,0 +1,398 @@
+// Part of the elixir_b200 CUDA library (C ABI: include/elixir_b200.h).  See elx_common.cuh for the
+// overview of the kernels and of how the sources are divided.
+#include "elx_common.cuh"
+
+using namespace elx;
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// probe (+ copy, + sum of squares)
+// ------------------------------------------------------------------------------------------------
+
+struct ProbeArgs {
+    const ElxChunkDesc* descs;
+    uint32_t* chunk_flags;   // indexed by descriptor index, may be null
+    uint32_t* one_flag;      // single-shard form, may be null
+    ElxCtl* ctl;             // may be null
+    float* scratch;          // per-tile partial sums of squares (NORM only)
+    void* copy_dst;          // COPY only (single-shard form)
+    int first, count, inline_tables, pad;
+    int64_t n_tiles;
+    ElxChunkDesc one_desc;
+};
+
+// kProbeUnroll = tiles whose loads are in flight together in one CTA iteration
+template <int DT, bool COPY, bool NORM, int kProbeUnroll>
+__global__ void __launch_bounds__(kProbeThreads) probe_kernel(const __grid_constant__ ProbeArgs a) {
+    constexpr int EPT = kTile / kProbeThreads;                   // 16
+    constexpr int WORDS = EPT * Lp<DT>::kBytes / 4;              // 8 (16-bit) or 16 (fp32)
+    using T = typename Lp<DT>::T;
+    __shared__ float s_part[kProbeUnroll][kProbeThreads / 32];
+
+    const ElxChunkDesc* __restrict__ descs = a.inline_tables ? &a.one_desc : a.descs;
+    const int64_t tile_lo = descs[a.first].tile_begin;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ ChunkCursor s_cur;
+    cursor_reset(s_cur);
+    bool bad_desc = false;
+
+    const int64_t n_groups_of_tiles = (a.n_tiles + kProbeUnroll - 1) / kProbeUnroll;
+    for (int64_t q = blockIdx.x; q < n_groups_of_tiles; q += gridDim.x) {
+        uint32_t w[kProbeUnroll][WORDS];
+        bool vec[kProbeUnroll];
+        bool probed[kProbeUnroll];
+        int chunk_of[kProbeUnroll];
+        float sq[kProbeUnroll];
+        uint32_t bad[kProbeUnroll];
+
+        // issue every load of the group first, so that they are all in flight together
+#pragma unroll
+        for (int j = 0; j < kProbeUnroll; ++j) {
+            vec[j] = false;
+            probed[j] = false;
+            chunk_of[j] = -1;
+            sq[j] = 0.0f;
+            bad[j] = 0;
+            const int64_t it = q * kProbeUnroll + j;
+            if (it >= a.n_tiles) continue;
+            const int64_t t = tile_lo + it;
+            if (!locate_chunk(descs, a.first, a.count, t, s_cur) || s_cur.d.dtype != DT) {
+                bad_desc = true;
+                continue;
+            }
+            chunk_of[j] = s_cur.index;
+            struct { const void* grad_param; int64_t n_shard, n_valid; } d = {s_cur.d.grad_param, s_cur.d.n_shard,
+                                                                              s_cur.d.n_valid};
+            const int64_t e0 = (t - s_cur.t0) * kTile;
+            const bool dst_ok = !COPY || (reinterpret_cast<uintptr_t>(a.copy_dst) & 31u) == 0;
+            const bool src_ok = (reinterpret_cast<uintptr_t>(d.grad_param) & 31u) == 0;
+            const bool all_valid = e0 + kTile <= d.n_valid;     // every element is probed
+            const bool none_valid = e0 >= d.n_valid;            // padding only: copied, never probed
+            if (!COPY && none_valid) continue;
+            if (src_ok && dst_ok && e0 + kTile <= d.n_shard && (all_valid || none_valid)) {
+                vec[j] = true;
+                probed[j] = all_valid;
+                ld_words<WORDS>(static_cast<const char*>(d.grad_param) +
+                                    (e0 + static_cast<int64_t>(threadIdx.x) * EPT) * Lp<DT>::kBytes, w[j]);
+            } else {
+                // ragged tile: probe [e0, n_valid), copy [e0, n_shard)
+                const T* src = static_cast<const T*>(d.grad_param);
+                const int64_t e1 = min(e0 + kTile, d.n_shard);
+                for (int64_t e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
+                    const T x = src[e];
+                    if (e < d.n_valid) {
+                        if (Lp<DT>::nonfinite(x)) bad[j] = 1;
+                        if (NORM) {
+                            const float f = Lp<DT>::to_float(x);
+                            sq[j] = fmaf(f, f, sq[j]);
+                        }
+                    }
+                    if (COPY) static_cast<T*>(a.copy_dst)[e] = x;
+                }
+            }
+        }
+
+#pragma unroll
+        for (int j = 0; j < kProbeUnroll; ++j) {
+            if (vec[j]) {
+                uint32_t acc = 0;
+#pragma unroll
+                for (int i = 0; i < WORDS; ++i) acc |= Lp<DT>::nonfinite_word(w[j][i]);
+                bad[j] = probed[j] ? acc : 0u;
+                if (NORM && probed[j]) {
+                    float s = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < WORDS; ++i) {
+                        if constexpr (DT == ELX_F32) {
+                            const float f = __uint_as_float(w[j][i]);
+                            s = fmaf(f, f, s);
+                        } else {
+                            const float2 f = Lp<DT>::unpack2(w[j][i]);
+                            s = fmaf(f.x, f.x, s);
+                            s = fmaf(f.y, f.y, s);
+                        }
+                    }
+                    sq[j] = s;
+                }
+                if (COPY) {
+                    const int64_t it = q * kProbeUnroll + j;
+                    // single-shard form: tile index == it
+                    st_words<WORDS>(static_cast<char*>(a.copy_dst) +
+                                        (it * kTile + static_cast<int64_t>(threadIdx.x) * EPT) * Lp<DT>::kBytes, w[j]);
+                }
+            }
+            // warp-reduced overflow report
+            const unsigned any_bad = __ballot_sync(0xFFFFFFFFu, bad[j] != 0);
+            if (any_bad && lane == 0 && chunk_of[j] >= 0) {
+                if (a.chunk_flags) atomicOr(&a.chunk_flags[chunk_of[j]], 1u);
+                if (a.one_flag) atomicOr(a.one_flag, 1u);
+                if (a.ctl) atomicOr(&a.ctl->found_inf, 1u);
+            }
+        }
+
+        if (NORM) {
+            // fixed-order block reduction of each tile's partial: lanes, then warps 0..7
+#pragma unroll
+            for (int j = 0; j < kProbeUnroll; ++j) {
+                float s = sq[j];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xFFFFFFFFu, s, o);
+                if (lane == 0) s_part[j][warp] = s;
+            }
+            __syncthreads();
+            if (threadIdx.x < kProbeUnroll) {
+                const int64_t it = q * kProbeUnroll + threadIdx.x;
+                if (it < a.n_tiles) {
+                    float s = 0.0f;
+                    for (int wi = 0; wi < kProbeThreads / 32; ++wi) s += s_part[threadIdx.x][wi];
+                    a.scratch[it] = s;
+                }
+            }
+            __syncthreads();
+        }
+    }
+
+    const unsigned ballot_desc = __ballot_sync(0xFFFFFFFFu, bad_desc);
+    if (ballot_desc && lane == 0 && a.ctl) atomicOr(&a.ctl->status, ELX_STAT_BAD_DESC);
+}
+
+struct NormArgs {
+    const ElxChunkDesc* descs;
+    const float* scratch;
+    float* chunk_l2sq;   // indexed by descriptor index, may be null
+    float* one_l2sq;     // single-shard form
+    float* total_l2sq;   // may be null
+    int first, count, inline_tables, pad;
+    ElxChunkDesc one_desc;
+};
+
+// One CTA.  Sums each descriptor's per-tile partials in a fixed order (strided per thread, then a
+// binary tree over threads) in double, so that the result does not depend on the probe grid.
+__global__ void __launch_bounds__(256) norm_finalize(const __grid_constant__ NormArgs a) {
+    __shared__ double s_red[256];
+    const ElxChunkDesc* __restrict__ descs = a.inline_tables ? &a.one_desc : a.descs;
+    const int64_t tile_lo = descs[a.first].tile_begin;
+    double total = 0.0;
+    for (int c = a.first; c < a.first + a.count; ++c) {
+        const int64_t b = descs[c].tile_begin - tile_lo;
+        const int64_t n = tiles_of(descs[c].n_shard);
+        double s = 0.0;
+        for (int64_t i = threadIdx.x; i < n; i += blockDim.x) s += static_cast<double>(a.scratch[b + i]);
+        s_red[threadIdx.x] = s;
+        __syncthreads();
+        for (int o = 128; o > 0; o >>= 1) {
+            if (threadIdx.x < o) s_red[threadIdx.x] += s_red[threadIdx.x + o];
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) {
+            const double r = s_red[0];
+            if (a.chunk_l2sq) a.chunk_l2sq[c] = static_cast<float>(r);
+            if (a.one_l2sq) *a.one_l2sq = static_cast<float>(r);
+            total += r;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && a.total_l2sq) *a.total_l2sq = static_cast<float>(total);
+}
+
+template <int DT, bool COPY, bool NORM, int UNROLL>
+int launch_probe_inst(const ProbeArgs& a, cudaStream_t s) {
+    static const int resident = resident_ctas(probe_kernel<DT, COPY, NORM, UNROLL>, kProbeThreads);
+    const int64_t groups = (a.n_tiles + UNROLL - 1) / UNROLL;
+    const int grid = grid_for(groups, capped(resident, g_tune.probe_ctas_per_sm));
+    if (grid < 0) return grid;
+    probe_kernel<DT, COPY, NORM, UNROLL><<<grid, kProbeThreads, 0, s>>>(a);
+    return record_cuda(cudaGetLastError());
+}
+
+template <int DT, bool COPY>
+int launch_probe_norm(const ProbeArgs& a, bool norm, cudaStream_t s) {
+    // fp32 tiles are twice as many bytes: half the unroll keeps the register budget
+    constexpr int kBig = DT == ELX_F32 ? 4 : 8;
+    constexpr int kSmall = DT == ELX_F32 ? 2 : 4;
+    const bool big = g_tune.probe_unroll >= 8;
+    if (norm) return big ? launch_probe_inst<DT, COPY, true, kBig>(a, s) : launch_probe_inst<DT, COPY, true, kSmall>(a, s);
+    return big ? launch_probe_inst<DT, COPY, false, kBig>(a, s) : launch_probe_inst<DT, COPY, false, kSmall>(a, s);
+}
+
+template <bool COPY>
+int launch_probe(const ProbeArgs& a, int dtype, bool norm, cudaStream_t s) {
+    switch (dtype) {
+        case ELX_F16: return launch_probe_norm<ELX_F16, COPY>(a, norm, s);
+        case ELX_BF16: return launch_probe_norm<ELX_BF16, COPY>(a, norm, s);
+        case ELX_F32: return launch_probe_norm<ELX_F32, COPY>(a, norm, s);
+    }
+    return ELX_ERR_DTYPE;
+}
+
+int probe_single(const void* src, void* dst, int dtype, int64_t n_shard, int64_t n_valid, uint32_t* flag,
+                 ElxCtl* ctl, float* l2sq, float* scratch, int64_t scratch_elems, void* stream, bool copy) {
+    if (!src || (copy && !dst)) return ELX_ERR_NULL;
+    if (!flag && !ctl && !l2sq && !copy) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (n_shard < 0 || n_valid < 0 || n_valid > n_shard) return ELX_ERR_SIZE;
+    if (!aligned(src, 32) || (copy && !aligned(dst, 32))) return ELX_ERR_ALIGN;
+    if ((flag && !aligned(flag, 4)) || (ctl && !aligned(ctl, 16)) || (l2sq && !aligned(l2sq, 4))) return ELX_ERR_ALIGN;
+    if (copy) {
+        const char* s0 = static_cast<const char*>(src);
+        const char* d0 = static_cast<const char*>(dst);
+        const int64_t bytes = n_shard * dtype_bytes(dtype);
+        if (s0 < d0 + bytes && d0 < s0 + bytes) return ELX_ERR_ARG;
+    }
+    const int64_t n_tiles = (n_shard + kTile - 1) / kTile;
+    if (l2sq) {
+        if (!scratch) return ELX_ERR_NULL;
+        if (!aligned(scratch, 4)) return ELX_ERR_ALIGN;
+        if (scratch_elems < elx_probe_scratch_elems(n_tiles)) return ELX_ERR_SIZE;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (n_tiles == 0) {
+        if (l2sq) return record_cuda(cudaMemsetAsync(l2sq, 0, sizeof(float), s));
+        return ELX_OK;
+    }
+    ProbeArgs a;
+    memset(&a, 0, sizeof(a));
+    a.one_flag = flag;
+    a.ctl = ctl;
+    a.scratch = scratch;
+    a.copy_dst = dst;
+    a.first = 0;
+    a.count = 1;
+    a.inline_tables = 1;
+    a.n_tiles = n_tiles;
+    a.one_desc.grad_param = const_cast<void*>(src);
+    a.one_desc.n_shard = n_shard;
+    a.one_desc.n_valid = n_valid;
+    a.one_desc.tile_begin = 0;
+    a.one_desc.dtype = dtype;
+    int rc = copy ? launch_probe<true>(a, dtype, l2sq != nullptr, s) : launch_probe<false>(a, dtype, l2sq != nullptr, s);
+    if (rc != ELX_OK) return rc;
+    if (l2sq) {
+        NormArgs na;
+        memset(&na, 0, sizeof(na));
+        na.scratch = scratch;
+        na.one_l2sq = l2sq;
+        na.first = 0;
+        na.count = 1;
+        na.inline_tables = 1;
+        na.one_desc = a.one_desc;
+        norm_finalize<<<1, 256, 0, s>>>(na);
+        rc = record_cuda(cudaGetLastError());
+    }
+    return rc;
+}
+
+// ------------------------------------------------------------------------------------------------
+// built-in scratch for callers that cannot allocate
+// ------------------------------------------------------------------------------------------------
+
+// One partial sum per tile, so the largest shard elx_grad_check_static accepts has this many tiles
+// (16384 tiles x 4096 elements = 67 108 864 elements).  64 KiB on every GPU that loads the library.
+constexpr int64_t kStaticScratchTiles = 16384;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchTiles];
+
+// Device address of g_static_scratch per device ordinal.  In host code the array's name is only a
+// handle for the runtime, not something a kernel may dereference; the address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+float* g_static_scratch_addr[64];
+
+int static_scratch(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        if (e != cudaSuccess) record_cuda(e);
+        (void)cudaGetLastError();
+        return ELX_ERR_NODEVICE;
+    }
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void* addr = nullptr;
+        e = cudaGetSymbolAddress(&addr, g_static_scratch);
+        if (e != cudaSuccess || addr == nullptr) {
+            record_cuda(e);
+            (void)cudaGetLastError();
+            return e == cudaSuccess ? ELX_ERR_NODEVICE : ELX_ERR_LAUNCH;
+        }
+        g_static_scratch_addr[dev] = static_cast<float*>(addr);
+    }
+    *out = g_static_scratch_addr[dev];
+    return ELX_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t elx_probe_scratch_elems(int64_t n_tiles) { return n_tiles < 0 ? 0 : n_tiles; }
+
+int elx_grad_check(const void* g, int dtype, int64_t n_valid, uint32_t* flag, ElxCtl* ctl, float* l2sq,
+                   float* scratch, int64_t scratch_elems, void* stream) {
+    return probe_single(g, nullptr, dtype, n_valid, n_valid, flag, ctl, l2sq, scratch, scratch_elems, stream, false);
+}
+
+int64_t elx_grad_check_static_max_elems(void) { return kStaticScratchTiles * kTile; }
+
+int elx_grad_check_static(const void* g, int dtype, int64_t n_valid, uint32_t* flag, ElxCtl* ctl, float* l2sq,
+                          void* stream) {
+    if (n_valid > kStaticScratchTiles * kTile) return ELX_ERR_CAPACITY;
+    float* scratch = nullptr;
+    if (l2sq) {
+        const int rc = static_scratch(&scratch);
+        if (rc != ELX_OK) return rc;
+    }
+    return probe_single(g, nullptr, dtype, n_valid, n_valid, flag, ctl, l2sq, scratch, kStaticScratchTiles, stream,
+                        false);
+}
+
+int elx_reduce_epilogue(const void* src, void* dst, int dtype, int64_t n_shard, int64_t n_valid, uint32_t* flag,
+                        ElxCtl* ctl, float* l2sq, float* scratch, int64_t scratch_elems, void* stream) {
+    return probe_single(src, dst, dtype, n_shard, n_valid, flag, ctl, l2sq, scratch, scratch_elems, stream, true);
+}
+
+int elx_grad_check_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                         uint32_t* chunk_flags, ElxCtl* ctl, float* chunk_l2sq, float* total_l2sq, float* scratch,
+                         int64_t scratch_elems, void* stream) {
+    if (!descs) return ELX_ERR_NULL;
+    if (!chunk_flags && !ctl && !chunk_l2sq && !total_l2sq) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (first < 0 || count < 0 || n_tiles < 0) return ELX_ERR_SIZE;
+    if (!aligned(descs, 8) || (chunk_flags && !aligned(chunk_flags, 4)) || (ctl && !aligned(ctl, 16)))
+        return ELX_ERR_ALIGN;
+    const bool norm = chunk_l2sq || total_l2sq;
+    if (norm) {
+        if (!scratch) return ELX_ERR_NULL;
+        if (!aligned(scratch, 4)) return ELX_ERR_ALIGN;
+        if (scratch_elems < elx_probe_scratch_elems(n_tiles)) return ELX_ERR_SIZE;
+    }
+    if (count == 0) return ELX_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int rc = ELX_OK;
+    if (n_tiles > 0) {
+        ProbeArgs a;
+        memset(&a, 0, sizeof(a));
+        a.descs = descs;
+        a.chunk_flags = chunk_flags;
+        a.ctl = ctl;
+        a.scratch = scratch;
+        a.first = first;
+        a.count = count;
+        a.n_tiles = n_tiles;
+        rc = launch_probe<false>(a, dtype, norm, s);
+        if (rc != ELX_OK) return rc;
+    }
+    if (norm) {
+        NormArgs na;
+        memset(&na, 0, sizeof(na));
+        na.descs = descs;
+        na.scratch = scratch;
+        na.chunk_l2sq = chunk_l2sq;
+        na.total_l2sq = total_l2sq;
+        na.first = first;
+        na.count = count;
+        norm_finalize<<<1, 256, 0, s>>>(na);
+        rc = record_cuda(cudaGetLastError());
+    }
+    return rc;
+}
+
+}  // extern "C"
