@@ -43,7 +43,6 @@ extern thread_local char t_cuda_err[256];
 // Launch-shape knobs (elx_set_tuning).  A CTAs-per-SM cap of 0 means "as many as are resident".
 struct Tuning {
     int adam_threads = 256;
-    int adam_min_blocks = 2;      // __launch_bounds__ minimum CTAs per SM the kernel is compiled for
     int adam_ctas_per_sm = 0;
     int probe_ctas_per_sm = 0;
     int probe_unroll = 4;

@@ -163,7 +163,6 @@ int elx_set_tuning(const char* name, int value) {
     };
     const Knob knobs[] = {
         {"adam_threads", &g_tune.adam_threads, def.adam_threads, 256, 512},
-        {"adam_min_blocks", &g_tune.adam_min_blocks, def.adam_min_blocks, 1, 3},
         {"adam_ctas_per_sm", &g_tune.adam_ctas_per_sm, def.adam_ctas_per_sm, 0, 32},
         {"probe_ctas_per_sm", &g_tune.probe_ctas_per_sm, def.probe_ctas_per_sm, 0, 32},
         {"probe_unroll", &g_tune.probe_unroll, def.probe_unroll, 4, 8},

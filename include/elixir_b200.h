@@ -151,9 +151,8 @@ const char* elx_last_cuda_error(void);
 /* Launch-shape knobs, by name; a negative value restores the default.  Affects later launches of
  * the calling process; results never depend on them (bit-identical for every setting except
  * math_mode).
- *   "adam_threads"       256 (16 elements per thread) or 512 (8 per thread)
- *   "adam_min_blocks"    1..3: CTAs per SM the Adam kernel is compiled for (register budget)
- *   "adam_ctas_per_sm"   cap on the persistent grid, 0 = every resident CTA
+ *   "adam_threads"       direct variant: 256 (16 elements per thread) or 512 (8 per thread)
+ *   "adam_ctas_per_sm"   direct variant: cap on the persistent grid, 0 = every resident CTA
  *   "probe_ctas_per_sm"  the same for the probe kernels
  *   "probe_unroll"       4 or 8 tiles in flight per probe CTA
  *   "adam_variant"       0 = direct 256-bit global accesses, 1 = bulk-copy (TMA) pipeline through

@@ -504,6 +504,40 @@ def test_bulk_copy_pipeline_variant_is_bit_identical_to_direct(K, oracle, cuda, 
             assert bits_equal(x, y)
 
 
+def test_peer_barrier_wait_is_bounded(K, cuda):
+    """A peer that never arrives: the barrier kernel gives up after its time limit, raises the sticky
+    ELX_STAT_TIMEOUT bit and returns; the context stays usable.  The "missing peer" is a second flag region
+    on the same GPU that nothing ever writes an epoch into — no other process, nothing hangs."""
+    import time
+    from elixir_b200 import _abi, _lib
+    lib = _lib.get()
+    mine = torch.zeros(256, dtype=torch.int32, device=cuda)
+    silent_peer = torch.zeros(256, dtype=torch.int32, device=cuda)
+    table = _abi.ElxPeerTable()
+    table.base[0], table.base[1] = mine.data_ptr(), silent_peer.data_ptr()
+    table.rank, table.world = 0, 2
+    ctl = K.ControlBlock(cuda, 1.0)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(cuda).cuda_stream)
+    t0 = time.time()
+    assert lib.elx_peer_barrier(table, 1, ctl.ptr, 1, 200, stream) == _abi.OK
+    torch.cuda.synchronize()
+    elapsed = time.time() - t0
+    assert 0.15 < elapsed < 5.0
+    c = ctl.read()
+    assert c.status & _abi.STAT_TIMEOUT
+    # what this rank announced did arrive in both regions (slot of sender 0, parity of epoch 1)
+    slot = (1 * _abi.MAX_PEERS + 0) * 2
+    assert mine[slot].item() == 1 and silent_peer[slot].item() == 1
+    # a world of one completes at once, and the device still works
+    solo = _abi.ElxPeerTable()
+    solo.base[0], solo.rank, solo.world = mine.data_ptr(), 0, 1
+    ctl2 = K.ControlBlock(cuda, 1.0)
+    assert lib.elx_peer_barrier(solo, 2, ctl2.ptr, 0, 200, stream) == _abi.OK
+    torch.cuda.synchronize()
+    assert ctl2.read().status == 0
+    assert lib.elx_peer_barrier(solo, 0, ctl2.ptr, 0, 200, stream) == _abi.ERR_ARG    # epochs start at 1
+
+
 # --------------------------------------------------------------------------------------------------
 # argument validation: errors are status codes, nothing is launched
 # --------------------------------------------------------------------------------------------------
