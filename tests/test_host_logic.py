@@ -1,0 +1,156 @@
+"""Host-side logic that needs no GPU: descriptor tables, segment merging, argument validation, planner and
+the ElixirOptimizer bookkeeping — with the elx_* ABI served by the oracle's host-memory shim (tests only)."""
+import pytest
+import torch
+import torch.distributed as dist
+
+import _dist_workers as W
+
+
+@pytest.fixture(scope='module')
+def host_backend():
+    from elixir_b200 import _lib
+    saved = (_lib._LIB, _lib._HOST_MEMORY)
+    W.use_host_shim()
+    if not dist.is_initialized():
+        dist.init_process_group('gloo', init_method='tcp://127.0.0.1:29790', rank=0, world_size=1)
+    yield
+    _lib._LIB, _lib._HOST_MEMORY = saved
+
+
+def _shard(n, dtype=torch.float16):
+    return torch.randn(n) * 0.02, torch.zeros(n), torch.zeros(n), torch.zeros(n, dtype=dtype)
+
+
+def test_chunk_table_merges_neighbouring_segments_and_counts_tiles(host_backend):
+    from elixir_b200 import kernels as K
+    table = K.ChunkTable('cpu', torch.float16)
+    a = _shard(10000)
+    i = table.add_chunk(*a, n_valid=9000, segments=[(0, 100, 0), (100, 300, 0), (300, 400, 1), (500, 9000, 1)])
+    assert table._segs_of(i) == [(0, 300, 0), (300, 400, 1), (500, 9000, 1)]
+    b = _shard(4096)
+    j = table.add_chunk(*b, n_valid=0)
+    c = _shard(1)
+    k = table.add_chunk(*c, n_valid=1, segments=[(0, 1, 2)])
+    assert (i, j, k) == (0, 1, 2)
+    assert table.tile_begin == [0, 3, 4, 5]
+    assert table.tiles() == 5 and table.tiles(1, 2) == 2
+    table.finalize()
+    with pytest.raises(RuntimeError):
+        table.add_chunk(*c, n_valid=1)
+
+
+@pytest.mark.parametrize('segments', [
+    [(10, 5, 0)],                 # empty / reversed
+    [(0, 10, 0), (5, 20, 0)],     # overlapping
+    [(20, 30, 0), (0, 10, 0)],    # unsorted
+    [(0, 200, 0)],                # beyond n_valid
+])
+def test_chunk_table_rejects_bad_segments(host_backend, segments):
+    from elixir_b200 import kernels as K
+    table = K.ChunkTable('cpu', torch.float16)
+    with pytest.raises(ValueError):
+        table.add_chunk(*_shard(256), n_valid=100, segments=segments)
+
+
+def test_chunk_table_rejects_mismatched_tensors(host_backend):
+    from elixir_b200 import kernels as K
+    table = K.ChunkTable('cpu', torch.float16)
+    p, m, v, g = _shard(256)
+    with pytest.raises(ValueError):
+        table.add_chunk(p, m[:100].clone(), v, g, n_valid=10)
+    with pytest.raises(TypeError):
+        table.add_chunk(p, m, v, g.float(), n_valid=10)
+    with pytest.raises(ValueError):
+        table.add_chunk(p, m, v, g, n_valid=300)
+    with pytest.raises(TypeError):
+        K.dtype_code(torch.int8)
+    with pytest.raises(ValueError):
+        table.set_hyper([K.hyper()] * 65)
+
+
+def test_simple_plan_packs_in_order_and_gives_tied_parameters_private_chunks(host_backend):
+    import torch.nn as nn
+    from elixir_b200.wrapper import simple_plan
+
+    class Tied(nn.Module):
+
+        def __init__(self):
+            super().__init__()
+            self.embed = nn.Embedding(20, 16)
+            self.fc1 = nn.Linear(16, 16)
+            self.fc2 = nn.Linear(16, 16)
+            self.head = nn.Linear(16, 20, bias=False)
+            self.head.weight = self.embed.weight
+
+    sr = simple_plan(Tied(), 4, split_number=10, unified_dtype=torch.float16, rcache_device='cpu')
+    plans = sr.param_chunk_plans
+    assert plans[0].name_list == ['embed.weight'] and plans[0].kwargs.get('rcache_fused') is True
+    assert plans[0].chunk_size == 320    # 20 x 16, already a multiple of 4 (elixir's test_simple.py expects 320 too)
+    public = [p for p in plans if not p.kwargs.get('rcache_fused')]
+    assert [p.name_list for p in public] == [['fc1.weight'], ['fc1.bias'], ['fc2.weight'], ['fc2.bias']]
+    assert {p.chunk_size for p in public} == {256} and all(p.chunk_size % 4 == 0 for p in plans)
+    sr2 = simple_plan(Tied(), 3, chunk_size=300, unified_dtype=torch.float16, rcache_device='cpu')
+    pub2 = [p for p in sr2.param_chunk_plans if not p.kwargs.get('rcache_fused')]
+    assert [p.name_list for p in pub2] == [['fc1.weight', 'fc1.bias'], ['fc2.weight', 'fc2.bias']]
+    assert pub2[0].chunk_size == 300
+    with pytest.raises(ValueError):
+        simple_plan(Tied(), 1, chunk_size=100, unified_dtype=torch.float16, rcache_device='cpu')
+
+
+def test_optimizer_bookkeeping_frozen_parameters_and_state_views(host_backend):
+    import torch.nn as nn
+    from elixir_b200.optim import CPUAdam, HybridAdam
+    from elixir_b200.wrapper import ElixirModule, ElixirOptimizer, simple_plan
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(8, 12), nn.Linear(12, 4))
+    model[0].bias.requires_grad_(False)    # frozen: stays out of the chunks and out of the optimizer
+    sr = simple_plan(model, 1, chunk_size=128, unified_dtype=torch.float16, shard_device='cpu', rcache_device='cpu')
+    inner = HybridAdam([p for p in model.parameters() if p.requires_grad], lr=1e-2)
+    emodel = ElixirModule(model, sr, dist.GroupMember.WORLD, dtype=torch.float16)
+    eopt = ElixirOptimizer(emodel, inner, initial_scale=8.0)
+    assert '0.bias' in emodel.no_grad_state_dict and model[0].bias.dtype == torch.float16
+    n_trainable = sum(p.numel() for p in model.parameters() if p.requires_grad)
+    covered = sum(e - b for b, e in eopt.param_to_range.values())
+    assert covered == n_trainable
+    for fake, (b, e) in eopt.param_to_range.items():
+        st = eopt.state[fake]
+        assert st['exp_avg'].numel() == e - b == st['exp_avg_sq'].numel()
+    # a step moves exactly the covered ranges; the state views alias the engine's flat moments
+    grads = {n: torch.full(p.shape, 0.5) for n, p in emodel.grad_state_dict.items()}
+    before = [s[0].clone() for s in eopt.engine.shards]
+    emodel.inject_gradients(grads)
+    eopt.step()
+    assert eopt.engine.read_control().step == 1 and eopt.loss_scale == 8.0
+    for (m, ea, es, lp, nv), old in zip(eopt.engine.shards, before):
+        assert not torch.equal(m[:nv], old[:nv]) and torch.equal(m[nv:], old[nv:])
+        assert torch.equal(lp, m.half())
+    first = next(iter(eopt.param_to_range))
+    assert float(eopt.state[first]['exp_avg'].abs().sum()) > 0
+    with pytest.raises(TypeError):
+        ElixirOptimizer(emodel, torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=0.1))
+    with pytest.raises(RuntimeError):
+        CPUAdam([torch.nn.Parameter(torch.zeros(1))])
+    with pytest.raises(RuntimeError):
+        HybridAdam([torch.nn.Parameter(torch.zeros(1))]).step()    # not wrapped: no chunk engine to step through
+
+
+def test_scaler_state_dict_round_trip(host_backend):
+    from elixir_b200 import kernels as K
+    from elixir_b200.scaler import DynamicGradScaler
+    scaler = DynamicGradScaler(initial_scale=1024.0, growth_interval=3, hysteresis=1)
+    scaler.attach(K.ControlBlock('cpu', scaler.initial_scale))
+    for found in (0, 0, 1, 0, 0, 0):
+        scaler.ctl.found_inf.fill_(found)
+        K.step_begin(scaler.ctl, scaler.cfg)
+    saved = scaler.state_dict()
+    assert saved == dict(scale=1024.0, growth_step=0, hysteresis_step=0, step=5, skipped_steps=1)
+    other = DynamicGradScaler(initial_scale=1.0)
+    other.attach(K.ControlBlock('cpu', 1.0))
+    other.load_state_dict(saved)
+    assert other.state_dict() == saved
+    assert float(other.scale) == 1024.0
+    with pytest.raises(ValueError):
+        DynamicGradScaler(growth_factor=1.0)
+    with pytest.raises(ValueError):
+        DynamicGradScaler(backoff_factor=1.5)
