@@ -203,3 +203,40 @@ def test_lr_schedule_and_param_groups_are_picked_up_every_step(cuda, oracle, sin
             ok, ratio = close_1e6(eopt.engine.shards[i][0], masters[i].double())
             assert ok, (step, i, ratio)
     assert inner.param_groups[0]['lr'] < 1e-3
+
+
+def test_checkpoint_resume_continues_bit_identically(cuda, single_group):
+    """Flat-state checkpoint (fp32 masters through ElixirModule.state_dict, moments + control block through
+    ElixirOptimizer.state_dict): a run resumed from it takes exactly the steps the original run takes."""
+    def fresh():
+        torch.manual_seed(11)
+        model = Mlp().to(cuda)
+        return _wrap(model, single_group, torch.float16, lr=2e-3, wd=0.01, initial_scale=512.0, growth_interval=3,
+                     hysteresis=1)
+
+    def train(emodel, eopt, steps, first):
+        for i in range(first, first + steps):
+            gen = torch.Generator(device=cuda).manual_seed(1000 + i)
+            x = torch.randn(8, 48, device=cuda, generator=gen)
+            eopt.zero_grad()
+            eopt.backward(emodel(x))
+            if i == 2:    # an overflow before the checkpoint, so the scaler counters are not trivial
+                eopt.engine.ctl.found_inf.fill_(1)
+            eopt.step()
+
+    emodel, eopt = fresh()
+    train(emodel, eopt, 4, 0)
+    model_state, optim_state = emodel.state_dict(), eopt.state_dict()
+    train(emodel, eopt, 3, 4)
+    want = [[t.cpu() for t in s[:4]] for s in eopt.engine.shards]
+    want_ctl = eopt.grad_scaler.state_dict()
+
+    emodel2, eopt2 = fresh()
+    emodel2.load_state_dict(model_state)
+    eopt2.load_state_dict(optim_state)
+    assert eopt2.grad_scaler.state_dict() == optim_state['scaler']
+    train(emodel2, eopt2, 3, 4)
+    assert eopt2.grad_scaler.state_dict() == want_ctl
+    for got, ref in zip(eopt2.engine.shards, want):
+        for a, b in zip(got[:4], ref):
+            assert bits_equal(a, b)
