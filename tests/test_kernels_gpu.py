@@ -291,6 +291,34 @@ def test_adam_chunk_unaligned_views(K, oracle, cuda):
     assert bits_equal(dp[:3], p[:3]) and bits_equal(dg[:3], g[:3])
 
 
+@pytest.mark.parametrize('mode', ['adamw', 'l2'])
+def test_adam_against_torch_fused_optimizer_on_the_gpu(K, cuda, mode):
+    """A second, independent GPU implementation: torch's fused multi-tensor Adam/AdamW (the Apex lineage the
+    reference's ColossalAI kernel also comes from), fed the unscaled fp32 gradients.  Dyadic betas keep
+    (1 - beta) exact in either precision, so only rounding order differs."""
+    n, scale, steps = 6 * 4096 + 123, 128.0, 4
+    betas, lr, eps, wd = (0.875, 0.99609375), 0.0009765625, 1e-8, 0.0078125
+    p, m, v, _ = make_chunk(n, torch.float16, seed=21)
+    dp, dm, dv = p.to(cuda), m.to(cuda), v.to(cuda)
+    ref = torch.nn.Parameter(p.to(cuda).clone())
+    Opt = torch.optim.AdamW if mode == 'adamw' else torch.optim.Adam
+    opt = Opt([ref], lr=lr, betas=betas, eps=eps, weight_decay=wd, fused=True)
+    h = K.hyper(lr, betas, eps, wd, adamw_mode=(mode == 'adamw'))
+    ctl = K.ControlBlock(cuda, scale)
+    for s in range(steps):
+        gen = torch.Generator().manual_seed(500 + s)
+        g16 = (torch.randn(n, generator=gen) * 1e-3 * scale).half().to(cuda)
+        ref.grad = g16.float() / scale
+        opt.step()
+        K.step_begin(ctl, K.scaler_cfg(False))
+        K.adam_chunk(dp, dm, dv, g16, h, ctl)
+    state = opt.state[ref]
+    for name, got, want in (('master', dp, ref.data), ('exp_avg', dm, state['exp_avg']),
+                            ('exp_avg_sq', dv, state['exp_avg_sq'])):
+        ok, ratio = close_1e6(got, want.double(), rtol=2e-6)
+        assert ok, (mode, name, ratio)
+
+
 def test_skip_leaves_state_untouched_and_restores_params(K, oracle, cuda):
     n = 4 * 4096 + 9
     p, m, v, g = make_chunk(n, torch.float16, seed=11, scale=65536.0)
