@@ -219,9 +219,11 @@ def run_ours(args):
             gen = torch.Generator(device=device).manual_seed(args.seed + 7919 * (c + 1))
             grad_blocks.append(synth_grad(shard, device, gen, scale, sigma, dtype))
         gather_blocks = None
-    elif args.collective == 'p2p':
+    elif args.collective in ('p2p', 'staged'):
         # NVLink path: every chunk owns a block in the peer-mapped gradient and gather slabs
-        engine.enable_p2p([chunk] * n_chunks, pool=args.pool or None)
+        engine.enable_p2p([chunk] * n_chunks, pool=(args.pool or None) if args.collective == 'p2p' else None)
+        if args.collective == 'staged':
+            engine.enable_staging(pool=4)
         seeds = 4
         for c in range(min(n_chunks, args.pool) if args.pool else n_chunks):
             if c < seeds:
@@ -258,6 +260,8 @@ def run_ours(args):
             engine.end_step()
         elif args.collective == 'p2p':
             engine.step_sharded_p2p()
+        elif args.collective == 'staged':
+            engine.step_sharded_staged()
         else:
             engine.step_sharded(grad_blocks, gather_blocks)
 
@@ -323,6 +327,8 @@ def run_ours(args):
             'collectives': 'none (1 GPU)' if world == 1 else
                            ('fused into the kernels over peer-mapped NVLink memory (pull reduce-scatter + probe, '
                             'Adam + push all-gather)' if args.collective == 'p2p' else
+                            'copy engines over peer-mapped NVLink memory (staged reduce + probe kernel, fused update, '
+                            'copies into the gather blocks)' if args.collective == 'staged' else
                             'NCCL reduce-scatter (pre-multiplied sum) and all-gather per chunk on side streams'),
         },
         'clocks': clocks,
@@ -362,6 +368,13 @@ def run_ours(args):
         elif args.collective == 'p2p':
             result['gpu_launches'] = args.steps * 6
             result['phases_ms'] = p2p_phases(engine)
+        elif args.collective == 'staged':
+            result['gpu_launches'] = args.steps * (2 * n_chunks + 4)
+            engine.profile = True
+            one_step()
+            torch.cuda.synchronize()
+            result['phases_ms'] = engine.phase_ms()
+            engine.profile = False
         else:
             result['gpu_launches'] = args.steps * (2 * n_chunks + 1)
             # one more, untimed, step with phase timestamps: where the step time goes
@@ -424,11 +437,11 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
     outs = [host_out[c % pool] for c in range(n_chunks)]
     if world == 1:
         fn = lambda: engine.step_from_host(grads, outs)
-    elif args.collective == 'p2p':
+    elif args.collective in ('p2p', 'staged'):
         def fn():
             for k in range(n_chunks):
                 grad_blocks[k].copy_(grads[k], non_blocking=True)
-            engine.step_sharded_p2p()
+            (engine.step_sharded_p2p if args.collective == 'p2p' else engine.step_sharded_staged)()
             for k in range(n_chunks):
                 outs[k].copy_(engine.shards[k][3], non_blocking=True)
     else:
@@ -582,7 +595,7 @@ def main():
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--seed', type=int, default=0)
-    ap.add_argument('--collective', default='p2p', choices=['p2p', 'nccl'],
+    ap.add_argument('--collective', default='p2p', choices=['p2p', 'staged', 'nccl'],
                     help='N > 1: collectives fused into the kernels over peer-mapped NVLink memory, or NCCL')
     ap.add_argument('--workload', default='auto', choices=['auto', 'opt66b_bf16'],
                     help='N > 1: auto = OPT-13B-shaped fp16 chunk set; opt66b_bf16 = OPT-66B-shaped bf16 chunk set (8 GPUs)')

@@ -22,6 +22,8 @@ struct PullArgs {
     ElxCtl* ctl;
     ElxPeerTable grads;
     const int64_t* block_off;   // per descriptor: element offset of the chunk's block inside the slabs
+    const int64_t* stage_off;   // null, or per descriptor: element offset of this rank's slice inside the buffers
+                                // of the OTHER ranks (they are local staging copies of that slice alone)
     int first, count;
     int64_t n_tiles;
 };
@@ -52,11 +54,13 @@ __global__ void __launch_bounds__(256) pull_reduce_kernel(const __grid_constant_
         const int64_t n_shard = s_cur.d.n_shard, n_valid = s_cur.d.n_valid;
         const int64_t e0 = (t - s_cur.t0) * kTile;
         const int64_t e1 = min(e0 + kTile, n_shard);
-        const int64_t src0 = a.block_off[s_cur.index] + static_cast<int64_t>(rank) * n_shard;   // element offset
+        const int64_t own0 = a.block_off[s_cur.index] + static_cast<int64_t>(rank) * n_shard;   // element offsets
+        const int64_t stg0 = a.stage_off ? a.stage_off[s_cur.index] : own0;
+        auto src0_of = [&](int j) { return j == rank ? own0 : stg0; };
         void* const dst = s_cur.d.grad_param;
         const bool all_valid = e0 + kTile <= n_valid, none_valid = e0 >= n_valid;
         uint32_t bad = 0;
-        if ((e1 - e0 == kTile) && (all_valid || none_valid) && (src0 & 15) == 0 &&
+        if ((e1 - e0 == kTile) && (all_valid || none_valid) && ((own0 | stg0) & 15) == 0 &&
             (reinterpret_cast<uintptr_t>(dst) & 31u) == 0) {
             const int64_t mine = e0 + static_cast<int64_t>(threadIdx.x) * EPT;
             float acc[EPT];
@@ -79,7 +83,7 @@ __global__ void __launch_bounds__(256) pull_reduce_kernel(const __grid_constant_
                 uint32_t raw[kWorld][WORDS];
 #pragma unroll
                 for (int j = 0; j < kWorld; ++j)
-                    ld_words<WORDS>(static_cast<const char*>(a.grads.base[j]) + (src0 + mine) * Lp<DT>::kBytes, raw[j]);
+                    ld_words<WORDS>(static_cast<const char*>(a.grads.base[j]) + (src0_of(j) + mine) * Lp<DT>::kBytes, raw[j]);
                 // keep every rank's words live until all loads are issued: the empty asm statements are ordered
                 // after the (volatile) loads, so the compiler cannot fold a load into its first use
 #pragma unroll
@@ -95,7 +99,7 @@ __global__ void __launch_bounds__(256) pull_reduce_kernel(const __grid_constant_
             } else {
                 for (int j = 0; j < world; ++j) {
                     uint32_t raw[WORDS];
-                    ld_words<WORDS>(static_cast<const char*>(a.grads.base[j]) + (src0 + mine) * Lp<DT>::kBytes, raw);
+                    ld_words<WORDS>(static_cast<const char*>(a.grads.base[j]) + (src0_of(j) + mine) * Lp<DT>::kBytes, raw);
                     accumulate(raw);
                 }
             }
@@ -117,7 +121,7 @@ __global__ void __launch_bounds__(256) pull_reduce_kernel(const __grid_constant_
             for (int64_t e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
                 float acc = 0.0f;
                 for (int j = 0; j < world; ++j)
-                    acc = fmaf(Lp<DT>::to_float(static_cast<const T*>(a.grads.base[j])[src0 + e]), inv_w, acc);
+                    acc = fmaf(Lp<DT>::to_float(static_cast<const T*>(a.grads.base[j])[src0_of(j) + e]), inv_w, acc);
                 const T val = Lp<DT>::from_float(acc);
                 out[e] = val;
                 if (e < n_valid && Lp<DT>::nonfinite(val)) bad = 1;
@@ -322,10 +326,19 @@ int elx_peer_barrier(ElxPeerTable flags, uint32_t epoch, ElxCtl* ctl, int exchan
     return record_cuda(cudaGetLastError());
 }
 
+int elx_copy_async(void* dst, const void* src, int64_t bytes, void* stream) {
+    if (!dst || !src) return ELX_ERR_NULL;
+    if (bytes < 0) return ELX_ERR_SIZE;
+    if (bytes == 0) return ELX_OK;
+    return record_cuda(cudaMemcpyAsync(dst, src, static_cast<size_t>(bytes), cudaMemcpyDefault,
+                                       static_cast<cudaStream_t>(stream)));
+}
+
 int elx_pull_reduce_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
-                          ElxPeerTable grads, const int64_t* block_off, uint32_t* chunk_flags, ElxCtl* ctl,
-                          void* stream) {
+                          ElxPeerTable grads, const int64_t* block_off, const int64_t* stage_off,
+                          uint32_t* chunk_flags, ElxCtl* ctl, void* stream) {
     if (!descs || !block_off) return ELX_ERR_NULL;
+    if (stage_off && !aligned(stage_off, 8)) return ELX_ERR_ALIGN;
     if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
     if (first < 0 || count < 0 || n_tiles < 0) return ELX_ERR_SIZE;
     const int rc = peer_table_ok(grads);
@@ -341,6 +354,7 @@ int elx_pull_reduce_multi(const ElxChunkDesc* descs, int first, int count, int64
     a.ctl = ctl;
     a.grads = grads;
     a.block_off = block_off;
+    a.stage_off = stage_off;
     a.first = first;
     a.count = count;
     a.n_tiles = n_tiles;

@@ -332,6 +332,102 @@ class ChunkStepEngine:
         self.end_step()
         self.peer_barrier(self.ctl)
 
+    def enable_staging(self, pool: int = 4):
+        """Local staging buffers for ``step_sharded_staged``: ``pool`` slots, each with room for the W - 1
+        slices of the largest shard that the other ranks hold for this rank."""
+        assert hasattr(self, 'grad_slab'), 'call enable_p2p() first'
+        from ._abi import ElxPeerTable
+        shard_max = (max(s[0].numel() for s in self.shards) + 15) // 16 * 16
+        self._stage_pool = pool
+        self._stage = torch.empty(pool * self.world * shard_max, dtype=self.dtype, device=self.device)
+        self._stage_tables = []
+        itemsize = self._stage.element_size()
+        for slot in range(pool):
+            table = ElxPeerTable()
+            for j in range(self.world):
+                table.base[j] = (self.grad_slab.table.base[j] if j == self.grad_slab.rank else
+                                 self._stage.data_ptr() + (slot * self.world + j) * shard_max * itemsize)
+            table.rank, table.world = self.grad_slab.rank, self.world
+            self._stage_tables.append(table)
+        self._stage_zero_off = torch.zeros(self.n_chunks, dtype=torch.int64, device=self.device)
+        self._copy_streams = [torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)]
+        return self
+
+    def step_sharded_staged(self):
+        """Sharded step over peer-mapped memory with the copy engines moving the slices over NVLink:
+
+            barrier                  every rank's gradient blocks are written
+            per chunk k              W - 1 copies (one per other rank, rotated so that at any moment every rank
+                                     reads from a different one) of this rank's slice of block k into a local
+                                     staging slot, on two copy streams; then the reduce + probe kernel on local
+                                     memory only (``elx_pull_reduce_multi`` with staged sources)
+            barrier + agree          overflow word OR-ed over the ranks
+            decision                 ``elx_step_begin``
+            per chunk k              fused update on the main stream; then W copies of the refreshed shard into
+                                     every rank's gather block k, on the copy streams
+            barrier                  every rank's copies have landed
+
+        Same results as ``step_sharded_p2p`` bit for bit (same reduction order and arithmetic); the difference
+        is who moves the bytes."""
+        rank, world = self.grad_slab.rank, self.world
+        main = torch.cuda.current_stream(self.device)
+        c0, c1 = self._copy_streams
+        itemsize = self._stage.element_size()
+        pool = self._stage_pool
+        marks = self._phase_marks(main)
+        self.peer_barrier(self.ctl)
+        for st in self._copy_streams:
+            st.wait_stream(main)
+        reduce_done = [None] * self.n_chunks
+        for k in range(self.n_chunks):
+            slot = k % pool
+            shard_elems = self.shards[k][0].numel()
+            nbytes = shard_elems * itemsize
+            src_off = (self._p2p_offsets[k] + rank * shard_elems) * itemsize
+            table = self._stage_tables[slot]
+            if k >= pool:
+                for st in self._copy_streams:
+                    st.wait_event(reduce_done[k - pool])    # the slot's previous user has been reduced
+            for t in range(1, world):
+                j = (rank + t) % world
+                kernels.copy_async(table.base[j], self.grad_slab.table.base[j] + src_off, nbytes, c0 if t % 2 else c1)
+            for st in self._copy_streams:
+                arrived = torch.cuda.Event()
+                arrived.record(st)
+                main.wait_event(arrived)
+            kernels.pull_reduce_multi(self.table, table, self.block_off, self.ctl, chunk_flags=self.chunk_flags,
+                                      first=k, count=1, stage_off=self._stage_zero_off)
+            reduce_done[k] = torch.cuda.Event()
+            reduce_done[k].record(main)
+        marks('reduced')
+        self.peer_barrier(self.ctl, exchange_overflow=self.sync_overflow)
+        norm_sq = None
+        if self.clipping:
+            kernels.grad_check_multi(self.table, None, chunk_l2sq=self.chunk_l2sq, total_l2sq=self.total_l2sq,
+                                     scratch=self._scratch)
+            dist.all_reduce(self.total_l2sq, group=self.group)
+            norm_sq = self.total_l2sq
+        kernels.step_begin(self.ctl, self.scaler.cfg, norm_sq)
+        for k in range(self.n_chunks):
+            self.update(first=k, count=1)
+            updated = torch.cuda.Event()
+            updated.record(main)
+            shard = self.shards[k][3]
+            nbytes = shard.numel() * itemsize
+            dst_off = (self._p2p_offsets[k] + rank * shard.numel()) * itemsize
+            for t in range(world):
+                j = (rank + t) % world
+                st = c0 if t % 2 else c1
+                if t < 2:
+                    st.wait_event(updated)
+                kernels.copy_async(self.gather_slab.table.base[j] + dst_off, shard.data_ptr(), nbytes, st)
+        marks('updated')
+        for st in self._copy_streams:
+            main.wait_stream(st)
+        marks('gathered')
+        self.end_step()
+        self.peer_barrier(self.ctl)
+
     def step_from_host(self, host_grads: Sequence[torch.Tensor], host_params: Sequence[torch.Tensor]):
         """A whole step with host buffers on both ends: ``host_grads[k]`` (pinned, shard_size elements of
         the chunk dtype) holds the reduced gradients of shard k; ``host_params[k]`` (pinned) receives the

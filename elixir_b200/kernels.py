@@ -393,7 +393,8 @@ def adam_multi(table: ChunkTable, ctl: ControlBlock, first: int = 0, count: Opti
 
 
 def pull_reduce_multi(table: ChunkTable, grads_table, block_off: torch.Tensor, ctl: Optional[ControlBlock],
-                      chunk_flags: Optional[torch.Tensor] = None, first: int = 0, count: Optional[int] = None):
+                      chunk_flags: Optional[torch.Tensor] = None, first: int = 0, count: Optional[int] = None,
+                      stage_off: Optional[torch.Tensor] = None):
     """NVLink pull reduce-scatter fused with the probe (``elx_pull_reduce_multi``).  ``grads_table`` is the
     ``ElxPeerTable`` of the ranks' gradient slabs, ``block_off`` (int64, device) the element offset of each
     chunk's block inside a slab."""
@@ -406,7 +407,7 @@ def pull_reduce_multi(table: ChunkTable, grads_table, block_off: torch.Tensor, c
     with _DeviceGuard(table.descs_dev):
         _lib.check(
             _lib.get().elx_pull_reduce_multi(_ptr(table.descs_dev), first, count, table.tiles(first, count), table.code,
-                                             grads_table, _ptr(block_off), _ptr(chunk_flags),
+                                             grads_table, _ptr(block_off), _ptr(stage_off), _ptr(chunk_flags),
                                              ctl.ptr if ctl else None, _stream(table.descs_dev)),
             'elx_pull_reduce_multi')
 
@@ -425,3 +426,9 @@ def adam_multi_push(table: ChunkTable, ctl: ControlBlock, gather_table, block_of
                                            _ptr(table.segs_dev), _ptr(table.hyper_dev), table.n_groups, ctl.ptr,
                                            gather_table, _ptr(block_off), _stream(table.descs_dev)),
             'elx_adam_multi_push')
+
+
+def copy_async(dst_ptr: int, src_ptr: int, nbytes: int, stream: torch.cuda.Stream):
+    """One copy-engine transfer between raw device addresses (local or peer-mapped) on ``stream``."""
+    _lib.check(_lib.get().elx_copy_async(ctypes.c_void_p(dst_ptr), ctypes.c_void_p(src_ptr), nbytes,
+                                         ctypes.c_void_p(stream.cuda_stream)), 'elx_copy_async')

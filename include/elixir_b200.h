@@ -309,10 +309,19 @@ int elx_peer_barrier(ElxPeerTable flags, uint32_t epoch, ElxCtl* ctl, int exchan
  * 345-356) for a group inside one NVLink domain; the reference's `x / W` then SUM differs from it
  * only in where the roundings fall.  Call it between two elx_peer_barrier calls: one after every rank
  * wrote its blocks, one before any rank overwrites them.
+ * stage_off == NULL: every grads.base[j] is rank j's whole slab.  stage_off != NULL: grads.base[j] for
+ * j != rank is a LOCAL buffer that already holds a copy of rank j's slice for this rank, chunk c's slice
+ * starting at element stage_off[c]; grads.base[rank] is still this rank's own slab.
  */
 int elx_pull_reduce_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
-                          ElxPeerTable grads, const int64_t* block_off, uint32_t* chunk_flags, ElxCtl* ctl,
-                          void* stream);
+                          ElxPeerTable grads, const int64_t* block_off, const int64_t* stage_off,
+                          uint32_t* chunk_flags, ElxCtl* ctl, void* stream);
+
+/* One asynchronous device-to-device copy on `stream` (cudaMemcpyAsync, any mix of local and peer-mapped
+ * addresses): the copy engines move whole slices over NVLink at a higher rate than SM-issued accesses.
+ * Used by the staged form of the sharded step: the other ranks' slices are first copied into local
+ * staging buffers, then elx_pull_reduce_multi runs with stage_off != NULL on local memory only. */
+int elx_copy_async(void* dst, const void* src, int64_t bytes, void* stream);
 
 /*
  * elx_adam_multi fused with the parameter all-gather: every refreshed low-precision tile is also

@@ -179,9 +179,9 @@ int elx_peer_barrier(ElxPeerTable flags, uint32_t epoch, ElxCtl* ctl, int exchan
     return ELX_ERR_NODEVICE;
 }
 int elx_pull_reduce_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
-                          ElxPeerTable grads, const int64_t* block_off, uint32_t* chunk_flags, ElxCtl* ctl,
-                          void* stream) {
-    (void)descs; (void)first; (void)count; (void)n_tiles; (void)dtype; (void)grads; (void)block_off;
+                          ElxPeerTable grads, const int64_t* block_off, const int64_t* stage_off,
+                          uint32_t* chunk_flags, ElxCtl* ctl, void* stream) {
+    (void)descs; (void)first; (void)count; (void)n_tiles; (void)dtype; (void)grads; (void)block_off; (void)stage_off;
     (void)chunk_flags; (void)ctl; (void)stream;
     return ELX_ERR_NODEVICE;
 }
@@ -212,4 +212,10 @@ int elx_peer_alloc(int64_t bytes, void** ptr, void* handle) {
 int elx_peer_free(void* ptr) {
     (void)ptr;
     return ELX_ERR_NODEVICE;
+}
+int elx_copy_async(void* dst, const void* src, int64_t bytes, void* stream) {
+    (void)stream;
+    if (!dst || !src) return ELX_ERR_NULL;
+    memmove(dst, src, (size_t)bytes);
+    return ELX_OK;
 }

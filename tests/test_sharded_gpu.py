@@ -103,7 +103,7 @@ def _worker(rank, world, port):
     dist.destroy_process_group()
 
 
-def _p2p_worker(rank, world, port, dtype_name='float16', pool=None):
+def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False):
     """The NVLink path: pull reduce-scatter + probe, overflow agreement inside the barrier, fused update with
     push all-gather — no NCCL collective in the step."""
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
@@ -146,6 +146,8 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None):
     engine.finalize()
     engine.set_hyper(hypers)
     engine.enable_p2p(chunk_sizes, timeout_ms=5000, pool=pool)
+    if staged:
+        engine.enable_staging(pool=2)
 
     def fill(step):
         per_rank = []
@@ -180,7 +182,10 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None):
 
     for step in range(5):
         per_rank = fill(step)
-        engine.step_sharded_p2p()
+        if staged:
+            engine.step_sharded_staged()
+        else:
+            engine.step_sharded_p2p()
         torch.cuda.synchronize()
         for c, C in enumerate(chunk_sizes):
             S = C // world
@@ -205,6 +210,15 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None):
                 assert bits_equal(engine.gather_block(c), torch.cat(others)), (step, rank, c)
     dist.barrier()
     dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('world', [2, 4])
+def test_sharded_step_staged_copy_engines(world):
+    """The same step with the copy engines moving the slices (local staging + reduce kernel on local memory,
+    copies of the refreshed shards into the gather blocks): same oracle, same bits."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f'needs {world} GPUs')
+    mp.spawn(_p2p_worker, args=(world, 29870 + world, 'float16', None, True), nprocs=world)
 
 
 def test_sharded_step_p2p_pooled_blocks():
