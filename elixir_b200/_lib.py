@@ -36,7 +36,18 @@ def get():
         if version != _abi.ABI_VERSION:
             raise RuntimeError(f'{_LIB_PATH} has ABI version {version}, this package expects {_abi.ABI_VERSION}')
         _LIB = cdll
+        _apply_env_tuning(cdll)
     return _LIB
+
+
+def _apply_env_tuning(cdll):
+    """``ELX_TUNING="knob=value,knob=value"`` sets launch-shape knobs (see ``elx_set_tuning``) at load time."""
+    spec = os.environ.get('ELX_TUNING', '').strip()
+    for item in filter(None, (part.strip() for part in spec.split(','))):
+        name, _, value = item.partition('=')
+        status = cdll.elx_set_tuning(name.strip().encode(), int(value))
+        if status != _abi.OK:
+            raise RuntimeError(f'ELX_TUNING: bad entry {item!r}')
 
 
 def host_memory_backend():

@@ -169,6 +169,7 @@ int elx_set_tuning(const char* name, int value) {
         {"math_mode", &g_tune.math_mode, def.math_mode, 1, 2},
         {"adam_variant", &g_tune.adam_variant, def.adam_variant, 0, 1},
         {"pull_ctas_per_sm", &g_tune.pull_ctas_per_sm, def.pull_ctas_per_sm, 0, 32},
+        {"pull_variant", &g_tune.pull_variant, def.pull_variant, 0, 1},
     };
     for (const Knob& k : knobs) {
         if (strcmp(name, k.name) != 0) continue;

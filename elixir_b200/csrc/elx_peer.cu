@@ -137,6 +137,203 @@ __global__ void __launch_bounds__(256) pull_reduce_kernel(const __grid_constant_
     if (ballot_desc && lane == 0 && a.ctl) atomicOr(&a.ctl->status, ELX_STAT_BAD_DESC);
 }
 
+// Bulk-copy variant of the pull for 16-bit chunks and a compile-time group size: one elected thread
+// fetches the W slices of a tile (W bulk loads of 8 KB, W - 1 of them from peer-mapped memory, never
+// multicast) into a shared-memory stage two tiles ahead; the warps sum the slices out of shared memory
+// in rank order, store the shard tile and probe it.  Larger NVLink requests than per-lane loads, and the
+// link stays busy while a tile is being summed.
+constexpr int kPullStages = 3;
+constexpr int kPullThreads = 256;
+
+struct PullSlot {
+    void* dst;            // shard base
+    int64_t e0, e1;       // tile range inside the shard
+    int64_t own0, stg0;   // element offsets of the slice in the own slab / in the other ranks' buffers
+    int64_t n_valid;
+    int chunk;
+    int kind;             // 1 = staged in shared memory, 2 = ragged (direct loads), 3 = bad descriptor
+};
+
+template <int DT, int kWorld>
+__global__ void __launch_bounds__(kPullThreads, 1) pull_reduce_tma_kernel(const __grid_constant__ PullArgs a) {
+    static_assert(DT != ELX_F32, "the staged pull is for 16-bit chunks");
+    using T = typename Lp<DT>::T;
+    constexpr int kSliceBytes = kTile * 2;
+    constexpr int kStageBytes = kWorld * kSliceBytes;
+    extern __shared__ __align__(128) unsigned char s_dyn[];
+    __shared__ PullSlot s_slot[kPullStages];
+    __shared__ __align__(8) uint64_t s_full[kPullStages];
+    __shared__ int s_abort;
+
+    const ElxChunkDesc* __restrict__ descs = a.descs;
+    const int rank = a.grads.rank;
+    const float inv_w = 1.0f / static_cast<float>(kWorld);
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPullStages; ++s) mbar_init(&s_full[s], 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int64_t tile_lo = descs[a.first].tile_begin;
+    const int64_t my_tiles = blockIdx.x < a.n_tiles ? (a.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    // producer-side cursor (thread 0 only)
+    int64_t pc_t0 = 0, pc_t1 = 0;
+    int pc_index = -1;
+    ElxChunkDesc pc_d;
+
+    auto produce = [&](int64_t k) {
+        const int s = static_cast<int>(k % kPullStages);
+        const int64_t t = tile_lo + blockIdx.x + k * gridDim.x;
+        PullSlot slot;
+        slot.kind = 3;
+        if (!(t >= pc_t0 && t < pc_t1)) {
+            int lo = a.first, hi = a.first + a.count - 1;
+            while (lo < hi) {
+                int mid = (lo + hi + 1) >> 1;
+                if (descs[mid].tile_begin <= t) lo = mid; else hi = mid - 1;
+            }
+            pc_d = descs[lo];
+            pc_index = lo;
+            pc_t0 = pc_d.tile_begin;
+            pc_t1 = pc_t0 + tiles_of(pc_d.n_shard);
+        }
+        if (t >= pc_t0 && t < pc_t1 && pc_d.dtype == DT) {
+            slot.dst = pc_d.grad_param;
+            slot.e0 = (t - pc_t0) * kTile;
+            slot.e1 = min(slot.e0 + kTile, pc_d.n_shard);
+            slot.own0 = a.block_off[pc_index] + static_cast<int64_t>(rank) * pc_d.n_shard;
+            slot.stg0 = a.stage_off ? a.stage_off[pc_index] : slot.own0;
+            slot.n_valid = pc_d.n_valid;
+            slot.chunk = pc_index;
+            const bool whole = slot.e1 - slot.e0 == kTile;
+            const bool uniform = slot.e0 + kTile <= pc_d.n_valid || slot.e0 >= pc_d.n_valid;
+            const bool lined_up = ((slot.own0 | slot.stg0) & 15) == 0 && (reinterpret_cast<uintptr_t>(slot.dst) & 31u) == 0;
+            slot.kind = (whole && uniform && lined_up) ? 1 : 2;
+        }
+        s_slot[s] = slot;
+        if (slot.kind == 1) {
+            unsigned char* base = s_dyn + static_cast<size_t>(s) * kStageBytes;
+            mbar_arrive_expect_tx(&s_full[s], kStageBytes);
+#pragma unroll
+            for (int i = 0; i < kWorld; ++i) {
+                // start with a different rank in every CTA so that the requests spread over all links at once
+                const int j = (rank + 1 + i + static_cast<int>(blockIdx.x)) % kWorld;
+                const int64_t src = (j == rank ? slot.own0 : slot.stg0) + slot.e0;
+                bulk_g2s(base + j * kSliceBytes, static_cast<const char*>(a.grads.base[j]) + src * 2, kSliceBytes,
+                         &s_full[s]);
+            }
+        } else {
+            mbar_arrive(&s_full[s]);
+        }
+    };
+
+    if (threadIdx.x == 0) {
+        for (int64_t k = 0; k < my_tiles && k < kPullStages; ++k) produce(k);
+    }
+
+    bool bad_desc = false;
+    int64_t k = 0;
+    for (; k < my_tiles; ++k) {
+        const int s = static_cast<int>(k % kPullStages);
+        const uint32_t parity = static_cast<uint32_t>((k / kPullStages) & 1);
+        if (!mbar_wait_bounded(&s_full[s], parity)) s_abort = 1;
+        __syncthreads();
+        if (s_abort) break;
+        const PullSlot slot = s_slot[s];
+        uint32_t bad = 0;
+        if (slot.kind == 1) {
+            const unsigned char* base = s_dyn + static_cast<size_t>(s) * kStageBytes;
+            const bool probed = slot.e0 + kTile <= slot.n_valid;
+            // a thread owns 2 x 8 consecutive elements, 2048 apart: conflict-free 128-bit shared reads
+#pragma unroll
+            for (int h = 0; h < kTile / (kPullThreads * 8); ++h) {
+                const int e = h * (kPullThreads * 8) + threadIdx.x * 8;
+                float acc[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+#pragma unroll
+                for (int j = 0; j < kWorld; ++j) {    // rank order
+                    const uint4 w = *reinterpret_cast<const uint4*>(base + j * kSliceBytes + e * 2);
+                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = Lp<DT>::unpack2(ww[i]);
+                        acc[2 * i] = fmaf(f.x, inv_w, acc[2 * i]);
+                        acc[2 * i + 1] = fmaf(f.y, inv_w, acc[2 * i + 1]);
+                    }
+                }
+                U4 out;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) out.x[i] = Lp<DT>::pack2(acc[2 * i], acc[2 * i + 1]);
+                st128(static_cast<char*>(slot.dst) + (slot.e0 + e) * 2, out);
+                if (probed) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) bad |= Lp<DT>::nonfinite_word(out.x[i]);
+                }
+            }
+        } else if (slot.kind == 2) {
+            T* out = static_cast<T*>(slot.dst);
+            for (int64_t e = slot.e0 + threadIdx.x; e < slot.e1; e += blockDim.x) {
+                float acc = 0.0f;
+                for (int j = 0; j < kWorld; ++j)
+                    acc = fmaf(Lp<DT>::to_float(static_cast<const T*>(a.grads.base[j])[(j == rank ? slot.own0 : slot.stg0) + e]),
+                               inv_w, acc);
+                const T val = Lp<DT>::from_float(acc);
+                out[e] = val;
+                if (e < slot.n_valid && Lp<DT>::nonfinite(val)) bad = 1;
+            }
+        } else {
+            bad_desc = true;
+        }
+        const unsigned any_bad = __ballot_sync(0xFFFFFFFFu, bad != 0);
+        if (any_bad && lane == 0) {
+            if (a.chunk_flags) atomicOr(&a.chunk_flags[slot.chunk], 1u);
+            if (a.ctl) atomicOr(&a.ctl->found_inf, 1u);
+        }
+        __syncthreads();   // the stage has been consumed by every warp
+        if (threadIdx.x == 0 && k + kPullStages < my_tiles) produce(k + kPullStages);
+    }
+    if (threadIdx.x == 0 && s_abort) {
+        // gave up on tile k: loads already issued for later tiles still target this CTA's shared memory
+        for (int64_t j = k; j < my_tiles && j < k + kPullStages; ++j)
+            (void)mbar_wait_bounded(&s_full[j % kPullStages], static_cast<uint32_t>((j / kPullStages) & 1));
+        if (a.ctl) atomicOr(&a.ctl->status, ELX_STAT_TIMEOUT);
+    }
+    const unsigned ballot_desc = __ballot_sync(0xFFFFFFFFu, bad_desc);
+    if (ballot_desc && lane == 0 && a.ctl) atomicOr(&a.ctl->status, ELX_STAT_BAD_DESC);
+}
+
+template <int DT, int kWorld>
+int launch_pull_tma(const PullArgs& a, cudaStream_t s) {
+    if constexpr (DT == ELX_F32) {
+        return ELX_ERR_DTYPE;
+    } else {
+        constexpr int smem = kPullStages * kWorld * kTile * 2;
+        static bool opted_in[64];
+        int dev = -1;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+            (void)cudaGetLastError();
+            return ELX_ERR_NODEVICE;
+        }
+        if (!opted_in[dev]) {
+            const cudaError_t attr = cudaFuncSetAttribute(pull_reduce_tma_kernel<DT, kWorld>,
+                                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (attr != cudaSuccess) {
+                const int rc = record_cuda(attr);
+                (void)cudaGetLastError();
+                return rc;
+            }
+            opted_in[dev] = true;
+        }
+        const int grid = grid_for(a.n_tiles, 1);
+        if (grid < 0) return grid;
+        pull_reduce_tma_kernel<DT, kWorld><<<grid, kPullThreads, smem, s>>>(a);
+        return record_cuda(cudaGetLastError());
+    }
+}
+
 template <int DT, int kWorld>
 int launch_pull_inst(const PullArgs& a, cudaStream_t s) {
     static const int resident = resident_ctas(pull_reduce_kernel<DT, kWorld>, 256);
@@ -148,6 +345,13 @@ int launch_pull_inst(const PullArgs& a, cudaStream_t s) {
 
 template <int DT>
 int launch_pull(const PullArgs& a, cudaStream_t s) {
+    if (g_tune.pull_variant == 1 && DT != ELX_F32) {
+        switch (a.grads.world) {
+            case 2: return launch_pull_tma<DT, 2>(a, s);
+            case 4: return launch_pull_tma<DT, 4>(a, s);
+            case 8: return launch_pull_tma<DT, 8>(a, s);
+        }
+    }
     switch (a.grads.world) {
         case 2: return launch_pull_inst<DT, 2>(a, s);
         case 4: return launch_pull_inst<DT, 4>(a, s);

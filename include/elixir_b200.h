@@ -158,6 +158,8 @@ const char* elx_last_cuda_error(void);
  *   "adam_variant"       0 = direct 256-bit global accesses, 1 = bulk-copy (TMA) pipeline through
  *                        shared memory
  *   "pull_ctas_per_sm"   cap on the grid of the pull reduce-scatter kernel, 0 = every resident CTA
+ *   "pull_variant"       0 = per-lane peer loads, 1 = bulk-copy staging through shared memory (16-bit
+ *                        chunks and groups of 2, 4 or 8 ranks; other cases use variant 0)
  *   "math_mode"          1 = IEEE division and square root in the update, 2 = reciprocal
  *                        multiplies and approximate division (both within 1e-6 relative) */
 int elx_set_tuning(const char* name, int value);

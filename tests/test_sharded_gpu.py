@@ -103,7 +103,7 @@ def _worker(rank, world, port):
     dist.destroy_process_group()
 
 
-def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False):
+def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False, pull_variant=1):
     """The NVLink path: pull reduce-scatter + probe, overflow agreement inside the barrier, fused update with
     push all-gather — no NCCL collective in the step."""
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
@@ -146,6 +146,7 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False
     engine.finalize()
     engine.set_hyper(hypers)
     engine.enable_p2p(chunk_sizes, timeout_ms=5000, pool=pool)
+    K.set_tuning(pull_variant=pull_variant)
     if staged:
         engine.enable_staging(pool=2)
 
@@ -219,6 +220,15 @@ def test_sharded_step_staged_copy_engines(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f'needs {world} GPUs')
     mp.spawn(_p2p_worker, args=(world, 29870 + world, 'float16', None, True), nprocs=world)
+
+
+@pytest.mark.parametrize('world,dtype_name', [(2, 'float16'), (2, 'bfloat16'), (4, 'float16')])
+def test_sharded_step_p2p_per_lane_pull(world, dtype_name):
+    """pull_variant=0: the slices are read with per-lane 256-bit peer loads instead of bulk copies into shared
+    memory (the default); same rank-order fp32 accumulation, so the same bits as the oracle."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f'needs {world} GPUs')
+    mp.spawn(_p2p_worker, args=(world, 29880 + world, dtype_name, None, False, 0), nprocs=world)
 
 
 def test_sharded_step_p2p_pooled_blocks():
