@@ -23,7 +23,6 @@ import statistics
 import subprocess
 import sys
 import tempfile
-import threading
 import time
 
 import torch
@@ -127,7 +126,7 @@ class ClockSampler:
 
 
 def chunk_layout(total, chunk, world):
-    """(n_chunks, [valid_end of this layout's LAST-rank-agnostic full chunk list]): used elements per chunk."""
+    """(number of chunks, used elements of each chunk) when `total` parameters are packed flat."""
     n = (total + chunk - 1) // chunk
     used = [chunk] * (n - 1) + [total - chunk * (n - 1)]
     return n, used
@@ -138,10 +137,10 @@ def valid_end(used, shard, rank):
     return max(0, min(shard, used - begin))
 
 
-def synth_shard(n, device, seed, scale, sigma, dtype):
+def synth_master(n, device, seed):
+    """Seeded fp32 master shard ~ N(0, 0.02)."""
     gen = torch.Generator(device=device).manual_seed(seed)
-    master = torch.empty(n, device=device, dtype=torch.float32).normal_(0.0, 0.02, generator=gen)
-    return master, gen
+    return torch.empty(n, device=device, dtype=torch.float32).normal_(0.0, 0.02, generator=gen)
 
 
 def synth_grad(n, device, gen, scale, sigma, dtype, out=None):
@@ -201,7 +200,7 @@ def run_ours(args):
                                    min_scale=1, max_scale=2**24, hysteresis=2)
     engine = ChunkStepEngine(device, dtype, scaler, process_group=group)
     for c in range(n_chunks):
-        master, gen = synth_shard(shard, device, args.seed + 1000 * rank + c, scale, sigma, dtype)
+        master = synth_master(shard, device, args.seed + 1000 * rank + c)
         nv = valid_end(used[c], shard, rank)
         if nv < shard:
             master[nv:].zero_()
@@ -210,7 +209,6 @@ def run_ours(args):
         engine.add_shard(master, lowp, nv, [(0, nv, 0)] if nv else [])
     engine.finalize()
     engine.set_hyper([K.hyper(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=wd, adamw_mode=True)])
-    owned = sum(valid_end(used[c], shard, rank) for c in range(n_chunks))
 
     # gradient sources
     if world == 1:

@@ -51,7 +51,6 @@ class ChunkStepEngine:
         self.total_l2sq: Optional[torch.Tensor] = None
         self._scratch: Optional[torch.Tensor] = None
         self._streams = None
-        self._finalized = False
 
     # ------------------------------------------------------------------ registration
 
@@ -79,7 +78,6 @@ class ChunkStepEngine:
         self.total_l2sq = torch.zeros(1, dtype=torch.float32, device=self.device)
         if self.clipping:
             self._scratch = torch.empty(max(1, self.table.tiles()), dtype=torch.float32, device=self.device)
-        self._finalized = True
         return self
 
     @property

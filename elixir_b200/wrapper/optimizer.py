@@ -15,10 +15,8 @@ from enum import Enum
 from typing import Dict, List, Set, Tuple
 
 import torch
-import torch.distributed as dist
 from torch.nn import Parameter
 
-from .. import kernels
 from ..chunk import Chunk
 from ..engine import ChunkStepEngine
 from ..optim import FusedAdam, HybridAdam
