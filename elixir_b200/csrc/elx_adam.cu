@@ -514,9 +514,12 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                 bulk_s2g(slot.exp_avg_sq + slot.e0, base + Stage::kLowpBytes + 2 * Stage::kF32Bytes, Stage::kF32Bytes);
                 // push all-gather: the same 8 KB of refreshed parameters to every rank's gather block,
                 // plain (non-multicast) bulk stores, W - 1 of them crossing NVLink
-                for (int j = 0; j < a.push.world; ++j)
+                // (start with a different rank in every CTA, so that the stores spread over all links at once)
+                for (int i = 0; i < a.push.world; ++i) {
+                    const int j = (a.push.rank + 1 + i + static_cast<int>(blockIdx.x)) % a.push.world;
                     bulk_s2g(static_cast<char*>(a.push.base[j]) + slot.push_elem * Lp<DT>::kBytes, base,
                              Stage::kLowpBytes);
+                }
             }
             bulk_commit();
             if (k + kTmaStages - 1 < my_tiles) {
