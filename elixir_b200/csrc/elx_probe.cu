@@ -208,7 +208,7 @@ int launch_probe_inst(const ProbeArgs& a, cudaStream_t s) {
 
 template <int DT, bool COPY>
 int launch_probe_norm(const ProbeArgs& a, bool norm, cudaStream_t s) {
-    // fp32 tiles are twice as many bytes: half the unroll keeps the register budget
+    // fp32 tiles are twice as many bytes: half the unroll keeps the register count
     constexpr int kBig = DT == ELX_F32 ? 4 : 8;
     constexpr int kSmall = DT == ELX_F32 ? 2 : 4;
     const bool big = g_tune.probe_unroll >= 8;

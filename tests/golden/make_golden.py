@@ -1,6 +1,6 @@
 """Generate the golden fixtures of this directory by running hpcaitech/Elixir's OWN Python code on CPU.
 
-    python tests/golden/make_golden.py [/path/to/Elixir]        (default /root/reference)
+    python tests/golden/make_golden.py /path/to/Elixir        (or set ELIXIR_REFERENCE)
 
 Needs the reference checkout; the fixtures it writes (`chunk_w*.pt`, `optim_w*.pt`) are committed, so
 the test-suite does not.  What runs is the reference's `elixir.chunk.Chunk` / `ChunkGroup` /
@@ -27,7 +27,7 @@ import torch.multiprocessing as mp
 import torch.nn as nn
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get('ELIXIR_REFERENCE', '/root/reference')    # overridden by the command-line argument in main()
+REF = os.environ.get('ELIXIR_REFERENCE', '')    # checkout of hpcaitech/Elixir; the command-line argument wins
 
 CHUNK_SHAPES = [(2, 64), (2, 2, 128), (128,), (4, 32)]    # 896 of 1024 elements used, as test/chunk/test_chunk.py
 CHUNK_SIZE = 1024
@@ -209,6 +209,8 @@ def main():
     global REF
     if len(sys.argv) > 1:
         REF = sys.argv[1]
+    if not os.path.isdir(os.path.join(REF, 'elixir')):
+        raise SystemExit('give the path of a checkout of hpcaitech/Elixir (argument or ELIXIR_REFERENCE)')
     os.environ['ELIXIR_REFERENCE'] = REF    # spawned workers re-import this module
     for i, world in enumerate((1, 2, 4)):
         with tempfile.TemporaryDirectory() as tmp:
