@@ -189,6 +189,8 @@ def run_ours(args):
         workload, total, chunk, scale, wd = f'opt13b_chunks_sharded_w{world}', OPT13B_PARAMS, CHUNK_SHARDED, 1024.0, 0.0
     if args.params:
         total, workload = args.params, workload + f'_params{args.params}'
+    if args.chunk_elems:
+        chunk, workload = args.chunk_elems, workload + f'_chunk{args.chunk_elems}'
     n_chunks, used = chunk_layout(total, chunk, world)
     shard = chunk // world
 
@@ -597,6 +599,7 @@ def main():
                     help='N > 1: collectives fused into the kernels over peer-mapped NVLink memory, or NCCL')
     ap.add_argument('--workload', default='auto', choices=['auto', 'opt66b_bf16'],
                     help='N > 1: auto = OPT-13B-shaped fp16 chunk set; opt66b_bf16 = OPT-66B-shaped bf16 chunk set (8 GPUs)')
+    ap.add_argument('--chunk-elems', type=int, default=0, help='override the chunk size in elements (profiling cases)')
     ap.add_argument('--params', type=int, default=0, help='override the parameter count (smoke runs of a workload)')
     ap.add_argument('--pool', type=int, default=0,
                     help='N > 1: number of replicated blocks per slab (0 = one per chunk); chunk k uses block k %% pool')
