@@ -39,7 +39,7 @@ BYTES_PER_ELEM = 28    # g 2 + p/m/v 12 read, p/m/v 12 + p16 2 written
 # dram__bytes_read.sum + dram__bytes_write.sum of one adam_tma_kernel launch over 67 108 864 elements,
 # from the ncu capture summarised in profiles/adam_tma_kernel_small_case_ncu.md; traffic grows in
 # proportion to the elements, so roofline.traffic scales it to the launch measured here.
-NCU_TRAFFIC_BYTES_PER_ELEM = 1819.3e6 / 67108864
+NCU_TRAFFIC_BYTES_PER_ELEM = 1819.9e6 / 67108864
 
 
 def load_peaks():
