@@ -232,7 +232,8 @@ int probe_single(const void* src, void* dst, int dtype, int64_t n_shard, int64_t
     if (!flag && !ctl && !l2sq && !copy) return ELX_ERR_NULL;
     if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
     if (n_shard < 0 || n_valid < 0 || n_valid > n_shard) return ELX_ERR_SIZE;
-    if (!aligned(src, 32) || (copy && !aligned(dst, 32))) return ELX_ERR_ALIGN;
+    // element alignment is enough: tiles whose addresses are not 32-byte aligned take the scalar path
+    if (!aligned(src, dtype_bytes(dtype)) || (copy && !aligned(dst, dtype_bytes(dtype)))) return ELX_ERR_ALIGN;
     if ((flag && !aligned(flag, 4)) || (ctl && !aligned(ctl, 16)) || (l2sq && !aligned(l2sq, 4))) return ELX_ERR_ALIGN;
     if (copy) {
         const char* s0 = static_cast<const char*>(src);

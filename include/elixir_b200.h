@@ -198,7 +198,8 @@ int elx_step_begin(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq, void* st
  * When l2sq != NULL the sum of squares of the same elements (each converted to fp32) is written
  * to *l2sq, reduced in a fixed order (bit-reproducible); replaces set_l2_norm (chunk.py:218-221).
  * That needs `scratch` (device floats, >= elx_probe_scratch_elems(ceil(n_valid/ELX_TILE))).
- * g: device, 32-byte aligned.  flag, l2sq may alias nothing else.
+ * g: device, aligned to its element size (32-byte alignment enables the vector path).  flag, l2sq may
+ * alias nothing else.
  */
 int elx_grad_check(const void* g, int dtype, int64_t n_valid, uint32_t* flag, ElxCtl* ctl,
                    float* l2sq, float* scratch, int64_t scratch_elems, void* stream);
@@ -229,8 +230,8 @@ int64_t elx_grad_check_static_max_elems(void);
 /*
  * The same probe fused with the copy that ends Chunk.reduce (chunk.py:313, 484-489): copies
  * n_shard elements src -> dst (the reduced slice of the replicated block into the persistent
- * shard) and probes the first n_valid of them in the same pass.  src, dst: device, 32-byte
- * aligned, must not overlap.
+ * shard) and probes the first n_valid of them in the same pass.  src, dst: device, aligned to the
+ * element size (32-byte alignment of both enables the vector path), must not overlap.
  */
 int elx_reduce_epilogue(const void* src, void* dst, int dtype, int64_t n_shard, int64_t n_valid,
                         uint32_t* flag, ElxCtl* ctl, float* l2sq, float* scratch,

@@ -71,6 +71,26 @@ def test_probe_respects_valid_end(K, oracle, cuda, dtype):
             assert flag.item() == 1 and oracle.probe(gc, n_valid)
 
 
+@pytest.mark.parametrize('dtype', DTYPES)
+def test_probe_and_epilogue_on_views_off_the_vector_alignment(K, oracle, cuda, dtype):
+    """A shard slice inside a replicated block starts wherever the shard size puts it: element-aligned views
+    take the scalar path and give the same answers."""
+    n = 3 * 4096 + 11
+    gen = torch.Generator().manual_seed(17)
+    base = (torch.randn(n + 5, generator=gen) * 10).to(dtype)
+    for off in (1, 3, 5):
+        src = base[off:off + n].clone()
+        src[n - 2] = float('inf')
+        block = torch.zeros(n + 8, dtype=dtype, device=cuda)
+        block[off:off + n].copy_(src)
+        dst_store = torch.zeros(n + 8, dtype=dtype, device=cuda)
+        flag = torch.zeros(1, dtype=torch.int32, device=cuda)
+        K.reduce_epilogue(block[off:off + n], dst_store[off + 2:off + 2 + n], n_valid=n - 2, flag=flag)
+        assert flag.item() == 0 and bits_equal(dst_store[off + 2:off + 2 + n], src)
+        K.grad_check(block[off:off + n], n_valid=n - 1, flag=flag)
+        assert flag.item() == 1 and oracle.probe(src, n - 1)
+
+
 def test_probe_largest_finite_values_do_not_flag(K, cuda):
     for dtype, big in ((torch.float16, 65504.0), (torch.bfloat16, 3.3895e38), (torch.float32, 3.4028e38)):
         g = torch.full((8192,), big, dtype=dtype, device=cuda)
@@ -582,7 +602,7 @@ def test_bad_arguments_are_rejected(K, cuda):
     assert lib.elx_grad_check(None, 0, 10, P(flag), None, None, None, 0, None) == _abi.ERR_NULL
     assert lib.elx_grad_check(P(g16), 7, 10, P(flag), None, None, None, 0, None) == _abi.ERR_DTYPE
     assert lib.elx_grad_check(P(g16), 0, -1, P(flag), None, None, None, 0, None) == _abi.ERR_SIZE
-    assert lib.elx_grad_check(ctypes.c_void_p(g16.data_ptr() + 2), 0, 10, P(flag), None, None, None, 0,
+    assert lib.elx_grad_check(ctypes.c_void_p(g16.data_ptr() + 1), 0, 10, P(flag), None, None, None, 0,
                               None) == _abi.ERR_ALIGN
     out = torch.zeros(1, device=cuda)
     assert lib.elx_grad_check(P(g16), 0, 4096, None, None, P(out), None, 0, None) == _abi.ERR_NULL

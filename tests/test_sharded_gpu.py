@@ -297,6 +297,60 @@ def test_wrapper_data_parallel_training_matches_plain_ddp():
     mp.spawn(_wrapper_worker, args=(2, 29840), nprocs=2)
 
 
+def _amp_worker(rank, world, port):
+    """fp16 working copies, fp32 gradient accumulation across ranks (reduce_always_fp32), loss scale 1: the
+    setting of the reference's test/wrapper/test_amp.py.  Compared with hand-written mixed precision: fp16
+    replica refreshed from fp32 masters, fp16 backward, gradients averaged in fp32, torch AdamW on the masters."""
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE='0')
+    sys.path.insert(0, ROOT)
+    import copy
+    import torch.distributed as dist
+    import torch.nn as nn
+    from elixir_b200.optim import HybridAdam
+    from elixir_b200.wrapper import ElixirModule, ElixirOptimizer, simple_plan
+    torch.cuda.set_device(rank)
+    dev = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    torch.manual_seed(0)
+    masters = nn.Sequential(nn.Linear(40, 72), nn.GELU(), nn.Linear(72, 72), nn.GELU(), nn.Linear(72, 6)).to(dev)
+    replica = copy.deepcopy(masters).half()
+    wrapped = copy.deepcopy(masters)
+    opt = torch.optim.AdamW(masters.parameters(), lr=1e-2, betas=(0.875, 0.99609375), weight_decay=0.0)
+    sr = simple_plan(wrapped, world, split_number=3, unified_dtype=torch.float16)
+    inner = HybridAdam(wrapped.parameters(), lr=1e-2, betas=(0.875, 0.99609375), weight_decay=0.0)
+    emodel = ElixirModule(wrapped, sr, dist.group.WORLD, dtype=torch.float16, reduce_always_fp32=True, output_fp32=True)
+    eopt = ElixirOptimizer(emodel, inner, initial_scale=1.0)
+    for step in range(2):
+        torch.manual_seed(100 * step + rank)
+        x = torch.randn(16, 40, device=dev)
+        with torch.no_grad():
+            for h, m in zip(replica.parameters(), masters.parameters()):
+                h.copy_(m)
+        replica.zero_grad()
+        replica(x.half()).float().pow(2).mean().backward()
+        for h, m in zip(replica.parameters(), masters.parameters()):
+            g = h.grad.float() / world    # divide, then sum, in fp32 (elixir/chunk/core/chunk.py:292-303)
+            dist.all_reduce(g)
+            m.grad = g.half().float()     # the averaged gradient goes back to the fp16 chunk (chunk.py:306-308)
+        opt.step()
+        eopt.zero_grad()
+        eopt.backward(emodel(x).pow(2).mean())
+        eopt.step()
+    got = emodel.state_dict()
+    for name, ref in masters.state_dict().items():
+        torch.testing.assert_close(got[name].to(dev), ref)
+    assert eopt.engine.read_control().status == 0
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_wrapper_amp_with_fp32_gradient_reduction():
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    mp.spawn(_amp_worker, args=(2, 29845), nprocs=2)
+
+
 def test_wrapper_training_with_the_nvlink_step_matches_plain_ddp():
     """The same training with the replica cache in peer-mapped memory: no NCCL collective after the first
     gather; reduce-scatter and all-gather happen inside the optimizer's kernels."""
