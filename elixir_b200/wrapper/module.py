@@ -21,6 +21,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from .. import comm
 from ..chunk import ChunkFetcher, ChunkGroup, MemoryPool, TensorState
 from .plan import SearchResult
 
@@ -225,6 +226,8 @@ class ElixirModule(nn.Module):
             loads = [state_dict[n].float() if state_dict is not None and n in state_dict else None for n in names]
             o_chunk.load_tensors(loads, only_rank_0)
             p_chunk.optim_update()
+            if p_chunk.is_replica:    # the chunk is gathered (e.g. left so by the NVLink step): refresh the replica too
+                comm.all_gather(p_chunk.rcb.payload, p_chunk.shard, p_chunk.torch_pg)
         for name, tensor in self.no_grad_state_dict.items():
             if state_dict is not None and name in state_dict:
                 tensor.data.copy_(state_dict[name])

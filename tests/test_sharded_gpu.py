@@ -287,6 +287,14 @@ def _wrapper_worker(rank, world, port, nvlink=False):
     for name, ref in plain.state_dict().items():
         torch.testing.assert_close(got[name].to(dev), ref, rtol=2e-6, atol=2e-5)
     assert eopt.engine.read_control().status == 0
+    # sharded checkpoint round trip: only rank 0 supplies the tensors, every rank ends with its shard
+    zeros = {k: torch.zeros_like(v) for k, v in got.items()}
+    emodel.load_state_dict(zeros if rank == 0 else None, only_rank_0=True)
+    assert all(float(v.abs().max()) == 0.0 for v in emodel.state_dict().values())
+    emodel.load_state_dict(got if rank == 0 else None, only_rank_0=True)
+    again = emodel.state_dict()
+    for name in got:
+        assert torch.equal(again[name], got[name])
     dist.barrier()
     dist.destroy_process_group()
 
