@@ -240,3 +240,52 @@ def test_checkpoint_resume_continues_bit_identically(cuda, single_group):
     for got, ref in zip(eopt2.engine.shards, want):
         for a, b in zip(got[:4], ref):
             assert bits_equal(a, b)
+
+
+def test_bf16_module_runs_with_a_constant_scale_and_matches_the_oracle(cuda, oracle, single_group):
+    """bfloat16 working copies (an extension: the reference accepts float and float16 only): constant loss scale
+    1, no unscale, same fused step."""
+    from elixir_b200 import kernels as K
+    from elixir_b200.scaler import ConstantGradScaler
+    torch.manual_seed(8)
+    model = Mlp().to(cuda)
+    emodel, eopt = _wrap(model, single_group, torch.bfloat16)
+    assert isinstance(eopt.grad_scaler, ConstantGradScaler) and not emodel.use_amp
+    host_ctl = oracle.new_ctl(1.0)
+    hyper = [K.hyper(lr=1e-3, weight_decay=0.01)]
+    chunks = emodel.param_chunks
+    for step in range(2):
+        eopt.zero_grad()
+        eopt.backward(emodel(torch.randn(8, 48, device=cuda)))
+        cs = oracle.ChunkSet(torch.bfloat16)
+        masters = []
+        for i in range(len(chunks)):
+            m, e1, e2, lowp, nv = (t.cpu().clone() if torch.is_tensor(t) else t for t in eopt.engine.shards[i])
+            cs.add_chunk(m, e1, e2, lowp, nv, [(0, nv, 0)] if nv else [])
+            masters.append(m)
+        eopt.step()
+        assert not cs.step(host_ctl, eopt.grad_scaler.cfg, hyper, probe=True, f64=True)
+        ctl = eopt.engine.read_control()
+        assert (ctl.scale, ctl.div_scale, ctl.step) == (1.0, -1.0, step + 1)
+        for i, c in enumerate(chunks):
+            assert close_1e6(eopt.engine.shards[i][0], masters[i].double())[0]
+            want16 = torch.empty(c.shard_size, dtype=torch.bfloat16)
+            oracle.cast(c.paired_chunk.shard.cpu(), want16)
+            assert bits_equal(c.shard, want16)
+
+
+def test_wrapper_gradient_clipping(cuda, single_group):
+    """max_norm at the wrapper level: the update is divided by clip x scale once the unscaled global norm exceeds
+    max_norm (the reference's dead clipping branch, elixir/wrapper/optimizer.py:149-183, made to work)."""
+    torch.manual_seed(9)
+    model = Mlp().to(cuda)
+    emodel, eopt = _wrap(model, single_group, torch.float16, initial_scale=256.0, max_norm=1e-3)
+    x = torch.randn(8, 48, device=cuda)
+    eopt.zero_grad()
+    eopt.backward(emodel(x))
+    eopt.step()
+    ctl = eopt.engine.read_control()
+    assert ctl.skip == 0 and ctl.status == 0
+    assert ctl.grad_norm > 1e-3 and ctl.clip_coef > 1.0
+    assert abs(ctl.div_scale - ctl.clip_coef * 256.0) <= 1e-5 * ctl.div_scale
+    assert abs(ctl.clip_coef - (ctl.grad_norm + 1e-6) / 1e-3) <= 1e-5 * ctl.clip_coef
