@@ -1,6 +1,6 @@
 """Generate the golden fixtures of this directory by running hpcaitech/Elixir's OWN Python code on CPU.
 
-    python tests/golden/make_golden.py /path/to/Elixir        (or set ELIXIR_REFERENCE)
+    python tests/golden/make_golden.py /path/to/Elixir [output directory]       (or set ELIXIR_REFERENCE)
 
 Needs the reference checkout; the fixtures it writes (`chunk_w*.pt`, `optim_w*.pt`) are committed, so
 the test-suite does not.  What runs is the reference's `elixir.chunk.Chunk` / `ChunkGroup` /
@@ -209,6 +209,7 @@ def main():
     global REF
     if len(sys.argv) > 1:
         REF = sys.argv[1]
+    out_dir = sys.argv[2] if len(sys.argv) > 2 else HERE
     if not os.path.isdir(os.path.join(REF, 'elixir')):
         raise SystemExit('give the path of a checkout of hpcaitech/Elixir (argument or ELIXIR_REFERENCE)')
     os.environ['ELIXIR_REFERENCE'] = REF    # spawned workers re-import this module
@@ -217,7 +218,7 @@ def main():
             mp.spawn(worker, args=(world, 29600 + i, tmp), nprocs=world)
             for kind in ('chunk', 'optim'):
                 per_rank = [torch.load(os.path.join(tmp, f'{kind}_{r}.pt')) for r in range(world)]
-                torch.save(dict(world=world, ranks=per_rank), os.path.join(HERE, f'{kind}_w{world}.pt'))
+                torch.save(dict(world=world, ranks=per_rank), os.path.join(out_dir, f'{kind}_w{world}.pt'))
         print(f'world {world}: fixtures written')
 
 

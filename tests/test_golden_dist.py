@@ -61,3 +61,31 @@ def test_oracle_replays_reference_steps(oracle):
                 for m, ref in zip(masters, want['master']):
                     ok, ratio = close_1e6(m, ref.double(), rtol=2e-6)
                     assert ok, (world, rank, s, ratio)
+
+
+def _same(a, b):
+    if torch.is_tensor(a):
+        return torch.is_tensor(b) and a.dtype == b.dtype and W.bits_equal(a, b)
+    if isinstance(a, dict):
+        return a.keys() == b.keys() and all(_same(a[k], b[k]) for k in a)
+    if isinstance(a, (list, tuple)):
+        return len(a) == len(b) and all(_same(x, y) for x, y in zip(a, b))
+    return a == b
+
+
+def test_committed_fixtures_are_what_the_reference_produces(tmp_path):
+    """Where a checkout of hpcaitech/Elixir is at hand (ELIXIR_REFERENCE, or the path this repository was
+    developed against), rerun the generator and compare with the committed fixtures bit for bit."""
+    import os
+    import subprocess
+    import sys
+    ref = os.environ.get('ELIXIR_REFERENCE') or '/root/reference'
+    if not os.path.isdir(os.path.join(ref, 'elixir')):
+        pytest.skip('no checkout of the reference')
+    script = os.path.join(W.GOLDEN, 'make_golden.py')
+    subprocess.run([sys.executable, script, ref, str(tmp_path)], check=True, capture_output=True, timeout=900)
+    for world in (1, 2, 4):
+        for kind in ('chunk', 'optim'):
+            fresh = torch.load(os.path.join(str(tmp_path), f'{kind}_w{world}.pt'))
+            committed = torch.load(os.path.join(W.GOLDEN, f'{kind}_w{world}.pt'))
+            assert _same(fresh, committed), (kind, world)
