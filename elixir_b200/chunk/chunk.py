@@ -107,6 +107,7 @@ class Chunk:
         self._l2_scratch = None
         self._ctl = None    # ControlBlock of the optimizer that steps this chunk (set by bind_control)
         self._probed = False
+        self.ready_event = None    # set by a gather issued ahead of time on a side stream; its consumer waits on it
 
     # ------------------------------------------------------------------ properties
 
@@ -153,6 +154,16 @@ class Chunk:
         idle = sum(self.tensor_state_cnter[s]
                    for s in (TensorState.HOLD, TensorState.HOLD_AFTER_BWD, TensorState.READY_FOR_REDUCE))
         return idle == self.num_tensors
+
+    @property
+    def evict_check(self) -> bool:
+        """Whether the replica may be dropped for another chunk: every tensor merely held.  Stricter than
+        ``scatter_check``: a chunk that already holds gradients of this backward pass in its block (tensors
+        in HOLD_AFTER_BWD or READY_FOR_REDUCE) keeps the block until it is reduced, since a scatter would
+        lose them."""
+        if self.rcache_fused:
+            return False
+        return self.tensor_state_cnter[TensorState.HOLD] == self.num_tensors
 
     @property
     def reduce_check(self) -> bool:
@@ -288,6 +299,7 @@ class Chunk:
             assert block in self.rcache.public_used_blocks
             assert self.rcb is None
             self.rcb = block
+        self.rcb.owner = self
         self.replicate()
 
     def release_chunk(self) -> TensorBlock:

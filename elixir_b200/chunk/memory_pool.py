@@ -29,6 +29,8 @@ class TensorBlock:
         self.payload = payload if payload is not None else torch.empty((numel,), dtype=dtype, device=device_type)
         assert self.payload.numel() == numel and self.payload.dtype == dtype
         self.memo_occ = numel * self.payload.element_size()
+        self.owner = None         # the chunk whose replica lives here at the moment
+        self.free_event = None    # CUDA event after which a new owner may overwrite the payload
 
     @property
     def numel(self):
@@ -140,7 +142,12 @@ class MemoryPool:
         return self.private_lookup_dict[BlockRequire(numel=numel, dtype=dtype)].pop()
 
     def get_public_block(self) -> PublicBlock:
+        """A free block.  If its last user gave it back from another CUDA stream, the current stream is made
+        to wait for that user's queued work before the caller may overwrite the payload."""
         block = self.public_free_blocks.pop()
+        if block.free_event is not None:
+            torch.cuda.current_stream(block.payload.device).wait_event(block.free_event)
+            block.free_event = None
         self.public_used_blocks.add(block)
         self.public_free_cnt -= 1
         self.public_used_cnt += 1
@@ -148,6 +155,10 @@ class MemoryPool:
 
     def free_public_block(self, block: TensorBlock) -> TensorBlock:
         assert isinstance(block, PublicBlock) and block in self.public_used_blocks
+        block.owner = None
+        if block.payload.is_cuda:
+            # whatever the current stream still has queued on this payload finishes before the next owner writes
+            block.free_event = torch.cuda.current_stream(block.payload.device).record_event()
         self.public_used_blocks.remove(block)
         self.public_free_blocks.append(block)
         self.public_free_cnt += 1

@@ -4,10 +4,12 @@
 produces what ``simple_search`` (``elixir/search/simple.py:77-110``) produces — parameters used by more
 than one module get a private chunk each, the others are split in order into ``split_number`` public
 chunks of one common size, every size rounded up to a multiple of the group size
-(``search/utils.py:5-6``) — with one difference: the replica cache gets a block for EVERY public chunk,
-because this package keeps all chunks gathered between forward and the end of backward instead of
-evicting them.  The memory- and bandwidth-model searches of the reference are planning-time tools
-outside the optimizer step and are not rebuilt.
+(``search/utils.py:5-6``).  The replica cache gets ``ceil(public chunks * allocate_factor)`` blocks as in
+the reference (``simple.py:72``), but ``allocate_factor`` defaults to 1 here (0.6 there): with a block per
+public chunk ``ElixirModule`` keeps everything gathered from forward to the end of backward, with fewer it
+schedules residency sub-module by sub-module.  ``public_block_number`` sets the count directly.  The
+memory- and bandwidth-model searches of the reference are planning-time tools outside the optimizer step
+and are not rebuilt.
 """
 import math
 from typing import Dict, List, NamedTuple, Optional
@@ -56,7 +58,8 @@ def simple_plan(m: nn.Module,
                 verbose: bool = False,
                 chunk_size: Optional[int] = None,
                 rcache_device=None,
-                peer_group=None) -> SearchResult:
+                peer_group=None,
+                public_block_number: Optional[int] = None) -> SearchResult:
     """Plan chunks for the parameters of ``m`` that require gradients.  ``chunk_size`` (elements) overrides
     the size derived from ``split_number``; parameters are then packed greedily in order.  ``peer_group`` (a
     single-node process group) places the replica cache in memory every rank of the group can address, which
@@ -110,9 +113,15 @@ def simple_plan(m: nn.Module,
         device = torch.device('cuda', torch.cuda.current_device())
         slab_factory = lambda numel, dtype: PeerBuffer(numel, dtype, device, peer_group)    # noqa: E731
     pool = MemoryPool(device_type, slab_factory=slab_factory)
+    if public_block_number is None:
+        public_block_number = math.ceil(len(groups) * allocate_factor)
+    if groups:
+        public_block_number = max(public_block_number, 1)
+    if peer_group is not None and public_block_number < len(groups):
+        raise ValueError('a replica cache in peer-mapped memory needs a block for every public chunk')
     pool.allocate(public_dtype=unified_dtype,
                   public_block_size=max(public_size, 1),
-                  public_block_number=max(len(groups), math.ceil(len(groups) * allocate_factor)),
+                  public_block_number=public_block_number,
                   private_block_list=[BlockRequire(pl.chunk_size, pl.chunk_dtype) for pl in plans
                                       if pl.kwargs.get('rcache_fused')])
     if verbose:

@@ -146,3 +146,115 @@ def optim_worker(rank, world, port, sync_overflow):
         assert any_rank_overflow == [s == INF_STEP for s in range(OPTIM_STEPS)]
     dist.barrier()
     dist.destroy_process_group()
+
+
+def _residency_model():
+    import torch.nn as nn
+
+    class TransposedLinear(nn.Module):
+        """Uses a VIEW of its parameter, which autograd saves for backward in place of the parameter."""
+
+        def __init__(self, n_in, n_out):
+            super().__init__()
+            self.weight = nn.Parameter(torch.randn(n_out, n_in) * 0.1)
+
+        def forward(self, x):
+            return x @ self.weight.t()
+
+    class Net(nn.Module):
+
+        def __init__(self):
+            super().__init__()
+            self.embed = nn.Embedding(50, 32)
+            self.blocks = nn.ModuleList()
+            for _ in range(4):
+                self.blocks.append(nn.Sequential(nn.LayerNorm(32), nn.Linear(32, 64), nn.Tanh(), TransposedLinear(64, 32)))
+            self.head = nn.Linear(32, 50, bias=False)
+            self.head.weight = self.embed.weight    # tied: a private chunk
+
+        def forward(self, ids):
+            x = self.embed(ids)
+            for block in self.blocks:
+                x = x + block(x)
+            return self.head(x).float().log_softmax(-1).mean().neg()
+
+    torch.manual_seed(11)
+    return Net()
+
+
+def residency_check(group, rank, world, prefetch, dtype, device):
+    """Scheduled residency (fewer blocks than public chunks) against everything-resident on the same model,
+    data and steps: same loss, same reduced gradients, same parameters after the steps, bit for bit."""
+    import copy
+    from elixir_b200.chunk import FIFOScheduler, PrefetchScheduler
+    from elixir_b200.optim import HybridAdam
+    from elixir_b200.wrapper import ElixirModule, ElixirOptimizer, simple_plan
+    base = _residency_model()
+    torch.manual_seed(100 + rank)
+    batches = [torch.randint(0, 50, (3, 7)).to(device) for _ in range(3)]
+    on_host = device.type == 'cpu'
+
+    def build(blocks):
+        model = copy.deepcopy(base)
+        sr = simple_plan(model, world, unified_dtype=dtype, shard_device=device, chunk_size=2400,
+                         rcache_device='cpu' if on_host else None, public_block_number=blocks)
+        emodel = ElixirModule(model, sr, group, prefetch=prefetch, dtype=dtype)
+        eoptim = ElixirOptimizer(emodel, HybridAdam(model.parameters(), lr=1e-2, weight_decay=0.01), initial_scale=4.0)
+        return emodel, eoptim
+
+    full, full_opt = build(None)
+    n_public = len(full.param_chunk_group.float_chunks)
+    assert n_public >= 5 and not full.scheduled
+    lean, lean_opt = build(2)
+    assert lean.scheduled and lean.param_chunk_group.rcache.public_free_cnt == 2
+    assert isinstance(lean.fetcher.scheduler, PrefetchScheduler if prefetch else FIFOScheduler)
+
+    with torch.no_grad():
+        assert bits_equal(full(batches[0]), lean(batches[0]))
+    assert lean.param_chunk_group.rcache.public_free_cnt == 2    # everything went back
+
+    for it, ids in enumerate(batches):
+        l_full, l_lean = full(ids), lean(ids)
+        assert bits_equal(l_full.detach(), l_lean.detach()), (it, rank)
+        full_opt.backward(l_full)
+        lean_opt.backward(l_lean)
+        stats = dict(lean.fetcher.stats)
+        assert stats['released'] > 0    # the replica cache really was too small
+        if prefetch and it > 0:
+            assert stats['ahead'] > 0 and stats['ahead_hit'] == stats['ahead'], stats    # the learnt trace was right
+        assert lean.param_chunk_group.rcache.public_free_cnt == 2
+        for a, b in zip(full.param_chunks, lean.param_chunks):
+            assert bits_equal(a.shard, b.shard), (it, rank, a.chunk_id)    # reduced gradients
+        full_opt.step()
+        lean_opt.step()
+        for a, b in zip(full.param_chunks, lean.param_chunks):
+            assert bits_equal(a.shard, b.shard) and bits_equal(a.paired_chunk.shard, b.paired_chunk.shard)
+        if not on_host:
+            assert lean_opt.engine.read_control().status == 0
+    if prefetch:
+        assert not lean.fetcher.scheduler.learning and lean.fetcher.scheduler.total_steps > 0
+
+
+def residency_worker(rank, world, port, prefetch, dtype_name):
+    """The check above on gloo ranks in host memory."""
+    use_host_shim()
+    dist = init_gloo(rank, world, port)
+    residency_check(dist.GroupMember.WORLD, rank, world, prefetch, getattr(torch, dtype_name), torch.device('cpu'))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def residency_worker_gpu(rank, world, port, prefetch, dtype_name):
+    """The same on one GPU per rank over NCCL (gathers ahead and reduces on side streams)."""
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE='0')
+    if ROOT not in sys.path:
+        sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    residency_check(dist.group.WORLD, rank, world, prefetch, getattr(torch, dtype_name), dev)
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()

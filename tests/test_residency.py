@@ -1,0 +1,125 @@
+"""Replica-cache scheduling: which chunk leaves (FIFO, Belady on a trace), gathers ahead of time, and the
+module-level residency hooks.  CPU: the schedulers on stand-in chunks, the rest on gloo ranks with the
+host-memory shim serving the elx_* ABI (the scheduling logic is all Python)."""
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+import _dist_workers as W
+from elixir_b200.chunk import FIFOScheduler, PrefetchScheduler
+
+
+class FakeChunk:
+    """What a scheduler needs of a chunk: identity and an order."""
+
+    def __init__(self, chunk_id):
+        self.chunk_id = chunk_id
+
+    def __hash__(self):
+        return self.chunk_id
+
+    def __eq__(self, other):
+        return self.chunk_id == other.chunk_id
+
+    def __lt__(self, other):
+        return self.chunk_id < other.chunk_id
+
+    def __repr__(self):
+        return f'c{self.chunk_id}'
+
+
+def test_fifo_releases_in_order_of_becoming_releasable():
+    a, b, c, d = (FakeChunk(i) for i in range(4))
+    s = FIFOScheduler()
+    s.reset()
+    assert s.top() is None
+    for x in (c, a, b):
+        assert s.add(x)
+    assert not s.add(c)    # already there: keeps its place
+    assert s.top() is c
+    assert s.remove(c) and not s.remove(c) and not s.remove(d)
+    assert s.top() is a
+    s.add(c)    # back of the queue
+    s.remove(a)
+    assert s.top() is b
+    s.remove(b)
+    assert s.top() is c
+    s.remove(c)
+    assert s.top() is None
+    s.clear()
+    with pytest.raises(AssertionError):
+        s.reset()
+        s.add(a)
+        s.clear()    # a chunk still waiting at the end of the pass
+
+
+def test_belady_releases_the_chunk_used_furthest_ahead():
+    a, b, c = (FakeChunk(i) for i in range(3))
+    trace = [[a], [b], [c], [a], [a, b], [c], [b]]
+    s = PrefetchScheduler(trace)
+    with torch.enable_grad():
+        s.reset()
+        s.step([a])    # step 0
+        assert s.next_use(a) == 3 and s.next_use(b) == 1 and s.next_use(c) == 2
+        s.add(a)
+        s.step([b])    # step 1
+        s.add(b)    # next use of b: 4, of a: 3
+        assert s.top() is b
+        s.step([c])    # step 2
+        s.add(c)    # next use of c: 5
+        assert s.top() is c
+        assert s.get_next_chunk([c]) is a
+        assert list(s.upcoming(exclude=[c])) == [(3, a), (4, b)]
+        s.remove(a)
+        s.step([a])    # step 3
+        s.add(a)    # a again at 4
+        assert s.top() is c
+        s.remove(c)
+        assert s.top() in (a, b) and s.top() is b    # both next used at step 4: the larger id goes
+        s.remove(a), s.remove(b)
+        s.step([a, b])    # step 4
+        s.add(a)    # never used again: 7 = len(trace)
+        s.add(b)    # 6
+        assert s.next_use(a) == 7 and s.top() is a
+        s.step([c])
+        s.step([b])
+        with pytest.raises(RuntimeError):
+            s.step([a])    # the pass is longer than the trace
+        s.remove(a), s.remove(b)
+        s.current_step = 6
+        s.clear()
+
+
+def test_prefetch_scheduler_learns_the_trace_from_the_first_pass():
+    a, b, c = (FakeChunk(i) for i in range(3))
+    s = PrefetchScheduler()
+    assert s.learning
+    with torch.no_grad():    # a pass without gradients is not the training trace
+        s.reset()
+        s.step([a])
+        s.clear()
+    assert s.learning
+    with torch.enable_grad():
+        s.reset()
+        for step in ([a], [b, c], [a], [c]):
+            s.step(step)
+            for x in step:
+                s.add(x)
+            assert s.top() is a    # FIFO while learning
+            assert s.get_next_chunk(step) is None and list(s.upcoming()) == []
+        for x in (a, b, c):
+            s.remove(x)
+        s.clear()
+        assert not s.learning and s.total_steps == 4
+        s.reset()
+        s.step([a])
+        assert s.next_use(a) == 2 and s.next_use(b) == 1 and s.next_use(c) == 1
+        assert list(s.upcoming(exclude=[a])) == [(1, b), (1, c)]
+        s.relearn()
+        assert s.learning
+
+
+@pytest.mark.parametrize('world', [1, 2])
+@pytest.mark.parametrize('prefetch', [False, True])
+def test_scheduled_residency_equals_everything_resident(world, prefetch):
+    mp.spawn(W.residency_worker, args=(world, 29740 + 2 * world + int(prefetch), prefetch, 'float32'), nprocs=world)

@@ -379,3 +379,11 @@ def test_sharded_step_nccl(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f'needs {world} GPUs')
     mp.spawn(_worker, args=(world, 29800 + world), nprocs=world)
+
+
+@pytest.mark.parametrize('prefetch', [False, True])
+def test_scheduled_residency_over_nccl(prefetch):
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    import _dist_workers as W
+    mp.spawn(W.residency_worker_gpu, args=(2, 29860 + int(prefetch), prefetch, 'float16'), nprocs=2)

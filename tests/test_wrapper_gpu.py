@@ -289,3 +289,12 @@ def test_wrapper_gradient_clipping(cuda, single_group):
     assert ctl.grad_norm > 1e-3 and ctl.clip_coef > 1.0
     assert abs(ctl.div_scale - ctl.clip_coef * 256.0) <= 1e-5 * ctl.div_scale
     assert abs(ctl.clip_coef - (ctl.grad_norm + 1e-6) / 1e-3) <= 1e-5 * ctl.clip_coef
+
+
+@pytest.mark.parametrize('prefetch', [False, True])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.float])
+def test_scheduled_residency_equals_everything_resident(cuda, single_group, prefetch, dtype):
+    """Two replica-cache blocks for five and more public chunks: chunks leave and come back during forward
+    and backward (FIFO; Belady with gathers ahead on a side stream), results bit-identical."""
+    import _dist_workers as W
+    W.residency_check(single_group, 0, 1, prefetch, dtype, cuda)
