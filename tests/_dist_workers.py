@@ -258,3 +258,87 @@ def residency_worker_gpu(rank, world, port, prefetch, dtype_name):
     torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()
+
+
+def gpt2_check(group, device, dtype):
+    """A micro GPT-2 (Hugging Face implementation, random weights, tied embedding) trained three steps:
+    plain torch AdamW, the wrapper with everything resident, the wrapper with two replica-cache blocks and
+    gathers ahead.  The two wrappers agree bit for bit; in fp32 they follow the plain run within the
+    tolerance of the reference's own wrapper test (rtol 2e-6, atol 2e-5; test/wrapper/test_optimizer.py:49)."""
+    import copy
+    import torch.nn as nn
+    from transformers import GPT2Config, GPT2LMHeadModel
+    from elixir_b200.optim import HybridAdam
+    from elixir_b200.wrapper import ElixirModule, ElixirOptimizer, simple_plan
+
+    class Lm(nn.Module):
+
+        def __init__(self):
+            super().__init__()
+            cfg = GPT2Config(n_embd=64, n_layer=3, n_head=4, n_positions=32, vocab_size=128, resid_pdrop=0.0,
+                             embd_pdrop=0.0, attn_pdrop=0.0)
+            self.module = GPT2LMHeadModel(cfg)
+
+        def forward(self, input_ids, attention_mask):
+            logits = self.module(input_ids=input_ids, attention_mask=attention_mask).logits
+            return nn.functional.cross_entropy(logits[:, :-1].reshape(-1, logits.size(-1)).float(),
+                                               input_ids[:, 1:].reshape(-1))
+
+    torch.manual_seed(0)
+    plain = Lm().to(device)
+    on_host = device.type == 'cpu'
+
+    def build(blocks, prefetch):
+        model = copy.deepcopy(plain)
+        sr = simple_plan(model, 1, unified_dtype=dtype, shard_device=device, chunk_size=40000,
+                         rcache_device='cpu' if on_host else None, public_block_number=blocks)
+        emodel = ElixirModule(model, sr, group, prefetch=prefetch, dtype=dtype)
+        return emodel, ElixirOptimizer(emodel, HybridAdam(model.parameters(), lr=1e-2, weight_decay=0.0),
+                                       initial_scale=128.0)
+
+    full, full_opt = build(None, False)
+    lean, lean_opt = build(2, True)
+    assert len(full.param_chunk_group.float_chunks) >= 4 and len(full.param_chunk_group.fused_chunks) == 1
+    assert lean.scheduled and not full.scheduled
+    opt = torch.optim.AdamW(plain.parameters(), lr=1e-2, weight_decay=0.0)
+    for it in range(3):
+        ids = torch.randint(0, 128, (4, 32), device=device)
+        mask = torch.ones_like(ids)
+        if dtype == torch.float:
+            opt.zero_grad()
+            loss = plain(ids, mask)
+            loss.backward()
+            opt.step()
+        l_full = full(input_ids=ids, attention_mask=mask)
+        l_lean = lean(input_ids=ids, attention_mask=mask)
+        assert bits_equal(l_full.detach(), l_lean.detach())
+        if dtype == torch.float:
+            torch.testing.assert_close(l_full.detach(), loss.detach(), rtol=1e-5, atol=1e-5)
+        full_opt.backward(l_full)
+        lean_opt.backward(l_lean)
+        stats = lean.fetcher.stats
+        assert stats['released'] > 0
+        if it > 0:
+            assert stats['ahead'] > 0 and stats['ahead_hit'] == stats['ahead'], stats
+        full_opt.step()
+        lean_opt.step()
+    got_full, got_lean = full.state_dict(), lean.state_dict()
+    for name, ref in plain.state_dict().items():
+        if name not in full.grad_state_dict:
+            continue
+        assert torch.equal(got_full[name], got_lean[name]), name
+        if dtype == torch.float:
+            a, b = got_full[name].to(device), ref
+            if name.endswith('c_attn.bias'):
+                # the key bias has no influence on the loss (softmax is shift-invariant): its gradient is
+                # rounding noise, which Adam normalises into steps of +-lr; compare the query and value parts
+                n = a.numel() // 3
+                a, b = torch.cat([a[:n], a[2 * n:]]), torch.cat([b[:n], b[2 * n:]])
+            torch.testing.assert_close(a, b, rtol=2e-6, atol=2e-5, msg=name)
+
+
+def gpt2_worker(rank, world, port):
+    use_host_shim()
+    dist = init_gloo(rank, world, port)
+    gpt2_check(dist.GroupMember.WORLD, torch.device('cpu'), torch.float)
+    dist.destroy_process_group()

@@ -123,3 +123,8 @@ def test_prefetch_scheduler_learns_the_trace_from_the_first_pass():
 @pytest.mark.parametrize('prefetch', [False, True])
 def test_scheduled_residency_equals_everything_resident(world, prefetch):
     mp.spawn(W.residency_worker, args=(world, 29740 + 2 * world + int(prefetch), prefetch, 'float32'), nprocs=world)
+
+
+def test_micro_gpt2_trains_identically_in_both_residency_modes_and_follows_plain_adamw():
+    pytest.importorskip('transformers')
+    mp.spawn(W.gpt2_worker, args=(1, 29760), nprocs=1)

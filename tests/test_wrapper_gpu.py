@@ -298,3 +298,10 @@ def test_scheduled_residency_equals_everything_resident(cuda, single_group, pref
     and backward (FIFO; Belady with gathers ahead on a side stream), results bit-identical."""
     import _dist_workers as W
     W.residency_check(single_group, 0, 1, prefetch, dtype, cuda)
+
+
+@pytest.mark.parametrize('dtype', [torch.float, torch.float16])
+def test_micro_gpt2_through_both_residency_modes(cuda, single_group, dtype):
+    pytest.importorskip('transformers')
+    import _dist_workers as W
+    W.gpt2_check(single_group, cuda, dtype)
