@@ -74,12 +74,12 @@ def _same(a, b):
 
 
 def test_committed_fixtures_are_what_the_reference_produces(tmp_path):
-    """Where a checkout of hpcaitech/Elixir is at hand (ELIXIR_REFERENCE, or the path this repository was
-    developed against), rerun the generator and compare with the committed fixtures bit for bit."""
+    """Where a checkout of hpcaitech/Elixir is at hand (ELIXIR_REFERENCE, or a directory `reference` beside
+    this repository), rerun the generator and compare with the committed fixtures bit for bit."""
     import os
     import subprocess
     import sys
-    ref = os.environ.get('ELIXIR_REFERENCE') or '/root/reference'
+    ref = os.environ.get('ELIXIR_REFERENCE') or os.path.join(os.path.dirname(W.ROOT), 'reference')
     if not os.path.isdir(os.path.join(ref, 'elixir')):
         pytest.skip('no checkout of the reference')
     script = os.path.join(W.GOLDEN, 'make_golden.py')
