@@ -357,7 +357,8 @@ def run_ours(args):
             'combined_bus_gbs': 2 * bus_bytes / (ms_per_step * 1e-3) / 1e9,
             'nominal_gbs_per_direction': 900.0, 'measured_peer_copy_gbs': 770.0,
         }
-        adam_bytes = engine.n_elements() * BYTES_PER_ELEM
+        # update/push phase: the 28 B/element of the update + 2 B/element for this rank's slot of its own gather block
+        adam_bytes = engine.n_elements() * (BYTES_PER_ELEM + 2)
         # the step is two phases in sequence, each bounded by the slower of its NVLink and its HBM time:
         # pull reduce-scatter (NVLink; HBM only reads and writes the own slice) and update + push all-gather
         link_ms = bus_bytes / 770.0e9 * 1e3
