@@ -64,6 +64,15 @@ class ChunkFetcher:
     # ------------------------------------------------------------------ one pass
 
     def reset(self) -> None:
+        """Start of a pass.  Replicas left behind by a pass that was abandoned (a forward with gradients
+        enabled that no backward followed) go back first, so that their blocks are not lost."""
+        for stream in (self.reduce_stream, self.prefetch_stream):
+            if stream is not None:
+                torch.cuda.current_stream(stream.device).wait_stream(stream)
+        for chunk in sorted(self.group.accessed_float_chunks):
+            chunk.ready_event = None
+            if chunk.evict_check:
+                self.group.release_chunk(chunk)
         self.scheduler.reset()
         self.current_step = -1
         self.predict_next_chunk = None

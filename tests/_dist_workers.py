@@ -342,3 +342,24 @@ def gpt2_worker(rank, world, port):
     dist = init_gloo(rank, world, port)
     gpt2_check(dist.GroupMember.WORLD, torch.device('cpu'), torch.float)
     dist.destroy_process_group()
+
+
+def abandoned_pass_worker(rank, world, port):
+    """A forward with gradients enabled that no backward follows must not cost replica-cache blocks."""
+    use_host_shim()
+    dist = init_gloo(rank, world, port)
+    import copy
+    from elixir_b200.wrapper import ElixirModule, simple_plan
+    cpu = torch.device('cpu')
+    model = copy.deepcopy(_residency_model())
+    sr = simple_plan(model, world, unified_dtype=torch.float, shard_device=cpu, chunk_size=2400, rcache_device='cpu',
+                     public_block_number=2)
+    emodel = ElixirModule(model, sr, dist.GroupMember.WORLD, dtype=torch.float)
+    ids = torch.randint(0, 50, (3, 7))
+    first = emodel(ids)    # leaves up to two chunks resident
+    assert emodel.param_chunk_group.rcache.public_free_cnt < 2
+    again = emodel(ids)
+    assert bits_equal(first.detach(), again.detach())
+    emodel.backward(again)
+    assert emodel.param_chunk_group.rcache.public_free_cnt == 2
+    dist.destroy_process_group()

@@ -128,3 +128,7 @@ def test_scheduled_residency_equals_everything_resident(world, prefetch):
 def test_micro_gpt2_trains_identically_in_both_residency_modes_and_follows_plain_adamw():
     pytest.importorskip('transformers')
     mp.spawn(W.gpt2_worker, args=(1, 29760), nprocs=1)
+
+
+def test_an_abandoned_forward_gives_its_blocks_back():
+    mp.spawn(W.abandoned_pass_worker, args=(1, 29761), nprocs=1)
