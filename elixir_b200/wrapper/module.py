@@ -27,6 +27,7 @@ Residency during forward / backward comes in two forms, chosen by the replica ca
   Limits: a parameter must be used through the module that owns it (or be shared, which gives it a
   private, always resident chunk); every parameter must receive a gradient in every backward pass.
 """
+import weakref
 from bisect import bisect_right
 from collections import OrderedDict
 from copy import copy
@@ -119,11 +120,20 @@ class ElixirModule(nn.Module):
             raise ValueError('the NVLink step keeps every chunk in its block; give the plan a block per chunk')
         self._init_chunk_fetcher(search_result, prefetch)
 
+        # The hook fires once per backward, after autograd has summed every use of the parameter.  It reaches this
+        # object through a weak reference: the tensor keeps its hooks on the C++ side, where the garbage collector
+        # cannot follow a parameter -> hook -> wrapper -> parameter cycle, and the whole model would never be freed.
+        me = weakref.ref(self)
+
+        def landed(param):
+            wrapper = me()
+            if wrapper is not None:
+                wrapper._post_accumulate(param)
+
         for name, param in module.named_parameters():
             if not param.requires_grad:
                 continue
-            # fires once per backward, after autograd has summed every use of the parameter
-            param.register_post_accumulate_grad_hook(self._post_accumulate)
+            param.register_post_accumulate_grad_hook(landed)
         if self.scheduled:
             self._install_residency_hooks()
 

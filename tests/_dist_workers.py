@@ -363,3 +363,34 @@ def abandoned_pass_worker(rank, world, port):
     emodel.backward(again)
     assert emodel.param_chunk_group.rcache.public_free_cnt == 2
     dist.destroy_process_group()
+
+
+def lifetime_worker(rank, world, port):
+    """Dropping the wrapper frees the model: no parameter -> hook -> wrapper cycle survives a collection."""
+    use_host_shim()
+    dist = init_gloo(rank, world, port)
+    import gc
+    import weakref
+    from elixir_b200.optim import HybridAdam
+    from elixir_b200.wrapper import ElixirModule, ElixirOptimizer, simple_plan
+    cpu = torch.device('cpu')
+
+    def train(blocks):
+        model = _residency_model()
+        sr = simple_plan(model, 1, unified_dtype=torch.float, shard_device=cpu, chunk_size=2400, rcache_device='cpu',
+                         public_block_number=blocks)
+        emodel = ElixirModule(model, sr, dist.GroupMember.WORLD, prefetch=True, dtype=torch.float)
+        eoptim = ElixirOptimizer(emodel, HybridAdam(model.parameters(), lr=1e-2), initial_scale=4.0)
+        ids = torch.randint(0, 50, (3, 7))
+        for _ in range(2):
+            eoptim.zero_grad()
+            eoptim.backward(emodel(ids))
+            eoptim.step()
+        chunk = emodel.param_chunks[0]
+        return [weakref.ref(o) for o in (emodel, eoptim, eoptim.engine, chunk, chunk.paired_chunk.shard)]
+
+    for blocks in (None, 2):
+        refs = train(blocks)
+        gc.collect()
+        assert all(r() is None for r in refs), (blocks, [r() is None for r in refs])
+    dist.destroy_process_group()

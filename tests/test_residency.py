@@ -132,3 +132,7 @@ def test_micro_gpt2_trains_identically_in_both_residency_modes_and_follows_plain
 
 def test_an_abandoned_forward_gives_its_blocks_back():
     mp.spawn(W.abandoned_pass_worker, args=(1, 29761), nprocs=1)
+
+
+def test_dropping_the_wrapper_frees_model_and_optimizer_state():
+    mp.spawn(W.lifetime_worker, args=(1, 29762), nprocs=1)
