@@ -86,8 +86,14 @@ class Chunk:
             self.chunk_temp.zero_()
         else:
             self.chunk_temp = torch.zeros(chunk_size, dtype=chunk_dtype, device=temp_device)
-        pin = cpu_pin_memory and shard_device.type == 'cpu'
+        # where the kernels that touch this chunk run: the shard's device, or -- for a shard kept in host
+        # memory beside a replica cache on a GPU (the reference's shard_device=cpu placement) -- that GPU;
+        # such a shard is always page-locked, because the kernels reach it through its mapped address
+        host_resident = shard_device.type == 'cpu' and default_device.type == 'cuda'
+        self.compute_device = default_device if host_resident else shard_device
+        pin = (cpu_pin_memory or host_resident) and shard_device.type == 'cpu'
         self.shard = torch.empty(self.shard_size, dtype=chunk_dtype, device=shard_device, pin_memory=pin)
+        self.host_resident = host_resident
 
         self.chunk_memo = chunk_size * self.chunk_temp.element_size()
         self.shard_memo = self.chunk_memo // self.pg_size
@@ -101,8 +107,8 @@ class Chunk:
         self.l2_norm_flag = False
 
         # probe results on the device: [0] overflow word; l2: sum of squares of the reduced gradients
-        self._flag = torch.zeros(1, dtype=torch.int32, device=shard_device)
-        self._l2sq = torch.zeros(1, dtype=torch.float32, device=shard_device)
+        self._flag = torch.zeros(1, dtype=torch.int32, device=self.compute_device)
+        self._l2sq = torch.zeros(1, dtype=torch.float32, device=self.compute_device)
         self._l2_valid = False
         self._l2_scratch = None
         self._ctl = None    # ControlBlock of the optimizer that steps this chunk (set by bind_control)
@@ -320,14 +326,19 @@ class Chunk:
         payload = self.rcb.payload
         my_slice = payload[self.shard_begin:self.shard_end]
         self._probed = False
-        if self.pg_size > 1 and not (always_fp32 and self.chunk_dtype != torch.float):
+        widen = always_fp32 and self.chunk_dtype != torch.float
+        if self.pg_size > 1 and not widen and not self.host_resident:
             # the collective writes this rank's average straight into the persistent shard; one read-only
             # pass then probes it
             comm.reduce_scatter_avg(self.shard, payload, self.torch_pg)
             kernels.grad_check(self.shard, n_valid=self.valid_end, flag=self._flag, ctl=self._ctl,
                                **self._norm_args())
         else:
-            if self.pg_size > 1:
+            if self.pg_size > 1 and not widen:
+                # shard in host memory: the collective cannot write there; it leaves the average in this rank's
+                # slice of the block (output aliased inside the input, as the reference does, chunk.py:299-303)
+                comm.reduce_scatter_avg(my_slice, payload, self.torch_pg)
+            elif self.pg_size > 1:
                 # fp32 accumulation (reduce_always_fp32): widen, average in fp32, narrow the own slice back
                 wide = payload.to(torch.float)
                 comm.reduce_scatter_avg(wide[self.shard_begin:self.shard_end], wide, self.torch_pg)
@@ -389,8 +400,8 @@ class Chunk:
     def _gathered_copy(self) -> torch.Tensor:
         if self.is_replica:
             return self.rcb.payload
-        buffer = torch.empty(self.chunk_size, dtype=self.chunk_dtype, device=self.shard_device)
-        comm.all_gather(buffer, self.shard, self.torch_pg)
+        buffer = torch.empty(self.chunk_size, dtype=self.chunk_dtype, device=self.compute_device)
+        self._gather_into(buffer, self.shard)
         return buffer
 
     def get_cpu_copy(self, only_rank_0: bool = False) -> List[Optional[torch.Tensor]]:
@@ -423,8 +434,14 @@ class Chunk:
     def _update_replica(self, replica: torch.Tensor, shard: torch.Tensor):
         assert self.is_replica
         assert replica.numel() == self.chunk_size and shard.numel() == self.shard_size
+        self._gather_into(replica, shard)
+
+    def _gather_into(self, replica: torch.Tensor, shard: torch.Tensor):
         if shard.device != replica.device:
-            shard = shard.to(replica.device, non_blocking=True)
+            # shard in host memory: into its own slot of the replica first, then gather in place
+            slot = replica[self.shard_begin:self.shard_end]
+            slot.copy_(shard, non_blocking=True)
+            shard = slot
         comm.all_gather(replica, shard, self.torch_pg)
 
     def _update_shard(self, replica: torch.Tensor, shard: torch.Tensor):
@@ -437,7 +454,10 @@ class Chunk:
         assert friend is not None, 'chunks should be paired before training'
         assert self.chunk_size == friend.chunk_size
         out = torch.empty(self.shard_size, dtype=self.chunk_dtype, device=self.rcb.payload.device)
-        kernels.cast_copyback(friend.shard.to(out.device), out)
+        source = friend.shard
+        if source.device != out.device and not kernels.is_mapped_host(source):
+            source = source.to(out.device)
+        kernels.cast_copyback(source, out)
         return out
 
     def _remove_tensors_ptr(self) -> None:

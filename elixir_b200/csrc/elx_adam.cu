@@ -78,6 +78,7 @@ struct AdamArgs {
     // push all-gather: the refreshed working copy also goes to every rank's gather block (world > 0)
     ElxPeerTable push;
     const int64_t* push_off;   // per descriptor: element offset of the chunk's block inside the slabs
+    int force_direct;          // always the ld/st variant (shards in mapped host memory)
     // single-shard form: the three tables travel in the kernel parameters
     ElxChunkDesc one_desc;
     ElxSeg one_seg;
@@ -610,7 +611,7 @@ int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
 template <int DT>
 int launch_adam_dt(const AdamArgs& a, cudaStream_t s) {
     const bool precise = g_tune.math_mode == 1;
-    if (g_tune.adam_variant == 1 || a.push.world > 0)
+    if ((g_tune.adam_variant == 1 && !a.force_direct) || a.push.world > 0)
         return precise ? launch_adam_tma<DT, 1>(a, s) : launch_adam_tma<DT, 2>(a, s);
     if (g_tune.adam_threads == 256)
         return precise ? launch_adam_minb<DT, 16, 1>(a, s) : launch_adam_minb<DT, 16, 2>(a, s);
@@ -630,8 +631,9 @@ int launch_adam(const AdamArgs& a, int dtype, cudaStream_t s) {
 
 extern "C" {
 
-int elx_adam_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype, const ElxSeg* segs,
-                   const ElxHyper* hyper, int n_groups, ElxCtl* ctl, void* stream) {
+static int adam_multi_common(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                             const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl, void* stream,
+                             int force_direct) {
     if (!descs || !ctl) return ELX_ERR_NULL;
     if (n_groups > 0 && (!segs || !hyper)) return ELX_ERR_NULL;
     if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
@@ -650,7 +652,18 @@ int elx_adam_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_ti
     a.count = count;
     a.n_groups = n_groups;
     a.n_tiles = n_tiles;
+    a.force_direct = force_direct;
     return launch_adam(a, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int elx_adam_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype, const ElxSeg* segs,
+                   const ElxHyper* hyper, int n_groups, ElxCtl* ctl, void* stream) {
+    return adam_multi_common(descs, first, count, n_tiles, dtype, segs, hyper, n_groups, ctl, stream, 0);
+}
+
+int elx_adam_multi_hostmem(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                           const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl, void* stream) {
+    return adam_multi_common(descs, first, count, n_tiles, dtype, segs, hyper, n_groups, ctl, stream, 1);
 }
 
 int elx_adam_multi_push(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,

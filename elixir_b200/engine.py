@@ -63,9 +63,15 @@ class ChunkStepEngine:
                   exp_avg_sq: Optional[torch.Tensor] = None) -> int:
         """Register a shard: fp32 master, the paired low-precision shard (gradient in / parameter out),
         ``valid_end`` and the (begin, end, param-group) ranges the optimizer updates.  The two moments
-        are allocated here, flat and congruent with the master, unless given."""
-        exp_avg = torch.zeros_like(master) if exp_avg is None else exp_avg
-        exp_avg_sq = torch.zeros_like(master) if exp_avg_sq is None else exp_avg_sq
+        are allocated here, flat and congruent with the master, unless given.  The four arrays may also be
+        pinned host tensors (a shard kept off the GPU): ``land``/``probe``/``step`` then reach them over PCIe
+        with the same kernels; the collective pipelines (``step_sharded*``) need device-resident shards."""
+        def zeros():    # where the master lives, page-locked if it is
+            return torch.zeros(master.shape, dtype=master.dtype, device=master.device,
+                               pin_memory=kernels.is_mapped_host(master))
+
+        exp_avg = zeros() if exp_avg is None else exp_avg
+        exp_avg_sq = zeros() if exp_avg_sq is None else exp_avg_sq
         index = self.table.add_chunk(master, exp_avg, exp_avg_sq, lowp, n_valid, segments)
         self.shards.append((master, exp_avg, exp_avg_sq, lowp, n_valid))
         return index
@@ -193,6 +199,7 @@ class ChunkStepEngine:
         gather stream:                                           AG(0)   AG(1) ...
         The update of any chunk starts only after every chunk was reduced and probed, because one
         overflow anywhere skips the whole step (``elixir/wrapper/optimizer.py:194-203``).
+        Shards must be device-resident (the collective writes into them).
 
         With ``host_grads`` (pinned, chunk_size each) block k is first filled from the host on the reduce
         stream; with ``host_params`` (pinned, shard_size each) the updated shard k is copied out on the
@@ -200,6 +207,8 @@ class ChunkStepEngine:
         collective that last read or wrote the block.
         """
         assert len(grad_blocks) == self.n_chunks and len(gather_blocks) == self.n_chunks
+        if self.table.host_resident:
+            raise RuntimeError('step_sharded needs device-resident shards: the collectives write into them')
         main = torch.cuda.current_stream(self.device)
         reduce_stream, gather_stream = self._side_streams()
         reduce_stream.wait_stream(main)

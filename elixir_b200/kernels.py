@@ -22,33 +22,53 @@ def dtype_code(dtype: torch.dtype) -> int:
         raise TypeError(f'elixir_b200 supports float16, bfloat16 and float32 chunks, not {dtype}') from None
 
 
-def _check_tensor(t: torch.Tensor, name: str, dtype: Optional[torch.dtype] = None):
+def is_mapped_host(t: torch.Tensor) -> bool:
+    """Page-locked host memory: under unified addressing a kernel reaches it through the same pointer."""
+    return t.device.type == 'cpu' and t.is_pinned()
+
+
+def _check_tensor(t: torch.Tensor, name: str, dtype: Optional[torch.dtype] = None, mapped_host: bool = False):
+    """``mapped_host``: the argument may also be a pinned host tensor (shard data of a host-resident chunk);
+    the kernels then read and write it over PCIe.  Pageable host memory is never accepted."""
     if not isinstance(t, torch.Tensor):
         raise TypeError(f'{name} must be a tensor')
     if not t.is_contiguous():
         raise ValueError(f'{name} must be contiguous')
     if dtype is not None and t.dtype != dtype:
         raise TypeError(f'{name} must be {dtype}, got {t.dtype}')
-    if not t.is_cuda and not _lib.host_memory_backend():
-        raise RuntimeError(f'{name} lives on {t.device}: the elixir_b200 kernels run on CUDA tensors only '
-                           '(there is no CPU path)')
+    if t.is_cuda or _lib.host_memory_backend():
+        return
+    if mapped_host and is_mapped_host(t):
+        return
+    raise RuntimeError(f'{name} lives on {t.device}: the elixir_b200 kernels run on CUDA tensors (and, for shard '
+                       'data, pinned host tensors) only; there is no CPU path')
 
 
 def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
 
-def _stream(t: torch.Tensor):
-    if t.is_cuda:
+def _stream(t: Optional[torch.Tensor]):
+    if t is not None and t.is_cuda:
         return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
     return None
+
+
+def _home(*tensors) -> Optional[torch.Tensor]:
+    """The first CUDA tensor among the arguments: its device runs the kernel, its current stream orders it."""
+    for t in tensors:
+        if t is not None and t.is_cuda:
+            return t
+    if _lib.host_memory_backend():
+        return None
+    raise RuntimeError('at least one argument must live on a CUDA device (flag, control block or data)')
 
 
 class _DeviceGuard:
     """Make the tensor's device current for the duration of a native call."""
 
-    def __init__(self, t: torch.Tensor):
-        self._ctx = torch.cuda.device(t.device) if t.is_cuda else None
+    def __init__(self, t: Optional[torch.Tensor]):
+        self._ctx = torch.cuda.device(t.device) if (t is not None and t.is_cuda) else None
 
     def __enter__(self):
         if self._ctx is not None:
@@ -143,7 +163,7 @@ def grad_check(g: torch.Tensor,
                scratch: Optional[torch.Tensor] = None):
     """Probe ``g[:n_valid]`` for inf/nan (``flag`` / ``ctl.found_inf`` are raised, never cleared) and,
     when ``l2sq`` is given, write its sum of squares there."""
-    _check_tensor(g, 'g')
+    _check_tensor(g, 'g', mapped_host=True)
     n_valid = g.numel() if n_valid is None else int(n_valid)
     if n_valid > g.numel():
         raise ValueError('n_valid exceeds the tensor')
@@ -154,11 +174,12 @@ def grad_check(g: torch.Tensor,
         if scratch is None:
             raise ValueError('l2sq needs a scratch tensor of probe_scratch_elems(n_tiles) floats')
         _check_tensor(scratch, 'scratch', torch.float32)
-    with _DeviceGuard(g):
+    home = _home(g, flag, ctl.tensor if ctl else None, l2sq)
+    with _DeviceGuard(home):
         _lib.check(
             _lib.get().elx_grad_check(_ptr(g), dtype_code(g.dtype), n_valid, _ptr(flag), ctl.ptr if ctl else None,
                                       _ptr(l2sq), _ptr(scratch), scratch.numel() if scratch is not None else 0,
-                                      _stream(g)), 'elx_grad_check')
+                                      _stream(home)), 'elx_grad_check')
 
 
 def reduce_epilogue(src: torch.Tensor,
@@ -169,8 +190,8 @@ def reduce_epilogue(src: torch.Tensor,
                     l2sq: Optional[torch.Tensor] = None,
                     scratch: Optional[torch.Tensor] = None):
     """``dst.copy_(src)`` fused with the probe of ``src[:n_valid]``."""
-    _check_tensor(src, 'src')
-    _check_tensor(dst, 'dst', src.dtype)
+    _check_tensor(src, 'src', mapped_host=True)
+    _check_tensor(dst, 'dst', src.dtype, mapped_host=True)
     if src.numel() != dst.numel():
         raise ValueError('src and dst differ in size')
     n_valid = src.numel() if n_valid is None else int(n_valid)
@@ -179,11 +200,12 @@ def reduce_epilogue(src: torch.Tensor,
     if l2sq is not None:
         _check_tensor(l2sq, 'l2sq', torch.float32)
         _check_tensor(scratch, 'scratch', torch.float32)
-    with _DeviceGuard(src):
+    home = _home(src, dst, flag, ctl.tensor if ctl else None)
+    with _DeviceGuard(home):
         _lib.check(
             _lib.get().elx_reduce_epilogue(_ptr(src), _ptr(dst), dtype_code(src.dtype), src.numel(), n_valid,
                                            _ptr(flag), ctl.ptr if ctl else None, _ptr(l2sq), _ptr(scratch),
-                                           scratch.numel() if scratch is not None else 0, _stream(src)),
+                                           scratch.numel() if scratch is not None else 0, _stream(home)),
             'elx_reduce_epilogue')
 
 
@@ -215,14 +237,20 @@ def adam_chunk(master: torch.Tensor,
 
 
 def cast_copyback(master: torch.Tensor, dst: torch.Tensor):
-    _check_tensor(master, 'master', torch.float32)
-    _check_tensor(dst, 'dst')
+    _check_tensor(master, 'master', torch.float32, mapped_host=True)
+    _check_tensor(dst, 'dst', mapped_host=True)
     if master.numel() != dst.numel():
         raise ValueError('master and dst differ in size')
-    with _DeviceGuard(master):
+    if _lib.host_memory_backend():
+        home = None
+    elif master.is_cuda or dst.is_cuda:
+        home = master if master.is_cuda else dst
+    else:
+        home = torch.empty(0, device='cuda')    # both ends in mapped host memory: run on the current device
+    with _DeviceGuard(home):
         _lib.check(
             _lib.get().elx_cast_copyback(_ptr(master), _ptr(dst), dtype_code(dst.dtype), master.numel(),
-                                         _stream(master)), 'elx_cast_copyback')
+                                         _stream(home)), 'elx_cast_copyback')
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -265,6 +293,7 @@ class ChunkTable:
         self._ring = []
         self._ring_events = []
         self._ring_pos = 0
+        self.host_resident = False    # some shard data lives in pinned host memory
 
     @property
     def n_chunks(self) -> int:
@@ -280,15 +309,17 @@ class ChunkTable:
         if self.descs_dev is not None:
             raise RuntimeError('the table is already finalized')
         for name, t in (('master', master), ('exp_avg', exp_avg), ('exp_avg_sq', exp_avg_sq)):
-            _check_tensor(t, name, torch.float32)
-        _check_tensor(grad_param, 'grad_param', self.dtype)
+            _check_tensor(t, name, torch.float32, mapped_host=True)
+        _check_tensor(grad_param, 'grad_param', self.dtype, mapped_host=True)
         n = master.numel()
         if not (exp_avg.numel() == exp_avg_sq.numel() == grad_param.numel() == n):
             raise ValueError('master, moments and the low-precision shard differ in size')
         if not 0 <= n_valid <= n:
             raise ValueError('n_valid outside [0, n_shard]')
         for t in (master, exp_avg, exp_avg_sq, grad_param):
-            if t.device != self.device and not _lib.host_memory_backend():
+            if is_mapped_host(t) and not _lib.host_memory_backend():
+                self.host_resident = True    # at least one array is reached over PCIe: see adam_multi
+            elif t.device != self.device and not _lib.host_memory_backend():
                 raise ValueError(f'tensor on {t.device}, table on {self.device}')
         merged: List[List[int]] = []
         last_end = 0
@@ -385,11 +416,13 @@ def adam_multi(table: ChunkTable, ctl: ControlBlock, first: int = 0, count: Opti
         raise RuntimeError('finalize() the table first')
     if table.n_groups and table.hyper_dev is None:
         raise RuntimeError('set_hyper() before the first step')
+    # shards in pinned host memory are updated in place over PCIe by the load/store variant of the kernel
+    entry, name = ((_lib.get().elx_adam_multi_hostmem, 'elx_adam_multi_hostmem') if table.host_resident else
+                   (_lib.get().elx_adam_multi, 'elx_adam_multi'))
     with _DeviceGuard(table.descs_dev):
         _lib.check(
-            _lib.get().elx_adam_multi(_ptr(table.descs_dev), first, count, table.tiles(first, count), table.code,
-                                      _ptr(table.segs_dev), _ptr(table.hyper_dev), table.n_groups, ctl.ptr,
-                                      _stream(table.descs_dev)), 'elx_adam_multi')
+            entry(_ptr(table.descs_dev), first, count, table.tiles(first, count), table.code, _ptr(table.segs_dev),
+                  _ptr(table.hyper_dev), table.n_groups, ctl.ptr, _stream(table.descs_dev)), name)
 
 
 def pull_reduce_multi(table: ChunkTable, grads_table, block_off: torch.Tensor, ctl: Optional[ControlBlock],
@@ -399,6 +432,8 @@ def pull_reduce_multi(table: ChunkTable, grads_table, block_off: torch.Tensor, c
     ``ElxPeerTable`` of the ranks' gradient slabs, ``block_off`` (int64, device) the element offset of each
     chunk's block inside a slab."""
     count = table.n_chunks - first if count is None else count
+    if table.host_resident:
+        raise RuntimeError('the NVLink reduce-scatter writes device-resident shards only')
     _check_tensor(block_off, 'block_off', torch.int64)
     if block_off.numel() < table.n_chunks:
         raise ValueError('block_off is shorter than the table')
@@ -417,6 +452,8 @@ def adam_multi_push(table: ChunkTable, ctl: ControlBlock, gather_table, block_of
     """Fused update whose refreshed low-precision tiles are also stored into every rank's gather slab
     (``elx_adam_multi_push``)."""
     count = table.n_chunks - first if count is None else count
+    if table.host_resident:
+        raise RuntimeError('the update fused with the push all-gather runs on device-resident shards only')
     _check_tensor(block_off, 'block_off', torch.int64)
     if block_off.numel() < table.n_chunks:
         raise ValueError('block_off is shorter than the table')

@@ -110,7 +110,7 @@ class ElixirOptimizer:
     def _init_engine(self, segments, sync_overflow: bool):
         chunks = sorted(self.param_chunk_set, key=lambda c: c.chunk_id)
         self._chunks = chunks
-        device = chunks[0].shard.device if chunks else torch.device('cuda', torch.cuda.current_device())
+        device = chunks[0].compute_device if chunks else torch.device('cuda', torch.cuda.current_device())
         dtype = self.module.dtype
         group = self.module.process_group
         self.engine = ChunkStepEngine(device, dtype, self.grad_scaler, process_group=group,
@@ -217,12 +217,20 @@ class ElixirOptimizer:
     def state_dict(self):
         """This rank's flat optimizer state: one (exp_avg, exp_avg_sq) pair per chunk shard plus the control
         block fields.  The reference saves none of this (its scaler state is lost on restart)."""
+        self._quiesce_host_shards()
         return dict(scaler=self.grad_scaler.state_dict(),
-                    shards=[dict(exp_avg=s[1].detach().cpu(), exp_avg_sq=s[2].detach().cpu())
+                    shards=[dict(exp_avg=s[1].detach().to('cpu', copy=True), exp_avg_sq=s[2].detach().to('cpu', copy=True))
                             for s in self.engine.shards],
                     param_groups=[{k: v for k, v in g.items() if k != 'params'} for g in self.optim.param_groups])
 
+    def _quiesce_host_shards(self):
+        """Shards in host memory are written by kernels and read here by plain host copies, which no stream
+        orders: wait for the device first."""
+        if self.engine.table.host_resident:
+            torch.cuda.synchronize(self.engine.device)
+
     def load_state_dict(self, state):
+        self._quiesce_host_shards()
         self.grad_scaler.load_state_dict(state['scaler'])
         for shard, saved in zip(self.engine.shards, state['shards']):
             shard[1].copy_(saved['exp_avg'])

@@ -267,6 +267,21 @@ int elx_adam_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_ti
                    const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl,
                    void* stream);
 
+/*
+ * elx_adam_multi for shards kept in page-locked host memory that is mapped into the device's address
+ * space (cudaHostAlloc / torch pinned memory: under unified addressing the host pointer is the device
+ * pointer) -- the reference's `shard_device=cpu` placement (chunk.py:101-111), where HybridAdam runs its
+ * CPU kernel on such shards (optimizer.py:19, 216).  Here the same GPU kernel updates them in place over
+ * PCIe: no host arithmetic, no staging copies, 14 bytes per element in each direction with 16-bit
+ * gradients.  Same arguments, results and status codes as elx_adam_multi; the master / exp_avg /
+ * exp_avg_sq / grad_param pointers of the descriptors may be any mix of device and mapped host memory,
+ * the tables (descs, segs, hyper, ctl) are device memory.  Always runs the direct load/store variant of
+ * the update (the bulk-copy pipeline is kept to device memory).
+ */
+int elx_adam_multi_hostmem(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                           const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl,
+                           void* stream);
+
 /* ---- NVLink paths (single node, peer-mapped memory) -------------------------------------------- */
 
 /* Enable access from the current device to memory of `peer_device` (cudaDeviceEnablePeerAccess;

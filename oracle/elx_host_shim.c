@@ -185,6 +185,11 @@ int elx_pull_reduce_multi(const ElxChunkDesc* descs, int first, int count, int64
     (void)chunk_flags; (void)ctl; (void)stream;
     return ELX_ERR_NODEVICE;
 }
+int elx_adam_multi_hostmem(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                           const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl, void* stream) {
+    return elx_adam_multi(descs, first, count, n_tiles, dtype, segs, hyper, n_groups, ctl, stream);
+}
+
 int elx_adam_multi_push(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
                         const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl, ElxPeerTable gather,
                         const int64_t* block_off, void* stream) {
