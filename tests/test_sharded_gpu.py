@@ -245,7 +245,7 @@ def test_sharded_step_p2p_kernels(world):
     mp.spawn(_p2p_worker, args=(world, 29820 + world), nprocs=world)
 
 
-def _wrapper_worker(rank, world, port, nvlink=False):
+def _wrapper_worker(rank, world, port, nvlink=False, host_shards=False):
     """ElixirModule + ElixirOptimizer over NCCL with a real forward / backward, against plain data-parallel
     training (gradients averaged by hand, torch.optim.AdamW): the reference's test/wrapper/test_optimizer.py
     in spirit, tolerance included."""
@@ -266,11 +266,13 @@ def _wrapper_worker(rank, world, port, nvlink=False):
     wrapped = copy.deepcopy(plain)
     opt = torch.optim.AdamW(plain.parameters(), lr=1e-2, betas=(0.875, 0.99609375), weight_decay=0.0)
     sr = simple_plan(wrapped, world, split_number=3, unified_dtype=torch.float,
-                     peer_group=dist.group.WORLD if nvlink else None)
+                     peer_group=dist.group.WORLD if nvlink else None,
+                     shard_device=torch.device('cpu') if host_shards else None)
     inner = HybridAdam(wrapped.parameters(), lr=1e-2, betas=(0.875, 0.99609375), weight_decay=0.0)
     emodel = ElixirModule(wrapped, sr, dist.group.WORLD, dtype=torch.float)
     eopt = ElixirOptimizer(emodel, inner)
     assert emodel.nvlink_step == nvlink
+    assert all(c.host_resident == host_shards for c in emodel.param_chunks)
     for step in range(3):
         torch.manual_seed(100 * step + rank)    # every rank its own batch
         x = torch.randn(16, 40, device=dev)
@@ -387,3 +389,11 @@ def test_scheduled_residency_over_nccl(prefetch):
         pytest.skip('needs 2 GPUs')
     import _dist_workers as W
     mp.spawn(W.residency_worker_gpu, args=(2, 29860 + int(prefetch), prefetch, 'float16'), nprocs=2)
+
+
+def test_wrapper_data_parallel_training_with_shards_in_host_memory():
+    """shard_device=cpu over NCCL: the reduce-scatter leaves the average in the block, the landing kernel moves
+    it to the pinned shard over PCIe, the update runs on the pinned arrays, the gather starts from them."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    mp.spawn(_wrapper_worker, args=(2, 29845, False, True), nprocs=2)
