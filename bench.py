@@ -187,10 +187,10 @@ def run_ours(args):
         args.pool = args.pool or 4
     else:
         workload, total, chunk, scale, wd = f'opt13b_chunks_sharded_w{world}', OPT13B_PARAMS, CHUNK_SHARDED, 1024.0, 0.0
-    if args.shards == 'host':
+    if args.shards != 'device':
         if world != 1:
             raise SystemExit('--shards host is a 1-GPU measurement (the collectives write device-resident shards)')
-        workload, args.no_e2e = workload + '_host_shards', True
+        workload, args.no_e2e = workload + '_' + args.shards.replace('-', '_') + '_shards', True
     if args.params:
         total, workload = args.params, workload + f'_params{args.params}'
     if args.chunk_elems:
@@ -212,13 +212,15 @@ def run_ours(args):
             master[nv:].zero_()
         lowp = torch.empty(shard, dtype=dtype, device=device)
         K.cast_copyback(master, lowp)
-        if args.shards == 'host':
+        if args.shards != 'device':
             # the reference's shard_device=cpu placement: master, moments and working copy in pinned host
             # memory, updated in place over PCIe by the same kernels
             master, lowp = master.cpu().pin_memory(), lowp.cpu().pin_memory()
         engine.add_shard(master, lowp, nv, [(0, nv, 0)] if nv else [])
     engine.finalize()
     engine.set_hyper([K.hyper(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=wd, adamw_mode=True)])
+    if args.shards == 'host-streamed':
+        engine.enable_streaming(slots=3)
 
     # gradient sources
     if world == 1:
@@ -254,7 +256,15 @@ def run_ours(args):
     adam_events = []
 
     def one_step(record=False):
-        if world == 1:
+        if world == 1 and args.shards == 'host-streamed':
+            engine.land_all(grad_blocks, streams=args.land_streams)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            engine.step_streamed()    # decision, then copy in / update / copy out per chunk on three streams
+            b.record()
+            if record:
+                adam_events.append((a, b))
+        elif world == 1:
             engine.land_all(grad_blocks, streams=args.land_streams)
             engine.begin_step()
             if record:
@@ -357,10 +367,12 @@ def run_ours(args):
             'frac_of_8TBs_nominal': achieved / 8000.0,
         }
         result['adam_gparams_per_s'] = n_elems / (adam_ms * 1e-3) / 1e9
-        if args.shards == 'host':
+        if args.shards != 'device':
             per_dir = n_elems * (BYTES_PER_ELEM // 2) / (adam_ms * 1e-3) / 1e9
             result['roofline'] = {
-                'bound': 'pcie', 'kernel': 'adam_kernel (load/store variant) on pinned host shards',
+                'bound': 'pcie',
+                'kernel': ('adam_kernel (load/store variant) on pinned host shards' if args.shards == 'host' else
+                           'copy engines in and out of three staging sets around adam_tma_kernel'),
                 'achieved': per_dir, 'peak': 64.0, 'unit': 'GB/s per direction', 'frac': per_dir / 64.0,
                 'peak_kind': 'nominal PCIe Gen5 x16 (no measured figure on this pool)', 'ms_per_launch': adam_ms,
                 'elements_per_launch': n_elems, 'bytes_per_element_each_direction': BYTES_PER_ELEM // 2, 'traffic': None,
@@ -632,8 +644,9 @@ def main():
                     help='N = 1: side streams the per-chunk landing launches alternate on')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true')
-    ap.add_argument('--shards', choices=['device', 'host'], default='device',
-                    help="'host': optimizer state in pinned host memory, updated in place over PCIe (N=1 only)")
+    ap.add_argument('--shards', choices=['device', 'host', 'host-streamed'], default='device',
+                    help="'host': optimizer state in pinned host memory, updated in place over PCIe by the kernel; "
+                    "'host-streamed': the same state moved by the copy engines through device staging sets (N=1 only)")
     ap.add_argument('--e2e-steps', type=int, default=10)
     args = ap.parse_args()
     if args.impl == 'reference':

@@ -14,7 +14,9 @@ shards are registered once in device tables, and a step is
 
 For sharded runs ``step_sharded`` pipelines reduce-scatter -> probe per chunk on a reduce stream and
 update -> all-gather per chunk on a gather stream; ``step_from_host`` does the same with host buffers
-on the two ends (pinned gradients in, updated low-precision parameters out).
+on the two ends (pinned gradients in, updated low-precision parameters out).  Shards may also live in
+pinned host memory: ``step`` then reaches them over PCIe with the same kernels, and after
+``enable_streaming`` the copy engines move them through device staging sets around the update.
 """
 from typing import List, Optional, Sequence, Tuple
 
@@ -51,6 +53,7 @@ class ChunkStepEngine:
         self.total_l2sq: Optional[torch.Tensor] = None
         self._scratch: Optional[torch.Tensor] = None
         self._streams = None
+        self._slots = None    # device staging sets of the streamed update (enable_streaming)
 
     # ------------------------------------------------------------------ registration
 
@@ -146,7 +149,12 @@ class ChunkStepEngine:
         kernels.step_begin(self.ctl, self.scaler.cfg, norm_sq)
 
     def update(self, first: int = 0, count: Optional[int] = None):
-        kernels.adam_multi(self.table, self.ctl, first=first, count=count)
+        """The fused update of shards [first, first + count).  After ``enable_streaming`` the update of the whole
+        set goes through the staging sets (shards in host memory travel with the copy engines)."""
+        if self._slots is not None and first == 0 and count is None:
+            self._update_streamed()
+        else:
+            kernels.adam_multi(self.table, self.ctl, first=first, count=count)
 
     def end_step(self):
         self.chunk_flags.zero_()
@@ -461,6 +469,72 @@ class ChunkStepEngine:
                 d2h.wait_event(done)
                 dst.copy_(self.shards[k][3], non_blocking=True)
         self.end_step()
+        main.wait_stream(d2h)
+
+    # ------------------------------------------------------------------ shards in host memory, streamed
+
+    def enable_streaming(self, slots: int = 3):
+        """Prepare ``step_streamed``: ``slots`` device staging sets (master, two moments, working copy) of the
+        largest shard's size, and a second descriptor table whose entry k points into set ``k % slots``."""
+        assert self.table.descs_dev is not None, 'finalize() first'
+        assert self.table.host_resident, 'streaming is for shards kept in pinned host memory'
+        size = max(s[0].numel() for s in self.shards)
+        f32 = lambda: torch.empty(size, dtype=torch.float32, device=self.device)    # noqa: E731
+        self._slots = [(f32(), f32(), f32(), torch.empty(size, dtype=self.dtype, device=self.device))
+                       for _ in range(slots)]
+        self._stage_table = kernels.ChunkTable(self.device, self.dtype)
+        self._streamed = []    # per shard: its arrays are in host memory and travel through a staging set
+        for k, (master, exp_avg, exp_avg_sq, lowp, n_valid) in enumerate(self.shards):
+            n = master.numel()
+            on_host = kernels.is_mapped_host(master)
+            assert all(kernels.is_mapped_host(t) == on_host for t in (exp_avg, exp_avg_sq, lowp)), \
+                'the four arrays of a shard live in the same kind of memory'
+            self._streamed.append(on_host)
+            if on_host:
+                slot = self._slots[k % slots]
+                self._stage_table.add_chunk(slot[0][:n], slot[1][:n], slot[2][:n], slot[3][:n], n_valid,
+                                            self.table._segs_of(k))
+            else:    # a device-resident shard is updated where it is
+                self._stage_table.add_chunk(master, exp_avg, exp_avg_sq, lowp, n_valid, self.table._segs_of(k))
+        self._stage_table.finalize()
+        self._slot_free = [None] * slots
+
+    def step_streamed(self):
+        """``step`` after ``enable_streaming`` (kept as a name of its own for call sites that want to say so)."""
+        assert self._slots is not None, 'enable_streaming() first'
+        self.step()
+
+    def _update_streamed(self):
+        """The update for shards in pinned host memory, with the copy engines instead of kernel accesses over
+        PCIe: chunk by chunk, the four arrays are copied into a device staging set (h2d stream), updated there
+        by the same fused kernel (main stream) and copied back (d2h stream); with three staging sets the three
+        stages overlap, so the update takes what the slower PCIe direction takes (14 bytes per element each way
+        with 16-bit gradients).  Gradients must already sit, probed, in the host shards."""
+        slots = len(self._slots)
+        main = torch.cuda.current_stream(self.device)
+        h2d, d2h = self._side_streams()
+        self._stage_table.set_hyper_from(self.table)
+        h2d.wait_stream(main)
+        for k, host in enumerate(self.shards):
+            if not self._streamed[k]:
+                kernels.adam_multi(self._stage_table, self.ctl, first=k, count=1)
+                continue
+            n = host[0].numel()
+            stage = [t[:n] for t in self._slots[k % slots]]
+            with torch.cuda.stream(h2d):
+                if self._slot_free[k % slots] is not None:
+                    h2d.wait_event(self._slot_free[k % slots])    # the set's previous tenant has been copied out
+                for dst, src in zip(stage, host[:4]):
+                    dst.copy_(src, non_blocking=True)
+                arrived = h2d.record_event()
+            main.wait_event(arrived)
+            kernels.adam_multi(self._stage_table, self.ctl, first=k, count=1)
+            updated = main.record_event()
+            with torch.cuda.stream(d2h):
+                d2h.wait_event(updated)
+                for dst, src in zip(host[:4], stage):
+                    dst.copy_(src, non_blocking=True)
+                self._slot_free[k % slots] = d2h.record_event()
         main.wait_stream(d2h)
 
     # ------------------------------------------------------------------ introspection (synchronising)

@@ -353,6 +353,10 @@ class ChunkTable:
         count = self.n_chunks - first if count is None else count
         return self.tile_begin[first + count] - self.tile_begin[first]
 
+    def set_hyper_from(self, other: 'ChunkTable'):
+        """Use the hyper-parameter table of ``other`` (same device): nothing is uploaded twice."""
+        self.hyper_dev, self.n_groups = other.hyper_dev, other.n_groups
+
     def set_hyper(self, groups: Sequence[ElxHyper]):
         if len(groups) > _abi.MAX_GROUPS:
             raise ValueError(f'at most {_abi.MAX_GROUPS} param groups are supported')

@@ -18,8 +18,8 @@ def _engine(device, dtype, shards, host, segments, scaler_kw=None):
     scaler = DynamicGradScaler(**(scaler_kw or dict(initial_scale=64.0, growth_interval=2, hysteresis=1)))
     eng = ChunkStepEngine(device, dtype, scaler)
     held = []
-    for (master, m, v, lowp), (n_valid, segs) in zip(shards, segments):
-        if host:
+    for k, ((master, m, v, lowp), (n_valid, segs)) in enumerate(zip(shards, segments)):
+        if host is True or (host == 'mixed' and k % 2 == 0):
             arrays = [t.clone().pin_memory() for t in (master, m, v, lowp)]
         else:
             arrays = [t.clone().to(device) for t in (master, m, v, lowp)]
@@ -39,11 +39,15 @@ def test_host_resident_step_equals_device_resident_step(cuda, oracle, dtype):
     hypers = [K.hyper(lr=1e-3, weight_decay=0.01), K.hyper(lr=3e-3, betas=(0.8, 0.95), weight_decay=0.0, adamw_mode=False)]
     on_dev, dev_arrays = _engine(cuda, dtype, shards, False, segments)
     on_host, host_arrays = _engine(cuda, dtype, shards, True, segments)
+    streamed, streamed_arrays = _engine(cuda, dtype, shards, True, segments)
+    streamed.enable_streaming(slots=3)    # copy engines + staging sets instead of kernel accesses over PCIe
+    mixed, mixed_arrays = _engine(cuda, dtype, shards, 'mixed', segments)    # shards 0 and 2 on the host, 1 and 3 not
+    mixed.enable_streaming(slots=2)
     assert on_host.table.host_resident and not on_dev.table.host_resident
     assert all(K.is_mapped_host(t) for t in on_host.shards[0][:4])    # moments included
     gen = torch.Generator().manual_seed(3)
     for step in range(4):
-        for eng, arrays in ((on_dev, dev_arrays), (on_host, host_arrays)):
+        for eng in (on_dev, on_host, streamed, mixed):
             eng.set_hyper(hypers)
         grads = []
         for n in sizes:
@@ -51,17 +55,22 @@ def test_host_resident_step_equals_device_resident_step(cuda, oracle, dtype):
             if step == 2 and n == sizes[1]:
                 g[777] = float('inf')    # one overflow: the whole step is skipped, the scale backs off
             grads.append(g)
-        for eng in (on_dev, on_host):
+        for eng in (on_dev, on_host, streamed, mixed):
             for k, g in enumerate(grads):
                 eng.land(k, g.to(cuda))    # device block -> shard (host shard: written over PCIe) + probe
-            eng.step()
+            if eng in (streamed, mixed):
+                eng.step_streamed()
+            else:
+                eng.step()
         torch.cuda.synchronize()
-        a, b = on_dev.read_control(), on_host.read_control()
-        assert (a.skip, a.scale, a.step, a.status) == (b.skip, b.scale, b.step, b.status) and a.status == 0
-        assert bool(a.skip) == (step == 2)
-        for da, ha in zip(dev_arrays, host_arrays):
-            for x, y in zip(da, ha):
-                assert bits_equal(x, y), step
+        a = on_dev.read_control()
+        assert a.status == 0 and bool(a.skip) == (step == 2)
+        for eng, arrays in ((on_host, host_arrays), (streamed, streamed_arrays), (mixed, mixed_arrays)):
+            b = eng.read_control()
+            assert (a.skip, a.scale, a.step, a.status) == (b.skip, b.scale, b.step, b.status)
+            for da, ha in zip(dev_arrays, arrays):
+                for x, y in zip(da, ha):
+                    assert bits_equal(x, y), step
     # and the host-resident result is the oracle's, within the usual bounds, for the last clean step
     # (both engines agree bit for bit, so one comparison covers them)
     assert on_host.read_control().step == 3
