@@ -166,3 +166,19 @@ def test_wrapper_with_shards_in_host_memory_trains_identically(cuda, blocks):
         assert torch.equal(got_a[name], got_b[name])
     ok, ratio = close_1e6(got_b['net.0.weight'], got_a['net.0.weight'].double())
     assert ok
+    # checkpoint round trip with the shards in host memory: zero everything, load it back, train on identically
+    saved_model, saved_opt = host.state_dict(), host_opt.state_dict()
+    host.load_state_dict({k: torch.zeros_like(v) for k, v in saved_model.items()})
+    assert all(float(v.abs().max()) == 0.0 for v in host.state_dict().values())
+    host.load_state_dict(saved_model)
+    host_opt.load_state_dict(saved_opt)
+    x = torch.randn(16, 48, device=cuda)
+    la, lb = dev(x), host(x)
+    assert bits_equal(la.detach(), lb.detach())
+    dev_opt.backward(la)
+    host_opt.backward(lb)
+    dev_opt.step()
+    host_opt.step()
+    torch.cuda.synchronize()
+    for a, b in zip(dev.param_chunks, host.param_chunks):
+        assert bits_equal(a.shard, b.shard) and bits_equal(a.paired_chunk.shard, b.paired_chunk.shard)
