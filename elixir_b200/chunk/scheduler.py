@@ -58,8 +58,9 @@ class ChunkScheduler(ABC):
         """The first chunk a later fetch will ask for that is not among ``chunks`` (None: unknown)."""
         return None
 
-    def upcoming(self, exclude: Sequence[Chunk] = ()) -> Iterator[Tuple[int, Chunk]]:
-        """(step, chunk) of later fetches in order, each chunk once.  Nothing when the future is unknown."""
+    def upcoming(self, exclude: Sequence[Chunk] = (), horizon: int = 32) -> Iterator[Tuple[int, Chunk]]:
+        """(step, chunk) of the next ``horizon`` fetches in order, each chunk once.  Nothing when the future is
+        unknown."""
         return iter(())
 
     def next_use(self, chunk: Chunk) -> int:
@@ -211,11 +212,11 @@ class PrefetchScheduler(ChunkScheduler):
             self.search_step += 1
         return None
 
-    def upcoming(self, exclude: Sequence[Chunk] = ()) -> Iterator[Tuple[int, Chunk]]:
+    def upcoming(self, exclude: Sequence[Chunk] = (), horizon: int = 32) -> Iterator[Tuple[int, Chunk]]:
         if self.learning:
             return
         seen = set(exclude)
-        for step in range(self.current_step + 1, self.total_steps):
+        for step in range(self.current_step + 1, min(self.total_steps, self.current_step + 1 + horizon)):
             for chunk in self.chunks_per_step[step]:
                 if chunk not in seen:
                     seen.add(chunk)
