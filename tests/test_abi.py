@@ -82,6 +82,7 @@ def test_version_strerror_and_argument_checks_need_no_gpu(lib):
     assert lib.elx_ctl_init(None, 1.0, None) == _abi.ERR_NULL
     assert lib.elx_grad_check(None, 0, 1, None, None, None, None, 0, None) == _abi.ERR_NULL
     assert lib.elx_adam_multi(None, 0, 1, 1, 0, None, None, 1, None, None) == _abi.ERR_NULL
+    assert lib.elx_adam_multi_hostmem(None, 0, 1, 1, 0, None, None, 1, None, None) == _abi.ERR_NULL
     assert lib.elx_cast_copyback(ctypes.c_void_p(64), ctypes.c_void_p(128), 9, 1, None) == _abi.ERR_DTYPE
     assert lib.elx_set_tuning(b'adam_threads', 512) == _abi.OK
     assert lib.elx_set_tuning(b'adam_threads', -1) == _abi.OK
