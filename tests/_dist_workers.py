@@ -394,3 +394,70 @@ def lifetime_worker(rank, world, port):
         gc.collect()
         assert all(r() is None for r in refs), (blocks, [r() is None for r in refs])
     dist.destroy_process_group()
+
+
+def fetcher_scenario_worker(rank, world, port):
+    """Four chunks, two blocks, the access trace A B C A D: every decision of the fetcher spelled out."""
+    use_host_shim()
+    dist = init_gloo(rank, world, port)
+    from elixir_b200.chunk import ChunkFetcher, ChunkGroup, FIFOScheduler, MemoryPool, PrefetchScheduler
+    cpu = torch.device('cpu')
+
+    def build(scheduler_of):
+        pool = MemoryPool('cpu')
+        pool.allocate(public_dtype=torch.float, public_block_size=64, public_block_number=2)
+        group = ChunkGroup(pool)
+        tensors = [torch.full((64,), float(i + 1)) for i in range(4)]
+        chunks = [group.allocate_chunk([t], 64, torch.float, dist.GroupMember.WORLD,
+                                       dict(shard_device=cpu, temp_device=cpu)) for t in tensors]
+        fetcher = ChunkFetcher(scheduler_of(chunks), group, overlap=True)
+        return pool, group, tensors, chunks, fetcher
+
+    order = [0, 1, 2, 0, 3]
+
+    def run(fetcher, group, tensors, chunks, log):
+        with torch.no_grad():
+            fetcher.reset()
+            for i in order:
+                got = fetcher.trans_to_compute([tensors[i]])
+                assert got == [chunks[i]]
+                fetcher.fetch_chunks(got)
+                assert group.is_accessed(chunks[i]) and float(tensors[i][0]) == i + 1    # the data is there
+                log.append((i, dict(fetcher.stats), sorted(c.chunk_id - chunks[0].chunk_id
+                                                          for c in group.accessed_float_chunks)))
+                fetcher.trans_to_hold([tensors[i]], phase='f')
+            fetcher.release_all()
+            fetcher.clear()
+
+    # Belady on the known trace, gathers ahead
+    pool, group, tensors, chunks, fetcher = build(lambda cs: PrefetchScheduler([[cs[i]] for i in order]))
+    log = []
+    run(fetcher, group, tensors, chunks, log)
+    resident = [entry[2] for entry in log]
+    #            after fetch of A: B gathered ahead; C cannot come (A is in use, nothing to release)
+    assert resident == [[0, 1], [1, 2], [0, 2], [0, 3], [0, 3]], resident
+    #            B: A (next use 3) leaves for C (use 2);  C: B (never again) leaves for A;  A: C leaves for D
+    final = log[-1][1]
+    assert final == dict(fetched=1, released=3, ahead=4, ahead_hit=4), final
+    assert pool.public_free_cnt == 2
+
+    # FIFO, nothing known about the future: every chunk is fetched on demand, the oldest releasable one leaves
+    pool, group, tensors, chunks, fetcher = build(lambda cs: FIFOScheduler())
+    log = []
+    run(fetcher, group, tensors, chunks, log)
+    assert [entry[2] for entry in log] == [[0], [0, 1], [1, 2], [0, 2], [0, 3]], [entry[2] for entry in log]
+    assert log[-1][1] == dict(fetched=5, released=3, ahead=0, ahead_hit=0), log[-1][1]
+    assert pool.public_free_cnt == 2
+
+    # a replica cache that cannot hold what one fetch asks for
+    pool, group, tensors, chunks, fetcher = build(lambda cs: FIFOScheduler())
+    with torch.no_grad():
+        fetcher.reset()
+        both = fetcher.trans_to_compute(tensors[:3])
+        try:
+            fetcher.fetch_chunks(both)
+        except RuntimeError as err:
+            assert 'R cache is not enough' in str(err)
+        else:
+            raise AssertionError('three chunks in use at once fitted two blocks')
+    dist.destroy_process_group()

@@ -136,3 +136,7 @@ def test_an_abandoned_forward_gives_its_blocks_back():
 
 def test_dropping_the_wrapper_frees_model_and_optimizer_state():
     mp.spawn(W.lifetime_worker, args=(1, 29762), nprocs=1)
+
+
+def test_fetcher_decisions_on_a_spelled_out_trace():
+    mp.spawn(W.fetcher_scenario_worker, args=(1, 29763), nprocs=1)
