@@ -132,6 +132,7 @@ PROTOTYPES = {
     'elx_grad_check_multi': (_i, [_p, _i, _i, _i64, _i, _p, _p, _p, _p, _p, _i64, _p]),
     'elx_adam_multi': (_i, [_p, _i, _i, _i64, _i, _p, _p, _i, _p, _p]),
     'elx_adam_multi_hostmem': (_i, [_p, _i, _i, _i64, _i, _p, _p, _i, _p, _p]),
+    'elx_adam_multi_shadow': (_i, [_p, _p, _i, _i, _i64, _i, _p, _p, _i, _p, _p]),
     'elx_enable_peer_access': (_i, [_i]),
     'elx_peer_alloc': (_i, [_i64, C.POINTER(C.c_void_p), _p]),
     'elx_peer_free': (_i, [_p]),

@@ -79,6 +79,9 @@ struct AdamArgs {
     ElxPeerTable push;
     const int64_t* push_off;   // per descriptor: element offset of the chunk's block inside the slabs
     int force_direct;          // always the ld/st variant (shards in mapped host memory)
+    // out-of-place update: the new master and moments of descriptor c go to shadow[c]'s arrays (bulk-copy
+    // variant only); NULL = in place
+    const ElxChunkDesc* shadow;
     // single-shard form: the three tables travel in the kernel parameters
     ElxChunkDesc one_desc;
     ElxSeg one_seg;
@@ -283,6 +286,9 @@ struct TileSlot {
     float* master;
     float* exp_avg;
     float* exp_avg_sq;
+    float* out_master;      // where the updated values go: the same arrays, or the shadow set's
+    float* out_exp_avg;
+    float* out_exp_avg_sq;
     void* lowp;
     const ElxSeg* segs;
     int64_t e0, e1;
@@ -306,6 +312,10 @@ struct ProducerCursor {
     int index = -1;
     bool vec_ok = false;
     ElxChunkDesc d;
+    float* out_master = nullptr;
+    float* out_exp_avg = nullptr;
+    float* out_exp_avg_sq = nullptr;
+    bool shadow_ok = true;
     int64_t seg_b = 0, seg_e = 0;
     int seg_group = -1;
     int seg_chunk = -1;
@@ -325,12 +335,26 @@ __device__ __forceinline__ void classify_tile(const AdamArgs& a, const ElxChunkD
         pc.index = lo;
         pc.t0 = pc.d.tile_begin;
         pc.t1 = pc.t0 + tiles_of(pc.d.n_shard);
-        const uintptr_t bits = reinterpret_cast<uintptr_t>(pc.d.master) | reinterpret_cast<uintptr_t>(pc.d.exp_avg) |
-                               reinterpret_cast<uintptr_t>(pc.d.exp_avg_sq) |
-                               reinterpret_cast<uintptr_t>(pc.d.grad_param);
+        uintptr_t bits = reinterpret_cast<uintptr_t>(pc.d.master) | reinterpret_cast<uintptr_t>(pc.d.exp_avg) |
+                         reinterpret_cast<uintptr_t>(pc.d.exp_avg_sq) | reinterpret_cast<uintptr_t>(pc.d.grad_param);
+        pc.out_master = pc.d.master;
+        pc.out_exp_avg = pc.d.exp_avg;
+        pc.out_exp_avg_sq = pc.d.exp_avg_sq;
+        pc.shadow_ok = true;
+        if (a.shadow) {
+            const ElxChunkDesc sd = a.shadow[lo];
+            pc.out_master = sd.master;
+            pc.out_exp_avg = sd.exp_avg;
+            pc.out_exp_avg_sq = sd.exp_avg_sq;
+            // the shadow descriptor must describe the same shard, with arrays of its own
+            pc.shadow_ok = sd.n_shard == pc.d.n_shard && sd.tile_begin == pc.d.tile_begin && sd.master &&
+                           sd.exp_avg && sd.exp_avg_sq;
+            bits |= reinterpret_cast<uintptr_t>(sd.master) | reinterpret_cast<uintptr_t>(sd.exp_avg) |
+                    reinterpret_cast<uintptr_t>(sd.exp_avg_sq);
+        }
         pc.vec_ok = (bits & 31u) == 0;
     }
-    if (!(t >= pc.t0 && t < pc.t1) || pc.d.dtype != DT) {
+    if (!(t >= pc.t0 && t < pc.t1) || pc.d.dtype != DT || !pc.shadow_ok) {
         out.kind = kTileBad;
         return;
     }
@@ -353,6 +377,9 @@ __device__ __forceinline__ void classify_tile(const AdamArgs& a, const ElxChunkD
     out.master = pc.d.master;
     out.exp_avg = pc.d.exp_avg;
     out.exp_avg_sq = pc.d.exp_avg_sq;
+    out.out_master = pc.out_master;
+    out.out_exp_avg = pc.out_exp_avg;
+    out.out_exp_avg_sq = pc.out_exp_avg_sq;
     out.lowp = pc.d.grad_param;
     out.segs = csegs;
     out.n_segs = pc.d.seg_count;
@@ -436,7 +463,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         if (!mbar_wait_bounded(&s_full[s], parity)) s_abort = 1;
         __syncthreads();
         if (s_abort) break;
-        const TileSlot slot = s_slot[s];
+        const TileSlot& slot = s_slot[s];   // stable until this stage is produced again, two iterations on
         unsigned char* base = s_dyn + static_cast<size_t>(s) * Stage::kBytes;
 
         if (slot.kind == kTileBulk) {
@@ -492,9 +519,9 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                         float m = slot.exp_avg[e], v = slot.exp_avg_sq[e];
                         nan_acc = fmaf(0.0f, g, nan_acc);
                         adam_elem<MATH>(p, m, v, g, k_, div_mode, div, inv_div);
-                        slot.master[e] = p;
-                        slot.exp_avg[e] = m;
-                        slot.exp_avg_sq[e] = v;
+                        slot.out_master[e] = p;
+                        slot.out_exp_avg[e] = m;
+                        slot.out_exp_avg_sq[e] = v;
                     }
                 }
                 const typename Lp<DT>::T val = Lp<DT>::from_float(p);
@@ -510,9 +537,10 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         if (threadIdx.x == 0) {
             if (slot.kind == kTileBulk) {
                 bulk_s2g(static_cast<char*>(slot.lowp) + slot.e0 * Lp<DT>::kBytes, base, Stage::kLowpBytes);
-                bulk_s2g(slot.master + slot.e0, base + Stage::kLowpBytes, Stage::kF32Bytes);
-                bulk_s2g(slot.exp_avg + slot.e0, base + Stage::kLowpBytes + Stage::kF32Bytes, Stage::kF32Bytes);
-                bulk_s2g(slot.exp_avg_sq + slot.e0, base + Stage::kLowpBytes + 2 * Stage::kF32Bytes, Stage::kF32Bytes);
+                bulk_s2g(slot.out_master + slot.e0, base + Stage::kLowpBytes, Stage::kF32Bytes);
+                bulk_s2g(slot.out_exp_avg + slot.e0, base + Stage::kLowpBytes + Stage::kF32Bytes, Stage::kF32Bytes);
+                bulk_s2g(slot.out_exp_avg_sq + slot.e0, base + Stage::kLowpBytes + 2 * Stage::kF32Bytes,
+                         Stage::kF32Bytes);
                 // push all-gather: the same 8 KB of refreshed parameters to every rank's gather block,
                 // plain (non-multicast) bulk stores, W - 1 of them crossing NVLink
                 // (start with a different rank in every CTA, so that the stores spread over all links at once)
@@ -611,7 +639,7 @@ int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
 template <int DT>
 int launch_adam_dt(const AdamArgs& a, cudaStream_t s) {
     const bool precise = g_tune.math_mode == 1;
-    if ((g_tune.adam_variant == 1 && !a.force_direct) || a.push.world > 0)
+    if ((g_tune.adam_variant == 1 && !a.force_direct) || a.push.world > 0 || a.shadow)
         return precise ? launch_adam_tma<DT, 1>(a, s) : launch_adam_tma<DT, 2>(a, s);
     if (g_tune.adam_threads == 256)
         return precise ? launch_adam_minb<DT, 16, 1>(a, s) : launch_adam_minb<DT, 16, 2>(a, s);
@@ -633,8 +661,9 @@ extern "C" {
 
 static int adam_multi_common(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
                              const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl, void* stream,
-                             int force_direct) {
+                             int force_direct, const ElxChunkDesc* shadow = nullptr) {
     if (!descs || !ctl) return ELX_ERR_NULL;
+    if (shadow && !aligned(shadow, 8)) return ELX_ERR_ALIGN;
     if (n_groups > 0 && (!segs || !hyper)) return ELX_ERR_NULL;
     if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
     if (first < 0 || count < 0 || n_tiles < 0 || n_groups < 0) return ELX_ERR_SIZE;
@@ -653,6 +682,7 @@ static int adam_multi_common(const ElxChunkDesc* descs, int first, int count, in
     a.n_groups = n_groups;
     a.n_tiles = n_tiles;
     a.force_direct = force_direct;
+    a.shadow = shadow;
     return launch_adam(a, dtype, static_cast<cudaStream_t>(stream));
 }
 
@@ -664,6 +694,13 @@ int elx_adam_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_ti
 int elx_adam_multi_hostmem(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
                            const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl, void* stream) {
     return adam_multi_common(descs, first, count, n_tiles, dtype, segs, hyper, n_groups, ctl, stream, 1);
+}
+
+int elx_adam_multi_shadow(const ElxChunkDesc* descs, const ElxChunkDesc* shadow, int first, int count,
+                          int64_t n_tiles, int dtype, const ElxSeg* segs, const ElxHyper* hyper, int n_groups,
+                          ElxCtl* ctl, void* stream) {
+    if (!shadow) return ELX_ERR_NULL;
+    return adam_multi_common(descs, first, count, n_tiles, dtype, segs, hyper, n_groups, ctl, stream, 0, shadow);
 }
 
 int elx_adam_multi_push(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,

@@ -54,6 +54,7 @@ class ChunkStepEngine:
         self._scratch: Optional[torch.Tensor] = None
         self._streams = None
         self._slots = None    # device staging sets of the streamed update (enable_streaming)
+        self._twin = None     # second set of master/moment arrays and its table (enable_speculation)
 
     # ------------------------------------------------------------------ registration
 
@@ -443,12 +444,18 @@ class ChunkStepEngine:
         self.end_step()
         self.peer_barrier(self.ctl)
 
-    def step_from_host(self, host_grads: Sequence[torch.Tensor], host_params: Sequence[torch.Tensor]):
+    def step_from_host(self, host_grads: Sequence[torch.Tensor], host_params: Sequence[torch.Tensor],
+                       speculative: bool = False):
         """A whole step with host buffers on both ends: ``host_grads[k]`` (pinned, shard_size elements of
         the chunk dtype) holds the reduced gradients of shard k; ``host_params[k]`` (pinned) receives the
         updated low-precision parameters.  Copies in, probes, updates and copies out are pipelined per
-        chunk on three streams; fp32 master and moments never leave the device."""
+        chunk on three streams; fp32 master and moments never leave the device.  No parameter is updated
+        before the last gradient has been probed, so the two directions of the link cannot overlap;
+        ``speculative`` (after ``enable_speculation``) lifts that, see ``_step_from_host_speculative``."""
         assert len(host_grads) == self.n_chunks and len(host_params) == self.n_chunks
+        if speculative:
+            assert self._twin is not None, 'enable_speculation() first'
+            return self._step_from_host_speculative(host_grads, host_params)
         main = torch.cuda.current_stream(self.device)
         h2d, d2h = self._side_streams()
         h2d.wait_stream(main)
@@ -470,6 +477,78 @@ class ChunkStepEngine:
                 dst.copy_(self.shards[k][3], non_blocking=True)
         self.end_step()
         main.wait_stream(d2h)
+
+    # ------------------------------------------------------------------ speculative step with host buffers
+
+    def enable_speculation(self):
+        """Prepare ``step_from_host(..., speculative=True)``: a second set of master and moment arrays per shard
+        (12 bytes per element more) and its descriptor table.  The update then reads one set and writes the
+        other, and the sets swap roles after every applied step."""
+        assert self.table.descs_dev is not None, 'finalize() first'
+        if self.world > 1 or self.clipping or self.table.host_resident:
+            raise RuntimeError('the speculative step is for one rank, device-resident shards and no gradient clipping '
+                               '(the clip factor needs every gradient before the first update)')
+        other = kernels.ChunkTable(self.device, self.dtype)
+        other_shards = []
+        for k, (master, exp_avg, exp_avg_sq, lowp, n_valid) in enumerate(self.shards):
+            twin = (master.clone(), exp_avg.clone(), exp_avg_sq.clone())
+            other.add_chunk(twin[0], twin[1], twin[2], lowp, n_valid, self.table._segs_of(k))
+            other_shards.append((twin[0], twin[1], twin[2], lowp, n_valid))
+        other.finalize()
+        self._twin = (other, other_shards)
+        self._ctl_backup = torch.empty_like(self.ctl.tensor)
+
+    def _swap_sets(self):
+        (other, other_shards), mine = self._twin, (self.table, self.shards)
+        other.set_hyper_from(self.table)
+        self.table, self.shards = other, other_shards
+        self._twin = mine
+
+    def _step_from_host_speculative(self, host_grads, host_params):
+        """Update chunk by chunk while gradients are still arriving, on the assumption that none of them
+        overflows; parameters leave for the host while later gradients come in (PCIe in both directions at
+        once).  The update writes into the second set of arrays, so if an overflow does turn up the result is
+        simply not adopted: the control block is put back, the real decision (skip, scale back-off) is taken,
+        and the parameters of the old masters are sent out again.  Returns True if the step was applied."""
+        other = self._twin[0]
+        other.set_hyper_from(self.table)
+        main = torch.cuda.current_stream(self.device)
+        h2d, d2h = self._side_streams()
+        self._ctl_backup.copy_(self.ctl.tensor)
+        kernels.step_begin(self.ctl, self.scaler.cfg, None)    # no overflow known: "apply", divisor, step count
+        h2d.wait_stream(main)
+        d2h.wait_stream(main)
+        for k, src in enumerate(host_grads):
+            lowp = self.shards[k][3]
+            with torch.cuda.stream(h2d):
+                lowp.copy_(src, non_blocking=True)
+                arrived = h2d.record_event()
+            main.wait_event(arrived)
+            self.probe_one(k)
+            kernels.adam_multi_shadow(self.table, other, self.ctl, first=k, count=1)
+            done = main.record_event()
+            with torch.cuda.stream(d2h):
+                d2h.wait_event(done)
+                host_params[k].copy_(lowp, non_blocking=True)
+        main.wait_stream(d2h)
+        overflow = bool(self.ctl.found_inf.item())    # the step's result, read by the host (synchronises)
+        if not overflow:
+            self._swap_sets()
+            self.end_step()
+            return True
+        # late overflow: nothing of the speculative update is adopted
+        self.ctl.tensor.copy_(self._ctl_backup)
+        self.ctl.found_inf.fill_(1)
+        kernels.step_begin(self.ctl, self.scaler.cfg, None)    # skip, back-off
+        for k, dst in enumerate(host_params):
+            self.update(first=k, count=1)    # skipped step: the working copy is refreshed from the old master
+            done = main.record_event()
+            with torch.cuda.stream(d2h):
+                d2h.wait_event(done)
+                dst.copy_(self.shards[k][3], non_blocking=True)
+        self.end_step()
+        main.wait_stream(d2h)
+        return False
 
     # ------------------------------------------------------------------ shards in host memory, streamed
 

@@ -429,6 +429,26 @@ def adam_multi(table: ChunkTable, ctl: ControlBlock, first: int = 0, count: Opti
                   _ptr(table.hyper_dev), table.n_groups, ctl.ptr, _stream(table.descs_dev)), name)
 
 
+def adam_multi_shadow(table: ChunkTable, shadow: ChunkTable, ctl: ControlBlock, first: int = 0,
+                      count: Optional[int] = None):
+    """The fused update out of place (``elx_adam_multi_shadow``): reads the arrays of ``table``, writes the new
+    master and moments into those of ``shadow`` (same shards, registered in the same order) and the refreshed
+    working copy over the gradients as usual."""
+    count = table.n_chunks - first if count is None else count
+    if table.descs_dev is None or shadow.descs_dev is None:
+        raise RuntimeError('finalize() both tables first')
+    if shadow.n_chunks != table.n_chunks or shadow.tile_begin != table.tile_begin:
+        raise ValueError('the shadow table does not describe the same shards')
+    if table.host_resident or shadow.host_resident:
+        raise RuntimeError('the out-of-place update runs on device-resident shards only')
+    with _DeviceGuard(table.descs_dev):
+        _lib.check(
+            _lib.get().elx_adam_multi_shadow(_ptr(table.descs_dev), _ptr(shadow.descs_dev), first, count,
+                                             table.tiles(first, count), table.code, _ptr(table.segs_dev),
+                                             _ptr(table.hyper_dev), table.n_groups, ctl.ptr,
+                                             _stream(table.descs_dev)), 'elx_adam_multi_shadow')
+
+
 def pull_reduce_multi(table: ChunkTable, grads_table, block_off: torch.Tensor, ctl: Optional[ControlBlock],
                       chunk_flags: Optional[torch.Tensor] = None, first: int = 0, count: Optional[int] = None,
                       stage_off: Optional[torch.Tensor] = None):

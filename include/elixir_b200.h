@@ -282,6 +282,21 @@ int elx_adam_multi_hostmem(const ElxChunkDesc* descs, int first, int count, int6
                            const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl,
                            void* stream);
 
+/*
+ * elx_adam_multi out of place: the updated master and moments of descriptor c are written to the arrays of
+ * shadow[c] (same n_shard and tile_begin; its grad_param is ignored) while descs[c]'s arrays are only read;
+ * the refreshed working copy still replaces the gradients in descs[c].grad_param.  Elements no segment
+ * covers are not written, so both sets must start out equal.  No counterpart in the reference: it lets a
+ * host start updating before the last gradient has arrived (elx_step_begin called on the assumption of no
+ * overflow) and drop the result, by not swapping the two sets, when an overflow turns up afterwards --
+ * the reference's rule that one overflow skips every parameter (optimizer.py:194-203) then still holds.
+ * Always runs the bulk-copy variant.  A skipped step (ctl->skip) refreshes the working copy from descs as
+ * elx_adam_multi does and writes nothing to the shadow set.
+ */
+int elx_adam_multi_shadow(const ElxChunkDesc* descs, const ElxChunkDesc* shadow, int first, int count,
+                          int64_t n_tiles, int dtype, const ElxSeg* segs, const ElxHyper* hyper,
+                          int n_groups, ElxCtl* ctl, void* stream);
+
 /* ---- NVLink paths (single node, peer-mapped memory) -------------------------------------------- */
 
 /* Enable access from the current device to memory of `peer_device` (cudaDeviceEnablePeerAccess;

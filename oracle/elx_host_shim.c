@@ -185,6 +185,38 @@ int elx_pull_reduce_multi(const ElxChunkDesc* descs, int first, int count, int64
     (void)chunk_flags; (void)ctl; (void)stream;
     return ELX_ERR_NODEVICE;
 }
+int elx_adam_multi_shadow(const ElxChunkDesc* descs, const ElxChunkDesc* shadow, int first, int count,
+                          int64_t n_tiles, int dtype, const ElxSeg* segs, const ElxHyper* hyper, int n_groups,
+                          ElxCtl* ctl, void* stream) {
+    (void)n_tiles;
+    (void)stream;
+    if (!descs || !shadow || !ctl) return ELX_ERR_NULL;
+    if (n_groups > 64) return ELX_ERR_CAPACITY;
+    for (int c = first; c < first + count; ++c) {
+        const ElxChunkDesc* d = &descs[c];
+        const ElxChunkDesc* o = &shadow[c];
+        if (d->dtype != dtype || o->n_shard != d->n_shard) {
+            ctl->status |= ELX_STAT_BAD_DESC;
+            continue;
+        }
+        if (ctl->skip) {
+            orc_cast(d->master, d->grad_param, d->dtype, d->n_shard);
+            continue;
+        }
+        for (int s = d->seg_first; s < d->seg_first + d->seg_count; ++s) {
+            if (segs[s].group < 0 || segs[s].group >= n_groups) continue;
+            const int64_t b = segs[s].begin, n = segs[s].end - segs[s].begin;
+            memcpy(o->master + b, d->master + b, (size_t)n * sizeof(float));
+            memcpy(o->exp_avg + b, d->exp_avg + b, (size_t)n * sizeof(float));
+            memcpy(o->exp_avg_sq + b, d->exp_avg_sq + b, (size_t)n * sizeof(float));
+            orc_adam_f64(o->master, o->exp_avg, o->exp_avg_sq, d->grad_param, d->dtype, segs[s].begin, segs[s].end,
+                         hyper[segs[s].group], ctl->step, ctl->div_scale);
+        }
+        orc_cast(o->master, d->grad_param, d->dtype, d->n_shard);
+    }
+    return ELX_OK;
+}
+
 int elx_adam_multi_hostmem(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
                            const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl, void* stream) {
     return elx_adam_multi(descs, first, count, n_tiles, dtype, segs, hyper, n_groups, ctl, stream);
