@@ -251,16 +251,28 @@ class ElixirModule(nn.Module):
         if self.scheduled:
             with torch.no_grad():    # not a pass a learning scheduler should take for the model's access trace
                 self.fetcher.reset()
-                for name, param in self.grad_state_dict.items():
-                    self._gradient_handler(grads[name].to(self.dtype), param)
+                for param, grad in self._unique_grads(grads):
+                    self._gradient_handler(grad, param)
                 self._end_backward()
             return
         self._gather_all()
         self._set_states(TensorState.COMPUTE)
         self._set_states(TensorState.HOLD_AFTER_BWD)
-        for name, param in self.grad_state_dict.items():
-            self._gradient_handler(grads[name].to(self.dtype), param)
+        for param, grad in self._unique_grads(grads):
+            self._gradient_handler(grad, param)
         self._end_backward()
+
+    def _unique_grads(self, grads: Dict[str, torch.Tensor]):
+        """(parameter, gradient) once per parameter; a shared parameter is listed under each of its names in the
+        state dict and takes the gradient given under any of them."""
+        names: Dict[nn.Parameter, List[str]] = dict()
+        for name, param in self.grad_state_dict.items():
+            names.setdefault(param, []).append(name)
+        for param, aliases in names.items():
+            given = [n for n in aliases if n in grads]
+            if not given:
+                raise KeyError(f'no gradient for {aliases[0]}')
+            yield param, grads[given[0]].to(self.dtype)
 
     # ------------------------------------------------------------------ forward / backward
 
@@ -402,8 +414,12 @@ class ElixirModule(nn.Module):
         (``module.py:294-344``)."""
         for p_chunk in self.param_chunks:
             o_chunk = p_chunk.paired_chunk
-            names = [n for t in p_chunk.get_tensors() for n, q in self.grad_state_dict.items() if q is t]
-            loads = [state_dict[n].float() if state_dict is not None and n in state_dict else None for n in names]
+            loads = []
+            for tensor in p_chunk.get_tensors():
+                # a shared parameter appears under several names; any of them that the state dict holds will do
+                aliases = [n for n, q in self.grad_state_dict.items() if q is tensor]
+                held = [n for n in aliases if state_dict is not None and n in state_dict]
+                loads.append(state_dict[held[0]].float() if held else None)
             o_chunk.load_tensors(loads, only_rank_0)
             p_chunk.optim_update()
             if p_chunk.is_replica:    # the chunk is gathered (e.g. left so by the NVLink step): refresh the replica too

@@ -461,3 +461,32 @@ def fetcher_scenario_worker(rank, world, port):
         else:
             raise AssertionError('three chunks in use at once fitted two blocks')
     dist.destroy_process_group()
+
+
+def inject_worker(rank, world, port):
+    """Gradients handed over by name (no autograd pass) land identically with a replica cache of two blocks."""
+    use_host_shim()
+    dist = init_gloo(rank, world, port)
+    import copy
+    from elixir_b200.wrapper import ElixirModule, simple_plan
+    cpu = torch.device('cpu')
+    base = _residency_model()
+    gen = torch.Generator().manual_seed(9 + rank)
+    grads = {n: torch.randn(p.shape, generator=gen) * 1e-2 for n, p in base.named_parameters()}
+
+    def build(blocks, prefetch):
+        model = copy.deepcopy(base)
+        sr = simple_plan(model, world, unified_dtype=torch.float, shard_device=cpu, chunk_size=2400, rcache_device='cpu',
+                         public_block_number=blocks)
+        return ElixirModule(model, sr, dist.GroupMember.WORLD, prefetch=prefetch, dtype=torch.float)
+
+    full, lean, ahead = build(None, False), build(2, False), build(2, True)
+    for emodel in (full, lean, ahead):
+        emodel.inject_gradients(grads)
+    for a, b, c in zip(full.param_chunks, lean.param_chunks, ahead.param_chunks):
+        assert bits_equal(a.shard, b.shard) and bits_equal(a.shard, c.shard)
+        assert not b.is_replica and not c.is_replica
+    assert lean.param_chunk_group.rcache.public_free_cnt == 2 and ahead.param_chunk_group.rcache.public_free_cnt == 2
+    assert ahead.fetcher.scheduler.learning    # handing gradients over is not the model's access trace
+    dist.barrier()
+    dist.destroy_process_group()

@@ -140,3 +140,8 @@ def test_dropping_the_wrapper_frees_model_and_optimizer_state():
 
 def test_fetcher_decisions_on_a_spelled_out_trace():
     mp.spawn(W.fetcher_scenario_worker, args=(1, 29763), nprocs=1)
+
+
+@pytest.mark.parametrize('world', [1, 2])
+def test_injected_gradients_land_identically_with_a_small_replica_cache(world):
+    mp.spawn(W.inject_worker, args=(world, 29764 + world), nprocs=world)
