@@ -166,6 +166,36 @@ class ChunkStepEngine:
         self.update()
         self.end_step()
 
+    def capture_step(self, srcs: Sequence[torch.Tensor]) -> 'torch.cuda.CUDAGraph':
+        """Record ``land_all(srcs)`` + ``step()`` as one CUDA graph and return it; ``graph.replay()`` then runs
+        a whole step (landing copies with their probes, decision, update, flag reset) with a single launch
+        from the host.  Possible because nothing in the step reads the device: the skip decision, the loss
+        scale and the step count live in the control block and the kernels branch on them.  It frees the host
+        thread (one call per step); it does not shorten the step itself: eager launches already run ahead of
+        the device (measured on 4 chunks of 4 Mi elements: 150 us eager, 167 us replayed).  The gradient sources are the
+        tensors given here: refill them in place between replays.  Hyper-parameter changes (``set_hyper``) take
+        effect without a new capture as long as the number of groups stays the same; one rank only."""
+        assert self.world == 1 and self._slots is None and not self.table.host_resident
+        assert len(srcs) == self.n_chunks
+        current = torch.cuda.current_stream(self.device)
+        warm = torch.cuda.Stream(self.device)
+        warm.wait_stream(current)
+        with torch.cuda.stream(warm):    # first launches outside the capture: per-device set-up of the kernels
+            backup = self.ctl.tensor.clone()
+            saved = [[t.clone() for t in shard[:4]] for shard in self.shards]
+            self.land_all(srcs, streams=1)
+            self.step()
+            self.ctl.tensor.copy_(backup)    # the warm-up step must leave no trace
+            for shard, kept in zip(self.shards, saved):
+                for t, old in zip(shard[:4], kept):
+                    t.copy_(old)
+        current.wait_stream(warm)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.land_all(srcs, streams=1)
+            self.step()
+        return graph
+
     # ------------------------------------------------------------------ pipelines
 
     def _phase_marks(self, stream):
