@@ -145,3 +145,54 @@ def test_fetcher_decisions_on_a_spelled_out_trace():
 @pytest.mark.parametrize('world', [1, 2])
 def test_injected_gradients_land_identically_with_a_small_replica_cache(world):
     mp.spawn(W.inject_worker, args=(world, 29764 + world), nprocs=world)
+
+
+def _simulate(scheduler, trace, chunks, blocks, check_top=None):
+    """Drive a scheduler the way the fetcher does (one chunk per fetch, released right after use) and count the
+    fetches that found their chunk absent."""
+    resident, misses = set(), 0
+    with torch.no_grad():
+        scheduler.reset()
+        for step, i in enumerate(trace):
+            chunk = chunks[i]
+            scheduler.remove(chunk)
+            scheduler.step([chunk])
+            if chunk not in resident:
+                misses += 1
+                if len(resident) == blocks:
+                    victim = scheduler.top()
+                    assert victim is not None and victim in resident and victim is not chunk
+                    if check_top is not None:
+                        check_top(step, victim, resident - {chunk})
+                    scheduler.remove(victim)
+                    resident.remove(victim)
+                resident.add(chunk)
+            scheduler.add(chunk)
+        for chunk in list(resident):
+            scheduler.remove(chunk)
+        scheduler.clear()
+    return misses
+
+
+def test_belady_choice_is_the_furthest_next_use_and_never_loses_to_fifo():
+    hypothesis = pytest.importorskip('hypothesis')
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=150, deadline=None)
+    @given(st.lists(st.integers(0, 5), min_size=1, max_size=40), st.integers(1, 4))
+    def run(trace, blocks):
+        chunks = [FakeChunk(i) for i in range(6)]
+
+        def brute_force(step, victim, candidates):
+            def next_use(c):
+                later = [s for s in range(step + 1, len(trace)) if trace[s] == c.chunk_id]
+                return later[0] if later else len(trace)
+            best = max(candidates, key=lambda c: (next_use(c), c.chunk_id))
+            assert victim is best, (trace, blocks, step)
+
+        belady = _simulate(PrefetchScheduler([[chunks[i]] for i in trace]), trace, chunks, blocks, brute_force)
+        fifo = _simulate(FIFOScheduler(), trace, chunks, blocks)
+        assert belady <= fifo, (trace, blocks, belady, fifo)
+        assert belady >= len(set(trace))    # every chunk has to come in at least once
+
+    run()
