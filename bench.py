@@ -6,13 +6,17 @@ N = 1: the GPT-2-XL-shaped chunk set (1 557 611 200 parameters in 64 MiB fp16 ch
 moments, AdamW wd 0.01, gradients ~ N(0, 1e-3) * 2^16).  One step = for every chunk the reduce epilogue
 (copy of the reduced gradient block into the shard fused with the inf/nan probe), then the device-side
 decision / loss-scaler update, then ONE fused unscale + AdamW + fp16 copy-back launch over all chunks.
-N > 1 (under torchrun): the OPT-13B-shaped chunk set sharded over the ranks; one step = per chunk
-reduce-scatter (rank average) -> probe, the decision, then per chunk fused update -> all-gather,
-pipelined on side streams.
+N > 1 (under torchrun): the OPT-13B-shaped chunk set sharded over the ranks; one step = reduce-scatter (rank
+average) fused with the probe, the decision, then the fused update with the all-gather: by default inside
+the kernels over peer-mapped NVLink memory (``--collective p2p``), or copy-engine staged (``staged``) or over
+NCCL on side streams (``nccl``).  ``--workload opt66b_bf16``: the OPT-66B-shaped bf16 set.
 
 Prints ONE JSON line (rank 0).  ``value`` is whole-job parameters per second with all inputs resident
 in HBM; ``e2e`` is the same step through ``ChunkStepEngine.step_from_host`` with pinned host buffers on
-both ends (gradients in, updated low-precision parameters out).  ``--impl reference`` times the
+both ends (gradients in, updated low-precision parameters out); at N = 1 it is the speculative form of
+that call (updates start while gradients still arrive and are dropped if an overflow turns up), with the
+plain form's time beside it.  ``--shards host`` / ``host-streamed`` (N = 1): the optimizer state kept in
+pinned host memory.  ``--impl reference`` times the
 reference's CPU Adam path (torch.optim.AdamW on the host cores — ColossalAI's CPUAdam is not installable
 offline — next to the C oracle with all threads) on a bounded sample of the same workload.
 """
