@@ -13,6 +13,8 @@ Gradients are injected straight into the chunks (the reference's forward hooks d
 current PyTorch), through the same calls its autograd hook makes (`_gradient_handler`).
 
 Fixture contents
+  scheduler.json which chunk the reference's FIFOScheduler / PrefetchScheduler (elixir/chunk/scheduler/) gives
+                 up at every eviction of seeded random access traces (stand-in chunk objects; no process group)
   chunk_w{W}.pt  per rank: shard after close, valid_end, gathered payload, reduced shard and overflow
                  flag for a clean and for an inf-carrying gradient set (elixir/chunk/core/chunk.py)
   optim_w{W}.pt  per rank and step: overflow decision, loss scale after the step, fp32 master shards
@@ -193,6 +195,72 @@ def run_optim(rank, world):
     return out
 
 
+class StandIn:
+    """All a scheduler needs of a chunk: identity and an order."""
+
+    def __init__(self, chunk_id):
+        self.chunk_id = chunk_id
+
+    def __hash__(self):
+        return self.chunk_id
+
+    def __eq__(self, other):
+        return self.chunk_id == other.chunk_id
+
+    def __lt__(self, other):
+        return self.chunk_id < other.chunk_id
+
+
+def scheduler_cases(n_cases=40, seed=4242):
+    """Seeded (trace, blocks) pairs: up to 7 chunks, up to 60 fetches, 1 to 4 blocks."""
+    import random
+    rng = random.Random(seed)
+    cases = []
+    for _ in range(n_cases):
+        n_chunks = rng.randint(2, 7)
+        trace = [rng.randrange(n_chunks) for _ in range(rng.randint(5, 60))]
+        cases.append((trace, rng.randint(1, 4)))
+    return cases
+
+
+def drive_scheduler(scheduler, trace, blocks, step_with_chunks=False):
+    """One chunk per fetch, released right after use; returns the ids of the chunks given up, in order."""
+    chunks = {i: StandIn(i) for i in set(trace)}
+    resident, victims = set(), []
+    scheduler.reset()
+    for i in trace:
+        chunk = chunks[i]
+        scheduler.remove(chunk)
+        if step_with_chunks:
+            scheduler.step([chunk])
+        else:
+            scheduler.step()
+        if chunk not in resident:
+            if len(resident) == blocks:
+                victim = scheduler.top()
+                scheduler.remove(victim)
+                resident.remove(victim)
+                victims.append(victim.chunk_id)
+            resident.add(chunk)
+        scheduler.add(chunk)
+    for chunk in list(resident):
+        scheduler.remove(chunk)
+    scheduler.clear()
+    return victims
+
+
+def run_scheduler():
+    sys.path.insert(0, REF)
+    from elixir.chunk.scheduler import FIFOScheduler, PrefetchScheduler
+    out = []
+    for trace, blocks in scheduler_cases():
+        stand_ins = {i: StandIn(i) for i in set(trace)}
+        belady = drive_scheduler(PrefetchScheduler([[stand_ins[i]] for i in trace]), trace, blocks)
+        fifo = drive_scheduler(FIFOScheduler(), trace, blocks)
+        out.append(dict(trace=trace, blocks=blocks, prefetch_victims=belady, fifo_victims=fifo))
+    return out
+
+
 def worker(rank, world, port, result_dir):
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
                       MASTER_PORT=str(port))
@@ -213,6 +281,10 @@ def main():
     if not os.path.isdir(os.path.join(REF, 'elixir')):
         raise SystemExit('give the path of a checkout of hpcaitech/Elixir (argument or ELIXIR_REFERENCE)')
     os.environ['ELIXIR_REFERENCE'] = REF    # spawned workers re-import this module
+    import json
+    with open(os.path.join(out_dir, 'scheduler.json'), 'w') as f:
+        json.dump(run_scheduler(), f)
+    print('scheduler traces written')
     for i, world in enumerate((1, 2, 4)):
         with tempfile.TemporaryDirectory() as tmp:
             mp.spawn(worker, args=(world, 29600 + i, tmp), nprocs=world)

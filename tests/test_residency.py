@@ -196,3 +196,26 @@ def test_belady_choice_is_the_furthest_next_use_and_never_loses_to_fifo():
         assert belady >= len(set(trace))    # every chunk has to come in at least once
 
     run()
+
+
+def test_schedulers_give_up_the_chunks_the_reference_schedulers_give_up():
+    """tests/golden/scheduler.json: evictions of the reference's own FIFOScheduler / PrefetchScheduler on 40
+    seeded random traces (generated by tests/golden/make_golden.py); ties included, the sequences are equal."""
+    import json
+    import os
+    import sys
+    sys.path.insert(0, W.GOLDEN)
+    from make_golden import StandIn, drive_scheduler, scheduler_cases
+    cases = json.load(open(os.path.join(W.GOLDEN, 'scheduler.json')))
+    assert [(c['trace'], c['blocks']) for c in cases] == [(t, b) for t, b in scheduler_cases()]
+    evictions = 0
+    for case in cases:
+        trace, blocks = case['trace'], case['blocks']
+        stand_ins = {i: StandIn(i) for i in set(trace)}
+        with torch.enable_grad():
+            got = drive_scheduler(PrefetchScheduler([[stand_ins[i]] for i in trace]), trace, blocks, step_with_chunks=True)
+            assert got == case['prefetch_victims'], (trace, blocks)
+            got = drive_scheduler(FIFOScheduler(), trace, blocks, step_with_chunks=True)
+            assert got == case['fifo_victims'], (trace, blocks)
+        evictions += len(case['prefetch_victims']) + len(case['fifo_victims'])
+    assert evictions > 500
