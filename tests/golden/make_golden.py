@@ -15,6 +15,8 @@ current PyTorch), through the same calls its autograd hook makes (`_gradient_han
 Fixture contents
   scheduler.json which chunk the reference's FIFOScheduler / PrefetchScheduler (elixir/chunk/scheduler/) gives
                  up at every eviction of seeded random access traces (stand-in chunk objects; no process group)
+  plans.json     the chunk plans of the reference's simple search (elixir/search/simple.py: SearchSimple.search +
+                 generate_chunk_plans) for two small models over group sizes, split numbers and allocate factors
   chunk_w{W}.pt  per rank: shard after close, valid_end, gathered payload, reduced shard and overflow
                  flag for a clean and for an inf-carrying gradient set (elixir/chunk/core/chunk.py)
   optim_w{W}.pt  per rank and step: overflow decision, loss scale after the step, fp32 master shards
@@ -261,6 +263,41 @@ def run_scheduler():
     return out
 
 
+class TiedNet(nn.Module):
+    """An embedding shared with the output projection (a parameter used by two modules) around a few layers."""
+
+    def __init__(self):
+        super().__init__()
+        self.embed = nn.Embedding(50, 32)
+        self.body = nn.Sequential(nn.LayerNorm(32), nn.Linear(32, 64), nn.Tanh(), nn.Linear(64, 32), nn.LayerNorm(32))
+        self.head = nn.Linear(32, 50, bias=False)
+        self.head.weight = self.embed.weight
+
+
+PLAN_MODELS = dict(tiny=TinyNet, tied=TiedNet)
+PLAN_GRID = [(g, s, a) for g in (1, 2, 4) for s in (1, 3, 10, 50) for a in (0.6, 1.0)]
+
+
+def run_plans():
+    sys.path.insert(0, os.path.join(HERE, 'colossalai_stub'))
+    sys.path.insert(0, REF)
+    from elixir.search.simple import SearchSimple
+    out = []
+    for name, cls in PLAN_MODELS.items():
+        torch.manual_seed(3)
+        model = cls()
+        for group_size, split_number, allocate_factor in PLAN_GRID:
+            search = SearchSimple(model, group_size, dtype=torch.float16)
+            private, public = search.search(split_number, allocate_factor)
+            plans = search.generate_chunk_plans(private, public)
+            out.append(dict(model=name, group_size=group_size, split_number=split_number,
+                            allocate_factor=allocate_factor, public_block_size=search.public_block_size,
+                            public_block_number=search.public_block_number,
+                            plans=[dict(names=list(p.name_list), chunk_size=p.chunk_size,
+                                        fused=bool(p.kwargs.get('rcache_fused', False))) for p in plans]))
+    return out
+
+
 def worker(rank, world, port, result_dir):
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
                       MASTER_PORT=str(port))
@@ -284,7 +321,9 @@ def main():
     import json
     with open(os.path.join(out_dir, 'scheduler.json'), 'w') as f:
         json.dump(run_scheduler(), f)
-    print('scheduler traces written')
+    with open(os.path.join(out_dir, 'plans.json'), 'w') as f:
+        json.dump(run_plans(), f)
+    print('scheduler traces and chunk plans written')
     for i, world in enumerate((1, 2, 4)):
         with tempfile.TemporaryDirectory() as tmp:
             mp.spawn(worker, args=(world, 29600 + i, tmp), nprocs=world)

@@ -154,3 +154,32 @@ def test_scaler_state_dict_round_trip(host_backend):
         DynamicGradScaler(growth_factor=1.0)
     with pytest.raises(ValueError):
         DynamicGradScaler(backoff_factor=1.5)
+
+
+def test_simple_plan_equals_the_reference_simple_search():
+    """tests/golden/plans.json holds what the reference's SearchSimple.search + generate_chunk_plans produce for
+    two small models over group sizes, split numbers and allocate factors (tests/golden/make_golden.py):
+    same name lists, same chunk sizes, same private chunks, same number and size of public blocks."""
+    import json
+    import os
+    import sys
+    import torch
+    sys.path.insert(0, W.GOLDEN)
+    from make_golden import PLAN_GRID, PLAN_MODELS
+    from elixir_b200.wrapper import simple_plan
+    cases = json.load(open(os.path.join(W.GOLDEN, 'plans.json')))
+    assert len(cases) == len(PLAN_MODELS) * len(PLAN_GRID)
+    for case in cases:
+        torch.manual_seed(3)
+        model = PLAN_MODELS[case['model']]()
+        sr = simple_plan(model, case['group_size'], split_number=case['split_number'],
+                         allocate_factor=case['allocate_factor'], unified_dtype=torch.float16, rcache_device='cpu',
+                         shard_device=torch.device('cpu'))
+        got = [dict(names=list(p.name_list), chunk_size=p.chunk_size, fused=bool(p.kwargs.get('rcache_fused', False)))
+               for p in sr.param_chunk_plans]
+        key = (case['model'], case['group_size'], case['split_number'], case['allocate_factor'])
+        assert got == case['plans'], key
+        pool = sr.chunk_group.rcache
+        assert pool.public_free_cnt == case['public_block_number'], key
+        if any(not p['fused'] for p in got):
+            assert pool.public_block_size == case['public_block_size'], key
