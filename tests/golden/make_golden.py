@@ -15,6 +15,7 @@ current PyTorch), through the same calls its autograd hook makes (`_gradient_han
 Fixture contents
   scheduler.json which chunk the reference's FIFOScheduler / PrefetchScheduler (elixir/chunk/scheduler/) gives
                  up at every eviction of seeded random access traces (stand-in chunk objects; no process group)
+  states.json    the legal tensor-state transitions (elixir/chunk/core/states.py)
   plans.json     the chunk plans of the reference's simple search (elixir/search/simple.py: SearchSimple.search +
                  generate_chunk_plans) for two small models over group sizes, split numbers and allocate factors
   chunk_w{W}.pt  per rank: shard after close, valid_end, gathered payload, reduced shard and overflow
@@ -323,6 +324,9 @@ def main():
         json.dump(run_scheduler(), f)
     with open(os.path.join(out_dir, 'plans.json'), 'w') as f:
         json.dump(run_plans(), f)
+    from elixir.chunk.core.states import legal_ts_update_list
+    with open(os.path.join(out_dir, 'states.json'), 'w') as f:
+        json.dump(sorted([old.name, new.name] for old, new in legal_ts_update_list), f)
     print('scheduler traces and chunk plans written')
     for i, world in enumerate((1, 2, 4)):
         with tempfile.TemporaryDirectory() as tmp:

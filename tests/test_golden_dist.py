@@ -90,5 +90,5 @@ def test_committed_fixtures_are_what_the_reference_produces(tmp_path):
             committed = torch.load(os.path.join(W.GOLDEN, f'{kind}_w{world}.pt'))
             assert _same(fresh, committed), (kind, world)
     import json
-    for name in ('scheduler.json', 'plans.json'):
+    for name in ('scheduler.json', 'plans.json', 'states.json'):
         assert json.load(open(os.path.join(str(tmp_path), name))) == json.load(open(os.path.join(W.GOLDEN, name))), name

@@ -183,3 +183,21 @@ def test_simple_plan_equals_the_reference_simple_search():
         assert pool.public_free_cnt == case['public_block_number'], key
         if any(not p['fused'] for p in got):
             assert pool.public_block_size == case['public_block_size'], key
+
+
+def test_tensor_state_machine_equals_the_reference():
+    """tests/golden/states.json: the reference's legal transitions; every other pair must raise."""
+    import json
+    import os
+    from elixir_b200.chunk import TensorState, ts_update_sanity_check
+    from elixir_b200.chunk.states import legal_ts_update_list
+    legal = json.load(open(os.path.join(W.GOLDEN, 'states.json')))
+    assert sorted([old.name, new.name] for old, new in legal_ts_update_list) == legal
+    assert [s.name for s in TensorState] == ['FREE', 'COMPUTE', 'HOLD', 'HOLD_AFTER_BWD', 'READY_FOR_REDUCE']
+    for old in TensorState:
+        for new in TensorState:
+            if [old.name, new.name] in legal:
+                assert ts_update_sanity_check(old, new)
+            else:
+                with pytest.raises(RuntimeError):
+                    ts_update_sanity_check(old, new)
