@@ -490,3 +490,68 @@ def inject_worker(rank, world, port):
     assert ahead.fetcher.scheduler.learning    # handing gradients over is not the model's access trace
     dist.barrier()
     dist.destroy_process_group()
+
+
+def group_worker(rank, world, port):
+    """ChunkGroup / MemoryPool bookkeeping the way the reference's test/chunk/test_group.py and test_block.py
+    exercise it: lookups, gathers into public and private blocks, block accounting, release, reduce."""
+    use_host_shim()
+    dist = init_gloo(rank, world, port)
+    from elixir_b200.chunk import BlockRequire, ChunkGroup, MemoryPool, PrivateBlock, PublicBlock, TensorState
+    cpu = torch.device('cpu')
+    block = PublicBlock(123, torch.float16, 'cpu')
+    assert block.payload.numel() == 123 and block.payload.dtype == torch.float16 and block.memo_occ == 246
+    assert PrivateBlock(77, torch.float, 'cpu').memo_occ == 308
+
+    gen = torch.Generator().manual_seed(77)
+    shapes = dict(a=(5, 48), b=(3, 16), c=(288,), d=(2, 3, 48), e=(2, 35))
+    tensors = {k: torch.randn(s, generator=gen) for k, s in shapes.items()}
+    originals = {k: t.clone() for k, t in tensors.items()}
+    pool = MemoryPool('cpu')
+    pool.allocate(public_block_size=288, public_block_number=2, private_block_list=[BlockRequire(72, torch.float)])
+    assert (pool.public_free_cnt, pool.public_used_cnt) == (2, 0)
+    group = ChunkGroup(rcache=pool)
+    config = dict(shard_device=cpu, temp_device=cpu)
+    c0 = group.allocate_chunk([tensors['a'], tensors['b']], 288, torch.float, dist.GroupMember.WORLD, dict(config))
+    c1 = group.allocate_chunk([tensors['c']], 288, torch.float, dist.GroupMember.WORLD, dict(config))
+    c2 = group.allocate_chunk([tensors['d']], 288, torch.float, dist.GroupMember.WORLD, dict(config))
+    c3 = group.allocate_chunk([tensors['e']], 72, torch.float, dist.GroupMember.WORLD, dict(config, rcache_fused=True))
+    assert group.float_chunks == {c0, c1, c2} and group.fused_chunks == {c3}
+    assert group.tensors_to_chunks([tensors['e'], tensors['a'], tensors['b']]) == [c0, c3]    # by chunk id, once each
+
+    def intact(*names):
+        return all(torch.equal(tensors[n], originals[n]) for n in names)
+
+    def hollow(name):    # shape kept, one element of storage: the data lives in the shards
+        return tensors[name].shape == originals[name].shape and tensors[name].untyped_storage().nbytes() == 4
+
+    assert hollow('a') and hollow('e')
+    assert group.access_chunk(c0) and group.access_chunk(c1) and not group.access_chunk(c1)
+    assert intact('a', 'b', 'c') and (pool.public_free_cnt, pool.public_used_cnt) == (0, 2)
+    assert not group.rcache_enough_check(c2) and group.rcache_enough_check(c3)
+    group.access_chunk(c3)    # private block: always there
+    assert intact('e') and (pool.public_free_cnt, pool.public_used_cnt) == (0, 2)
+    group.release_chunk(c1)
+    assert hollow('c') and not group.is_accessed(c1) and group.rcache_enough_check(c2)
+    group.access_chunk(c2)
+    assert intact('d')
+    try:
+        group.access_chunk(c1)
+    except IndexError:
+        pass    # no free public block
+    else:
+        raise AssertionError('a third public chunk fitted two blocks')
+    for state in (TensorState.COMPUTE, TensorState.HOLD_AFTER_BWD, TensorState.READY_FOR_REDUCE):
+        group.tensor_trans_state(tensors['e'], state)
+    assert c3.reduce_check
+    group.reduce_chunk(c3)
+    assert not c3.is_replica and not group.is_accessed(c3)
+    group.release_chunk(c0)
+    group.release_chunk(c2)
+    assert (pool.public_free_cnt, pool.public_used_cnt) == (2, 0)
+    for chunk, names in ((c0, 'ab'), (c1, 'c'), (c2, 'd')):    # everything survives a round trip through the shards
+        group.access_chunk(chunk)
+        assert intact(*names)
+        group.release_chunk(chunk)
+    dist.barrier()
+    dist.destroy_process_group()

@@ -201,3 +201,9 @@ def test_tensor_state_machine_equals_the_reference():
             else:
                 with pytest.raises(RuntimeError):
                     ts_update_sanity_check(old, new)
+
+
+@pytest.mark.parametrize('world', [1, 2])
+def test_chunk_group_and_memory_pool_bookkeeping(world):
+    import torch.multiprocessing as mp
+    mp.spawn(W.group_worker, args=(world, 29730 + world), nprocs=world)
