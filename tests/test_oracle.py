@@ -160,3 +160,20 @@ def test_scaler_state_machine_against_a_python_restatement(oracle):
                     scale = min(np.float32(scale * np.float32(2.0)), np.float32(2.0**24))
             assert (ctl.scale, ctl.growth_step, ctl.hysteresis_step, ctl.step, ctl.skip, ctl.div_scale,
                     ctl.found_inf) == (float(scale), growth, hyst, step, want_skip, want_div, 0)
+
+
+def test_scaler_trajectory_equals_torch_amp_update_scale(oracle):
+    """An implementation nobody here wrote: torch's own loss-scale update (`torch._amp_update_scale_`, what
+    torch.amp.GradScaler.update runs).  With hysteresis 1 and no clamping in reach it is the same state machine:
+    back off and reset the growth tracker on an overflow, grow after `growth_interval` clean steps."""
+    from elixir_b200 import kernels as K
+    for growth_interval, growth, backoff in ((2, 2.0, 0.5), (5, 2.0, 0.5), (3, 4.0, 0.25)):
+        cfg = K.scaler_cfg(True, growth, backoff, 0.0, 0.0, growth_interval=growth_interval, hysteresis=1)
+        ctl = oracle.new_ctl(2.0**10)
+        scale, tracker = torch.full((1,), 2.0**10), torch.zeros(1, dtype=torch.int32)
+        gen = torch.Generator().manual_seed(growth_interval)
+        for found in (torch.rand(400, generator=gen) < 0.3).tolist():
+            ctl.found_inf = int(found)
+            oracle.step_begin(ctl, cfg)
+            torch._amp_update_scale_(scale, tracker, torch.tensor([float(found)]), growth, backoff, growth_interval)
+            assert ctl.scale == float(scale) and ctl.growth_step == int(tracker) and ctl.skip == int(found)
