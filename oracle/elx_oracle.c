@@ -6,8 +6,9 @@
  * copy-back on skip, shard geometry) is pinned against hpcaitech/Elixir's own Python code run on
  * CPU (fixtures under tests/golden/).  The Adam arithmetic and the dynamic loss scaler live in
  * ColossalAI, which Elixir does not pin and which is not available offline: for those two the
- * oracle restates the published algorithm and is pinned against torch.optim.Adam / AdamW on CPU —
- * "parity unpinned" with respect to ColossalAI itself.
+ * oracle restates the published algorithm and is pinned against torch.optim.Adam / AdamW on CPU and,
+ * for the scaler with hysteresis 1, against torch's own AMP scale update — "parity unpinned" with
+ * respect to ColossalAI itself.
  *
  * What each function follows (paths inside hpcaitech/Elixir unless stated otherwise):
  *   orc_probe        elixir/chunk/core/chunk.py:214-216  set_overflow_flag (isinf|isnan, any)
