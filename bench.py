@@ -3,9 +3,11 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 N = 1: the GPT-2-XL-shaped chunk set (1 557 611 200 parameters in 64 MiB fp16 chunks, fp32 master and
-moments, AdamW wd 0.01, gradients ~ N(0, 1e-3) * 2^16).  One step = for every chunk the reduce epilogue
-(copy of the reduced gradient block into the shard fused with the inf/nan probe), then the device-side
-decision / loss-scaler update, then ONE fused unscale + AdamW + fp16 copy-back launch over all chunks.
+moments, AdamW wd 0.01, gradients ~ N(0, 1e-3) * 2^16).  One step = ONE inf/nan probe launch over the
+gradient blocks of all chunks (read where the backward pass left them), the device-side decision /
+loss-scaler update, then ONE fused unscale + AdamW + fp16 copy-back launch over all chunks that reads the
+gradients from the same blocks and writes the working copies into the shards.  ``--landing copy`` times the
+older form instead, in which every block is first copied into its shard (fused with the probe).
 N > 1 (under torchrun): the OPT-13B-shaped chunk set sharded over the ranks; one step = reduce-scatter (rank
 average) fused with the probe, the decision, then the fused update with the all-gather: by default inside
 the kernels over peer-mapped NVLink memory (``--collective p2p``), or copy-engine staged (``staged``) or over
@@ -39,11 +41,8 @@ OPT13B_PARAMS = 40 * (12 * 5120 * 5120 + 13 * 5120) + 50272 * 5120 + 2050 * 5120
 OPT66B_PARAMS = 64 * (12 * 9216 * 9216 + 13 * 9216) + 50272 * 9216 + 2050 * 9216 + 2 * 9216
 CHUNK_1GPU = 32 * 1024 * 1024    # 64 MiB of fp16
 CHUNK_SHARDED = 256 * 1024 * 1024    # 512 MiB of fp16
-BYTES_PER_ELEM = 28    # g 2 + p/m/v 12 read, p/m/v 12 + p16 2 written
-# dram__bytes_read.sum + dram__bytes_write.sum of one adam_tma_kernel launch over 67 108 864 elements,
-# from the ncu capture summarised in profiles/adam_tma_kernel_small_case_ncu.md; traffic grows in
-# proportion to the elements, so roofline.traffic scales it to the launch measured here.
-NCU_TRAFFIC_BYTES_PER_ELEM = 1819.9e6 / 67108864
+BYTES_PER_ELEM = 28    # updated element: g 2 + p/m/v 12 read, p/m/v 12 + p16 2 written
+BYTES_PER_PAD_ELEM = 6    # element past valid_end: master read, working copy written
 
 
 def load_peaks():
@@ -156,6 +155,133 @@ def synth_grad(n, device, gen, scale, sigma, dtype, out=None):
 
 
 # ------------------------------------------------------------------------------------------------------
+# multi-GPU parity self-check (outside the timed region)
+# ------------------------------------------------------------------------------------------------------
+
+
+_KEEP_ALIVE = []
+
+
+def sharded_parity_check(collective, world, rank, device, group, seed):
+    """Run a small sharded case through the SAME engine method the benchmark times and compare it, on every
+    rank, with the CPU oracle (used here only as the checker): ragged chunks, a chunk whose used length ends
+    inside one rank's shard, a chunk that fits in the first shard, one inf that lands in rank 0's shard only
+    (every rank must skip), five steps, fp16 and bf16.  Checked: the reduced gradients bit for bit (NVLink
+    paths) or to fp16 rounding (NCCL, whose summation order is its own), skip decision, loss scale and step
+    count on all ranks, fp32 masters within 1e-6 of the double-precision oracle, and the gathered block equal
+    to all ranks' refreshed shards.  Returns (ok, number of cases, first failure or None), agreed across ranks."""
+    import torch.distributed as dist
+    from elixir_b200 import comm
+    from elixir_b200 import kernels as K
+    from elixir_b200.engine import ChunkStepEngine
+    from elixir_b200.scaler import DynamicGradScaler
+    from oracle import oracle as orc
+
+    def bits_equal(a, b):
+        a, b = a.detach().cpu().contiguous(), b.detach().cpu().contiguous()
+        view = {2: torch.int16, 4: torch.int32}[a.element_size()]
+        return a.shape == b.shape and a.dtype == b.dtype and torch.equal(a.view(view), b.view(view))
+
+    def close(actual, ref64, rtol=2e-6):
+        a, r = actual.detach().double().cpu(), ref64.double()
+        bound = rtol * torch.maximum(r.abs(), r.pow(2).mean().sqrt().expand_as(r)).clamp(min=1e-45)
+        return bool(((a - r).abs() <= bound).all())
+
+    failure, cases = None, 0
+    for dtype in (torch.float16, torch.bfloat16):
+        cases += 1
+        scale = 256.0
+        chunk_sizes = [world * 4096 * 40, world * (4096 + 16), world * 4096 * 5, world * 24]
+        used = [chunk_sizes[0], chunk_sizes[1], chunk_sizes[2] // 2 + 7, 9]
+        engine = ChunkStepEngine(device, dtype, DynamicGradScaler(initial_scale=scale, hysteresis=1, growth_interval=3),
+                                 process_group=group)
+        host, host_ctl, host_state = orc.ChunkSet(dtype), orc.new_ctl(scale), []
+        hypers = [K.hyper(weight_decay=0.01)]
+        for c, (C, u) in enumerate(zip(chunk_sizes, used)):
+            S = C // world
+            gen = torch.Generator().manual_seed(seed + c)
+            full = torch.randn(C, generator=gen) * 0.02
+            full[u:] = 0
+            mine = full[rank * S:(rank + 1) * S].clone()
+            nv = max(0, min(S, u - rank * S))
+            lowp = torch.zeros(S, dtype=dtype)
+            host.add_chunk(mine, torch.zeros(S), torch.zeros(S), lowp, nv, [(0, nv, 0)] if nv else [])
+            host_state.append((mine, lowp))
+            engine.add_shard(mine.to(device), torch.zeros(S, dtype=dtype, device=device), nv, [(0, nv, 0)] if nv else [])
+        engine.finalize()
+        engine.set_hyper(hypers)
+        if collective in ('p2p', 'staged'):
+            engine.enable_p2p(chunk_sizes, timeout_ms=5000)
+            if collective == 'staged':
+                engine.enable_staging(pool=2)
+            gather = [engine.gather_block(c) for c in range(len(chunk_sizes))]
+        else:
+            gather = [torch.empty(C, dtype=dtype, device=device) for C in chunk_sizes]
+        for step in range(5):
+            per_rank, blocks = [], []
+            for c, C in enumerate(chunk_sizes):
+                rank_grads = []
+                for r in range(world):
+                    gen = torch.Generator().manual_seed(seed + 1000 * step + 10 * c + r)
+                    g = (torch.randn(C, generator=gen) * 1e-3 * host_ctl.scale).to(dtype)
+                    if step == 2 and c == 1 and r == world - 1:
+                        g[5] = float('inf')    # lands in rank 0's shard only
+                    rank_grads.append(g)
+                per_rank.append(rank_grads)
+                if collective in ('p2p', 'staged'):
+                    engine.grad_block(c).copy_(rank_grads[rank])
+                else:
+                    blocks.append(rank_grads[rank].to(device))
+            reduced = []
+            for c, C in enumerate(chunk_sizes):
+                S = C // world
+                mine = [g[rank * S:(rank + 1) * S].contiguous() for g in per_rank[c]]
+                if collective in ('p2p', 'staged'):
+                    reduced.append(orc.reduce_avg_f32acc(mine))    # rank-order fp32 accumulation, one rounding
+                else:
+                    out = torch.empty(S, dtype=dtype, device=device)
+                    comm.reduce_scatter_avg(out, blocks[c].clone(), group)
+                    reduced.append(out.cpu())
+                    want = orc.reduce_avg(mine).float()
+                    finite = torch.isfinite(want)
+                    if not torch.equal(finite, torch.isfinite(reduced[c].float())) or float(
+                            (reduced[c].float() - want).abs()[finite].max()) > 2 * 2.0**-8 * float(want.abs()[finite].max()):
+                        failure = failure or f'{dtype} step {step} chunk {c}: NCCL average off the divide-then-sum value'
+            if collective == 'p2p':
+                engine.step_sharded_p2p()
+            elif collective == 'staged':
+                engine.step_sharded_staged()
+            else:
+                engine.step_sharded(blocks, gather)
+            torch.cuda.synchronize()
+            for c in range(len(chunk_sizes)):
+                host_state[c][1].copy_(reduced[c])
+            if step == 2:
+                host_ctl.found_inf = 1    # agreement: every rank skips, also those whose shards are clean
+            skipped = host.step(host_ctl, engine.scaler.cfg, hypers, probe=True, f64=True)
+            ctl = engine.read_control()
+            if ctl.status or bool(ctl.skip) != skipped or skipped != (step == 2) or \
+                    (ctl.scale, ctl.step) != (host_ctl.scale, host_ctl.step):
+                failure = failure or f'{dtype} step {step}: control block status={ctl.status} skip={ctl.skip} scale={ctl.scale}'
+            for c, C in enumerate(chunk_sizes):
+                S = C // world
+                if not close(engine.shards[c][0], host_state[c][0]):
+                    failure = failure or f'{dtype} step {step} chunk {c}: master off the oracle'
+                want16 = torch.empty(S, dtype=dtype)
+                orc.cast(engine.shards[c][0].cpu(), want16)
+                if not bits_equal(engine.shards[c][3], want16):
+                    failure = failure or f'{dtype} step {step} chunk {c}: working copy is not the rounded master'
+                others = [torch.empty_like(engine.shards[c][3]) for _ in range(world)]
+                dist.all_gather(others, engine.shards[c][3], group=group)
+                if not bits_equal(gather[c], torch.cat(others)):
+                    failure = failure or f'{dtype} step {step} chunk {c}: gathered block differs from the ranks\' shards'
+        _KEEP_ALIVE.append(engine)    # peer-mapped buffers stay allocated while other ranks have them mapped
+    verdict = torch.tensor([0 if failure is None else 1], device=device)
+    dist.all_reduce(verdict, op=dist.ReduceOp.MAX, group=group)
+    return verdict.item() == 0, cases, failure
+
+
+# ------------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------------
 
@@ -179,11 +305,24 @@ def run_ours(args):
         dist.init_process_group('nccl', rank=rank, world_size=world, device_id=device)
         group = dist.group.WORLD
 
+    parity = None
+    if world > 1 and not args.no_parity_check:
+        ok, cases, failure = sharded_parity_check(args.collective, world, rank, device, group, args.seed)
+        parity = {'ok': ok, 'world': world, 'cases': cases, 'collective': args.collective,
+                  'what': 'small ragged chunk set, 5 steps (1 skipped by an inf in one rank\'s shard), fp16 and bf16, '
+                          'against the CPU oracle on every rank'}
+        if not ok:
+            if failure:
+                print(f'bench: parity check failed on rank {rank}: {failure}', file=sys.stderr)
+            dist.barrier()
+            dist.destroy_process_group()
+            raise SystemExit(3)
+
     dtype, sigma = torch.float16, 1e-3
     if world == 1:
         workload, total, chunk, scale, wd = 'gpt2xl_chunks_1gpu', GPT2XL_PARAMS, CHUNK_1GPU, 65536.0, 0.01
     elif args.workload == 'opt66b_bf16':
-        # BASELINE config 5: bf16 chunks, constant scale 1, AdamW, ~8.2 G elements of state per rank at W = 8.
+        # OPT-66B-shaped set: bf16 chunks, constant scale 1, AdamW, ~8.2 G elements of state per rank at W = 8.
         # The replicated blocks cannot all be resident next to 115 GB of state, so they come from a small pool,
         # as in training, and the step runs chunk by chunk.
         workload, total, chunk, scale, wd = f'opt66b_bf16_chunks_sharded_w{world}', OPT66B_PARAMS, CHUNK_SHARDED, 1.0, 0.01
@@ -209,6 +348,8 @@ def run_ours(args):
         scaler = DynamicGradScaler(initial_scale=scale, growth_factor=2, backoff_factor=0.5, growth_interval=1000,
                                    min_scale=1, max_scale=2**24, hysteresis=2)
     engine = ChunkStepEngine(device, dtype, scaler, process_group=group)
+    in_place_sources = world == 1 and args.shards == 'device' and args.landing == 'none'
+    grad_blocks, n_valid_total = [], 0
     for c in range(n_chunks):
         master = synth_master(shard, device, args.seed + 1000 * rank + c)
         nv = valid_end(used[c], shard, rank)
@@ -220,7 +361,14 @@ def run_ours(args):
             # the reference's shard_device=cpu placement: master, moments and working copy in pinned host
             # memory, updated in place over PCIe by the same kernels
             master, lowp = master.cpu().pin_memory(), lowp.cpu().pin_memory()
-        engine.add_shard(master, lowp, nv, [(0, nv, 0)] if nv else [])
+        src = None
+        if in_place_sources:
+            # the gradient block of this chunk: the probe and the update read it where it is
+            gen = torch.Generator(device=device).manual_seed(args.seed + 7919 * (c + 1))
+            src = synth_grad(shard, device, gen, scale, sigma, dtype)
+            grad_blocks.append(src)
+        engine.add_shard(master, lowp, nv, [(0, nv, 0)] if nv else [], grad_src=src)
+        n_valid_total += nv
     engine.finalize()
     engine.set_hyper([K.hyper(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=wd, adamw_mode=True)])
     if args.shards == 'host-streamed':
@@ -228,10 +376,10 @@ def run_ours(args):
 
     # gradient sources
     if world == 1:
-        grad_blocks = []
-        for c in range(n_chunks):
-            gen = torch.Generator(device=device).manual_seed(args.seed + 7919 * (c + 1))
-            grad_blocks.append(synth_grad(shard, device, gen, scale, sigma, dtype))
+        if not in_place_sources:
+            for c in range(n_chunks):
+                gen = torch.Generator(device=device).manual_seed(args.seed + 7919 * (c + 1))
+                grad_blocks.append(synth_grad(shard, device, gen, scale, sigma, dtype))
         gather_blocks = None
     elif args.collective in ('p2p', 'staged'):
         # NVLink path: every chunk owns a block in the peer-mapped gradient and gather slabs
@@ -269,7 +417,10 @@ def run_ours(args):
             if record:
                 adam_events.append((a, b))
         elif world == 1:
-            engine.land_all(grad_blocks, streams=args.land_streams)
+            if in_place_sources:
+                engine.probe()
+            else:
+                engine.land_all(grad_blocks, streams=args.land_streams)
             engine.begin_step()
             if record:
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -362,12 +513,17 @@ def run_ours(args):
     if world == 1:
         adam_ms = statistics.mean(a.elapsed_time(b) for a, b in adam_events)
         n_elems = engine.n_elements()
-        achieved = n_elems * BYTES_PER_ELEM / (adam_ms * 1e-3) / 1e9
+        # algorithmic bytes of one update launch: 28 per updated element, 6 per element past valid_end
+        algo_bytes = BYTES_PER_ELEM * n_valid_total + BYTES_PER_PAD_ELEM * (n_elems - n_valid_total)
+        achieved = algo_bytes / (adam_ms * 1e-3) / 1e9
         result['roofline'] = {
             'bound': 'hbm', 'kernel': 'adam_tma_kernel', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s',
             'frac': achieved / peak, 'peak_kind': peak_kind, 'ms_per_launch': adam_ms,
-            'elements_per_launch': n_elems, 'bytes_per_element': BYTES_PER_ELEM,
-            'traffic': NCU_TRAFFIC_BYTES_PER_ELEM * n_elems, 'traffic_note': 'ncu capture of a 67M-element launch scaled by elements',
+            'elements_per_launch': n_elems, 'updated_elements_per_launch': n_valid_total,
+            'algorithmic_bytes_per_launch': algo_bytes,
+            'bytes_per_element': {'updated': BYTES_PER_ELEM, 'past_valid_end': BYTES_PER_PAD_ELEM},
+            # DRAM bytes of one launch as an ncu capture of this command counted them, when given on the command line
+            'traffic': args.ncu_traffic_bytes or None,
             'frac_of_8TBs_nominal': achieved / 8000.0,
         }
         result['adam_gparams_per_s'] = n_elems / (adam_ms * 1e-3) / 1e9
@@ -381,28 +537,30 @@ def run_ours(args):
                 'peak_kind': 'nominal PCIe Gen5 x16 (no measured figure on this pool)', 'ms_per_launch': adam_ms,
                 'elements_per_launch': n_elems, 'bytes_per_element_each_direction': BYTES_PER_ELEM // 2, 'traffic': None,
             }
-        result['gpu_launches'] = args.steps * (n_chunks + 2)
+        result['gpu_launches'] = args.steps * ((1 if in_place_sources else n_chunks) + 2)
     else:
         bus_bytes = 2 * chunk * (world - 1) / world * n_chunks    # per collective kind, per rank, per step
+        nominal, peer_copy = 900.0, 770.0    # GB/s per direction: NVLink 5 nominal; one copy-engine peer copy on this pool
         result['collective'] = {
             'per_step_bus_bytes_rs': bus_bytes, 'per_step_bus_bytes_ag': bus_bytes,
             'combined_bus_gbs': 2 * bus_bytes / (ms_per_step * 1e-3) / 1e9,
-            'nominal_gbs_per_direction': 900.0, 'measured_peer_copy_gbs': 770.0,
+            'nominal_gbs_per_direction': nominal, 'peer_copy_gbs_per_direction': peer_copy,
         }
         # update/push phase: the 28 B/element of the update + 2 B/element for this rank's slot of its own gather block
         adam_bytes = engine.n_elements() * (BYTES_PER_ELEM + 2)
         # the step is two phases in sequence, each bounded by the slower of its NVLink and its HBM time:
         # pull reduce-scatter (NVLink; HBM only reads and writes the own slice) and update + push all-gather
-        link_ms = bus_bytes / 770.0e9 * 1e3
+        link_ms = bus_bytes / (nominal * 1e9) * 1e3
         adam_hbm_ms = adam_bytes / (peak * 1e9) * 1e3
         pull_hbm_ms = engine.n_elements() * 2 * 2 / (peak * 1e9) * 1e3
         target_ms = max(link_ms, pull_hbm_ms) + max(link_ms, adam_hbm_ms)
+        achieved = 2 * bus_bytes / (ms_per_step * 1e-3) / 1e9
         result['roofline'] = {
-            'bound': 'nvlink', 'achieved': 2 * bus_bytes / (ms_per_step * 1e-3) / 1e9, 'peak': 770.0,
-            'unit': 'GB/s', 'frac': 2 * bus_bytes / (ms_per_step * 1e-3) / 1e9 / 770.0, 'peak_kind': 'measured',
+            'bound': 'nvlink', 'achieved': achieved, 'peak': nominal, 'unit': 'GB/s', 'frac': achieved / nominal,
+            'peak_kind': 'nominal NVLink 5 rate per direction', 'frac_of_peer_copy_rate': achieved / peer_copy,
             'traffic': None, 'adam_hbm_ms_at_peak': adam_hbm_ms, 'link_ms_per_collective_at_peak': link_ms,
             'target_ms': target_ms, 'frac_of_target': target_ms / ms_per_step,
-            'target_note': 'max(NVLink, HBM) time of the pull phase + max(NVLink, HBM) time of the update/push phase',
+            'target_note': 'max(NVLink at 900 GB/s, HBM) time of the pull phase + max(NVLink, HBM) time of the update/push phase',
         }
         if args.collective == 'p2p' and args.pool:
             result['gpu_launches'] = args.steps * (3 * n_chunks + 3)
@@ -431,6 +589,9 @@ def run_ours(args):
         e2e = run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, scale, sigma, total, timed,
                       grad_blocks, gather_blocks)
     result['e2e'] = e2e
+    if parity is not None:
+        result['parity_check'] = parity
+    engine.check_status()
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         result['cpu_baseline'] = cpu_baseline(args, chunk, scale, sigma, wd, steps=3, chunks=4)
@@ -490,11 +651,15 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
             conservative_ms = timed(plain, max(1, min(args.steps, args.e2e_steps))) / max(1, min(args.steps, args.e2e_steps))
             engine.enable_speculation()
             fn = lambda: engine.step_from_host(grads, outs, speculative=True)    # noqa: E731
-    elif args.collective in ('p2p', 'staged'):
+    elif args.collective == 'p2p':
+        # chunk by chunk: block k filled from the host while earlier chunks are pulled, shard k copied out behind
+        # its update while later chunks are updated and pushed
+        fn = lambda: engine.step_sharded_p2p(host_grads=grads, host_params=outs)    # noqa: E731
+    elif args.collective == 'staged':
         def fn():
             for k in range(n_chunks):
                 grad_blocks[k].copy_(grads[k], non_blocking=True)
-            (engine.step_sharded_p2p if args.collective == 'p2p' else engine.step_sharded_staged)()
+            engine.step_sharded_staged()
             for k in range(n_chunks):
                 outs[k].copy_(engine.shards[k][3], non_blocking=True)
     else:
@@ -511,9 +676,14 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
         'h2d_bytes_per_step': n_chunks * in_elems * 2 * world, 'd2h_bytes_per_step': n_chunks * shard * 2 * world,
         'conservative_ms_per_step': conservative_ms,
         'api': ('ChunkStepEngine.step_from_host' + ('' if conservative_ms is None else '(speculative=True)')) if world == 1 else
-               ('H2D into the gradient slab + ChunkStepEngine.step_sharded_p2p + D2H of the shards' if args.collective == 'p2p'
-                else 'ChunkStepEngine.step_sharded(host_grads=, host_params=)'),
-        'note': 'pinned fp16 gradients in, updated fp16 parameters out; fp32 master and moments stay in HBM',
+               ('ChunkStepEngine.step_sharded_p2p(host_grads=, host_params=)' if args.collective == 'p2p' else
+                'H2D into the gradient slab + ChunkStepEngine.step_sharded_staged + D2H of the shards'
+                if args.collective == 'staged' else 'ChunkStepEngine.step_sharded(host_grads=, host_params=)'),
+        'h2d_gbs_per_gpu': n_chunks * in_elems * 2 / (ms * 1e-3) / 1e9,
+        'note': ('pinned fp16 gradients in, updated fp16 parameters out; fp32 master and moments stay in HBM; the host '
+                 f'side is a pool of {pool} pinned buffers per direction reused over the chunks (every byte is still moved '
+                 'every step)' + ('' if world == 1 else '; every rank uploads its own full-size gradient block of every '
+                                  'chunk, so this leg is bound by PCIe and host memory, not by the step')),
     }
 
 
@@ -657,9 +827,17 @@ def main():
     ap.add_argument('--params', type=int, default=0, help='override the parameter count (smoke runs of a workload)')
     ap.add_argument('--pool', type=int, default=0,
                     help='N > 1: number of replicated blocks per slab (0 = one per chunk); chunk k uses block k %% pool')
+    ap.add_argument('--landing', choices=['none', 'copy'], default='none',
+                    help='N = 1: none = probe and update read the gradient blocks in place; copy = every block is first '
+                    'copied into its shard by the reduce epilogue (probe fused), one launch per chunk')
+    ap.add_argument('--ncu-traffic-bytes', type=float, default=0.0,
+                    help='dram__bytes_read.sum + dram__bytes_write.sum of one update launch of this command, from an ncu '
+                    'capture, to be reported as roofline.traffic')
     ap.add_argument('--land-streams', type=int, default=2,
                     help='N = 1: side streams the per-chunk landing launches alternate on')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-parity-check', action='store_true',
+                    help='N > 1: skip the small sharded case that is checked against the CPU oracle before the warm-up')
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-speculation', action='store_true',
                     help='N=1 end-to-end leg: only the step that updates nothing before the last gradient is probed')

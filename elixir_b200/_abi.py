@@ -6,7 +6,7 @@ these symbols.
 """
 import ctypes as C
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 TILE = 4096
 
 F16, BF16, F32 = 0, 1, 2
@@ -35,7 +35,7 @@ class ElxCtl(C.Structure):
         ('skipped_steps', C.c_uint32),
         ('status', C.c_uint32),
         ('late_inf', C.c_uint32),
-        ('ticket', C.c_uint32),
+        ('forced_skips', C.c_uint32),
         ('clip_coef', C.c_float),
         ('grad_norm', C.c_float),
         ('reserved', C.c_uint32 * 18),
@@ -90,6 +90,7 @@ class ElxChunkDesc(C.Structure):
         ('seg_count', C.c_int32),
         ('dtype', C.c_int32),
         ('reserved', C.c_int32),
+        ('grad_src', C.c_void_p),
     ]
 
 
@@ -109,7 +110,7 @@ assert C.sizeof(ElxCtl) == 128
 assert C.sizeof(ElxScalerCfg) == 32
 assert C.sizeof(ElxHyper) == 32
 assert C.sizeof(ElxSeg) == 24
-assert C.sizeof(ElxChunkDesc) == 72
+assert C.sizeof(ElxChunkDesc) == 80
 
 _p = C.c_void_p
 _i = C.c_int
@@ -124,7 +125,7 @@ PROTOTYPES = {
     'elx_set_tuning': (_i, [C.c_char_p, _i]),
     'elx_probe_scratch_elems': (_i64, [_i64]),
     'elx_ctl_init': (_i, [_p, _f, _p]),
-    'elx_step_begin': (_i, [_p, ElxScalerCfg, _p, _p]),
+    'elx_step_begin': (_i, [_p, ElxScalerCfg, _p, _p, _i, _p]),
     'elx_grad_check': (_i, [_p, _i, _i64, _p, _p, _p, _p, _i64, _p]),
     'elx_grad_check_static': (_i, [_p, _i, _i64, _p, _p, _p, _p]),
     'elx_grad_check_static_max_elems': (_i64, []),

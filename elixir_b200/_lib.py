@@ -7,7 +7,7 @@ from . import _abi
 
 _LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'libelixir_b200.so')
 _LIB = None
-# True only while a test has substituted a host-memory implementation of the ABI (see tests/conftest.py).
+# True only while a test has substituted a host-memory implementation of the ABI (tests/_dist_workers.py does).
 _HOST_MEMORY = False
 
 

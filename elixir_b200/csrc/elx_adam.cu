@@ -178,6 +178,7 @@ __global__ void __launch_bounds__(kTile / EPT, MINB) adam_kernel(const __grid_co
         const bool full = (e1 - e0 == kTile) && s_cur.vec_ok;
         float* const master = s_cur.d.master;
         void* const lowp = s_cur.d.grad_param;
+        const void* const gsrc = grad_source(s_cur.d);
 
         // segment that contains e0 (CTA-uniform; refreshed by one thread when e0 leaves the cached one)
         const ElxSeg* csegs = segs + s_cur.d.seg_first;
@@ -206,7 +207,7 @@ __global__ void __launch_bounds__(kTile / EPT, MINB) adam_kernel(const __grid_co
         if (full && one_group) {
             const GroupK k = s_group[grp];
             float g[EPT], p[EPT], m[EPT], v[EPT];
-            load_lowp<DT, EPT>(lowp, e0, g);
+            load_lowp<DT, EPT>(gsrc, e0, g);
             load_f32<EPT>(master, e0, p);
             load_f32<EPT>(exp_avg, e0, m);
             load_f32<EPT>(exp_avg_sq, e0, v);
@@ -219,9 +220,15 @@ __global__ void __launch_bounds__(kTile / EPT, MINB) adam_kernel(const __grid_co
             store_f32<EPT>(exp_avg, e0, m);
             store_f32<EPT>(exp_avg_sq, e0, v);
             store_lowp<DT, EPT>(lowp, e0, p);
+        } else if (full && e0 >= s_cur.d.n_valid) {
+            // padding past valid_end: no segment reaches it, only the working copy is refreshed
+            float p[EPT];
+            load_f32<EPT>(master, e0, p);
+            store_lowp<DT, EPT>(lowp, e0, p);
         } else {
             // ragged tile: shard tail, segment boundary, uncovered elements or unaligned pointers
             typename Lp<DT>::T* gp = static_cast<typename Lp<DT>::T*>(lowp);
+            const typename Lp<DT>::T* gin = static_cast<const typename Lp<DT>::T*>(gsrc);
             for (int64_t e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
                 float p = master[e];
                 const int si = find_seg(csegs, n_segs, e);
@@ -229,7 +236,7 @@ __global__ void __launch_bounds__(kTile / EPT, MINB) adam_kernel(const __grid_co
                     const int ge = csegs[si].group;
                     if (ge >= 0 && ge < a.n_groups) {
                         const GroupK k = s_group[ge];
-                        float g = Lp<DT>::to_float(gp[e]);
+                        float g = Lp<DT>::to_float(gin[e]);
                         float m = exp_avg[e], v = exp_avg_sq[e];
                         nan_acc = fmaf(0.0f, g, nan_acc);
                         adam_elem<MATH>(p, m, v, g, k, div_mode, div, inv_div);
@@ -279,7 +286,9 @@ __global__ void __launch_bounds__(kTile / EPT, MINB) adam_kernel(const __grid_co
 constexpr int kTmaStages = 3;
 constexpr int kTmaThreads = 512;
 
-enum { kTileNone = 0, kTileBulk = 1, kTileRagged = 2, kTileBad = 3 };
+// kTileRefresh: a whole tile that no segment covers (the padding past valid_end, a gap between segments):
+// only its master goes through the pipeline and only the working copy comes back (6 bytes per element)
+enum { kTileNone = 0, kTileBulk = 1, kTileRagged = 2, kTileBad = 3, kTileRefresh = 4 };
 
 // What the producer thread decided about one tile, published to the CTA through shared memory.
 struct TileSlot {
@@ -290,6 +299,7 @@ struct TileSlot {
     float* out_exp_avg;
     float* out_exp_avg_sq;
     void* lowp;
+    const void* gsrc;       // where the gradient is read: the low-precision shard itself or a separate source
     const ElxSeg* segs;
     int64_t e0, e1;
     int64_t push_elem;   // element offset of this tile inside every rank's gather slab (push all-gather)
@@ -336,7 +346,8 @@ __device__ __forceinline__ void classify_tile(const AdamArgs& a, const ElxChunkD
         pc.t0 = pc.d.tile_begin;
         pc.t1 = pc.t0 + tiles_of(pc.d.n_shard);
         uintptr_t bits = reinterpret_cast<uintptr_t>(pc.d.master) | reinterpret_cast<uintptr_t>(pc.d.exp_avg) |
-                         reinterpret_cast<uintptr_t>(pc.d.exp_avg_sq) | reinterpret_cast<uintptr_t>(pc.d.grad_param);
+                         reinterpret_cast<uintptr_t>(pc.d.exp_avg_sq) | reinterpret_cast<uintptr_t>(pc.d.grad_param) |
+                         reinterpret_cast<uintptr_t>(pc.d.grad_src);
         pc.out_master = pc.d.master;
         pc.out_exp_avg = pc.d.exp_avg;
         pc.out_exp_avg_sq = pc.d.exp_avg_sq;
@@ -381,6 +392,7 @@ __device__ __forceinline__ void classify_tile(const AdamArgs& a, const ElxChunkD
     out.out_exp_avg = pc.out_exp_avg;
     out.out_exp_avg_sq = pc.out_exp_avg_sq;
     out.lowp = pc.d.grad_param;
+    out.gsrc = grad_source(pc.d);
     out.segs = csegs;
     out.n_segs = pc.d.seg_count;
     out.e0 = e0;
@@ -388,7 +400,10 @@ __device__ __forceinline__ void classify_tile(const AdamArgs& a, const ElxChunkD
     out.group = pc.seg_group;
     out.push_elem = a.push.world > 0 ? push_base_elem(a, pc.index, pc.d.n_shard) + e0 : 0;
     const bool push_ok = a.push.world == 0 || (out.push_elem & 15) == 0;   // bulk copies need 16-byte alignment
-    out.kind = (e1 - e0 == kTile && pc.vec_ok && one_group && push_ok) ? kTileBulk : kTileRagged;
+    const bool whole = e1 - e0 == kTile && pc.vec_ok && push_ok;
+    if (whole && one_group) out.kind = kTileBulk;
+    else if (whole && range_uncovered(csegs, pc.d.seg_count, e0, e1, pc.d.n_valid)) out.kind = kTileRefresh;
+    else out.kind = kTileRagged;
 }
 
 template <int DT, int MATH>
@@ -442,11 +457,15 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         if (slot.kind == kTileBulk) {
             unsigned char* base = s_dyn + static_cast<size_t>(s) * Stage::kBytes;
             mbar_arrive_expect_tx(&s_full[s], Stage::kBytes);
-            bulk_g2s(base, static_cast<const char*>(slot.lowp) + slot.e0 * Lp<DT>::kBytes, Stage::kLowpBytes, &s_full[s]);
+            bulk_g2s(base, static_cast<const char*>(slot.gsrc) + slot.e0 * Lp<DT>::kBytes, Stage::kLowpBytes, &s_full[s]);
             bulk_g2s(base + Stage::kLowpBytes, slot.master + slot.e0, Stage::kF32Bytes, &s_full[s]);
             bulk_g2s(base + Stage::kLowpBytes + Stage::kF32Bytes, slot.exp_avg + slot.e0, Stage::kF32Bytes, &s_full[s]);
             bulk_g2s(base + Stage::kLowpBytes + 2 * Stage::kF32Bytes, slot.exp_avg_sq + slot.e0, Stage::kF32Bytes,
                      &s_full[s]);
+        } else if (slot.kind == kTileRefresh) {
+            unsigned char* base = s_dyn + static_cast<size_t>(s) * Stage::kBytes;
+            mbar_arrive_expect_tx(&s_full[s], Stage::kF32Bytes);
+            bulk_g2s(base + Stage::kLowpBytes, slot.master + slot.e0, Stage::kF32Bytes, &s_full[s]);
         } else {
             mbar_arrive(&s_full[s]);   // nothing to load: the phase completes at once and publishes the slot
         }
@@ -506,8 +525,25 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                 }
             }
             fence_async_smem();   // the bulk stores below read what the threads just wrote
+        } else if (slot.kind == kTileRefresh) {
+            const float* sp = reinterpret_cast<const float*>(base + Stage::kLowpBytes);
+#pragma unroll
+            for (int h = 0; h < kTile / (kTmaThreads * 4); ++h) {
+                const int e = h * (kTmaThreads * 4) + threadIdx.x * 4;
+                const float4 p = *reinterpret_cast<const float4*>(sp + e);
+                if constexpr (DT == ELX_F32) {
+                    *reinterpret_cast<float4*>(base + static_cast<size_t>(e) * 4) = p;
+                } else {
+                    uint2 out;
+                    out.x = Lp<DT>::pack2(p.x, p.y);
+                    out.y = Lp<DT>::pack2(p.z, p.w);
+                    *reinterpret_cast<uint2*>(base + static_cast<size_t>(e) * 2) = out;
+                }
+            }
+            fence_async_smem();
         } else if (slot.kind == kTileRagged) {
             typename Lp<DT>::T* gp = static_cast<typename Lp<DT>::T*>(slot.lowp);
+            const typename Lp<DT>::T* gin = static_cast<const typename Lp<DT>::T*>(slot.gsrc);
             for (int64_t e = slot.e0 + threadIdx.x; e < slot.e1; e += blockDim.x) {
                 float p = slot.master[e];
                 const int si = find_seg(slot.segs, slot.n_segs, e);
@@ -515,7 +551,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                     const int ge = slot.segs[si].group;
                     if (ge >= 0 && ge < a.n_groups) {
                         const GroupK k_ = s_group[ge];
-                        float g = Lp<DT>::to_float(gp[e]);
+                        float g = Lp<DT>::to_float(gin[e]);
                         float m = slot.exp_avg[e], v = slot.exp_avg_sq[e];
                         nan_acc = fmaf(0.0f, g, nan_acc);
                         adam_elem<MATH>(p, m, v, g, k_, div_mode, div, inv_div);
@@ -535,12 +571,14 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         __syncthreads();   // the stage is fully written (bulk) / fully consumed
 
         if (threadIdx.x == 0) {
-            if (slot.kind == kTileBulk) {
+            if (slot.kind == kTileBulk || slot.kind == kTileRefresh) {
                 bulk_s2g(static_cast<char*>(slot.lowp) + slot.e0 * Lp<DT>::kBytes, base, Stage::kLowpBytes);
-                bulk_s2g(slot.out_master + slot.e0, base + Stage::kLowpBytes, Stage::kF32Bytes);
-                bulk_s2g(slot.out_exp_avg + slot.e0, base + Stage::kLowpBytes + Stage::kF32Bytes, Stage::kF32Bytes);
-                bulk_s2g(slot.out_exp_avg_sq + slot.e0, base + Stage::kLowpBytes + 2 * Stage::kF32Bytes,
-                         Stage::kF32Bytes);
+                if (slot.kind == kTileBulk) {
+                    bulk_s2g(slot.out_master + slot.e0, base + Stage::kLowpBytes, Stage::kF32Bytes);
+                    bulk_s2g(slot.out_exp_avg + slot.e0, base + Stage::kLowpBytes + Stage::kF32Bytes, Stage::kF32Bytes);
+                    bulk_s2g(slot.out_exp_avg_sq + slot.e0, base + Stage::kLowpBytes + 2 * Stage::kF32Bytes,
+                             Stage::kF32Bytes);
+                }
                 // push all-gather: the same 8 KB of refreshed parameters to every rank's gather block,
                 // plain (non-multicast) bulk stores, W - 1 of them crossing NVLink
                 // (start with a different rank in every CTA, so that the stores spread over all links at once)

@@ -307,7 +307,7 @@ __device__ __forceinline__ void store_f32(float* base, int64_t e0, const float (
 struct ChunkCursor {
     int64_t t0, t1;   // tile range of the cached descriptor
     int index;
-    int vec_ok;       // all four pointers are 32-byte aligned
+    int vec_ok;       // every pointer of the descriptor is 32-byte aligned
     ElxChunkDesc d;
 };
 
@@ -342,7 +342,7 @@ __device__ __forceinline__ bool locate_chunk(const ElxChunkDesc* __restrict__ de
             cur.t1 = t1;
             const uintptr_t bits = reinterpret_cast<uintptr_t>(d.master) | reinterpret_cast<uintptr_t>(d.exp_avg) |
                                    reinterpret_cast<uintptr_t>(d.exp_avg_sq) |
-                                   reinterpret_cast<uintptr_t>(d.grad_param);
+                                   reinterpret_cast<uintptr_t>(d.grad_param) | reinterpret_cast<uintptr_t>(d.grad_src);
             cur.vec_ok = (bits & 31u) == 0;
         }
     }
@@ -357,6 +357,9 @@ struct SegCursor {
     int chunk;      // descriptor index the cache belongs to
 };
 
+// Where the kernels read the gradient of a shard: a separate source, or the low-precision shard itself.
+__device__ __forceinline__ const void* grad_source(const ElxChunkDesc& d) { return d.grad_src ? d.grad_src : d.grad_param; }
+
 // Index (relative to the chunk's first segment) of the last segment with begin <= e, or -1.
 __device__ __forceinline__ int find_seg(const ElxSeg* __restrict__ segs, int n, int64_t e) {
     int lo = 0, hi = n;   // first segment with begin > e
@@ -365,6 +368,14 @@ __device__ __forceinline__ int find_seg(const ElxSeg* __restrict__ segs, int n, 
         if (segs[mid].begin <= e) lo = mid + 1; else hi = mid;
     }
     return lo - 1;
+}
+
+// No segment of the chunk intersects [e0, e1): nothing to update there, only the working copy to refresh.
+__device__ __forceinline__ bool range_uncovered(const ElxSeg* __restrict__ segs, int n, int64_t e0, int64_t e1,
+                                                int64_t n_valid) {
+    if (e0 >= n_valid) return true;   // segments lie inside [0, n_valid)
+    const int si = find_seg(segs, n, e1 - 1);
+    return si < 0 || segs[si].end <= e0;
 }
 
 

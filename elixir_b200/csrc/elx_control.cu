@@ -78,11 +78,22 @@ __device__ __forceinline__ bool is_pow2_float(float x) {
     return (u >> 31) == 0 && (u & 0x7FFFFFu) == 0 && ex >= 2 && ex <= 252;
 }
 
-__global__ void step_begin_kernel(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+__global__ void step_begin_kernel(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq, uint32_t* chunk_flags,
+                                  int n_chunk_flags) {
+    // the per-chunk overflow words have been consumed through found_inf: clear them (all threads)
+    for (int i = threadIdx.x; i < n_chunk_flags; i += blockDim.x) chunk_flags[i] = 0;
+    if (threadIdx.x != 0) return;
     const bool found = ctl->found_inf != 0;
     float scale = ctl->scale;
-    if (found) {
+    if (ctl->status & ELX_STAT_TIMEOUT) {
+        // a wait gave up earlier (a peer never arrived, a copy never completed): the gradients may be
+        // incomplete, so nothing is updated; the scaler is left alone because no overflow was observed
+        ctl->skip = 1;
+        ctl->skipped_steps += 1;
+        ctl->forced_skips += 1;
+        ctl->div_scale = -1.0f;
+        ctl->inv_div = 0.0f;
+    } else if (found) {
         ctl->skip = 1;
         ctl->skipped_steps += 1;
         ctl->div_scale = -1.0f;
@@ -195,16 +206,20 @@ int elx_ctl_init(ElxCtl* ctl, float initial_scale, void* stream) {
     return record_cuda(cudaGetLastError());
 }
 
-int elx_step_begin(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq, void* stream) {
+int elx_step_begin(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq, uint32_t* chunk_flags, int n_chunk_flags,
+                   void* stream) {
     if (!ctl) return ELX_ERR_NULL;
-    if (!aligned(ctl, 16) || (norm_sq && !aligned(norm_sq, 4))) return ELX_ERR_ALIGN;
+    if (!aligned(ctl, 16) || (norm_sq && !aligned(norm_sq, 4)) || (chunk_flags && !aligned(chunk_flags, 4)))
+        return ELX_ERR_ALIGN;
+    if (n_chunk_flags < 0) return ELX_ERR_SIZE;
+    if (!chunk_flags) n_chunk_flags = 0;
     if (cfg.dynamic) {
         if (!(cfg.growth_factor > 0.0f) || !(cfg.backoff_factor > 0.0f) || cfg.growth_interval <= 0 ||
             cfg.hysteresis < 0)
             return ELX_ERR_ARG;
     }
     if (cfg.max_norm > 0.0f && !norm_sq) return ELX_ERR_NULL;
-    step_begin_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ctl, cfg, norm_sq);
+    step_begin_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(ctl, cfg, norm_sq, chunk_flags, n_chunk_flags);
     return record_cuda(cudaGetLastError());
 }
 

@@ -14,7 +14,8 @@ namespace {
 // (peer-mapped memory).  Rank r produces its shard of a chunk by READING the r-th slice of that
 // chunk's block from every rank with ordinary loads (its own slice from local HBM, W - 1 slices over
 // NVLink), summing float(x) * (1/W) in rank order in fp32, rounding once to the chunk dtype, storing
-// the shard and probing the rounded result for inf/nan in the same pass.  No TMA, no multicast.
+// the shard and probing the rounded result for inf/nan in the same pass.  Two variants: per-lane 256-bit
+// peer loads, and bulk copies (cp.async.bulk, never multicast) of whole slices into shared memory.
 
 struct PullArgs {
     const ElxChunkDesc* descs;
@@ -381,6 +382,8 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // One warp.  Lane j tells rank j "rank `rank` reached barrier `epoch`" (with this rank's overflow word
 // riding along), then waits — for at most timeout_ns — until rank j has told this rank the same.
 // On expiry the sticky ELX_STAT_TIMEOUT bit is raised and the kernel returns; it never traps.
+// The word that rides along carries the overflow in bit 0 and "a wait of mine expired" in bit 1, so that a
+// rank that gave up anywhere makes every rank skip the step (elx_step_begin skips while the bit is set).
 __global__ void peer_barrier_kernel(ElxPeerTable flags, uint32_t epoch, ElxCtl* ctl, int exchange_overflow,
                                     uint64_t timeout_ns) {
     const int j = threadIdx.x;
@@ -388,7 +391,9 @@ __global__ void peer_barrier_kernel(ElxPeerTable flags, uint32_t epoch, ElxCtl* 
     uint32_t seen_inf = 0;
     bool expired = false;
     if (j < world) {
-        const uint32_t mine = (exchange_overflow && ctl) ? ctl->found_inf : 0u;
+        const uint32_t mine = (exchange_overflow && ctl)
+                                  ? ((ctl->found_inf ? 1u : 0u) | ((ctl->status & ELX_STAT_TIMEOUT) ? 2u : 0u))
+                                  : 0u;
         __threadfence_system();   // everything this rank wrote before the barrier is visible to the peers first
         uint32_t* out = flag_slot(flags.base[j], epoch, rank);
         asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(out + 1), "r"(mine) : "memory");
@@ -407,8 +412,8 @@ __global__ void peer_barrier_kernel(ElxPeerTable flags, uint32_t epoch, ElxCtl* 
         }
         if (!expired) asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(seen_inf) : "l"(in + 1) : "memory");
     }
-    const unsigned any_inf = __ballot_sync(0xFFFFFFFFu, seen_inf != 0);
-    const unsigned any_expired = __ballot_sync(0xFFFFFFFFu, expired);
+    const unsigned any_inf = __ballot_sync(0xFFFFFFFFu, (seen_inf & 1u) != 0);
+    const unsigned any_expired = __ballot_sync(0xFFFFFFFFu, expired || (seen_inf & 2u) != 0);
     if (j == 0 && ctl) {
         if (exchange_overflow && any_inf) atomicOr(&ctl->found_inf, 1u);
         if (any_expired) atomicOr(&ctl->status, ELX_STAT_TIMEOUT);

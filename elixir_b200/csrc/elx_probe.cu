@@ -1,5 +1,7 @@
 // Part of the elixir_b200 CUDA library (C ABI: include/elixir_b200.h).  See elx_common.cuh for the
 // overview of the kernels and of how the sources are divided.
+#include <atomic>
+
 #include "elx_common.cuh"
 
 using namespace elx;
@@ -62,7 +64,7 @@ __global__ void __launch_bounds__(kProbeThreads) probe_kernel(const __grid_const
                 continue;
             }
             chunk_of[j] = s_cur.index;
-            struct { const void* grad_param; int64_t n_shard, n_valid; } d = {s_cur.d.grad_param, s_cur.d.n_shard,
+            struct { const void* grad_param; int64_t n_shard, n_valid; } d = {grad_source(s_cur.d), s_cur.d.n_shard,
                                                                               s_cur.d.n_valid};
             const int64_t e0 = (t - s_cur.t0) * kTile;
             const bool dst_ok = !COPY || (reinterpret_cast<uintptr_t>(a.copy_dst) & 31u) == 0;
@@ -295,8 +297,9 @@ static __device__ __align__(256) float g_static_scratch[kStaticScratchTiles];
 
 // Device address of g_static_scratch per device ordinal.  In host code the array's name is only a
 // handle for the runtime, not something a kernel may dereference; the address comes from
-// cudaGetSymbolAddress, asked once per device with that device current.
-float* g_static_scratch_addr[64];
+// cudaGetSymbolAddress, asked once per device with that device current.  Atomic: several host threads
+// may make the first call on a device at once (they all store the same value).
+std::atomic<float*> g_static_scratch_addr[64];
 
 int static_scratch(float** out) {
     int dev = -1;
@@ -306,7 +309,8 @@ int static_scratch(float** out) {
         (void)cudaGetLastError();
         return ELX_ERR_NODEVICE;
     }
-    if (g_static_scratch_addr[dev] == nullptr) {
+    float* cached = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+    if (cached == nullptr) {
         void* addr = nullptr;
         e = cudaGetSymbolAddress(&addr, g_static_scratch);
         if (e != cudaSuccess || addr == nullptr) {
@@ -314,9 +318,10 @@ int static_scratch(float** out) {
             (void)cudaGetLastError();
             return e == cudaSuccess ? ELX_ERR_NODEVICE : ELX_ERR_LAUNCH;
         }
-        g_static_scratch_addr[dev] = static_cast<float*>(addr);
+        cached = static_cast<float*>(addr);
+        g_static_scratch_addr[dev].store(cached, std::memory_order_release);
     }
-    *out = g_static_scratch_addr[dev];
+    *out = cached;
     return ELX_OK;
 }
 
@@ -335,9 +340,10 @@ int64_t elx_grad_check_static_max_elems(void) { return kStaticScratchTiles * kTi
 
 int elx_grad_check_static(const void* g, int dtype, int64_t n_valid, uint32_t* flag, ElxCtl* ctl, float* l2sq,
                           void* stream) {
-    if (n_valid > kStaticScratchTiles * kTile) return ELX_ERR_CAPACITY;
     float* scratch = nullptr;
     if (l2sq) {
+        // only the sum of squares uses the built-in array; the plain probe needs no scratch at any size
+        if (g && dtype_ok(dtype) && n_valid > kStaticScratchTiles * kTile) return ELX_ERR_CAPACITY;
         const int rc = static_scratch(&scratch);
         if (rc != ELX_OK) return rc;
     }

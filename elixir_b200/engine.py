@@ -6,11 +6,10 @@ shards are registered once in device tables, and a step is
 
     [gradients arrive]   land() / probe()   copy into the shard + inf/nan probe, per chunk
     begin_step()         overflow agreement across ranks (4-byte MAX all-reduce), the optional global
-                         norm, then ``elx_step_begin``: skip decision, divisor, scaler update — on the
-                         device, no host read
+                         norm, then ``elx_step_begin``: skip decision, divisor, scaler update, per-chunk
+                         overflow words cleared — on the device, no host read
     update()             ``elx_adam_multi``: unscale + Adam/AdamW + low-precision copy-back (or the
                          copy-back alone on a skipped step)
-    end_step()           clear the per-chunk overflow words
 
 For sharded runs ``step_sharded`` pipelines reduce-scatter -> probe per chunk on a reduce stream and
 update -> all-gather per chunk on a gather stream; ``step_from_host`` does the same with host buffers
@@ -48,6 +47,7 @@ class ChunkStepEngine:
         self.scaler.attach(self.ctl)
         self.table = kernels.ChunkTable(self.device, dtype)
         self.shards: List[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, int]] = []
+        self.grad_srcs: List[Optional[torch.Tensor]] = []    # per shard: separate gradient source, or None
         self.chunk_flags: Optional[torch.Tensor] = None
         self.chunk_l2sq: Optional[torch.Tensor] = None
         self.total_l2sq: Optional[torch.Tensor] = None
@@ -64,10 +64,14 @@ class ChunkStepEngine:
                   n_valid: int,
                   segments: Sequence[Tuple[int, int, int]],
                   exp_avg: Optional[torch.Tensor] = None,
-                  exp_avg_sq: Optional[torch.Tensor] = None) -> int:
+                  exp_avg_sq: Optional[torch.Tensor] = None,
+                  grad_src: Optional[torch.Tensor] = None) -> int:
         """Register a shard: fp32 master, the paired low-precision shard (gradient in / parameter out),
         ``valid_end`` and the (begin, end, param-group) ranges the optimizer updates.  The two moments
-        are allocated here, flat and congruent with the master, unless given.  The four arrays may also be
+        are allocated here, flat and congruent with the master, unless given.  With ``grad_src`` the probe
+        and the update read the gradient from that tensor (the block the backward pass filled) instead of
+        from ``lowp``, so that nothing has to be copied into the shard before the step (``probe`` instead of
+        ``land``); ``lowp`` still receives the refreshed working copy.  The four arrays may also be
         pinned host tensors (a shard kept off the GPU): ``land``/``probe``/``step`` then reach them over PCIe
         with the same kernels; the collective pipelines (``step_sharded*``) need device-resident shards."""
         def zeros():    # where the master lives, page-locked if it is
@@ -76,8 +80,9 @@ class ChunkStepEngine:
 
         exp_avg = zeros() if exp_avg is None else exp_avg
         exp_avg_sq = zeros() if exp_avg_sq is None else exp_avg_sq
-        index = self.table.add_chunk(master, exp_avg, exp_avg_sq, lowp, n_valid, segments)
+        index = self.table.add_chunk(master, exp_avg, exp_avg_sq, lowp, n_valid, segments, grad_src=grad_src)
         self.shards.append((master, exp_avg, exp_avg_sq, lowp, n_valid))
+        self.grad_srcs.append(grad_src)
         return index
 
     def finalize(self):
@@ -105,6 +110,9 @@ class ChunkStepEngine:
     def land(self, index: int, src: torch.Tensor):
         """Copy reduced gradients ``src`` into shard ``index`` and probe them in the same pass."""
         lowp, n_valid = self.shards[index][3], self.shards[index][4]
+        if self.grad_srcs[index] is not None:
+            raise RuntimeError(f'shard {index} reads its gradient from a separate source: fill that tensor and call '
+                               'probe() instead of land()')
         kernels.reduce_epilogue(src, lowp, n_valid=n_valid, flag=self.chunk_flags[index:index + 1], ctl=self.ctl)
 
     def land_all(self, srcs: Sequence[torch.Tensor], streams: int = 2):
@@ -127,13 +135,19 @@ class ChunkStepEngine:
         for st in self._land_streams:
             main.wait_stream(st)
 
+    def _grad_home(self, index: int) -> torch.Tensor:
+        """Where the kernels read shard ``index``'s gradient: its separate source, or the shard itself."""
+        src = self.grad_srcs[index]
+        return src if src is not None else self.shards[index][3]
+
     def probe(self, first: int = 0, count: Optional[int] = None):
-        """Probe gradients that were written straight into the shards."""
+        """Probe, in one launch, gradients that sit where the update will read them: in the shards, or in the
+        separate sources given to ``add_shard``."""
         kernels.grad_check_multi(self.table, self.ctl, chunk_flags=self.chunk_flags, first=first, count=count)
 
     def probe_one(self, index: int):
-        lowp, n_valid = self.shards[index][3], self.shards[index][4]
-        kernels.grad_check(lowp, n_valid=n_valid, flag=self.chunk_flags[index:index + 1], ctl=self.ctl)
+        kernels.grad_check(self._grad_home(index), n_valid=self.shards[index][4],
+                           flag=self.chunk_flags[index:index + 1], ctl=self.ctl)
 
     # ------------------------------------------------------------------ the step
 
@@ -147,7 +161,7 @@ class ChunkStepEngine:
             if self.world > 1:
                 dist.all_reduce(self.total_l2sq, group=self.group)
             norm_sq = self.total_l2sq
-        kernels.step_begin(self.ctl, self.scaler.cfg, norm_sq)
+        kernels.step_begin(self.ctl, self.scaler.cfg, norm_sq, self.chunk_flags)
 
     def update(self, first: int = 0, count: Optional[int] = None):
         """The fused update of shards [first, first + count).  After ``enable_streaming`` the update of the whole
@@ -158,7 +172,9 @@ class ChunkStepEngine:
             kernels.adam_multi(self.table, self.ctl, first=first, count=count)
 
     def end_step(self):
-        self.chunk_flags.zero_()
+        """Nothing left to do: ``elx_step_begin`` clears the per-chunk overflow words together with
+        ``found_inf``, where the reference clears ``Chunk.overflow`` (``optimizer.py:144-147``).  Kept so that
+        call sites written against the begin / update / end sequence stay valid."""
 
     def step(self):
         """Decision + fused update of every shard.  Gradients must already sit (probed) in the shards."""
@@ -337,7 +353,8 @@ class ChunkStepEngine:
     def gather_block(self, k: int) -> torch.Tensor:
         return self.gather_slab.local[self._p2p_offsets[k]:self._p2p_offsets[k] + self._p2p_sizes[k]]
 
-    def step_sharded_p2p(self):
+    def step_sharded_p2p(self, host_grads: Optional[Sequence[torch.Tensor]] = None,
+                         host_params: Optional[Sequence[torch.Tensor]] = None):
         """Sharded step with both collectives fused into the kernels, over peer-mapped memory:
 
             barrier            every rank's gradient blocks are written
@@ -351,9 +368,40 @@ class ChunkStepEngine:
 
         With pooled blocks (``enable_p2p(pool=P)``) the two fused kernels are launched chunk by chunk, with a
         barrier before each pull (chunk k's gradients are in block ``k % P`` on every rank) — the order in which
-        a backward pass produces them; the decision still waits for the last chunk."""
+        a backward pass produces them; the decision still waits for the last chunk.
+
+        With ``host_grads`` (pinned, chunk_size elements each: this rank's gradients of chunk k) the step also runs
+        chunk by chunk: block k is filled from the host on a copy stream while earlier chunks are being pulled.
+        With ``host_params`` (pinned, shard_size each) the refreshed shard k leaves for the host on a second copy
+        stream behind its update, while later chunks are updated and pushed."""
         pooled = getattr(self, '_p2p_pool', 0)
-        if pooled:
+        main = torch.cuda.current_stream(self.device)
+        if host_grads is not None or host_params is not None:
+            h2d, d2h = self._side_streams()
+            h2d.wait_stream(main)
+            d2h.wait_stream(main)
+        if host_grads is not None:
+            assert len(host_grads) == self.n_chunks
+            # Block k % P is refilled for chunk k while OTHER ranks may still be reading its previous tenant, chunk
+            # k - P.  A rank launches the barrier that precedes pull(k - P + 1) only behind its own pull(k - P), so
+            # once that barrier has completed here every rank is done with chunk k - P: the refill waits for it.
+            passed = [None] * (self.n_chunks + 1)    # passed[k]: the barrier before pull(k) has completed on this rank
+            for k in range(self.n_chunks):
+                refill = pooled and k >= pooled
+                if refill and passed[k - pooled + 1] is None:    # pool of one block: no later barrier exists yet
+                    self.peer_barrier(self.ctl)
+                    passed[k - pooled + 1] = main.record_event()
+                with torch.cuda.stream(h2d):
+                    if refill:
+                        h2d.wait_event(passed[k - pooled + 1])
+                    self.grad_block(k).copy_(host_grads[k], non_blocking=True)
+                    arrived = h2d.record_event()
+                main.wait_event(arrived)
+                self.peer_barrier(self.ctl)
+                passed[k] = passed[k] or main.record_event()
+                kernels.pull_reduce_multi(self.table, self.grad_slab.table, self.block_off, self.ctl,
+                                          chunk_flags=self.chunk_flags, first=k, count=1)
+        elif pooled:
             for k in range(self.n_chunks):
                 self.peer_barrier(self.ctl)
                 kernels.pull_reduce_multi(self.table, self.grad_slab.table, self.block_off, self.ctl,
@@ -369,13 +417,19 @@ class ChunkStepEngine:
                                      scratch=self._scratch)
             dist.all_reduce(self.total_l2sq, group=self.group)
             norm_sq = self.total_l2sq
-        kernels.step_begin(self.ctl, self.scaler.cfg, norm_sq)
-        if pooled:
+        kernels.step_begin(self.ctl, self.scaler.cfg, norm_sq, self.chunk_flags)
+        if pooled or host_params is not None:
             for k in range(self.n_chunks):
                 kernels.adam_multi_push(self.table, self.ctl, self.gather_slab.table, self.block_off, first=k, count=1)
+                if host_params is not None:
+                    updated = main.record_event()
+                    with torch.cuda.stream(d2h):
+                        d2h.wait_event(updated)
+                        host_params[k].copy_(self.shards[k][3], non_blocking=True)
         else:
             kernels.adam_multi_push(self.table, self.ctl, self.gather_slab.table, self.block_off)
-        self.end_step()
+        if host_params is not None:
+            main.wait_stream(d2h)
         self.peer_barrier(self.ctl)
 
     def enable_staging(self, pool: int = 4):
@@ -453,7 +507,7 @@ class ChunkStepEngine:
                                      scratch=self._scratch)
             dist.all_reduce(self.total_l2sq, group=self.group)
             norm_sq = self.total_l2sq
-        kernels.step_begin(self.ctl, self.scaler.cfg, norm_sq)
+        kernels.step_begin(self.ctl, self.scaler.cfg, norm_sq, self.chunk_flags)
         for k in range(self.n_chunks):
             self.update(first=k, count=1)
             updated = torch.cuda.Event()
@@ -490,9 +544,8 @@ class ChunkStepEngine:
         h2d, d2h = self._side_streams()
         h2d.wait_stream(main)
         for k, src in enumerate(host_grads):
-            lowp = self.shards[k][3]
             with torch.cuda.stream(h2d):
-                lowp.copy_(src, non_blocking=True)
+                self._grad_home(k).copy_(src, non_blocking=True)
                 arrived = torch.cuda.Event()
                 arrived.record(h2d)
             main.wait_event(arrived)
@@ -522,7 +575,7 @@ class ChunkStepEngine:
         other_shards = []
         for k, (master, exp_avg, exp_avg_sq, lowp, n_valid) in enumerate(self.shards):
             twin = (master.clone(), exp_avg.clone(), exp_avg_sq.clone())
-            other.add_chunk(twin[0], twin[1], twin[2], lowp, n_valid, self.table._segs_of(k))
+            other.add_chunk(twin[0], twin[1], twin[2], lowp, n_valid, self.table._segs_of(k), grad_src=self.grad_srcs[k])
             other_shards.append((twin[0], twin[1], twin[2], lowp, n_valid))
         other.finalize()
         self._twin = (other, other_shards)
@@ -545,13 +598,15 @@ class ChunkStepEngine:
         main = torch.cuda.current_stream(self.device)
         h2d, d2h = self._side_streams()
         self._ctl_backup.copy_(self.ctl.tensor)
-        kernels.step_begin(self.ctl, self.scaler.cfg, None)    # no overflow known: "apply", divisor, step count
+        # no overflow known: "apply", divisor, step count (an overflow that was already pending on entry, from
+        # a probe with no step after it, is decided here for real: skip, back-off)
+        kernels.step_begin(self.ctl, self.scaler.cfg, None, self.chunk_flags)
         h2d.wait_stream(main)
         d2h.wait_stream(main)
         for k, src in enumerate(host_grads):
             lowp = self.shards[k][3]
             with torch.cuda.stream(h2d):
-                lowp.copy_(src, non_blocking=True)
+                self._grad_home(k).copy_(src, non_blocking=True)
                 arrived = h2d.record_event()
             main.wait_event(arrived)
             self.probe_one(k)
@@ -561,15 +616,20 @@ class ChunkStepEngine:
                 d2h.wait_event(done)
                 host_params[k].copy_(lowp, non_blocking=True)
         main.wait_stream(d2h)
-        overflow = bool(self.ctl.found_inf.item())    # the step's result, read by the host (synchronises)
-        if not overflow:
+        result = self.ctl.read()    # the step's result, read by the host (synchronises)
+        if result.skip:
+            # the overflow was known before the first update: the launches above only refreshed the working
+            # copies and wrote nothing to the second set.  Gradients probed meanwhile belong to this step too.
+            self.ctl.found_inf.zero_()
+            self.chunk_flags.zero_()
+            return False
+        if not result.found_inf:
             self._swap_sets()
-            self.end_step()
             return True
         # late overflow: nothing of the speculative update is adopted
         self.ctl.tensor.copy_(self._ctl_backup)
         self.ctl.found_inf.fill_(1)
-        kernels.step_begin(self.ctl, self.scaler.cfg, None)    # skip, back-off
+        kernels.step_begin(self.ctl, self.scaler.cfg, None, self.chunk_flags)    # skip, back-off
         for k, dst in enumerate(host_params):
             self.update(first=k, count=1)    # skipped step: the working copy is refreshed from the old master
             done = main.record_event()
@@ -604,7 +664,8 @@ class ChunkStepEngine:
                 self._stage_table.add_chunk(slot[0][:n], slot[1][:n], slot[2][:n], slot[3][:n], n_valid,
                                             self.table._segs_of(k))
             else:    # a device-resident shard is updated where it is
-                self._stage_table.add_chunk(master, exp_avg, exp_avg_sq, lowp, n_valid, self.table._segs_of(k))
+                self._stage_table.add_chunk(master, exp_avg, exp_avg_sq, lowp, n_valid, self.table._segs_of(k),
+                                            grad_src=self.grad_srcs[k])
         self._stage_table.finalize()
         self._slot_free = [None] * slots
 
@@ -652,8 +713,12 @@ class ChunkStepEngine:
         return self.ctl.read()
 
     def check_status(self):
-        """Raise if a kernel reported an anomaly (sticky status word).  Synchronises."""
+        """Raise if a kernel reported an anomaly (sticky status word).  Synchronises, so it is called where the
+        host waits for the device anyway (``loss_scale``, ``state_dict``, the end of a benchmark).  While the
+        time-out bit is set every step is skipped on the device (``elx_step_begin``), on all ranks."""
         c = self.ctl.read()
         if c.status:
             raise RuntimeError(f'elixir_b200 kernels reported status {c.status:#x} '
-                               f'(1: non-finite gradient met on an applied step, 2: descriptor table mismatch)')
+                               '(1: non-finite gradient met on an applied step, 2: descriptor table mismatch, '
+                               '4: a bounded wait on a copy or on another rank expired; '
+                               f'{c.forced_skips} step(s) were skipped because of it)')

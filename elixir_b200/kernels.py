@@ -143,11 +143,18 @@ class ControlBlock:
         self.tensor.copy_(raw)
 
 
-def step_begin(ctl: ControlBlock, cfg: ElxScalerCfg, norm_sq: Optional[torch.Tensor] = None):
+def step_begin(ctl: ControlBlock, cfg: ElxScalerCfg, norm_sq: Optional[torch.Tensor] = None,
+               chunk_flags: Optional[torch.Tensor] = None):
+    """The device-side decision of a step (``elx_step_begin``).  ``chunk_flags`` (the per-chunk overflow words)
+    are cleared by the same launch, as the reference clears ``Chunk.overflow`` at this point."""
     if norm_sq is not None:
         _check_tensor(norm_sq, 'norm_sq', torch.float32)
+    if chunk_flags is not None:
+        _check_tensor(chunk_flags, 'chunk_flags', torch.int32)
     with _DeviceGuard(ctl.tensor):
-        _lib.check(_lib.get().elx_step_begin(ctl.ptr, cfg, _ptr(norm_sq), _stream(ctl.tensor)), 'elx_step_begin')
+        _lib.check(_lib.get().elx_step_begin(ctl.ptr, cfg, _ptr(norm_sq), _ptr(chunk_flags),
+                                             chunk_flags.numel() if chunk_flags is not None else 0,
+                                             _stream(ctl.tensor)), 'elx_step_begin')
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -305,7 +312,11 @@ class ChunkTable:
                   exp_avg_sq: torch.Tensor,
                   grad_param: torch.Tensor,
                   n_valid: int,
-                  segments: Sequence[Tuple[int, int, int]] = ()) -> int:
+                  segments: Sequence[Tuple[int, int, int]] = (),
+                  grad_src: Optional[torch.Tensor] = None) -> int:
+        """``grad_src``: where the kernels read this shard's gradient (same size and dtype as ``grad_param``),
+        when it is not copied into ``grad_param`` before the step; the working copy is written to
+        ``grad_param`` either way."""
         if self.descs_dev is not None:
             raise RuntimeError('the table is already finalized')
         for name, t in (('master', master), ('exp_avg', exp_avg), ('exp_avg_sq', exp_avg_sq)):
@@ -316,7 +327,11 @@ class ChunkTable:
             raise ValueError('master, moments and the low-precision shard differ in size')
         if not 0 <= n_valid <= n:
             raise ValueError('n_valid outside [0, n_shard]')
-        for t in (master, exp_avg, exp_avg_sq, grad_param):
+        if grad_src is not None:
+            _check_tensor(grad_src, 'grad_src', self.dtype, mapped_host=True)
+            if grad_src.numel() != n:
+                raise ValueError('grad_src and the shard differ in size')
+        for t in (master, exp_avg, exp_avg_sq, grad_param) + ((grad_src,) if grad_src is not None else ()):
             if is_mapped_host(t) and not _lib.host_memory_backend():
                 self.host_resident = True    # at least one array is reached over PCIe: see adam_multi
             elif t.device != self.device and not _lib.host_memory_backend():
@@ -332,10 +347,11 @@ class ChunkTable:
                 merged.append([begin, end, group])
             last_end = end
         desc = ElxChunkDesc(master.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), grad_param.data_ptr(), n,
-                            n_valid, self.tile_begin[-1], len(self._segs), len(merged), self.code, 0)
+                            n_valid, self.tile_begin[-1], len(self._segs), len(merged), self.code, 0,
+                            grad_src.data_ptr() if grad_src is not None else None)
         self._descs.append(desc)
         self._segs.extend(ElxSeg(b, e, g, 0) for b, e, g in merged)
-        self._keep.append((master, exp_avg, exp_avg_sq, grad_param))
+        self._keep.append((master, exp_avg, exp_avg_sq, grad_param, grad_src))
         self.tile_begin.append(self.tile_begin[-1] + n_tiles(n))
         return len(self._descs) - 1
 

@@ -2,10 +2,12 @@
  * elixir_b200 — C ABI of the chunk-level mixed-precision optimizer step for NVIDIA B200 (sm_100a).
  *
  * This is the boundary a host runtime binds to (ctypes / cffi / pybind / plain C).  Every pointer
- * marked "device" is a CUDA device pointer owned by the caller; the library never allocates, frees
- * or synchronises.  Every entry point is stream-ordered on the `stream` it is given (a cudaStream_t
- * passed as void*, NULL = the legacy default stream) and returns an `int` status: 0 on success,
- * a negative ELX_ERR_* code when an argument is rejected (nothing was launched) or a launch failed.
+ * marked "device" is a CUDA device pointer owned by the caller; on the step path the library never
+ * allocates, frees or synchronises (the set-up calls of the NVLink section are the exception:
+ * elx_peer_alloc / elx_peer_free allocate and free, elx_peek_u32 blocks).  Every entry point is
+ * stream-ordered on the `stream` it is given (a cudaStream_t passed as void*, NULL = the legacy default
+ * stream) and returns an `int` status: 0 on success, a negative ELX_ERR_* code when an argument is
+ * rejected (nothing was launched) or a launch failed.
  *
  * The functions replace the following pieces of hpcaitech/Elixir (paths inside that project):
  *   elixir/wrapper/optimizer.py   ElixirOptimizer.step / _check_overflow / _get_combined_scale
@@ -23,7 +25,7 @@
 extern "C" {
 #endif
 
-#define ELX_ABI_VERSION 1
+#define ELX_ABI_VERSION 2
 
 /* Elements per work tile.  `ElxChunkDesc.tile_begin` counts tiles of this many elements. */
 #define ELX_TILE 4096
@@ -47,7 +49,9 @@ extern "C" {
 /* sticky bits in ElxCtl.status */
 #define ELX_STAT_LATE_INF 1u   /* the Adam kernel met a non-finite gradient the probe had not flagged */
 #define ELX_STAT_BAD_DESC 2u   /* a kernel could not map a tile to a chunk descriptor                   */
-#define ELX_STAT_TIMEOUT 4u    /* a bounded wait on an on-chip barrier expired; the kernel gave up        */
+#define ELX_STAT_TIMEOUT 4u    /* a bounded wait (on-chip barrier or another rank) expired; the kernel gave up.
+                                  While the bit is set elx_step_begin decides "skip" and leaves the loss
+                                  scaler alone: parameters are never updated from data that may be incomplete */
 
 /*
  * Device-resident control block of one optimizer (128 bytes, 16-byte aligned).  It replaces the
@@ -67,7 +71,7 @@ typedef struct ElxCtl {
     uint32_t skipped_steps;    /* total skipped steps                                             */
     uint32_t status;           /* sticky ELX_STAT_* bits                                          */
     uint32_t late_inf;         /* set by the Adam kernel when it meets inf/nan on an applied step */
-    uint32_t ticket;           /* internal: last-block election of the probe kernels              */
+    uint32_t forced_skips;     /* steps skipped because ELX_STAT_TIMEOUT was set, not for an overflow */
     float    clip_coef;        /* clip factor of the last applied step (1 = not clipped)          */
     float    grad_norm;        /* unscaled global gradient norm of the last applied step          */
     uint32_t reserved[18];
@@ -109,10 +113,15 @@ typedef struct ElxSeg {
     int32_t reserved;
 } ElxSeg;
 
-/* One chunk shard of this rank (device table, 72 bytes each): the fp32 master chunk's shard, the
+/* One chunk shard of this rank (device table, 80 bytes each): the fp32 master chunk's shard, the
  * two Adam moments laid out congruently, and the paired low-precision shard that holds the
  * gradient before the step and the refreshed working copy after it (optimizer.py:115-124,
- * chunk.py:403-415).  All four pointers must be 32-byte aligned. */
+ * chunk.py:403-415).  All pointers must be 32-byte aligned.
+ * grad_src separates the two roles of the low-precision shard: when it is not NULL the probe and the
+ * update READ the gradient there (n_shard elements of `dtype`, e.g. the block autograd filled) and
+ * only WRITE the refreshed working copy to grad_param, so that no copy into the shard is needed
+ * before the step (the copy that ends Chunk.reduce at world size 1, chunk.py:310-313).  After the
+ * step the shard holds parameters either way. */
 typedef struct ElxChunkDesc {
     float*  master;            /* device, n_shard floats                                           */
     float*  exp_avg;           /* device, n_shard floats                                           */
@@ -125,6 +134,7 @@ typedef struct ElxChunkDesc {
     int32_t seg_count;
     int32_t dtype;             /* ELX_F16 / ELX_BF16 / ELX_F32                                      */
     int32_t reserved;
+    const void* grad_src;      /* device, n_shard elements of `dtype`, or NULL = the gradient is in grad_param */
 } ElxChunkDesc;
 
 /* Device addresses of one buffer per rank of a single-node group, as seen from THIS process: entry j
@@ -182,11 +192,15 @@ int elx_ctl_init(ElxCtl* ctl, float initial_scale, void* stream);
  *   else: div = loss scale read BEFORE the update, times the clip factor when clipping is on and
  *         the factor exceeds 1, or -1 when div == 1    (_get_combined_scale, :166-183)
  *         scaler.update(False); step += 1              (:208, optimizer state['step'])
- *   found_inf is cleared                               (_clear_optim_states, :144-147)
+ *   found_inf and the per-chunk overflow words are cleared   (_clear_optim_states, :144-147)
  * norm_sq: device pointer to the global sum of squared (still scaled) gradients, or NULL when
- * cfg.max_norm <= 0.
+ * cfg.max_norm <= 0.  chunk_flags: device array of n_chunk_flags per-chunk overflow words
+ * (Chunk.overflow) to clear, or NULL.
+ * While ELX_STAT_TIMEOUT is set in ctl->status the decision is "skip" whatever found_inf says, the
+ * loss scaler and the step count are left alone and ctl->forced_skips is incremented.
  */
-int elx_step_begin(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq, void* stream);
+int elx_step_begin(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq, uint32_t* chunk_flags,
+                   int n_chunk_flags, void* stream);
 
 /* ---- overflow / norm probe ------------------------------------------------------------------ */
 
@@ -212,10 +226,12 @@ int elx_grad_check(const void* g, int dtype, int64_t n_valid, uint32_t* flag, El
  * counterpart in the reference, whose norm goes through torch temporaries.
  *
  * The per-tile partial sums go to a 64 KiB array that is part of the library image on every GPU that
- * loads it, so n_valid is limited to elx_grad_check_static_max_elems() (67 108 864) elements; a larger
- * request returns ELX_ERR_CAPACITY and launches nothing.  The call allocates and frees nothing.
+ * loads it, so with l2sq != NULL n_valid is limited to elx_grad_check_static_max_elems() (67 108 864)
+ * elements; a larger request returns ELX_ERR_CAPACITY and launches nothing (without l2sq no scratch is
+ * used and any size is accepted).  The call allocates and frees nothing.
  * The first call on each device (with l2sq != NULL) looks up the array's device address once and
- * caches it; make that first call outside any stream capture, with the device current.
+ * caches it for the life of the process (the cache does not survive cudaDeviceReset); make that first
+ * call outside any stream capture, with the device current.
  * All calls on a device share the array and every call overwrites the slots it uses (nothing has to
  * start at zero), so two calls whose kernels can overlap on the GPU (different streams without an
  * ordering between them) race on it: keep calls on one device ordered.

@@ -1,7 +1,7 @@
 /*
  * TEST INFRASTRUCTURE — the elx_* C ABI implemented on HOST memory with the CPU oracle.
  *
- * The test-suite loads this in place of libelixir_b200.so (tests/conftest.py) to run the host-side
+ * The test-suite loads this in place of libelixir_b200.so (tests/_dist_workers.py) to run the host-side
  * logic of the package — chunk geometry, collectives over gloo, the ElixirOptimizer state machine —
  * on machines without a GPU.  The product never loads it.  Pointers are host pointers, the stream
  * argument is ignored, every call completes before it returns.  Arithmetic: elx_oracle.c (double
@@ -40,13 +40,28 @@ int elx_ctl_init(ElxCtl* ctl, float initial_scale, void* stream) {
     return ELX_OK;
 }
 
-int elx_step_begin(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq, void* stream) {
+int elx_step_begin(ElxCtl* ctl, ElxScalerCfg cfg, const float* norm_sq, uint32_t* chunk_flags, int n_chunk_flags,
+                   void* stream) {
     (void)stream;
     if (!ctl) return ELX_ERR_NULL;
     if (cfg.max_norm > 0.0f && !norm_sq) return ELX_ERR_NULL;
-    orc_step_begin(ctl, cfg, norm_sq);
+    if (n_chunk_flags < 0) return ELX_ERR_SIZE;
+    if (ctl->status & ELX_STAT_TIMEOUT) {
+        /* a wait gave up earlier: skip without touching the loss scaler (no reference counterpart) */
+        ctl->skip = 1;
+        ctl->skipped_steps += 1;
+        ctl->forced_skips += 1;
+        ctl->div_scale = -1.0f;
+        ctl->inv_div = 0.0f;
+        ctl->found_inf = 0;
+    } else {
+        orc_step_begin(ctl, cfg, norm_sq);
+    }
+    for (int i = 0; chunk_flags && i < n_chunk_flags; ++i) chunk_flags[i] = 0;
     return ELX_OK;
 }
+
+static const void* grad_of(const ElxChunkDesc* d) { return d->grad_src ? d->grad_src : d->grad_param; }
 
 static int probe_common(const void* g, int dtype, int64_t n_valid, uint32_t* flag, ElxCtl* ctl, float* l2sq) {
     if (!g) return ELX_ERR_NULL;
@@ -71,7 +86,7 @@ int elx_grad_check(const void* g, int dtype, int64_t n_valid, uint32_t* flag, El
 int elx_grad_check_static(const void* g, int dtype, int64_t n_valid, uint32_t* flag, ElxCtl* ctl, float* l2sq,
                           void* stream) {
     (void)stream;
-    if (n_valid > elx_grad_check_static_max_elems()) return ELX_ERR_CAPACITY;
+    if (l2sq && g && dtype_ok(dtype) && n_valid > elx_grad_check_static_max_elems()) return ELX_ERR_CAPACITY;
     return probe_common(g, dtype, n_valid, flag, ctl, l2sq);
 }
 
@@ -102,7 +117,7 @@ int elx_grad_check_multi(const ElxChunkDesc* descs, int first, int count, int64_
             continue;
         }
         float l2 = 0.0f;
-        int rc = probe_common(descs[c].grad_param, dtype, descs[c].n_valid, chunk_flags ? &chunk_flags[c] : 0, ctl,
+        int rc = probe_common(grad_of(&descs[c]), dtype, descs[c].n_valid, chunk_flags ? &chunk_flags[c] : 0, ctl,
                               (chunk_l2sq || total_l2sq) ? &l2 : 0);
         if (rc != ELX_OK) return rc;
         if (chunk_l2sq) chunk_l2sq[c] = l2;
@@ -117,7 +132,7 @@ static void step_one(const ElxChunkDesc* d, const ElxSeg* segs, const ElxHyper* 
     if (!ctl->skip) {
         for (int s = d->seg_first; s < d->seg_first + d->seg_count; ++s) {
             if (segs[s].group < 0 || segs[s].group >= n_groups) continue;
-            orc_adam_f64(d->master, d->exp_avg, d->exp_avg_sq, d->grad_param, d->dtype, segs[s].begin, segs[s].end,
+            orc_adam_f64(d->master, d->exp_avg, d->exp_avg_sq, grad_of(d), d->dtype, segs[s].begin, segs[s].end,
                          hyper[segs[s].group], ctl->step, ctl->div_scale);
         }
     }
@@ -209,7 +224,7 @@ int elx_adam_multi_shadow(const ElxChunkDesc* descs, const ElxChunkDesc* shadow,
             memcpy(o->master + b, d->master + b, (size_t)n * sizeof(float));
             memcpy(o->exp_avg + b, d->exp_avg + b, (size_t)n * sizeof(float));
             memcpy(o->exp_avg_sq + b, d->exp_avg_sq + b, (size_t)n * sizeof(float));
-            orc_adam_f64(o->master, o->exp_avg, o->exp_avg_sq, d->grad_param, d->dtype, segs[s].begin, segs[s].end,
+            orc_adam_f64(o->master, o->exp_avg, o->exp_avg_sq, grad_of(d), d->dtype, segs[s].begin, segs[s].end,
                          hyper[segs[s].group], ctl->step, ctl->div_scale);
         }
         orc_cast(o->master, d->grad_param, d->dtype, d->n_shard);

@@ -43,13 +43,13 @@ def test_struct_layouts_match_the_header():
     from elixir_b200 import _abi
     fields = {
         'ElxCtl': ['scale', 'found_inf', 'growth_step', 'hysteresis_step', 'step', 'skip', 'div_scale', 'inv_div',
-                   'skipped_steps', 'status', 'late_inf', 'ticket', 'clip_coef', 'grad_norm', 'reserved'],
+                   'skipped_steps', 'status', 'late_inf', 'forced_skips', 'clip_coef', 'grad_norm', 'reserved'],
         'ElxScalerCfg': ['dynamic', 'growth_factor', 'backoff_factor', 'min_scale', 'max_scale', 'growth_interval',
                          'hysteresis', 'max_norm'],
         'ElxHyper': ['lr', 'beta1', 'beta2', 'eps', 'weight_decay', 'adamw_mode', 'bias_correction', 'reserved'],
         'ElxSeg': ['begin', 'end', 'group', 'reserved'],
         'ElxChunkDesc': ['master', 'exp_avg', 'exp_avg_sq', 'grad_param', 'n_shard', 'n_valid', 'tile_begin',
-                         'seg_first', 'seg_count', 'dtype', 'reserved'],
+                         'seg_first', 'seg_count', 'dtype', 'reserved', 'grad_src'],
     }
     lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "elixir_b200.h"', 'int main(void){']
     for s, fs in fields.items():

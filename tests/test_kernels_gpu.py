@@ -586,6 +586,113 @@ def test_peer_barrier_wait_is_bounded(K, cuda):
     assert lib.elx_peer_barrier(solo, 0, ctl2.ptr, 0, 200, stream) == _abi.ERR_ARG    # epochs start at 1
 
 
+def test_expired_wait_forces_a_skip_instead_of_an_update(K, oracle, cuda):
+    """After a wait gave up (ELX_STAT_TIMEOUT, raised here by a barrier whose peer never arrives) the
+    gradients may be incomplete: the next decision is "skip" although no overflow was seen, the loss scaler and
+    the step count stay as they were, and the update launch only refreshes the working copy."""
+    from elixir_b200 import _abi, _lib
+    lib = _lib.get()
+    mine = torch.zeros(256, dtype=torch.int32, device=cuda)
+    silent_peer = torch.zeros(256, dtype=torch.int32, device=cuda)
+    table = _abi.ElxPeerTable()
+    table.base[0], table.base[1] = mine.data_ptr(), silent_peer.data_ptr()
+    table.rank, table.world = 0, 2
+    ctl = K.ControlBlock(cuda, 64.0)
+    cfg = K.scaler_cfg(True, growth_interval=1, hysteresis=1)
+    n = 3 * 4096 + 9
+    p, m, v, g = (t.to(cuda) for t in make_chunk(n, torch.float16, seed=5))
+    p0 = p.clone()
+    flags = torch.ones(3, dtype=torch.int32, device=cuda)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(cuda).cuda_stream)
+    assert lib.elx_peer_barrier(table, 1, ctl.ptr, 1, 100, stream) == _abi.OK
+    K.step_begin(ctl, cfg, chunk_flags=flags)
+    K.adam_chunk(p, m, v, g, K.hyper(), ctl)
+    c = ctl.read()
+    assert c.status & _abi.STAT_TIMEOUT
+    assert (c.skip, c.forced_skips, c.skipped_steps, c.step, c.scale, c.growth_step) == (1, 1, 1, 0, 64.0, 0)
+    assert flags.tolist() == [0, 0, 0]    # the decision clears the per-chunk overflow words
+    assert bits_equal(p, p0) and float(m.abs().max()) == 0.0 and float(v.abs().max()) == 0.0
+    want16 = torch.empty(n, dtype=torch.float16)
+    oracle.cast(p0.cpu(), want16)
+    assert bits_equal(g, want16)
+    # the bit is sticky: the next step is skipped too, until the host has looked (engine.check_status raises)
+    K.step_begin(ctl, cfg)
+    assert ctl.read().forced_skips == 2
+    from elixir_b200.engine import ChunkStepEngine
+    engine = ChunkStepEngine(cuda, torch.float16)
+    engine.ctl = ctl
+    with pytest.raises(RuntimeError, match='bounded wait'):
+        engine.check_status()
+
+
+@pytest.mark.parametrize('variant', [0, 1])
+@pytest.mark.parametrize('dtype', DTYPES)
+def test_gradient_source_separate_from_the_working_copy(K, oracle, cuda, dtype, variant):
+    """With ElxChunkDesc.grad_src the probe and the update read the gradient where it was produced and only
+    write the working copy into the shard: same bits as copying the gradient into the shard first, and the
+    source is left untouched.  Whole tiles that no segment covers (the tail past valid_end, a gap between two
+    segments) take the refresh-only path of the pipelined kernel."""
+    sizes = [40 * 4096, 5 * 4096 + 100, 4096, 3, 12 * 4096]
+    valid = [40 * 4096 - 5, 5 * 4096 + 100, 1000, 0, 7 * 4096 + 1]
+    seg_lists = [
+        _segments(valid[0], [100, 4096, 4096 + 7, 20 * 4096, 30 * 4096 + 2048], [0, 1, 2, -1, 0, 1]),
+        _segments(valid[1], [2 * 4096], [1, 0]),
+        _segments(valid[2], [], [2]),
+        [],
+        _segments(valid[4], [3 * 4096 + 5], [0, 2]),
+    ]
+    hypers = [K.hyper(1e-3, (0.9, 0.999), 1e-8, 0.01, True), K.hyper(5e-4, (0.9, 0.98), 1e-6, 0.0, True),
+              K.hyper(2e-3, (0.85, 0.99), 1e-8, 0.05, False)]
+    scale = 512.0
+    K.set_tuning(adam_variant=variant)
+    try:
+        # reference run: gradients copied into the shards
+        table, host, dev_t, host_t = _build_set(K, oracle, cuda, dtype, sizes, valid, seg_lists, 91, scale)
+        table.set_hyper(hypers)
+        # run under test: same state, gradients in tensors of their own
+        table2 = K.ChunkTable(cuda, dtype)
+        dev2, srcs = [], []
+        for c, (n, nv, segs) in enumerate(zip(sizes, valid, seg_lists)):
+            p, m, v, _ = (t.clone() for t in dev_t[c])
+            lowp = torch.full((n,), 3.0, dtype=dtype, device=cuda)    # stale parameters: must never be read
+            src = torch.empty(n, dtype=dtype, device=cuda)
+            table2.add_chunk(p, m, v, lowp, n_valid=nv, segments=segs, grad_src=src)
+            dev2.append((p, m, v, lowp))
+            srcs.append(src)
+        table2.finalize()
+        table2.set_hyper(hypers)
+        cfg = K.scaler_cfg(True, growth_interval=2, hysteresis=1)
+        ctl1, ctl2 = K.ControlBlock(cuda, scale), K.ControlBlock(cuda, scale)
+        flags1 = torch.zeros(table.n_chunks, dtype=torch.int32, device=cuda)
+        flags2 = torch.zeros(table.n_chunks, dtype=torch.int32, device=cuda)
+        for step in range(3):
+            for c, n in enumerate(sizes):
+                gen = torch.Generator().manual_seed(17 * step + c)
+                g = (torch.randn(n, generator=gen) * 1e-3 * scale).to(dtype)
+                if step == 1 and c == 4:
+                    g[valid[c] - 1] = float('nan')
+                    g[valid[c]] = float('inf')    # past valid_end: not probed, not used
+                dev_t[c][3].copy_(g)
+                srcs[c].copy_(g)
+            K.grad_check_multi(table, ctl1, chunk_flags=flags1)
+            K.grad_check_multi(table2, ctl2, chunk_flags=flags2)
+            assert flags1.tolist() == flags2.tolist() == [int(step == 1 and c == 4) for c in range(len(sizes))]
+            K.step_begin(ctl1, cfg, chunk_flags=flags1)
+            K.step_begin(ctl2, cfg, chunk_flags=flags2)
+            kept = [s.clone() for s in srcs]
+            K.adam_multi(table, ctl1)
+            K.adam_multi(table2, ctl2)
+            assert _ctl_fields(ctl1.read()) == _ctl_fields(ctl2.read())
+            assert bool(ctl2.read().skip) == (step == 1)
+            for c in range(len(sizes)):
+                for x, y in zip(dev_t[c], dev2[c]):
+                    assert bits_equal(x, y), (step, c)
+                assert bits_equal(srcs[c], kept[c]), (step, c)
+        assert ctl2.read().status == 0
+    finally:
+        K.set_tuning(adam_variant=-1)
+
+
 # --------------------------------------------------------------------------------------------------
 # argument validation: errors are status codes, nothing is launched
 # --------------------------------------------------------------------------------------------------

@@ -68,3 +68,19 @@ def test_static_scratch_entry_rejects_oversized_requests(cuda):
     too_many = lib.elx_grad_check_static_max_elems() + 1
     assert lib.elx_grad_check_static(_p(g), _abi.F16, too_many, _p(flag), None, _p(l2), None) == _abi.ERR_CAPACITY
     assert b'capacity' in lib.elx_strerror(_abi.ERR_CAPACITY)
+
+
+def test_static_scratch_entry_without_a_norm_has_no_size_limit(cuda):
+    """The limit belongs to the built-in array, and only the sum of squares uses it: a plain overflow probe of a
+    shard larger than the limit goes through."""
+    from elixir_b200 import _abi, _lib
+    lib = _lib.get()
+    n = lib.elx_grad_check_static_max_elems() + 4096 + 3
+    g = torch.zeros(n, dtype=torch.float16, device=cuda)
+    g[n - 2] = float('inf')
+    flag = torch.zeros(1, dtype=torch.int32, device=cuda)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(cuda).cuda_stream)
+    assert lib.elx_grad_check_static(_p(g), _abi.F16, n - 2, _p(flag), None, None, stream) == _abi.OK
+    assert flag.item() == 0
+    assert lib.elx_grad_check_static(_p(g), _abi.F16, n, _p(flag), None, None, stream) == _abi.OK
+    assert flag.item() == 1
