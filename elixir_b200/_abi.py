@@ -130,6 +130,8 @@ PROTOTYPES = {
     'elx_grad_check_static': (_i, [_p, _i, _i64, _p, _p, _p, _p]),
     'elx_grad_check_static_max_elems': (_i64, []),
     'elx_reduce_epilogue': (_i, [_p, _p, _i, _i64, _i64, _p, _p, _p, _p, _i64, _p]),
+    'elx_widen': (_i, [_p, _i, _p, _i64, _p]),
+    'elx_narrow_epilogue': (_i, [_p, _p, _i, _i64, _i64, _p, _p, _p]),
     'elx_grad_check_multi': (_i, [_p, _i, _i, _i64, _i, _p, _p, _p, _p, _p, _i64, _p]),
     'elx_adam_multi': (_i, [_p, _i, _i, _i64, _i, _p, _p, _i, _p, _p]),
     'elx_adam_multi_hostmem': (_i, [_p, _i, _i, _i64, _i, _p, _p, _i, _p, _p]),

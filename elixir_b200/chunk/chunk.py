@@ -213,7 +213,7 @@ class Chunk:
             return dict()
         if self._l2_scratch is None:
             self._l2_scratch = torch.empty(kernels.n_tiles(self.shard_size), dtype=torch.float32,
-                                           device=self.shard_device)
+                                           device=self.compute_device)
         self._l2_valid = True
         return dict(l2sq=self._l2sq, scratch=self._l2_scratch)
 
@@ -333,16 +333,23 @@ class Chunk:
             comm.reduce_scatter_avg(self.shard, payload, self.torch_pg)
             kernels.grad_check(self.shard, n_valid=self.valid_end, flag=self._flag, ctl=self._ctl,
                                **self._norm_args())
+        elif self.pg_size > 1 and widen:
+            # fp32 accumulation (reduce_always_fp32, ``chunk.py:288-308``): widen the block, average in fp32 inside
+            # the collective, then round this rank's slice of the average into the persistent shard and probe the
+            # rounded values, in one pass
+            wide = torch.empty(self.chunk_size, dtype=torch.float, device=payload.device)
+            kernels.widen(payload, wide)
+            wide_slice = wide[self.shard_begin:self.shard_end]
+            comm.reduce_scatter_avg(wide_slice, wide, self.torch_pg)
+            kernels.narrow_epilogue(wide_slice, self.shard, n_valid=self.valid_end, flag=self._flag, ctl=self._ctl)
+            norm = self._norm_args()
+            if norm:
+                kernels.grad_check(self.shard, n_valid=self.valid_end, **norm)
         else:
-            if self.pg_size > 1 and not widen:
+            if self.pg_size > 1:
                 # shard in host memory: the collective cannot write there; it leaves the average in this rank's
                 # slice of the block (output aliased inside the input, as the reference does, chunk.py:299-303)
                 comm.reduce_scatter_avg(my_slice, payload, self.torch_pg)
-            elif self.pg_size > 1:
-                # fp32 accumulation (reduce_always_fp32): widen, average in fp32, narrow the own slice back
-                wide = payload.to(torch.float)
-                comm.reduce_scatter_avg(wide[self.shard_begin:self.shard_end], wide, self.torch_pg)
-                my_slice.copy_(wide[self.shard_begin:self.shard_end])
             # copy into the persistent shard fused with the inf/nan probe (and the norm when asked for)
             kernels.reduce_epilogue(my_slice, self.shard, n_valid=self.valid_end, flag=self._flag, ctl=self._ctl,
                                     **self._norm_args())

@@ -287,6 +287,60 @@ int probe_single(const void* src, void* dst, int dtype, int64_t n_shard, int64_t
 }
 
 // ------------------------------------------------------------------------------------------------
+// fp32 gradient reduction: widen before the collective, narrow + land + probe after it
+// ------------------------------------------------------------------------------------------------
+
+// dst[i] = float(src[i]).  16 elements per thread and tile, whole-line warp accesses; scalar tail.
+template <int DT>
+__global__ void __launch_bounds__(kProbeThreads) widen_kernel(const void* __restrict__ src, float* __restrict__ dst,
+                                                              int64_t n, int vec_ok) {
+    constexpr int EPT = kTile / kProbeThreads;
+    const int64_t n_full = vec_ok ? n / kTile : 0;
+    for (int64_t t = blockIdx.x; t < n_full; t += gridDim.x) {
+        float g[EPT];
+        load_lowp<DT, EPT>(src, t * kTile, g);
+        store_f32<EPT>(dst, t * kTile, g);
+    }
+    const typename Lp<DT>::T* in = static_cast<const typename Lp<DT>::T*>(src);
+    for (int64_t e = n_full * kTile + blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; e < n;
+         e += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        dst[e] = Lp<DT>::to_float(in[e]);
+}
+
+// dst[i] = round_to_nearest_even(src[i]) for i in [0, n_shard); the rounded values of [0, n_valid) are probed.
+template <int DT>
+__global__ void __launch_bounds__(kProbeThreads) narrow_probe_kernel(const float* __restrict__ src, void* dst,
+                                                                     int64_t n_shard, int64_t n_valid, uint32_t* flag,
+                                                                     ElxCtl* ctl, int vec_ok) {
+    constexpr int EPT = kTile / kProbeThreads;
+    using T = typename Lp<DT>::T;
+    const int64_t n_full = vec_ok ? n_shard / kTile : 0;
+    uint32_t bad = 0;
+    for (int64_t t = blockIdx.x; t < n_full; t += gridDim.x) {
+        float p[EPT];
+        load_f32<EPT>(src, t * kTile, p);
+        store_lowp<DT, EPT>(dst, t * kTile, p);
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            const int64_t e = t * kTile + group_offset<EPT>(j / 8) + (j & 7);
+            if (e < n_valid && Lp<DT>::nonfinite(Lp<DT>::from_float(p[j]))) bad = 1;
+        }
+    }
+    T* out = static_cast<T*>(dst);
+    for (int64_t e = n_full * kTile + blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; e < n_shard;
+         e += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const T val = Lp<DT>::from_float(src[e]);
+        out[e] = val;
+        if (e < n_valid && Lp<DT>::nonfinite(val)) bad = 1;
+    }
+    const unsigned any_bad = __ballot_sync(0xFFFFFFFFu, bad != 0);
+    if (any_bad && (threadIdx.x & 31) == 0) {
+        if (flag) atomicOr(flag, 1u);
+        if (ctl) atomicOr(&ctl->found_inf, 1u);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // built-in scratch for callers that cannot allocate
 // ------------------------------------------------------------------------------------------------
 
@@ -354,6 +408,40 @@ int elx_grad_check_static(const void* g, int dtype, int64_t n_valid, uint32_t* f
 int elx_reduce_epilogue(const void* src, void* dst, int dtype, int64_t n_shard, int64_t n_valid, uint32_t* flag,
                         ElxCtl* ctl, float* l2sq, float* scratch, int64_t scratch_elems, void* stream) {
     return probe_single(src, dst, dtype, n_shard, n_valid, flag, ctl, l2sq, scratch, scratch_elems, stream, true);
+}
+
+int elx_widen(const void* src, int dtype, float* dst, int64_t n, void* stream) {
+    if (!src || !dst) return ELX_ERR_NULL;
+    if (dtype != ELX_F16 && dtype != ELX_BF16) return ELX_ERR_DTYPE;
+    if (n < 0) return ELX_ERR_SIZE;
+    if (!aligned(src, 2) || !aligned(dst, 4)) return ELX_ERR_ALIGN;
+    if (n == 0) return ELX_OK;
+    const int vec_ok = aligned(src, 32) && aligned(dst, 32);
+    const int grid = grid_for((n + kTile - 1) / kTile, 8);
+    if (grid < 0) return grid;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == ELX_F16) widen_kernel<ELX_F16><<<grid, kProbeThreads, 0, s>>>(src, dst, n, vec_ok);
+    else widen_kernel<ELX_BF16><<<grid, kProbeThreads, 0, s>>>(src, dst, n, vec_ok);
+    return record_cuda(cudaGetLastError());
+}
+
+int elx_narrow_epilogue(const float* src, void* dst, int dtype, int64_t n_shard, int64_t n_valid, uint32_t* flag,
+                        ElxCtl* ctl, void* stream) {
+    if (!src || !dst) return ELX_ERR_NULL;
+    if (dtype != ELX_F16 && dtype != ELX_BF16) return ELX_ERR_DTYPE;
+    if (n_shard < 0 || n_valid < 0 || n_valid > n_shard) return ELX_ERR_SIZE;
+    if (!aligned(src, 4) || !aligned(dst, 2) || (flag && !aligned(flag, 4)) || (ctl && !aligned(ctl, 16)))
+        return ELX_ERR_ALIGN;
+    if (n_shard == 0) return ELX_OK;
+    const int vec_ok = aligned(src, 32) && aligned(dst, 32);
+    const int grid = grid_for((n_shard + kTile - 1) / kTile, 8);
+    if (grid < 0) return grid;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == ELX_F16)
+        narrow_probe_kernel<ELX_F16><<<grid, kProbeThreads, 0, s>>>(src, dst, n_shard, n_valid, flag, ctl, vec_ok);
+    else
+        narrow_probe_kernel<ELX_BF16><<<grid, kProbeThreads, 0, s>>>(src, dst, n_shard, n_valid, flag, ctl, vec_ok);
+    return record_cuda(cudaGetLastError());
 }
 
 int elx_grad_check_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,

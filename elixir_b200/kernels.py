@@ -216,6 +216,39 @@ def reduce_epilogue(src: torch.Tensor,
             'elx_reduce_epilogue')
 
 
+def widen(src: torch.Tensor, dst: torch.Tensor):
+    """``dst = src.float()`` for a 16-bit ``src`` (``elx_widen``): the block that goes into an fp32 reduction."""
+    _check_tensor(src, 'src')
+    _check_tensor(dst, 'dst', torch.float32)
+    if src.numel() != dst.numel():
+        raise ValueError('src and dst differ in size')
+    home = _home(src, dst)
+    with _DeviceGuard(home):
+        _lib.check(_lib.get().elx_widen(_ptr(src), dtype_code(src.dtype), _ptr(dst), src.numel(), _stream(home)),
+                   'elx_widen')
+
+
+def narrow_epilogue(src: torch.Tensor,
+                    dst: torch.Tensor,
+                    n_valid: Optional[int] = None,
+                    flag: Optional[torch.Tensor] = None,
+                    ctl: Optional[ControlBlock] = None):
+    """``dst.copy_(src)`` from fp32 to the 16-bit ``dst`` fused with the probe of the rounded ``dst[:n_valid]``
+    (``elx_narrow_epilogue``): the fp32 rank average of this rank's slice lands in its shard."""
+    _check_tensor(src, 'src', torch.float32)
+    _check_tensor(dst, 'dst', mapped_host=True)
+    if src.numel() != dst.numel():
+        raise ValueError('src and dst differ in size')
+    n_valid = src.numel() if n_valid is None else int(n_valid)
+    if flag is not None:
+        _check_tensor(flag, 'flag', torch.int32)
+    home = _home(src, dst, flag, ctl.tensor if ctl else None)
+    with _DeviceGuard(home):
+        _lib.check(
+            _lib.get().elx_narrow_epilogue(_ptr(src), _ptr(dst), dtype_code(dst.dtype), src.numel(), n_valid, _ptr(flag),
+                                           ctl.ptr if ctl else None, _stream(home)), 'elx_narrow_epilogue')
+
+
 def hyper(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, adamw_mode=True, bias_correction=True) -> ElxHyper:
     return ElxHyper(float(lr), float(betas[0]), float(betas[1]), float(eps), float(weight_decay), int(bool(adamw_mode)),
                     int(bool(bias_correction)), 0)

@@ -10,6 +10,11 @@ Same constructor, methods and attributes as ``elixir/wrapper/optimizer.py`` (``E
        the clip factor), loss-scaler update, step count (``:192-209``, ``:166-183``);
     3. ``elx_adam_multi``: unscale + Adam/AdamW + low-precision copy-back, or the copy-back alone when
        the step is skipped (``:216-219``, ``_update_fp16_params`` ``:126-135``).
+
+Any other ``torch.optim.Optimizer`` is accepted as in the reference (``:52-56, 211-214``), for the case it allows:
+no division of the gradients (loss scale 1, no clipping).  Such an optimizer steps on views of the fp32 shards
+with the gradient views bound as ``.grad``; the decision still runs on the device and is read back once per step,
+because a foreign optimizer cannot branch on a device word.
 """
 from enum import Enum
 from typing import Dict, List, Set, Tuple
@@ -48,10 +53,12 @@ class ElixirOptimizer:
                  init_step: bool = False,
                  sync_overflow: bool = True):
         assert isinstance(module, ElixirModule)
-        if type(optimizer) not in _AVAIL_OPTIM_LIST:
-            raise TypeError(f'You should use an optimizer in the available list:\n{_AVAIL_OPTIM_LIST}')
+        if not isinstance(optimizer, torch.optim.Optimizer):
+            raise TypeError(f'ElixirOptimizer wraps a torch.optim.Optimizer, got {type(optimizer).__name__}')
         self.optim = optimizer
-        self.scaled_optimizer = True
+        # an optimizer of the available list takes the divisor from the device control block; any other one is
+        # stepped as it is and therefore only when the gradients need no division (``:211-214``)
+        self.scaled_optimizer = type(optimizer) in _AVAIL_OPTIM_LIST
         self.module = module
         self.param_chunk_group = module.param_chunk_group
         self.optim_chunk_group = module.optim_chunk_group
@@ -92,6 +99,8 @@ class ElixirOptimizer:
                 if not param.requires_grad:
                     continue
                 param_chunk = self.module.fetcher.get_one_chunk(param)
+                if param_chunk is None:
+                    raise ValueError('the optimizer holds a parameter that the wrapped module does not manage')
                 info = param_chunk.tensors_info[param]
                 begin = max(0, info.offset - param_chunk.shard_begin)
                 end = min(param_chunk.shard_size, info.end - param_chunk.shard_begin)
@@ -116,7 +125,11 @@ class ElixirOptimizer:
         self.engine = ChunkStepEngine(device, dtype, self.grad_scaler, process_group=group,
                                       sync_overflow=sync_overflow, max_norm=self.max_norm)
         for chunk in chunks:
-            self.engine.add_shard(chunk.paired_chunk.shard, chunk.shard, chunk.valid_end, segments[chunk])
+            master = chunk.paired_chunk.shard
+            # a foreign optimizer keeps its own state: no flat moments are allocated for it (the master stands in
+            # for them in the descriptor, which the update kernel never sees in that case)
+            moments = {} if self.scaled_optimizer else dict(exp_avg=master, exp_avg_sq=master)
+            self.engine.add_shard(master, chunk.shard, chunk.valid_end, segments[chunk], **moments)
         self.engine.finalize()
         if self.engine.table.host_resident:
             # shards in host memory: the update moves them through device staging sets with the copy engines
@@ -124,12 +137,17 @@ class ElixirOptimizer:
             self.engine.enable_streaming()
         for index, chunk in enumerate(chunks):
             chunk.bind_control(self.engine.ctl, self.engine.chunk_flags[index:index + 1])
+        self._index_of = {chunk.paired_chunk: i for i, chunk in enumerate(chunks)}
+        if not self.scaled_optimizer:
+            if self.engine.table.host_resident or self.module.nvlink_step:
+                raise RuntimeError(f'{type(self.optim).__name__} is stepped by torch on device-resident shards over '
+                                   f'NCCL; use an optimizer of {_AVAIL_OPTIM_LIST} for other placements')
+            return
         self.optim.bind_engine(self.engine)
         self.engine.set_hyper(self.optim.hyper_table())
         # per-parameter views of the flat moments, under the keys the reference's optimizers use
-        index_of = {chunk.paired_chunk: i for i, chunk in enumerate(chunks)}
         for fake, (begin, end) in self.param_to_range.items():
-            _, exp_avg, exp_avg_sq, _, _ = self.engine.shards[index_of[self.param_to_optim_chunk[fake]]]
+            _, exp_avg, exp_avg_sq, _, _ = self.engine.shards[self._index_of[self.param_to_optim_chunk[fake]]]
             self.optim.state[fake] = dict(step=0, exp_avg=exp_avg[begin:end], exp_avg_sq=exp_avg_sq[begin:end])
 
     def _zero_step(self):
@@ -138,6 +156,9 @@ class ElixirOptimizer:
         weight decay is applied once — are reproduced."""
         for _, _, _, lowp, _ in self.engine.shards:
             lowp.zero_()
+        if not self.scaled_optimizer:
+            self._step_foreign(decided=False)
+            return
         ctl = self.engine.read_control()
         ctl.skip, ctl.div_scale, ctl.inv_div = 0, -1.0, 0.0
         ctl.step += 1
@@ -153,7 +174,20 @@ class ElixirOptimizer:
 
     @property
     def state(self):
+        """Per-parameter optimizer state.  ``step`` is the number of applied updates, kept in the device control
+        block; it is copied into the per-parameter entries when the state is looked at (this property and
+        ``state_dict``), which waits for the device, and never during ``step()``."""
+        self._refresh_step_counts()
         return self.optim.state
+
+    def _refresh_step_counts(self):
+        if not self.scaled_optimizer:
+            return
+        applied = int(self.engine.read_control().step)
+        for fake in self.param_to_range:
+            entry = self.optim.state.get(fake)
+            if entry is not None:
+                entry['step'] = applied
 
     @property
     def defaults(self):
@@ -196,11 +230,40 @@ class ElixirOptimizer:
             self.zero_grad()
             return None
         self.engine.begin_step()
-        ret = self.optim.step(*args, **kwargs)
+        if self.scaled_optimizer:
+            ret = self.optim.step(*args, **kwargs)
+        else:
+            ret = self._step_foreign(True, *args, **kwargs)
         self.engine.end_step()
         for chunk in self._chunks:
             chunk._l2_valid = False
         self.zero_grad()
+        return ret
+
+    def _step_foreign(self, decided: bool, *args, **kwargs):
+        """Step an optimizer that is not in the available list (``:211-214``): bind, for every parameter range of
+        this rank, ``.data`` to the fp32 shard view and ``.grad`` to the gradient view (``_set_grad_ptr``,
+        ``:115-124``), let torch step, unbind, refresh the working copies (``_update_fp16_params``, ``:126-135``).
+        ``decided``: ``elx_step_begin`` has run; its decision is read back here (one synchronisation per step)."""
+        ret, skip = None, False
+        if decided:
+            ctl = self.engine.read_control()
+            skip = bool(ctl.skip)
+            if not skip and ctl.div_scale != -1.0:
+                raise AssertionError(f'You should use an optimizer in the available list:\n{_AVAIL_OPTIM_LIST}')
+        if not skip:
+            for fake, (begin, end) in self.param_to_range.items():
+                master, _, _, lowp, _ = self.engine.shards[self._index_of[self.param_to_optim_chunk[fake]]]
+                grad = lowp[begin:end]
+                fake.data = master[begin:end]
+                fake.grad = grad if grad.dtype == master.dtype else grad.to(master.dtype)
+            ret = self.optim.step(*args, **kwargs)
+        none_tensor = torch.empty([0], device=self.engine.device)
+        for fake in self.param_to_range:
+            fake.grad = None
+            fake.data = none_tensor
+        for chunk in self._chunks:
+            chunk.optim_update()
         return ret
 
     def clip_grad_norm(self, model: torch.nn.Module, max_norm: float, norm_type: float = 2.0):
@@ -222,6 +285,9 @@ class ElixirOptimizer:
         """This rank's flat optimizer state: one (exp_avg, exp_avg_sq) pair per chunk shard plus the control
         block fields.  The reference saves none of this (its scaler state is lost on restart)."""
         self._quiesce_host_shards()
+        if not self.scaled_optimizer:
+            return dict(scaler=self.grad_scaler.state_dict(), optim=self.optim.state_dict())
+        self._refresh_step_counts()
         return dict(scaler=self.grad_scaler.state_dict(),
                     shards=[dict(exp_avg=s[1].detach().to('cpu', copy=True), exp_avg_sq=s[2].detach().to('cpu', copy=True))
                             for s in self.engine.shards],
@@ -236,6 +302,9 @@ class ElixirOptimizer:
     def load_state_dict(self, state):
         self._quiesce_host_shards()
         self.grad_scaler.load_state_dict(state['scaler'])
+        if not self.scaled_optimizer:
+            self.optim.load_state_dict(state['optim'])
+            return
         for shard, saved in zip(self.engine.shards, state['shards']):
             shard[1].copy_(saved['exp_avg'])
             shard[2].copy_(saved['exp_avg_sq'])

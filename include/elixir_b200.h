@@ -254,6 +254,20 @@ int elx_reduce_epilogue(const void* src, void* dst, int dtype, int64_t n_shard, 
                         int64_t scratch_elems, void* stream);
 
 /*
+ * The two ends of a gradient reduction carried out in fp32 (Chunk.reduce with always_fp32,
+ * chunk.py:288-308: widen the low-precision block, divide and reduce-scatter in fp32, write the average
+ * back in the chunk dtype).
+ * elx_widen: dst[i] = float(src[i]) for i in [0, n); dtype is ELX_F16 or ELX_BF16.
+ * elx_narrow_epilogue: dst[i] = src[i] rounded to nearest-even in `dtype` for i in [0, n_shard) -- the
+ * fp32 average of this rank's slice into its persistent shard -- and the rounded values of [0, n_valid)
+ * are probed as elx_grad_check does (the copy ending Chunk.reduce and update_extra_reduce_info in one pass).
+ * Pointers need element alignment; 32-byte alignment of both enables the vector path.
+ */
+int elx_widen(const void* src, int dtype, float* dst, int64_t n, void* stream);
+int elx_narrow_epilogue(const float* src, void* dst, int dtype, int64_t n_shard, int64_t n_valid,
+                        uint32_t* flag, ElxCtl* ctl, void* stream);
+
+/*
  * Probe descriptors [first, first + count) of a descriptor table in ONE launch.  chunk_flags
  * (device, one uint32 per descriptor of the table, may be NULL) receives the per-chunk overflow
  * booleans (Chunk.overflow); ctl->found_inf receives their OR.  When chunk_l2sq != NULL it

@@ -102,6 +102,29 @@ int elx_reduce_epilogue(const void* src, void* dst, int dtype, int64_t n_shard, 
     return probe_common(src, dtype, n_valid, flag, ctl, l2sq);
 }
 
+float orc_f16_to_f32(uint16_t h);
+float orc_bf16_to_f32(uint16_t h);
+
+int elx_widen(const void* src, int dtype, float* dst, int64_t n, void* stream) {
+    (void)stream;
+    if (!src || !dst) return ELX_ERR_NULL;
+    if (dtype != ELX_F16 && dtype != ELX_BF16) return ELX_ERR_DTYPE;
+    if (n < 0) return ELX_ERR_SIZE;
+    const uint16_t* in = (const uint16_t*)src;
+    for (int64_t i = 0; i < n; ++i) dst[i] = dtype == ELX_F16 ? orc_f16_to_f32(in[i]) : orc_bf16_to_f32(in[i]);
+    return ELX_OK;
+}
+
+int elx_narrow_epilogue(const float* src, void* dst, int dtype, int64_t n_shard, int64_t n_valid, uint32_t* flag,
+                        ElxCtl* ctl, void* stream) {
+    (void)stream;
+    if (!src || !dst) return ELX_ERR_NULL;
+    if (dtype != ELX_F16 && dtype != ELX_BF16) return ELX_ERR_DTYPE;
+    if (n_shard < 0 || n_valid < 0 || n_valid > n_shard) return ELX_ERR_SIZE;
+    orc_cast(src, dst, dtype, n_shard);
+    return probe_common(dst, dtype, n_valid, flag, ctl, 0);
+}
+
 int elx_grad_check_multi(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
                          uint32_t* chunk_flags, ElxCtl* ctl, float* chunk_l2sq, float* total_l2sq, float* scratch,
                          int64_t scratch_elems, void* stream) {

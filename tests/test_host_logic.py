@@ -128,6 +128,8 @@ def test_optimizer_bookkeeping_frozen_parameters_and_state_views(host_backend):
     first = next(iter(eopt.param_to_range))
     assert float(eopt.state[first]['exp_avg'].abs().sum()) > 0
     with pytest.raises(TypeError):
+        ElixirOptimizer(emodel, object())    # not a torch optimizer at all
+    with pytest.raises(ValueError):          # any torch optimizer is accepted, but only over the module's parameters
         ElixirOptimizer(emodel, torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=0.1))
     with pytest.raises(RuntimeError):
         CPUAdam([torch.nn.Parameter(torch.zeros(1))])

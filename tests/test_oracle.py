@@ -177,3 +177,28 @@ def test_scaler_trajectory_equals_torch_amp_update_scale(oracle):
             oracle.step_begin(ctl, cfg)
             torch._amp_update_scale_(scale, tracker, torch.tensor([float(found)]), growth, backoff, growth_interval)
             assert ctl.scale == float(scale) and ctl.growth_step == int(tracker) and ctl.skip == int(found)
+
+
+@pytest.mark.parametrize('p_overflow', [0.7, 0.05])
+def test_scaler_trajectory_with_clamps_equals_torch_amp_update_scale_clamped(oracle, p_overflow):
+    """The same pin on trajectories that reach the bounds: with many overflows the scale sits on `min_scale`,
+    with few it sits on `max_scale`.  torch's update knows no bounds, so its scale tensor is clamped after every
+    update, which is what `max(scale * backoff, min_scale)` / `min(scale * growth, max_scale)` amount to when the
+    scale starts inside the bounds."""
+    from elixir_b200 import kernels as K
+    lo, hi = 1.0, 16.0
+    for growth_interval, growth, backoff in ((2, 2.0, 0.5), (3, 4.0, 0.25)):
+        cfg = K.scaler_cfg(True, growth, backoff, lo, hi, growth_interval=growth_interval, hysteresis=1)
+        ctl = oracle.new_ctl(4.0)
+        scale, tracker = torch.full((1,), 4.0), torch.zeros(1, dtype=torch.int32)
+        gen = torch.Generator().manual_seed(int(p_overflow * 100) + growth_interval)
+        hit_lo = hit_hi = 0
+        for found in (torch.rand(300, generator=gen) < p_overflow).tolist():
+            ctl.found_inf = int(found)
+            oracle.step_begin(ctl, cfg)
+            torch._amp_update_scale_(scale, tracker, torch.tensor([float(found)]), growth, backoff, growth_interval)
+            scale.clamp_(lo, hi)
+            assert ctl.scale == float(scale) and ctl.growth_step == int(tracker) and ctl.skip == int(found)
+            hit_lo += ctl.scale == lo
+            hit_hi += ctl.scale == hi
+        assert (hit_lo if p_overflow > 0.5 else hit_hi) > 50    # the bound was really in play

@@ -81,6 +81,72 @@ def test_fp32_mode_matches_plain_torch_training(cuda, single_group):
     assert eopt.engine.read_control().status == 0
 
 
+def test_an_optimizer_outside_the_available_list_is_stepped_unscaled(cuda, single_group):
+    """The reference accepts any torch optimizer as long as the gradients need no division (fp32, scale 1, no
+    clipping: elixir/wrapper/optimizer.py:52-56, 211-214) and steps it on the fp32 shard views.  SGD with
+    momentum behind the wrapper must train like the same SGD on a plain model, also across a skipped step."""
+    from elixir_b200.wrapper import ElixirModule, ElixirOptimizer, simple_plan
+    torch.manual_seed(5)
+    plain = Mlp().to(cuda)
+    wrapped_model = copy.deepcopy(plain)
+    opt = torch.optim.SGD(plain.parameters(), lr=5e-2, momentum=0.9, weight_decay=1e-3)
+    sr = simple_plan(wrapped_model, 1, split_number=3, unified_dtype=torch.float)
+    inner = torch.optim.SGD(wrapped_model.parameters(), lr=5e-2, momentum=0.9, weight_decay=1e-3)
+    emodel = ElixirModule(wrapped_model, sr, single_group, dtype=torch.float)
+    eopt = ElixirOptimizer(emodel, inner)
+    assert not eopt.scaled_optimizer
+    for step in range(4):
+        x = torch.randn(16, 48, device=cuda)
+        if step == 2:
+            x[0, 0] = float('inf')    # non-finite gradients: both sides leave the parameters alone
+        opt.zero_grad()
+        plain(x).backward()
+        if step != 2:
+            opt.step()
+        eopt.zero_grad()
+        eopt.backward(emodel(x))
+        eopt.step()
+    ctl = eopt.engine.read_control()
+    assert (ctl.step, ctl.skipped_steps, ctl.status) == (3, 1, 0)
+    got = emodel.state_dict()
+    for name, ref in plain.state_dict().items():
+        torch.testing.assert_close(got[name].to(cuda), ref, rtol=2e-6, atol=2e-5)
+    saved = eopt.state_dict()
+    assert 'optim' in saved and len(saved['optim']['state']) > 0
+    eopt.load_state_dict(saved)
+
+
+def test_an_optimizer_outside_the_available_list_is_refused_when_gradients_are_scaled(cuda, single_group):
+    from elixir_b200.wrapper import ElixirModule, ElixirOptimizer, simple_plan
+    torch.manual_seed(6)
+    model = Mlp().to(cuda)
+    sr = simple_plan(model, 1, split_number=3, unified_dtype=torch.float16)
+    emodel = ElixirModule(model, sr, single_group, dtype=torch.float16)
+    eopt = ElixirOptimizer(emodel, torch.optim.SGD(model.parameters(), lr=1e-2), initial_scale=64.0)
+    eopt.zero_grad()
+    eopt.backward(emodel(torch.randn(8, 48, device=cuda)))
+    with pytest.raises(AssertionError, match='available list'):
+        eopt.step()
+
+
+def test_per_parameter_step_counts_follow_the_device_counter(cuda, single_group):
+    """state[p]['step'] is the number of applied updates (skipped steps do not count), as the reference's
+    optimizers keep it; here it is read from the control block when the state is looked at."""
+    torch.manual_seed(7)
+    model = Mlp().to(cuda)
+    emodel, eopt = _wrap(model, single_group, torch.float16, initial_scale=64.0, hysteresis=1)
+    for step in range(4):
+        x = torch.randn(8, 48, device=cuda)
+        if step == 1:
+            x[0, 0] = float('nan')
+        eopt.zero_grad()
+        eopt.backward(emodel(x))
+        eopt.step()
+    steps = {entry['step'] for entry in eopt.state.values()}
+    assert steps == {3}
+    assert eopt.state_dict()['scaler']['step'] == 3
+
+
 @pytest.mark.parametrize('model_cls', [Mlp, TiedNet])
 def test_fp16_step_matches_oracle_on_the_gradients_autograd_produced(cuda, oracle, single_group, model_cls):
     from elixir_b200 import kernels as K
