@@ -210,7 +210,11 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
             engine.add_shard(mine.to(device), torch.zeros(S, dtype=dtype, device=device), nv, [(0, nv, 0)] if nv else [])
         engine.finalize()
         engine.set_hyper(hypers)
-        if collective in ('p2p', 'staged'):
+        if collective == 'mm':
+            engine.enable_single_pass()
+            engine.enable_multicast(chunk_sizes, timeout_ms=5000)
+            gather = [engine.gather_block(c) for c in range(len(chunk_sizes))]
+        elif collective in ('p2p', 'staged'):
             engine.enable_p2p(chunk_sizes, timeout_ms=5000)
             if collective == 'staged':
                 engine.enable_staging(pool=2)
@@ -223,12 +227,18 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
                 rank_grads = []
                 for r in range(world):
                     gen = torch.Generator().manual_seed(seed + 1000 * step + 10 * c + r)
-                    g = (torch.randn(C, generator=gen) * 1e-3 * host_ctl.scale).to(dtype)
+                    if collective == 'mm':
+                        # the switch adds in an order of its own: multiples of a power of two, small enough for
+                        # every partial sum to be exact, make the expected average independent of that order
+                        quantum, limit = (2.0**-6, 31.0) if dtype == torch.float16 else (2.0**-3, 15.0)
+                        g = (torch.round((torch.randn(C, generator=gen) * 4).clamp(-limit, limit) / quantum) * quantum).to(dtype)
+                    else:
+                        g = (torch.randn(C, generator=gen) * 1e-3 * host_ctl.scale).to(dtype)
                     if step == 2 and c == 1 and r == world - 1:
                         g[5] = float('inf')    # lands in rank 0's shard only
                     rank_grads.append(g)
                 per_rank.append(rank_grads)
-                if collective in ('p2p', 'staged'):
+                if collective in ('p2p', 'staged', 'mm'):
                     engine.grad_block(c).copy_(rank_grads[rank])
                 else:
                     blocks.append(rank_grads[rank].to(device))
@@ -236,7 +246,7 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
             for c, C in enumerate(chunk_sizes):
                 S = C // world
                 mine = [g[rank * S:(rank + 1) * S].contiguous() for g in per_rank[c]]
-                if collective in ('p2p', 'staged'):
+                if collective in ('p2p', 'staged', 'mm'):
                     reduced.append(orc.reduce_avg_f32acc(mine))    # rank-order fp32 accumulation, one rounding
                 else:
                     out = torch.empty(S, dtype=dtype, device=device)
@@ -249,11 +259,14 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
                         failure = failure or f'{dtype} step {step} chunk {c}: NCCL average off the divide-then-sum value'
             if collective == 'p2p':
                 engine.step_sharded_p2p()
+            elif collective == 'mm':
+                engine.step_sharded_single_pass()
             elif collective == 'staged':
                 engine.step_sharded_staged()
             else:
                 engine.step_sharded(blocks, gather)
             torch.cuda.synchronize()
+            shards = engine.current_shards()
             for c in range(len(chunk_sizes)):
                 host_state[c][1].copy_(reduced[c])
             if step == 2:
@@ -265,14 +278,14 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
                 failure = failure or f'{dtype} step {step}: control block status={ctl.status} skip={ctl.skip} scale={ctl.scale}'
             for c, C in enumerate(chunk_sizes):
                 S = C // world
-                if not close(engine.shards[c][0], host_state[c][0]):
+                if not close(shards[c][0], host_state[c][0]):
                     failure = failure or f'{dtype} step {step} chunk {c}: master off the oracle'
                 want16 = torch.empty(S, dtype=dtype)
-                orc.cast(engine.shards[c][0].cpu(), want16)
-                if not bits_equal(engine.shards[c][3], want16):
+                orc.cast(shards[c][0].cpu(), want16)
+                if not bits_equal(shards[c][3], want16):
                     failure = failure or f'{dtype} step {step} chunk {c}: working copy is not the rounded master'
-                others = [torch.empty_like(engine.shards[c][3]) for _ in range(world)]
-                dist.all_gather(others, engine.shards[c][3], group=group)
+                others = [torch.empty_like(shards[c][3]) for _ in range(world)]
+                dist.all_gather(others, shards[c][3], group=group)
                 if not bits_equal(gather[c], torch.cat(others)):
                     failure = failure or f'{dtype} step {step} chunk {c}: gathered block differs from the ranks\' shards'
         _KEEP_ALIVE.append(engine)    # peer-mapped buffers stay allocated while other ranks have them mapped
@@ -373,6 +386,9 @@ def run_ours(args):
     engine.set_hyper([K.hyper(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=wd, adamw_mode=True)])
     if args.shards == 'host-streamed':
         engine.enable_streaming(slots=3)
+    single_pass = in_place_sources and args.step == 'single-pass'
+    if single_pass or (world > 1 and args.collective == 'mm'):
+        engine.enable_single_pass()    # second set of master and moments: the update runs out of place
 
     # gradient sources
     if world == 1:
@@ -381,9 +397,12 @@ def run_ours(args):
                 gen = torch.Generator(device=device).manual_seed(args.seed + 7919 * (c + 1))
                 grad_blocks.append(synth_grad(shard, device, gen, scale, sigma, dtype))
         gather_blocks = None
-    elif args.collective in ('p2p', 'staged'):
+    elif args.collective in ('p2p', 'staged', 'mm'):
         # NVLink path: every chunk owns a block in the peer-mapped gradient and gather slabs
-        engine.enable_p2p([chunk] * n_chunks, pool=(args.pool or None) if args.collective == 'p2p' else None)
+        if args.collective == 'mm':
+            engine.enable_multicast([chunk] * n_chunks)
+        else:
+            engine.enable_p2p([chunk] * n_chunks, pool=(args.pool or None) if args.collective == 'p2p' else None)
         if args.collective == 'staged':
             engine.enable_staging(pool=4)
         seeds = 4
@@ -416,6 +435,19 @@ def run_ours(args):
             b.record()
             if record:
                 adam_events.append((a, b))
+        elif single_pass:
+            # ChunkStepEngine.step_single_pass, spelled out so that the update launch can be timed on its own
+            (t0, _), (t1, _) = engine._sets
+            K.step_begin_optimistic(engine.ctl, engine.scaler.cfg, engine.chunk_flags)
+            if record:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+            K.adam_multi_single_pass(t0, t1, engine.ctl, engine.chunk_flags)
+            if record:
+                b.record()
+                adam_events.append((a, b))
+            K.step_commit(engine.ctl, engine.scaler.cfg, engine.chunk_flags)
+            K.adam_multi_repair(t0, t1, engine.ctl)
         elif world == 1:
             if in_place_sources:
                 engine.probe()
@@ -433,6 +465,8 @@ def run_ours(args):
             engine.end_step()
         elif args.collective == 'p2p':
             engine.step_sharded_p2p()
+        elif args.collective == 'mm':
+            engine.step_sharded_single_pass()
         elif args.collective == 'staged':
             engine.step_sharded_staged()
         else:
@@ -500,6 +534,9 @@ def run_ours(args):
             'collectives': 'none (1 GPU)' if world == 1 else
                            ('fused into the kernels over peer-mapped NVLink memory (pull reduce-scatter + probe, '
                             'Adam + push all-gather)' if args.collective == 'p2p' else
+                            'ONE kernel per step through the NVLink switch: per tile the sum of all ranks\' gradients '
+                            '(multimem.ld_reduce), Adam out of place with inf/nan detection, working copy to all ranks '
+                            '(multimem.st); symmetric memory' if args.collective == 'mm' else
                             'copy engines over peer-mapped NVLink memory (staged reduce + probe kernel, fused update, '
                             'copies into the gather blocks)' if args.collective == 'staged' else
                             'NCCL reduce-scatter (pre-multiplied sum) and all-gather per chunk on side streams'),
@@ -537,7 +574,9 @@ def run_ours(args):
                 'peak_kind': 'nominal PCIe Gen5 x16 (no measured figure on this pool)', 'ms_per_launch': adam_ms,
                 'elements_per_launch': n_elems, 'bytes_per_element_each_direction': BYTES_PER_ELEM // 2, 'traffic': None,
             }
-        result['gpu_launches'] = args.steps * ((1 if in_place_sources else n_chunks) + 2)
+        result['gpu_launches'] = args.steps * (4 if single_pass else (1 if in_place_sources else n_chunks) + 2)
+        result['config']['step'] = ('single pass: inf/nan detection inside the update kernel, out of place between two state sets'
+                                    if single_pass else 'probe launch(es), decision, update launch')
     else:
         bus_bytes = 2 * chunk * (world - 1) / world * n_chunks    # per collective kind, per rank, per step
         nominal, peer_copy = 900.0, 770.0    # GB/s per direction: NVLink 5 nominal; one copy-engine peer copy on this pool
@@ -562,7 +601,24 @@ def run_ours(args):
             'target_ms': target_ms, 'frac_of_target': target_ms / ms_per_step,
             'target_note': 'max(NVLink at 900 GB/s, HBM) time of the pull phase + max(NVLink, HBM) time of the update/push phase',
         }
-        if args.collective == 'p2p' and args.pool:
+        if args.collective == 'mm':
+            # one kernel carries both collectives and the update: its bound is the slower of the links (each direction
+            # carries the switch-side sum in and the shard out once, plus every rank's share of the other transfers:
+            # (W + 1) / W of the chunk bytes) and HBM (per own element: master and moments in and out 24 B, working copy
+            # 2 B, plus what the switch reads from this rank's gradient blocks, 2 W B, and writes into its gather
+            # blocks, 2 W B; the reduced gradient itself never touches memory)
+            wire = 2 * chunk * (world + 1) / world * n_chunks
+            mm_link_ms = wire / (nominal * 1e9) * 1e3
+            mm_hbm_ms = engine.n_elements() * (26 + 4 * world) / (peak * 1e9) * 1e3
+            result['roofline'].update(
+                wire_bytes_per_direction=wire, wire_gbs_per_direction=wire / (ms_per_step * 1e-3) / 1e9,
+                target_ms=max(mm_link_ms, mm_hbm_ms), frac_of_target=max(mm_link_ms, mm_hbm_ms) / ms_per_step,
+                target_note='one kernel: max(NVLink time of (W + 1) / W of the chunk bytes per direction at 900 GB/s, HBM time)',
+                note='achieved / frac keep the reduce-scatter + all-gather bus-byte convention (2 (W - 1) / W of the chunk '
+                     'bytes per collective) so that the variants compare; the switch-side sum moves fewer bytes than that')
+            result['gpu_launches'] = args.steps * 7
+            result['phases_ms'] = mm_phases(engine)
+        elif args.collective == 'p2p' and args.pool:
             result['gpu_launches'] = args.steps * (3 * n_chunks + 3)
         elif args.collective == 'p2p':
             result['gpu_launches'] = args.steps * 6
@@ -600,6 +656,26 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def mm_phases(engine):
+    """CUDA-event time of the one fused kernel of an (untimed) single-pass sharded step, barriers not included."""
+    from elixir_b200 import kernels as K
+    (t0, _), (t1, _) = engine._sets
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    engine.peer_barrier(engine.ctl)
+    K.step_begin_optimistic(engine.ctl, engine.scaler.cfg, engine.chunk_flags)
+    ev[0].record()
+    K.adam_multi_single_pass(t0, t1, engine.ctl, engine.chunk_flags, grads_table=engine.grad_slab.table,
+                             gather_table=engine.gather_slab.table, block_off=engine.block_off,
+                             grads_mc=engine.grad_slab.mc_ptr, gather_mc=engine.gather_slab.mc_ptr)
+    ev[1].record()
+    engine.peer_barrier(engine.ctl, exchange_overflow=True)
+    K.step_commit(engine.ctl, engine.scaler.cfg, engine.chunk_flags)
+    K.adam_multi_repair(t0, t1, engine.ctl, gather_table=engine.gather_slab.table, block_off=engine.block_off)
+    engine.peer_barrier(engine.ctl)
+    torch.cuda.synchronize()
+    return {'reduce_adam_gather_one_kernel': ev[0].elapsed_time(ev[1])}
 
 
 def p2p_phases(engine):
@@ -655,6 +731,8 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
         # chunk by chunk: block k filled from the host while earlier chunks are pulled, shard k copied out behind
         # its update while later chunks are updated and pushed
         fn = lambda: engine.step_sharded_p2p(host_grads=grads, host_params=outs)    # noqa: E731
+    elif args.collective == 'mm':
+        fn = lambda: engine.step_sharded_single_pass(host_grads=grads, host_params=outs)    # noqa: E731
     elif args.collective == 'staged':
         def fn():
             for k in range(n_chunks):
@@ -677,6 +755,7 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
         'conservative_ms_per_step': conservative_ms,
         'api': ('ChunkStepEngine.step_from_host' + ('' if conservative_ms is None else '(speculative=True)')) if world == 1 else
                ('ChunkStepEngine.step_sharded_p2p(host_grads=, host_params=)' if args.collective == 'p2p' else
+                'ChunkStepEngine.step_sharded_single_pass(host_grads=, host_params=)' if args.collective == 'mm' else
                 'H2D into the gradient slab + ChunkStepEngine.step_sharded_staged + D2H of the shards'
                 if args.collective == 'staged' else 'ChunkStepEngine.step_sharded(host_grads=, host_params=)'),
         'h2d_gbs_per_gpu': n_chunks * in_elems * 2 / (ms * 1e-3) / 1e9,
@@ -819,14 +898,19 @@ def main():
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--seed', type=int, default=0)
-    ap.add_argument('--collective', default='p2p', choices=['p2p', 'staged', 'nccl'],
-                    help='N > 1: collectives fused into the kernels over peer-mapped NVLink memory, or NCCL')
+    ap.add_argument('--collective', default='auto', choices=['auto', 'p2p', 'mm', 'staged', 'nccl'],
+                    help='N > 1: p2p = pull reduce-scatter and push all-gather kernels over peer-mapped NVLink memory; '
+                    'mm = ONE kernel per step that reduces, updates and gathers tile by tile through the NVLink switch '
+                    '(multimem); staged = copy engines; nccl = NCCL on side streams; auto = mm from 8 ranks on, else p2p')
     ap.add_argument('--workload', default='auto', choices=['auto', 'opt66b_bf16'],
                     help='N > 1: auto = OPT-13B-shaped fp16 chunk set; opt66b_bf16 = OPT-66B-shaped bf16 chunk set (8 GPUs)')
     ap.add_argument('--chunk-elems', type=int, default=0, help='override the chunk size in elements (profiling cases)')
     ap.add_argument('--params', type=int, default=0, help='override the parameter count (smoke runs of a workload)')
     ap.add_argument('--pool', type=int, default=0,
                     help='N > 1: number of replicated blocks per slab (0 = one per chunk); chunk k uses block k %% pool')
+    ap.add_argument('--step', choices=['single-pass', 'probe-update'], default='single-pass',
+                    help='N = 1: single-pass = ONE update launch that also detects inf/nan, out of place between two sets '
+                    'of master/moment arrays; probe-update = a probe launch over all gradient blocks, then the update in place')
     ap.add_argument('--landing', choices=['none', 'copy'], default='none',
                     help='N = 1: none = probe and update read the gradient blocks in place; copy = every block is first '
                     'copied into its shard by the reduce epilogue (probe fused), one launch per chunk')
@@ -846,6 +930,8 @@ def main():
                     "'host-streamed': the same state moved by the copy engines through device staging sets (N=1 only)")
     ap.add_argument('--e2e-steps', type=int, default=10)
     args = ap.parse_args()
+    if args.collective == 'auto':
+        args.collective = 'mm' if args.gpus >= 8 and args.workload == 'auto' and not args.pool else 'p2p'
     if args.impl == 'reference':
         run_reference(args)
     else:

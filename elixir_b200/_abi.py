@@ -38,7 +38,14 @@ class ElxCtl(C.Structure):
         ('forced_skips', C.c_uint32),
         ('clip_coef', C.c_float),
         ('grad_norm', C.c_float),
-        ('reserved', C.c_uint32 * 18),
+        ('cur_set', C.c_uint32),
+        ('spec_state', C.c_uint32),
+        ('repair', C.c_uint32),
+        ('saved_scale', C.c_float),
+        ('saved_growth_step', C.c_int32),
+        ('saved_hysteresis_step', C.c_int32),
+        ('saved_step', C.c_int32),
+        ('reserved', C.c_uint32 * 11),
     ]
 
 
@@ -136,6 +143,11 @@ PROTOTYPES = {
     'elx_adam_multi': (_i, [_p, _i, _i, _i64, _i, _p, _p, _i, _p, _p]),
     'elx_adam_multi_hostmem': (_i, [_p, _i, _i, _i64, _i, _p, _p, _i, _p, _p]),
     'elx_adam_multi_shadow': (_i, [_p, _p, _i, _i, _i64, _i, _p, _p, _i, _p, _p]),
+    'elx_step_begin_optimistic': (_i, [_p, ElxScalerCfg, _p, _i, _p]),
+    'elx_step_commit': (_i, [_p, ElxScalerCfg, _p, _i, _p]),
+    'elx_adam_multi_single_pass': (_i, [_p, _p, _i, _i, _i64, _i, _p, _p, _i, _p, _p, ElxPeerTable, ElxPeerTable, _p, _p,
+                                        _p, _p]),
+    'elx_adam_multi_repair': (_i, [_p, _p, _i, _i, _i64, _i, _p, ElxPeerTable, _p, _p, _p]),
     'elx_enable_peer_access': (_i, [_i]),
     'elx_peer_alloc': (_i, [_i64, C.POINTER(C.c_void_p), _p]),
     'elx_peer_free': (_i, [_p]),

@@ -82,6 +82,14 @@ struct AdamArgs {
     // out-of-place update: the new master and moments of descriptor c go to shadow[c]'s arrays (bulk-copy
     // variant only); NULL = in place
     const ElxChunkDesc* shadow;
+    // single-pass step over two sets of state (descs = set 0, shadow = set 1)
+    int spec;                  // 1: read the set ctl->cur_set names, write the other one, probe the gradients in flight
+    int repair;                // 1: run only when ctl->repair is set; rebuild the working copies from the current set
+    uint32_t* chunk_flags;     // per-descriptor overflow words raised by the in-flight probe (may be null)
+    // collectives through the switch: multicast addresses of all ranks' gradient / gather slabs (null = none)
+    const char* mc_grads;
+    char* mc_gather;
+    ElxPeerTable grads;        // the gradient slabs as plain peer addresses (ragged tiles)
     // single-shard form: the three tables travel in the kernel parameters
     ElxChunkDesc one_desc;
     ElxSeg one_seg;
@@ -295,18 +303,19 @@ struct TileSlot {
     float* master;
     float* exp_avg;
     float* exp_avg_sq;
-    float* out_master;      // where the updated values go: the same arrays, or the shadow set's
+    float* out_master;      // where the updated values go: the same arrays, or the other set's
     float* out_exp_avg;
     float* out_exp_avg_sq;
     void* lowp;
     const void* gsrc;       // where the gradient is read: the low-precision shard itself or a separate source
     const ElxSeg* segs;
     int64_t e0, e1;
-    int64_t push_elem;   // element offset of this tile inside every rank's gather slab (push all-gather)
+    int64_t n_valid;
+    int64_t push_elem;   // element offset of this tile inside every rank's gather (and gradient) slab
     int n_segs;
     int group;
     int kind;
-    int pad;
+    int chunk;
 };
 
 template <int DT>
@@ -331,17 +340,20 @@ struct ProducerCursor {
     int seg_chunk = -1;
 };
 
+// src: the table whose master and moments are read.  dst: the table whose arrays receive the update, or
+// null for an update in place.  probe_gaps: whole tiles below valid_end that no segment covers still have
+// their gradients looked at (single-pass step), so they are not refresh-only.
 template <int DT>
-__device__ __forceinline__ void classify_tile(const AdamArgs& a, const ElxChunkDesc* __restrict__ descs,
-                                              const ElxSeg* __restrict__ segs, int64_t t, ProducerCursor& pc,
-                                              TileSlot& out) {
+__device__ __forceinline__ void classify_tile(const AdamArgs& a, const ElxChunkDesc* __restrict__ src,
+                                              const ElxChunkDesc* __restrict__ dst, const ElxSeg* __restrict__ segs,
+                                              bool probe_gaps, int64_t t, ProducerCursor& pc, TileSlot& out) {
     if (!(t >= pc.t0 && t < pc.t1)) {
         int lo = a.first, hi = a.first + a.count - 1;
         while (lo < hi) {
             int mid = (lo + hi + 1) >> 1;
-            if (descs[mid].tile_begin <= t) lo = mid; else hi = mid - 1;
+            if (src[mid].tile_begin <= t) lo = mid; else hi = mid - 1;
         }
-        pc.d = descs[lo];
+        pc.d = src[lo];
         pc.index = lo;
         pc.t0 = pc.d.tile_begin;
         pc.t1 = pc.t0 + tiles_of(pc.d.n_shard);
@@ -352,12 +364,12 @@ __device__ __forceinline__ void classify_tile(const AdamArgs& a, const ElxChunkD
         pc.out_exp_avg = pc.d.exp_avg;
         pc.out_exp_avg_sq = pc.d.exp_avg_sq;
         pc.shadow_ok = true;
-        if (a.shadow) {
-            const ElxChunkDesc sd = a.shadow[lo];
+        if (dst) {
+            const ElxChunkDesc sd = dst[lo];
             pc.out_master = sd.master;
             pc.out_exp_avg = sd.exp_avg;
             pc.out_exp_avg_sq = sd.exp_avg_sq;
-            // the shadow descriptor must describe the same shard, with arrays of its own
+            // the other descriptor must describe the same shard, with arrays of its own
             pc.shadow_ok = sd.n_shard == pc.d.n_shard && sd.tile_begin == pc.d.tile_begin && sd.master &&
                            sd.exp_avg && sd.exp_avg_sq;
             bits |= reinterpret_cast<uintptr_t>(sd.master) | reinterpret_cast<uintptr_t>(sd.exp_avg) |
@@ -397,18 +409,43 @@ __device__ __forceinline__ void classify_tile(const AdamArgs& a, const ElxChunkD
     out.n_segs = pc.d.seg_count;
     out.e0 = e0;
     out.e1 = e1;
+    out.n_valid = pc.d.n_valid;
     out.group = pc.seg_group;
+    out.chunk = pc.index;
     out.push_elem = a.push.world > 0 ? push_base_elem(a, pc.index, pc.d.n_shard) + e0 : 0;
     const bool push_ok = a.push.world == 0 || (out.push_elem & 15) == 0;   // bulk copies need 16-byte alignment
     const bool whole = e1 - e0 == kTile && pc.vec_ok && push_ok;
     if (whole && one_group) out.kind = kTileBulk;
-    else if (whole && range_uncovered(csegs, pc.d.seg_count, e0, e1, pc.d.n_valid)) out.kind = kTileRefresh;
+    else if (whole && (e0 >= pc.d.n_valid || (!probe_gaps && range_uncovered(csegs, pc.d.seg_count, e0, e1, pc.d.n_valid))))
+        out.kind = kTileRefresh;
     else out.kind = kTileRagged;
 }
 
-template <int DT, int MATH>
+// multimem: one access for all ranks of an NVLink domain, carried out by the switch.  ld_reduce returns the
+// sum over the ranks' copies of the addressed words (fp32 accumulation, one rounding to the 16-bit format);
+// st delivers the words to every rank's copy.  8 bytes (4 elements) per access.
+template <int DT>
+__device__ __forceinline__ uint2 mm_ld_reduce8(const void* mc) {
+    uint2 r;
+    if constexpr (DT == ELX_BF16) {
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v2.bf16x2 {%0,%1}, [%2];"
+                     : "=r"(r.x), "=r"(r.y) : "l"(mc) : "memory");
+    } else {
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v2.f16x2 {%0,%1}, [%2];"
+                     : "=r"(r.x), "=r"(r.y) : "l"(mc) : "memory");
+    }
+    return r;
+}
+__device__ __forceinline__ void mm_st8(void* mc, uint2 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1,%2};" ::"l"(mc), "r"(v.x), "r"(v.y) : "memory");
+}
+
+// MM: the gradient tile is the switch-side sum over all ranks' gradient slabs and the refreshed working copy
+// is multicast to all ranks' gather slabs (16-bit chunks only).
+template <int DT, int MATH, bool MM>
 __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_constant__ AdamArgs a) {
     using Stage = TmaStage<DT>;
+    static_assert(!MM || DT != ELX_F32, "the multicast form is for 16-bit chunks");
     extern __shared__ __align__(128) unsigned char s_dyn[];
     __shared__ GroupK s_group[kMaxGroups];
     __shared__ TileSlot s_slot[kTmaStages];
@@ -420,11 +457,19 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
     const ElxHyper* __restrict__ hyper = a.inline_tables ? &a.one_hyper : a.hyper;
     ElxCtl* ctl = a.ctl;
 
-    if (ctl->skip != 0) {
+    // which table is read and which is written: in place, out of place (shadow), or the two sets of the
+    // single-pass step whose roles follow ctl->cur_set
+    const bool spec = a.spec != 0;
+    const bool flipped = spec && ctl->cur_set != 0;
+    const ElxChunkDesc* __restrict__ src = flipped ? a.shadow : descs;
+    const ElxChunkDesc* __restrict__ dst = spec ? (flipped ? descs : a.shadow) : a.shadow;
+
+    if (a.repair && ctl->repair == 0) return;
+    if (ctl->skip != 0 || a.repair) {
         // skipped step: copy-back only, with direct accesses (6 bytes per element, no staging needed)
         __shared__ ChunkCursor s_cur;
         cursor_reset(s_cur);
-        const bool bad = copyback_tiles<DT, kTile / kTmaThreads>(a, descs, s_cur);
+        const bool bad = copyback_tiles<DT, kTile / kTmaThreads>(a, src, s_cur);
         if (__ballot_sync(0xFFFFFFFFu, bad) && (threadIdx.x & 31) == 0) atomicOr(&ctl->status, ELX_STAT_BAD_DESC);
         return;
     }
@@ -441,8 +486,10 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
     }
     __syncthreads();
 
-    const int64_t tile_lo = descs[a.first].tile_begin;
+    const int64_t tile_lo = src[a.first].tile_begin;
     const int64_t my_tiles = blockIdx.x < a.n_tiles ? (a.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const float inv_w = MM ? 1.0f / static_cast<float>(a.push.world) : 1.0f;
+    constexpr uint32_t kLoadBytes = MM ? 3 * Stage::kF32Bytes : Stage::kBytes;   // MM: no gradient tile from HBM
     ProducerCursor pc;
     float nan_acc = 0.0f;
     bool bad_desc = false;
@@ -452,12 +499,14 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         const int s = static_cast<int>(k % kTmaStages);
         TileSlot slot;
         slot.kind = kTileNone;
-        classify_tile<DT>(a, descs, segs, tile_lo + blockIdx.x + k * gridDim.x, pc, slot);
+        classify_tile<DT>(a, src, dst, segs, spec, tile_lo + blockIdx.x + k * gridDim.x, pc, slot);
         s_slot[s] = slot;
         if (slot.kind == kTileBulk) {
             unsigned char* base = s_dyn + static_cast<size_t>(s) * Stage::kBytes;
-            mbar_arrive_expect_tx(&s_full[s], Stage::kBytes);
-            bulk_g2s(base, static_cast<const char*>(slot.gsrc) + slot.e0 * Lp<DT>::kBytes, Stage::kLowpBytes, &s_full[s]);
+            mbar_arrive_expect_tx(&s_full[s], kLoadBytes);
+            if (!MM)
+                bulk_g2s(base, static_cast<const char*>(slot.gsrc) + slot.e0 * Lp<DT>::kBytes, Stage::kLowpBytes,
+                         &s_full[s]);
             bulk_g2s(base + Stage::kLowpBytes, slot.master + slot.e0, Stage::kF32Bytes, &s_full[s]);
             bulk_g2s(base + Stage::kLowpBytes + Stage::kF32Bytes, slot.exp_avg + slot.e0, Stage::kF32Bytes, &s_full[s]);
             bulk_g2s(base + Stage::kLowpBytes + 2 * Stage::kF32Bytes, slot.exp_avg_sq + slot.e0, Stage::kF32Bytes,
@@ -475,6 +524,25 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         for (int64_t k = 0; k < my_tiles && k < kTmaStages - 1; ++k) produce(k);
     }
 
+    // MM: the thread's own 2 x 4 gradient elements of the NEXT tile, asked from the switch one tile ahead and
+    // held in registers (a thread consumes exactly the elements it fetched)
+    constexpr int kHalves = kTile / (kTmaThreads * 4);   // 2
+    uint2 g_now[kHalves], g_next[kHalves];
+    auto fetch = [&](int64_t k, uint2 (&g)[kHalves]) {
+        if (k >= my_tiles) return;
+        const TileSlot& nx = s_slot[k % kTmaStages];
+        if (nx.kind != kTileBulk) return;
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h) {
+            const int e = h * (kTmaThreads * 4) + threadIdx.x * 4;
+            g[h] = mm_ld_reduce8<DT == ELX_F32 ? ELX_F16 : DT>(a.mc_grads + (nx.push_elem + e) * 2);
+        }
+    };
+    if constexpr (MM) {
+        __syncthreads();   // the first slots are published
+        fetch(0, g_now);
+    }
+
     int64_t k = 0;
     for (; k < my_tiles; ++k) {
         const int s = static_cast<int>(k % kTmaStages);
@@ -484,6 +552,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         if (s_abort) break;
         const TileSlot slot = s_slot[s];   // into registers: measured 1.3 % faster than reading the fields from shared memory
         unsigned char* base = s_dyn + static_cast<size_t>(s) * Stage::kBytes;
+        if constexpr (MM) fetch(k + 1, g_next);   // slot k + 1 was published before the barrier above
 
         if (slot.kind == kTileBulk) {
             const GroupK k_ = s_group[slot.group];
@@ -492,7 +561,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
             float* sv = sm + kTile;
             // a thread owns 2 x 4 consecutive elements, 2048 apart: conflict-free 128-bit shared accesses
 #pragma unroll
-            for (int h = 0; h < kTile / (kTmaThreads * 4); ++h) {
+            for (int h = 0; h < kHalves; ++h) {
                 const int e = h * (kTmaThreads * 4) + threadIdx.x * 4;
                 float4 p = *reinterpret_cast<float4*>(sp + e);
                 float4 m = *reinterpret_cast<float4*>(sm + e);
@@ -502,9 +571,15 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                     const float4 gg = *reinterpret_cast<const float4*>(base + static_cast<size_t>(e) * 4);
                     g[0] = gg.x; g[1] = gg.y; g[2] = gg.z; g[3] = gg.w;
                 } else {
-                    const uint2 gg = *reinterpret_cast<const uint2*>(base + static_cast<size_t>(e) * 2);
+                    uint2 gg;
+                    if constexpr (MM) gg = g_now[h];
+                    else gg = *reinterpret_cast<const uint2*>(base + static_cast<size_t>(e) * 2);
                     const float2 a0 = Lp<DT>::unpack2(gg.x), a1 = Lp<DT>::unpack2(gg.y);
                     g[0] = a0.x; g[1] = a0.y; g[2] = a1.x; g[3] = a1.y;
+                    if constexpr (MM) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) g[j] *= inv_w;   // the switch summed; the step wants the average
+                    }
                 }
                 float pp[4] = {p.x, p.y, p.z, p.w}, mm[4] = {m.x, m.y, m.z, m.w}, vv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -522,13 +597,15 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                     out.x = Lp<DT>::pack2(pp[0], pp[1]);
                     out.y = Lp<DT>::pack2(pp[2], pp[3]);
                     *reinterpret_cast<uint2*>(base + static_cast<size_t>(e) * 2) = out;
+                    // all-gather: one store to the multicast address reaches every rank's gather block
+                    if constexpr (MM) mm_st8(a.mc_gather + (slot.push_elem + e) * 2, out);
                 }
             }
             fence_async_smem();   // the bulk stores below read what the threads just wrote
         } else if (slot.kind == kTileRefresh) {
             const float* sp = reinterpret_cast<const float*>(base + Stage::kLowpBytes);
 #pragma unroll
-            for (int h = 0; h < kTile / (kTmaThreads * 4); ++h) {
+            for (int h = 0; h < kHalves; ++h) {
                 const int e = h * (kTmaThreads * 4) + threadIdx.x * 4;
                 const float4 p = *reinterpret_cast<const float4*>(sp + e);
                 if constexpr (DT == ELX_F32) {
@@ -538,6 +615,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                     out.x = Lp<DT>::pack2(p.x, p.y);
                     out.y = Lp<DT>::pack2(p.z, p.w);
                     *reinterpret_cast<uint2*>(base + static_cast<size_t>(e) * 2) = out;
+                    if constexpr (MM) mm_st8(a.mc_gather + (slot.push_elem + e) * 2, out);
                 }
             }
             fence_async_smem();
@@ -546,12 +624,25 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
             const typename Lp<DT>::T* gin = static_cast<const typename Lp<DT>::T*>(slot.gsrc);
             for (int64_t e = slot.e0 + threadIdx.x; e < slot.e1; e += blockDim.x) {
                 float p = slot.master[e];
+                float g = 0.0f;
+                if (e < slot.n_valid) {
+                    if constexpr (MM) {
+                        // the same value the switch would return: rank-order fp32 sum, one rounding, then 1/W
+                        float acc = 0.0f;
+                        for (int j = 0; j < a.grads.world; ++j)
+                            acc += Lp<DT>::to_float(
+                                static_cast<const typename Lp<DT>::T*>(a.grads.base[j])[slot.push_elem + (e - slot.e0)]);
+                        g = Lp<DT>::to_float(Lp<DT>::from_float(acc)) * inv_w;
+                    } else {
+                        g = Lp<DT>::to_float(gin[e]);
+                    }
+                    if (spec) nan_acc = fmaf(0.0f, g, nan_acc);   // the single-pass step probes all of [0, n_valid)
+                }
                 const int si = find_seg(slot.segs, slot.n_segs, e);
                 if (si >= 0 && e < slot.segs[si].end) {
                     const int ge = slot.segs[si].group;
                     if (ge >= 0 && ge < a.n_groups) {
                         const GroupK k_ = s_group[ge];
-                        float g = Lp<DT>::to_float(gin[e]);
                         float m = slot.exp_avg[e], v = slot.exp_avg_sq[e];
                         nan_acc = fmaf(0.0f, g, nan_acc);
                         adam_elem<MATH>(p, m, v, g, k_, div_mode, div, inv_div);
@@ -568,6 +659,16 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         } else if (slot.kind == kTileBad) {
             bad_desc = true;
         }
+        if (spec) {
+            // single-pass step: a non-finite gradient met in this tile raises the overflow words now
+            // (the update went to the other set and will not be adopted)
+            const unsigned hit = __ballot_sync(0xFFFFFFFFu, nan_acc != nan_acc);
+            if (hit && (threadIdx.x & 31) == 0) {
+                atomicOr(&ctl->found_inf, 1u);
+                if (a.chunk_flags) atomicOr(&a.chunk_flags[slot.chunk], 1u);
+            }
+            nan_acc = 0.0f;
+        }
         __syncthreads();   // the stage is fully written (bulk) / fully consumed
 
         if (threadIdx.x == 0) {
@@ -579,13 +680,15 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                     bulk_s2g(slot.out_exp_avg_sq + slot.e0, base + Stage::kLowpBytes + 2 * Stage::kF32Bytes,
                              Stage::kF32Bytes);
                 }
-                // push all-gather: the same 8 KB of refreshed parameters to every rank's gather block,
-                // plain (non-multicast) bulk stores, W - 1 of them crossing NVLink
-                // (start with a different rank in every CTA, so that the stores spread over all links at once)
-                for (int i = 0; i < a.push.world; ++i) {
-                    const int j = (a.push.rank + 1 + i + static_cast<int>(blockIdx.x)) % a.push.world;
-                    bulk_s2g(static_cast<char*>(a.push.base[j]) + slot.push_elem * Lp<DT>::kBytes, base,
-                             Stage::kLowpBytes);
+                if constexpr (!MM) {
+                    // push all-gather: the same 8 KB of refreshed parameters to every rank's gather block,
+                    // plain (non-multicast) bulk stores, W - 1 of them crossing NVLink
+                    // (start with a different rank in every CTA, so that the stores spread over all links at once)
+                    for (int i = 0; i < a.push.world; ++i) {
+                        const int j = (a.push.rank + 1 + i + static_cast<int>(blockIdx.x)) % a.push.world;
+                        bulk_s2g(static_cast<char*>(a.push.base[j]) + slot.push_elem * Lp<DT>::kBytes, base,
+                                 Stage::kLowpBytes);
+                    }
                 }
             }
             bulk_commit();
@@ -593,6 +696,10 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                 bulk_wait_read<1>();   // the stage of tile k-1 has been read out by its stores
                 produce(k + kTmaStages - 1);
             }
+        }
+        if constexpr (MM) {
+#pragma unroll
+            for (int h = 0; h < kHalves; ++h) g_now[h] = g_next[h];
         }
     }
     if (threadIdx.x == 0) {
@@ -606,7 +713,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         bulk_wait_all();
     }
 
-    const bool late = nan_acc != nan_acc;
+    const bool late = !spec && nan_acc != nan_acc;
     const unsigned ballot = __ballot_sync(0xFFFFFFFFu, late);
     const unsigned ballot_desc = __ballot_sync(0xFFFFFFFFu, bad_desc);
     if ((threadIdx.x & 31) == 0) {
@@ -617,6 +724,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         if (ballot_desc) atomicOr(&ctl->status, ELX_STAT_BAD_DESC);
     }
 }
+
 
 template <int DT>
 __global__ void __launch_bounds__(256) cast_kernel(const float* __restrict__ src, void* dst, int64_t n, int vec_ok) {
@@ -648,7 +756,7 @@ int launch_adam_minb(const AdamArgs& a, cudaStream_t s) {
     return launch_adam_inst<DT, EPT, MATH, 2>(a, s);
 }
 
-template <int DT, int MATH>
+template <int DT, int MATH, bool MM = false>
 int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
     constexpr int smem = kTmaStages * TmaStage<DT>::kBytes;
     // the opt-in to more than 48 KB of dynamic shared memory is per device: once for each ordinal
@@ -660,7 +768,7 @@ int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
     }
     if (!opted_in[dev]) {
         const cudaError_t attr =
-            cudaFuncSetAttribute(adam_tma_kernel<DT, MATH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            cudaFuncSetAttribute(adam_tma_kernel<DT, MATH, MM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (attr != cudaSuccess) {
             const int rc = record_cuda(attr);
             (void)cudaGetLastError();
@@ -670,13 +778,17 @@ int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
     }
     const int grid = grid_for(a.n_tiles, 1);
     if (grid < 0) return grid;
-    adam_tma_kernel<DT, MATH><<<grid, kTmaThreads, smem, s>>>(a);
+    adam_tma_kernel<DT, MATH, MM><<<grid, kTmaThreads, smem, s>>>(a);
     return record_cuda(cudaGetLastError());
 }
 
 template <int DT>
 int launch_adam_dt(const AdamArgs& a, cudaStream_t s) {
     const bool precise = g_tune.math_mode == 1;
+    if (a.mc_grads) {
+        if constexpr (DT == ELX_F32) return ELX_ERR_DTYPE;   // the switch-side sum is used for 16-bit chunks
+        else return precise ? launch_adam_tma<DT, 1, true>(a, s) : launch_adam_tma<DT, 2, true>(a, s);
+    }
     if ((g_tune.adam_variant == 1 && !a.force_direct) || a.push.world > 0 || a.shadow)
         return precise ? launch_adam_tma<DT, 1>(a, s) : launch_adam_tma<DT, 2>(a, s);
     if (g_tune.adam_threads == 256)
@@ -739,6 +851,79 @@ int elx_adam_multi_shadow(const ElxChunkDesc* descs, const ElxChunkDesc* shadow,
                           ElxCtl* ctl, void* stream) {
     if (!shadow) return ELX_ERR_NULL;
     return adam_multi_common(descs, first, count, n_tiles, dtype, segs, hyper, n_groups, ctl, stream, 0, shadow);
+}
+
+static int single_pass_common(const ElxChunkDesc* descs, const ElxChunkDesc* shadow, int first, int count,
+                              int64_t n_tiles, int dtype, const ElxSeg* segs, const ElxHyper* hyper, int n_groups,
+                              ElxCtl* ctl, uint32_t* chunk_flags, const ElxPeerTable* grads, const ElxPeerTable* gather,
+                              const int64_t* block_off, const void* grads_mc, void* gather_mc, int repair, void* stream) {
+    if (!descs || !shadow || !ctl) return ELX_ERR_NULL;
+    if (!repair && n_groups > 0 && (!segs || !hyper)) return ELX_ERR_NULL;
+    if (!dtype_ok(dtype)) return ELX_ERR_DTYPE;
+    if (first < 0 || count < 0 || n_tiles < 0 || n_groups < 0) return ELX_ERR_SIZE;
+    if (n_groups > kMaxGroups) return ELX_ERR_CAPACITY;
+    if (!aligned(descs, 8) || !aligned(shadow, 8) || !aligned(ctl, 16) || (segs && !aligned(segs, 8)) ||
+        (hyper && !aligned(hyper, 4)) || (chunk_flags && !aligned(chunk_flags, 4)))
+        return ELX_ERR_ALIGN;
+    const bool sharded = gather && gather->world > 0;
+    if (sharded) {
+        if (!block_off) return ELX_ERR_NULL;
+        if (!aligned(block_off, 8)) return ELX_ERR_ALIGN;
+        int rc = peer_table_ok(*gather);
+        if (rc != ELX_OK) return rc;
+        if (!repair) {
+            // the gradient of a shard is the sum over the ranks' slabs: both views of the slabs are needed
+            if (!grads || !grads_mc || !gather_mc) return ELX_ERR_NULL;
+            rc = peer_table_ok(*grads);
+            if (rc != ELX_OK) return rc;
+            if (grads->world != gather->world || grads->rank != gather->rank) return ELX_ERR_ARG;
+            if (!aligned(grads_mc, 32) || !aligned(gather_mc, 32)) return ELX_ERR_ALIGN;
+            if (dtype == ELX_F32) return ELX_ERR_DTYPE;
+        }
+    } else if (grads_mc || gather_mc) {
+        return ELX_ERR_ARG;
+    }
+    if (count == 0 || n_tiles == 0) return ELX_OK;
+    AdamArgs a;
+    memset(&a, 0, sizeof(a));
+    a.descs = descs;
+    a.shadow = shadow;
+    a.segs = segs;
+    a.hyper = hyper;
+    a.ctl = ctl;
+    a.first = first;
+    a.count = count;
+    a.n_groups = n_groups;
+    a.n_tiles = n_tiles;
+    a.spec = 1;
+    a.repair = repair;
+    a.chunk_flags = chunk_flags;
+    if (sharded) {
+        a.push = *gather;
+        a.push_off = block_off;
+        if (!repair) {
+            a.grads = *grads;
+            a.mc_grads = static_cast<const char*>(grads_mc);
+            a.mc_gather = static_cast<char*>(gather_mc);
+        }
+    }
+    return launch_adam(a, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int elx_adam_multi_single_pass(const ElxChunkDesc* descs, const ElxChunkDesc* shadow, int first, int count,
+                               int64_t n_tiles, int dtype, const ElxSeg* segs, const ElxHyper* hyper, int n_groups,
+                               ElxCtl* ctl, uint32_t* chunk_flags, ElxPeerTable grads, ElxPeerTable gather,
+                               const int64_t* block_off, const void* grads_mc, void* gather_mc, void* stream) {
+    return single_pass_common(descs, shadow, first, count, n_tiles, dtype, segs, hyper, n_groups, ctl, chunk_flags,
+                              &grads, &gather, block_off, grads_mc, gather_mc, 0, stream);
+}
+
+int elx_adam_multi_repair(const ElxChunkDesc* descs, const ElxChunkDesc* shadow, int first, int count, int64_t n_tiles,
+                          int dtype, ElxCtl* ctl, ElxPeerTable gather, const int64_t* block_off, void* gather_mc,
+                          void* stream) {
+    (void)gather_mc;   // the rebuilt working copies go out with plain peer stores
+    return single_pass_common(descs, shadow, first, count, n_tiles, dtype, nullptr, nullptr, 0, ctl, nullptr, nullptr,
+                              &gather, block_off, nullptr, nullptr, 1, stream);
 }
 
 int elx_adam_multi_push(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,

@@ -54,7 +54,7 @@ class ChunkStepEngine:
         self._scratch: Optional[torch.Tensor] = None
         self._streams = None
         self._slots = None    # device staging sets of the streamed update (enable_streaming)
-        self._twin = None     # second set of master/moment arrays and its table (enable_speculation)
+        self._sets = None     # the two sets of master/moment arrays of the single-pass step (enable_single_pass)
 
     # ------------------------------------------------------------------ registration
 
@@ -538,7 +538,7 @@ class ChunkStepEngine:
         ``speculative`` (after ``enable_speculation``) lifts that, see ``_step_from_host_speculative``."""
         assert len(host_grads) == self.n_chunks and len(host_params) == self.n_chunks
         if speculative:
-            assert self._twin is not None, 'enable_speculation() first'
+            assert self._sets is not None, 'enable_speculation() first'
             return self._step_from_host_speculative(host_grads, host_params)
         main = torch.cuda.current_stream(self.device)
         h2d, d2h = self._side_streams()
@@ -561,15 +561,18 @@ class ChunkStepEngine:
         self.end_step()
         main.wait_stream(d2h)
 
-    # ------------------------------------------------------------------ speculative step with host buffers
+    # ------------------------------------------------------------------ single-pass step over two state sets
 
-    def enable_speculation(self):
-        """Prepare ``step_from_host(..., speculative=True)``: a second set of master and moment arrays per shard
-        (12 bytes per element more) and its descriptor table.  The update then reads one set and writes the
-        other, and the sets swap roles after every applied step."""
+    def enable_single_pass(self):
+        """Prepare the single-pass step: a second set of master and moment arrays per shard (12 bytes per element
+        more) and its descriptor table.  ``step_single_pass`` / ``step_sharded_single_pass`` then read the current
+        set and write the other one; which one is current is a word of the device control block, so the host never
+        has to know (``current_shards`` reads it back for checkpoints and tests)."""
         assert self.table.descs_dev is not None, 'finalize() first'
-        if self.world > 1 or self.clipping or self.table.host_resident:
-            raise RuntimeError('the speculative step is for one rank, device-resident shards and no gradient clipping '
+        if self._sets is not None:
+            return self
+        if self.clipping or self.table.host_resident:
+            raise RuntimeError('the single-pass step is for device-resident shards and no gradient clipping '
                                '(the clip factor needs every gradient before the first update)')
         other = kernels.ChunkTable(self.device, self.dtype)
         other_shards = []
@@ -578,29 +581,147 @@ class ChunkStepEngine:
             other.add_chunk(twin[0], twin[1], twin[2], lowp, n_valid, self.table._segs_of(k), grad_src=self.grad_srcs[k])
             other_shards.append((twin[0], twin[1], twin[2], lowp, n_valid))
         other.finalize()
-        self._twin = (other, other_shards)
-        self._ctl_backup = torch.empty_like(self.ctl.tensor)
+        self._sets = ((self.table, self.shards), (other, other_shards))
+        return self
 
-    def _swap_sets(self):
-        (other, other_shards), mine = self._twin, (self.table, self.shards)
-        other.set_hyper_from(self.table)
-        self.table, self.shards = other, other_shards
-        self._twin = mine
+    def current_shards(self):
+        """The shard tuples of the state set that is current (synchronises: reads the control block)."""
+        if self._sets is None:
+            return self.shards
+        return self._sets[int(self.ctl.read().cur_set)][1]
+
+    def normalize_sets(self):
+        """Make the current state set "set 0" again (``self.table`` / ``self.shards``), so that the in-place paths
+        (``step``, ``step_from_host``, checkpoints) see the live state after single-pass steps.  Synchronises."""
+        if self._sets is None:
+            return
+        c = self.ctl.read()
+        if c.cur_set:
+            self._sets = (self._sets[1], self._sets[0])
+            self._sets[0][0].set_hyper_from(self._sets[1][0])
+            self.table, self.shards = self._sets[0]
+            c.cur_set = 0
+            self.ctl.write(c)
+
+    def step_single_pass(self):
+        """One rank's step as ONE pass over memory (28 bytes per element with 16-bit gradients, no separate probe):
+
+            elx_step_begin_optimistic    decision on the assumption of no overflow
+            elx_adam_multi_single_pass   unscale + inf/nan detection + Adam/AdamW + working copy, out of place
+            elx_step_commit              clean: the sets change roles; overflow: the decision is taken back -> skip
+            elx_adam_multi_repair        only after an overflow: working copies rebuilt from the untouched set
+
+        Four launches, nothing read back.  Gradients sit, unprobed, where the update reads them (the shards or the
+        sources given to ``add_shard``)."""
+        (t0, _), (t1, _) = self._sets
+        t1.set_hyper_from(t0)
+        kernels.step_begin_optimistic(self.ctl, self.scaler.cfg, self.chunk_flags)
+        kernels.adam_multi_single_pass(t0, t1, self.ctl, self.chunk_flags)
+        kernels.step_commit(self.ctl, self.scaler.cfg, self.chunk_flags)
+        kernels.adam_multi_repair(t0, t1, self.ctl)
+
+    def enable_multicast(self, chunk_sizes: Sequence[int], timeout_ms: int = 20000):
+        """Slabs for ``step_sharded_single_pass``: like ``enable_p2p`` (a gradient block and a gather block of
+        ``chunk_sizes[k]`` elements per chunk on every rank), but in symmetric memory bound to an NVLink multicast
+        object, so that the switch can add up the ranks' gradient blocks and deliver one store to all gather blocks."""
+        from .peer import PeerBarrier, SymmBuffer
+        assert len(chunk_sizes) == self.n_chunks
+        for k, size in enumerate(chunk_sizes):
+            if size != self.shards[k][0].numel() * self.world:
+                raise ValueError(f'chunk {k}: chunk size {size} is not world x shard size')
+        offsets, total = [], 0
+        for size in chunk_sizes:
+            offsets.append(total)
+            total += (size + 15) // 16 * 16
+        self._p2p_pool = 0
+        self._p2p_sizes = list(chunk_sizes)
+        self._p2p_offsets = offsets
+        self.block_off = torch.tensor(offsets, dtype=torch.int64, device=self.device)
+        self.grad_slab = SymmBuffer(total, self.dtype, self.device, self.group)
+        self.gather_slab = SymmBuffer(total, self.dtype, self.device, self.group)
+        self.peer_barrier = PeerBarrier(self.device, self.group, timeout_ms)
+        return self
+
+    def step_sharded_single_pass(self, host_grads: Optional[Sequence[torch.Tensor]] = None,
+                                 host_params: Optional[Sequence[torch.Tensor]] = None):
+        """The sharded step with reduce-scatter, update and all-gather in ONE kernel, tile by tile, through the
+        NVLink switch (after ``enable_single_pass`` and ``enable_multicast``):
+
+            barrier                      every rank's gradient blocks are written
+            elx_step_begin_optimistic
+            elx_adam_multi_single_pass   per tile: sum of all ranks' gradient tiles fetched from the switch
+                                         (multimem.ld_reduce) -> 1/W -> unscale, inf/nan detection, Adam/AdamW ->
+                                         working-copy tile stored once to all ranks' gather blocks (multimem.st)
+            barrier + agree              overflow words OR-ed over the ranks; all stores have landed
+            elx_step_commit              every rank adopts the update, or none does
+            elx_adam_multi_repair        only after an overflow: old parameters re-sent
+            barrier                      (the gather blocks are final)
+
+        Seven launches, no NCCL call, nothing read back by the host.  Each direction of a rank's links carries
+        about (W + 1) / W of the chunk bytes instead of 2 (W - 1) / W; the reduced gradients never touch HBM.
+
+        With ``host_grads`` / ``host_params`` (pinned; chunk_size and shard_size elements per chunk) the kernel is
+        launched chunk by chunk behind a barrier each: block k is filled from the host while earlier chunks are in
+        flight, and shard k leaves for the host right behind its update — before the step is known to be clean, so
+        after an overflow the rebuilt shards are sent again (the host reads the result once, at the end)."""
+        (t0, _), (t1, _) = self._sets
+        t1.set_hyper_from(t0)
+        fused = dict(grads_table=self.grad_slab.table, gather_table=self.gather_slab.table, block_off=self.block_off,
+                     grads_mc=self.grad_slab.mc_ptr, gather_mc=self.gather_slab.mc_ptr)
+        if host_grads is None and host_params is None:
+            self.peer_barrier(self.ctl)
+            kernels.step_begin_optimistic(self.ctl, self.scaler.cfg, self.chunk_flags)
+            kernels.adam_multi_single_pass(t0, t1, self.ctl, self.chunk_flags, **fused)
+        else:
+            main = torch.cuda.current_stream(self.device)
+            h2d, d2h = self._side_streams()
+            h2d.wait_stream(main)
+            d2h.wait_stream(main)
+            kernels.step_begin_optimistic(self.ctl, self.scaler.cfg, self.chunk_flags)
+            for k in range(self.n_chunks):
+                if host_grads is not None:
+                    with torch.cuda.stream(h2d):
+                        self.grad_block(k).copy_(host_grads[k], non_blocking=True)
+                        arrived = h2d.record_event()
+                    main.wait_event(arrived)
+                self.peer_barrier(self.ctl)    # chunk k's gradients are in place on every rank
+                kernels.adam_multi_single_pass(t0, t1, self.ctl, self.chunk_flags, first=k, count=1, **fused)
+                if host_params is not None:
+                    updated = main.record_event()
+                    with torch.cuda.stream(d2h):
+                        d2h.wait_event(updated)
+                        host_params[k].copy_(self.shards[k][3], non_blocking=True)
+        self.peer_barrier(self.ctl, exchange_overflow=True)
+        kernels.step_commit(self.ctl, self.scaler.cfg, self.chunk_flags)
+        kernels.adam_multi_repair(t0, t1, self.ctl, gather_table=self.gather_slab.table, block_off=self.block_off)
+        self.peer_barrier(self.ctl)
+        if host_params is not None:
+            main.wait_stream(d2h)
+            if self.ctl.read().repair:    # the step's result, read by the host (synchronises)
+                for k, dst in enumerate(host_params):
+                    dst.copy_(self.shards[k][3], non_blocking=True)
+                main.synchronize()
+
+    # ------------------------------------------------------------------ single-pass step with host buffers
+
+    def enable_speculation(self):
+        """Prepare ``step_from_host(..., speculative=True)``: the two state sets of the single-pass step."""
+        if self.world > 1:
+            raise RuntimeError('the host-buffer form of the single-pass step is for one rank')
+        return self.enable_single_pass()
 
     def _step_from_host_speculative(self, host_grads, host_params):
-        """Update chunk by chunk while gradients are still arriving, on the assumption that none of them
-        overflows; parameters leave for the host while later gradients come in (PCIe in both directions at
-        once).  The update writes into the second set of arrays, so if an overflow does turn up the result is
-        simply not adopted: the control block is put back, the real decision (skip, scale back-off) is taken,
-        and the parameters of the old masters are sent out again.  Returns True if the step was applied."""
-        other = self._twin[0]
-        other.set_hyper_from(self.table)
+        """The single-pass step fed from host buffers: every chunk is updated (out of place, with the inf/nan
+        test inside the update kernel) as soon as its gradients have arrived, and its parameters leave for the
+        host while later gradients still come in — PCIe busy in both directions at once.  If an overflow turns
+        up the update is not adopted (``elx_step_commit``), the working copies are rebuilt from the untouched set
+        (``elx_adam_multi_repair``) and sent out again.  The host reads the step's result once, at the end.
+        Returns True if the step was applied."""
+        (t0, _), (t1, _) = self._sets
+        t1.set_hyper_from(t0)
         main = torch.cuda.current_stream(self.device)
         h2d, d2h = self._side_streams()
-        self._ctl_backup.copy_(self.ctl.tensor)
-        # no overflow known: "apply", divisor, step count (an overflow that was already pending on entry, from
-        # a probe with no step after it, is decided here for real: skip, back-off)
-        kernels.step_begin(self.ctl, self.scaler.cfg, None, self.chunk_flags)
+        kernels.step_begin_optimistic(self.ctl, self.scaler.cfg, self.chunk_flags)
         h2d.wait_stream(main)
         d2h.wait_stream(main)
         for k, src in enumerate(host_grads):
@@ -609,36 +730,21 @@ class ChunkStepEngine:
                 self._grad_home(k).copy_(src, non_blocking=True)
                 arrived = h2d.record_event()
             main.wait_event(arrived)
-            self.probe_one(k)
-            kernels.adam_multi_shadow(self.table, other, self.ctl, first=k, count=1)
+            kernels.adam_multi_single_pass(t0, t1, self.ctl, self.chunk_flags, first=k, count=1)
             done = main.record_event()
             with torch.cuda.stream(d2h):
                 d2h.wait_event(done)
                 host_params[k].copy_(lowp, non_blocking=True)
+        kernels.step_commit(self.ctl, self.scaler.cfg, self.chunk_flags)
+        kernels.adam_multi_repair(t0, t1, self.ctl)
         main.wait_stream(d2h)
         result = self.ctl.read()    # the step's result, read by the host (synchronises)
-        if result.skip:
-            # the overflow was known before the first update: the launches above only refreshed the working
-            # copies and wrote nothing to the second set.  Gradients probed meanwhile belong to this step too.
-            self.ctl.found_inf.zero_()
-            self.chunk_flags.zero_()
-            return False
-        if not result.found_inf:
-            self._swap_sets()
-            return True
-        # late overflow: nothing of the speculative update is adopted
-        self.ctl.tensor.copy_(self._ctl_backup)
-        self.ctl.found_inf.fill_(1)
-        kernels.step_begin(self.ctl, self.scaler.cfg, None, self.chunk_flags)    # skip, back-off
-        for k, dst in enumerate(host_params):
-            self.update(first=k, count=1)    # skipped step: the working copy is refreshed from the old master
-            done = main.record_event()
-            with torch.cuda.stream(d2h):
-                d2h.wait_event(done)
+        if result.repair:
+            # late overflow: the parameters that left were those of the dropped update; send the rebuilt ones
+            for k, dst in enumerate(host_params):
                 dst.copy_(self.shards[k][3], non_blocking=True)
-        self.end_step()
-        main.wait_stream(d2h)
-        return False
+            main.synchronize()
+        return not result.skip
 
     # ------------------------------------------------------------------ shards in host memory, streamed
 

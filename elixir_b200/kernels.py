@@ -498,6 +498,80 @@ def adam_multi_shadow(table: ChunkTable, shadow: ChunkTable, ctl: ControlBlock, 
                                              _stream(table.descs_dev)), 'elx_adam_multi_shadow')
 
 
+def _no_peers():
+    table = _abi.ElxPeerTable()
+    table.rank, table.world = 0, 0
+    return table
+
+
+def step_begin_optimistic(ctl: ControlBlock, cfg: ElxScalerCfg, chunk_flags: Optional[torch.Tensor] = None):
+    """Decision of a single-pass step, taken before the gradients have been looked at (``elx_step_begin_optimistic``)."""
+    with _DeviceGuard(ctl.tensor):
+        _lib.check(_lib.get().elx_step_begin_optimistic(ctl.ptr, cfg, _ptr(chunk_flags),
+                                                        chunk_flags.numel() if chunk_flags is not None else 0,
+                                                        _stream(ctl.tensor)), 'elx_step_begin_optimistic')
+
+
+def step_commit(ctl: ControlBlock, cfg: ElxScalerCfg, chunk_flags: Optional[torch.Tensor] = None):
+    """Adopt the single-pass update (the two state sets change roles) or, after an overflow, take the optimistic
+    decision back and decide "skip" (``elx_step_commit``)."""
+    with _DeviceGuard(ctl.tensor):
+        _lib.check(_lib.get().elx_step_commit(ctl.ptr, cfg, _ptr(chunk_flags),
+                                              chunk_flags.numel() if chunk_flags is not None else 0,
+                                              _stream(ctl.tensor)), 'elx_step_commit')
+
+
+def _check_two_sets(table: 'ChunkTable', other: 'ChunkTable'):
+    if table.descs_dev is None or other.descs_dev is None:
+        raise RuntimeError('finalize() both tables first')
+    if other.n_chunks != table.n_chunks or other.tile_begin != table.tile_begin:
+        raise ValueError('the two tables do not describe the same shards')
+    if table.host_resident or other.host_resident:
+        raise RuntimeError('the single-pass step runs on device-resident shards only')
+
+
+def adam_multi_single_pass(table: 'ChunkTable', other: 'ChunkTable', ctl: ControlBlock,
+                           chunk_flags: Optional[torch.Tensor] = None, first: int = 0, count: Optional[int] = None,
+                           grads_table=None, gather_table=None, block_off: Optional[torch.Tensor] = None,
+                           grads_mc: int = 0, gather_mc: int = 0):
+    """Unscale + inf/nan detection + Adam/AdamW + working copy in one pass, out of place between the two state
+    sets ``table`` (set 0) and ``other`` (set 1) (``elx_adam_multi_single_pass``).  With the peer tables and the
+    multicast addresses of the ranks' gradient and gather slabs the same launch also reduce-scatters the gradients
+    and all-gathers the working copies through the NVLink switch."""
+    count = table.n_chunks - first if count is None else count
+    _check_two_sets(table, other)
+    sharded = gather_table is not None
+    if sharded:
+        _check_tensor(block_off, 'block_off', torch.int64)
+        if block_off.numel() < table.n_chunks:
+            raise ValueError('block_off is shorter than the table')
+    with _DeviceGuard(table.descs_dev):
+        _lib.check(
+            _lib.get().elx_adam_multi_single_pass(
+                _ptr(table.descs_dev), _ptr(other.descs_dev), first, count, table.tiles(first, count), table.code,
+                _ptr(table.segs_dev), _ptr(table.hyper_dev), table.n_groups, ctl.ptr, _ptr(chunk_flags),
+                grads_table if sharded else _no_peers(), gather_table if sharded else _no_peers(),
+                _ptr(block_off) if sharded else None, ctypes.c_void_p(grads_mc) if sharded else None,
+                ctypes.c_void_p(gather_mc) if sharded else None, _stream(table.descs_dev)),
+            'elx_adam_multi_single_pass')
+
+
+def adam_multi_repair(table: 'ChunkTable', other: 'ChunkTable', ctl: ControlBlock, first: int = 0,
+                      count: Optional[int] = None, gather_table=None, block_off: Optional[torch.Tensor] = None):
+    """Does nothing unless ``elx_step_commit`` asked for it; then rebuilds the working copies (and re-sends them to
+    the gather blocks) from the current state set (``elx_adam_multi_repair``)."""
+    count = table.n_chunks - first if count is None else count
+    _check_two_sets(table, other)
+    sharded = gather_table is not None
+    with _DeviceGuard(table.descs_dev):
+        _lib.check(
+            _lib.get().elx_adam_multi_repair(_ptr(table.descs_dev), _ptr(other.descs_dev), first, count,
+                                             table.tiles(first, count), table.code, ctl.ptr,
+                                             gather_table if sharded else _no_peers(),
+                                             _ptr(block_off) if sharded else None, None, _stream(table.descs_dev)),
+            'elx_adam_multi_repair')
+
+
 def pull_reduce_multi(table: ChunkTable, grads_table, block_off: torch.Tensor, ctl: Optional[ControlBlock],
                       chunk_flags: Optional[torch.Tensor] = None, first: int = 0, count: Optional[int] = None,
                       stage_off: Optional[torch.Tensor] = None):

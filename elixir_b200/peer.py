@@ -112,3 +112,36 @@ class PeerBarrier:
             _lib.check(
                 _lib.get().elx_peer_barrier(self.flags.table, self.epoch, ctl.ptr if ctl is not None else None,
                                             int(exchange_overflow), self.timeout_ms, stream), 'elx_peer_barrier')
+
+
+class SymmBuffer:
+    """A buffer allocated identically on every rank of one NVLink domain and bound to a multicast object, so that
+    the switch can serve one access for all ranks (``multimem`` instructions): ``local`` is this rank's tensor,
+    ``table`` the ``ElxPeerTable`` of the ranks' copies as plain peer addresses, ``mc_ptr`` the multicast address
+    that stands for all copies at once.  Allocation, handle exchange and the multicast binding are torch's
+    symmetric memory (plumbing); the kernels that use the addresses are this library's."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device, group):
+        import torch.distributed._symmetric_memory as symm
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if self.world > _abi.MAX_PEERS:
+            raise ValueError(f'at most {_abi.MAX_PEERS} ranks per NVLink domain')
+        device = torch.device(device)
+        self.local = symm.empty(numel, dtype=dtype, device=device)
+        self._handle = symm.rendezvous(self.local, group if group is not None else dist.group.WORLD)
+        mc = int(getattr(self._handle, 'multicast_ptr', 0) or 0)
+        if mc == 0:
+            raise RuntimeError('this process group has no multicast address for symmetric memory '
+                               '(the GPUs or the driver lack NVLink multicast): use the peer-mapped path instead')
+        ptrs = list(self._handle.buffer_ptrs)
+        if ptrs[self.rank] != self.local.data_ptr():
+            raise RuntimeError('symmetric memory: the local buffer does not start at the exchanged address')
+        table = ElxPeerTable()
+        for j, ptr in enumerate(ptrs):
+            table.base[j] = ptr
+        table.rank, table.world = self.rank, self.world
+        self.table = table
+        self.mc_ptr = mc
+        dist.barrier(group=group)

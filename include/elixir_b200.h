@@ -74,7 +74,15 @@ typedef struct ElxCtl {
     uint32_t forced_skips;     /* steps skipped because ELX_STAT_TIMEOUT was set, not for an overflow */
     float    clip_coef;        /* clip factor of the last applied step (1 = not clipped)          */
     float    grad_norm;        /* unscaled global gradient norm of the last applied step          */
-    uint32_t reserved[18];
+    /* single-pass (two-set) step, see elx_step_begin_optimistic: */
+    uint32_t cur_set;          /* which of the two sets of master/moment arrays is the current one */
+    uint32_t spec_state;       /* 0 idle, 1 optimistic decision pending its commit, 2 decided up front */
+    uint32_t repair;           /* set by elx_step_commit when the working copies must be rebuilt   */
+    float    saved_scale;      /* scaler state as it was before the optimistic decision            */
+    int32_t  saved_growth_step;
+    int32_t  saved_hysteresis_step;
+    int32_t  saved_step;
+    uint32_t reserved[11];
 } ElxCtl;
 
 /* Loss-scaler configuration, passed by value.  Mirrors DynamicGradScaler / ConstantGradScaler as
@@ -326,6 +334,58 @@ int elx_adam_multi_hostmem(const ElxChunkDesc* descs, int first, int count, int6
 int elx_adam_multi_shadow(const ElxChunkDesc* descs, const ElxChunkDesc* shadow, int first, int count,
                           int64_t n_tiles, int dtype, const ElxSeg* segs, const ElxHyper* hyper,
                           int n_groups, ElxCtl* ctl, void* stream);
+
+/* ---- single-pass step over two sets of state ---------------------------------------------------- */
+
+/*
+ * The step as ONE pass over memory: unscale, inf/nan detection, Adam / AdamW and the rounded working copy in
+ * the same kernel, 28 bytes per element with 16-bit gradients and no separate probe.  The reference's rule
+ * that one overflow anywhere skips every parameter (optimizer.py:194-203) is kept by updating OUT OF PLACE:
+ * the state exists twice (descs = set 0, shadow = set 1, congruent tables as for elx_adam_multi_shadow; 12
+ * bytes per element more memory), the kernel reads the current set (ElxCtl.cur_set) and writes the other one,
+ * and the sets change roles only when the whole step turned out clean.  Nothing is read back by the host:
+ *
+ *   elx_step_begin_optimistic   decision on the assumption of no overflow: divisor from the current loss scale,
+ *                               scaler "clean step" update, step count (the state before it is kept in the
+ *                               control block).  An overflow already pending in found_inf, or a set
+ *                               ELX_STAT_TIMEOUT, is decided here for real (skip), as elx_step_begin would.
+ *                               Gradient clipping needs the global norm first and is not available here.
+ *   elx_adam_multi_single_pass  per element of every segment the update of elx_adam_multi, written to the other
+ *                               set; every gradient element of [0, n_valid) it reads is tested for inf/nan
+ *                               (chunk_flags, ctl->found_inf).  May be launched chunk by chunk.  When the step
+ *                               was decided as skipped up front it only refreshes the working copies.
+ *   [W > 1: elx_peer_barrier with exchange_overflow, so that every rank commits the same way]
+ *   elx_step_commit             clean: cur_set flips.  Overflow: the saved scaler state comes back, the overflow
+ *                               branch of elx_step_begin runs on it (skip, back-off), cur_set stays, and
+ *                               ctl->repair is set.  found_inf and chunk_flags are cleared.
+ *   elx_adam_multi_repair       returns at once unless ctl->repair is set; then rebuilds the working copies
+ *                               (and re-sends them to the gather blocks) from the current, untouched set.
+ *
+ * With grads_mc / gather_mc (multicast addresses of the ranks' gradient and gather slabs in one NVLink domain,
+ * from a multicast object bound to all of them) the kernel also carries both collectives of the sharded step:
+ * the gradient tile of this rank's shard is fetched as the sum over all ranks, added up inside the switch
+ * (multimem.ld_reduce, fp32 accumulation, one rounding to the chunk dtype) and multiplied by 1/W, and the
+ * refreshed working-copy tile is stored once to the multicast address (multimem.st), which delivers it to every
+ * rank's gather block -- reduce-scatter (Chunk.reduce, chunk.py:282-315), update and all-gather
+ * (Chunk.__update_replica, chunk.py:475-482) tile by tile in one launch, with about (W + 1) / W of a chunk's
+ * bytes on each direction of the links instead of 2 (W - 1) / W.  The reduced gradient is never written to
+ * memory.  The overflow test then sees the rounded SUM: a sum that leaves the range of fp16 while the average
+ * would not is treated as an overflow (a skipped step and a scale back-off), where the reference, which divides
+ * before it sums, would have applied the step.  grads / gather are the same slabs as peer tables (for ragged
+ * tiles, which use plain peer accesses); block_off as for elx_adam_multi_push.  All NULL / world 0: one rank,
+ * gradients read from grad_src / grad_param.
+ */
+int elx_step_begin_optimistic(ElxCtl* ctl, ElxScalerCfg cfg, uint32_t* chunk_flags, int n_chunk_flags,
+                              void* stream);
+int elx_step_commit(ElxCtl* ctl, ElxScalerCfg cfg, uint32_t* chunk_flags, int n_chunk_flags, void* stream);
+int elx_adam_multi_single_pass(const ElxChunkDesc* descs, const ElxChunkDesc* shadow, int first, int count,
+                               int64_t n_tiles, int dtype, const ElxSeg* segs, const ElxHyper* hyper,
+                               int n_groups, ElxCtl* ctl, uint32_t* chunk_flags, ElxPeerTable grads,
+                               ElxPeerTable gather, const int64_t* block_off, const void* grads_mc,
+                               void* gather_mc, void* stream);
+int elx_adam_multi_repair(const ElxChunkDesc* descs, const ElxChunkDesc* shadow, int first, int count,
+                          int64_t n_tiles, int dtype, ElxCtl* ctl, ElxPeerTable gather,
+                          const int64_t* block_off, void* gather_mc, void* stream);
 
 /* ---- NVLink paths (single node, peer-mapped memory) -------------------------------------------- */
 

@@ -255,6 +255,118 @@ int elx_adam_multi_shadow(const ElxChunkDesc* descs, const ElxChunkDesc* shadow,
     return ELX_OK;
 }
 
+/* ---- single-pass step over two sets of state (one rank; the collective form needs NVLink) ---- */
+
+static void forced_skip(ElxCtl* ctl) {
+    ctl->skip = 1;
+    ctl->skipped_steps += 1;
+    ctl->forced_skips += 1;
+    ctl->div_scale = -1.0f;
+    ctl->inv_div = 0.0f;
+    ctl->found_inf = 0;
+}
+
+int elx_step_begin_optimistic(ElxCtl* ctl, ElxScalerCfg cfg, uint32_t* chunk_flags, int n_chunk_flags, void* stream) {
+    (void)stream;
+    if (!ctl) return ELX_ERR_NULL;
+    if (cfg.max_norm > 0.0f) return ELX_ERR_ARG;
+    ctl->repair = 0;
+    if (ctl->status & ELX_STAT_TIMEOUT) {
+        forced_skip(ctl);
+        ctl->spec_state = 2;
+    } else if (ctl->found_inf) {
+        orc_step_begin(ctl, cfg, 0);
+        ctl->spec_state = 2;
+    } else {
+        ctl->saved_scale = ctl->scale;
+        ctl->saved_growth_step = ctl->growth_step;
+        ctl->saved_hysteresis_step = ctl->hysteresis_step;
+        ctl->saved_step = ctl->step;
+        orc_step_begin(ctl, cfg, 0);
+        ctl->spec_state = 1;
+    }
+    for (int i = 0; chunk_flags && i < n_chunk_flags; ++i) chunk_flags[i] = 0;
+    return ELX_OK;
+}
+
+int elx_step_commit(ElxCtl* ctl, ElxScalerCfg cfg, uint32_t* chunk_flags, int n_chunk_flags, void* stream) {
+    (void)stream;
+    if (!ctl) return ELX_ERR_NULL;
+    if (ctl->spec_state == 1) {
+        const int expired = (ctl->status & ELX_STAT_TIMEOUT) != 0;
+        if (expired || ctl->found_inf) {
+            ctl->scale = ctl->saved_scale;
+            ctl->growth_step = ctl->saved_growth_step;
+            ctl->hysteresis_step = ctl->saved_hysteresis_step;
+            ctl->step = ctl->saved_step;
+            if (expired) {
+                forced_skip(ctl);
+            } else {
+                ctl->found_inf = 1;
+                orc_step_begin(ctl, cfg, 0);
+            }
+            ctl->repair = 1;
+        } else {
+            ctl->cur_set ^= 1u;
+        }
+    }
+    ctl->spec_state = 0;
+    ctl->found_inf = 0;
+    for (int i = 0; chunk_flags && i < n_chunk_flags; ++i) chunk_flags[i] = 0;
+    return ELX_OK;
+}
+
+int elx_adam_multi_single_pass(const ElxChunkDesc* descs, const ElxChunkDesc* shadow, int first, int count,
+                               int64_t n_tiles, int dtype, const ElxSeg* segs, const ElxHyper* hyper, int n_groups,
+                               ElxCtl* ctl, uint32_t* chunk_flags, ElxPeerTable grads, ElxPeerTable gather,
+                               const int64_t* block_off, const void* grads_mc, void* gather_mc, void* stream) {
+    (void)n_tiles; (void)grads; (void)block_off; (void)stream;
+    if (!descs || !shadow || !ctl) return ELX_ERR_NULL;
+    if (gather.world > 0 || grads_mc || gather_mc) return ELX_ERR_NODEVICE;
+    if (n_groups > 64) return ELX_ERR_CAPACITY;
+    const ElxChunkDesc* src = ctl->cur_set ? shadow : descs;
+    const ElxChunkDesc* dst = ctl->cur_set ? descs : shadow;
+    for (int c = first; c < first + count; ++c) {
+        const ElxChunkDesc* d = &src[c];
+        const ElxChunkDesc* o = &dst[c];
+        if (d->dtype != dtype || o->n_shard != d->n_shard) {
+            ctl->status |= ELX_STAT_BAD_DESC;
+            continue;
+        }
+        if (ctl->skip) {
+            orc_cast(d->master, d->grad_param, d->dtype, d->n_shard);
+            continue;
+        }
+        if (orc_probe(grad_of(d), d->dtype, d->n_valid)) {
+            ctl->found_inf = 1;
+            if (chunk_flags) chunk_flags[c] = 1;
+        }
+        for (int s = d->seg_first; s < d->seg_first + d->seg_count; ++s) {
+            if (segs[s].group < 0 || segs[s].group >= n_groups) continue;
+            const int64_t b = segs[s].begin, n = segs[s].end - segs[s].begin;
+            memcpy(o->master + b, d->master + b, (size_t)n * sizeof(float));
+            memcpy(o->exp_avg + b, d->exp_avg + b, (size_t)n * sizeof(float));
+            memcpy(o->exp_avg_sq + b, d->exp_avg_sq + b, (size_t)n * sizeof(float));
+            orc_adam_f64(o->master, o->exp_avg, o->exp_avg_sq, grad_of(d), d->dtype, segs[s].begin, segs[s].end,
+                         hyper[segs[s].group], ctl->step, ctl->div_scale);
+        }
+        orc_cast(o->master, d->grad_param, d->dtype, d->n_shard);
+    }
+    return ELX_OK;
+}
+
+int elx_adam_multi_repair(const ElxChunkDesc* descs, const ElxChunkDesc* shadow, int first, int count, int64_t n_tiles,
+                          int dtype, ElxCtl* ctl, ElxPeerTable gather, const int64_t* block_off, void* gather_mc,
+                          void* stream) {
+    (void)n_tiles; (void)dtype; (void)block_off; (void)gather_mc; (void)stream;
+    if (!descs || !shadow || !ctl) return ELX_ERR_NULL;
+    if (gather.world > 0) return ELX_ERR_NODEVICE;
+    if (!ctl->repair) return ELX_OK;
+    const ElxChunkDesc* src = ctl->cur_set ? shadow : descs;
+    for (int c = first; c < first + count; ++c) orc_cast(src[c].master, src[c].grad_param, src[c].dtype, src[c].n_shard);
+    return ELX_OK;
+}
+
 int elx_adam_multi_hostmem(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
                            const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl, void* stream) {
     return elx_adam_multi(descs, first, count, n_tiles, dtype, segs, hyper, n_groups, ctl, stream);

@@ -43,7 +43,8 @@ def test_struct_layouts_match_the_header():
     from elixir_b200 import _abi
     fields = {
         'ElxCtl': ['scale', 'found_inf', 'growth_step', 'hysteresis_step', 'step', 'skip', 'div_scale', 'inv_div',
-                   'skipped_steps', 'status', 'late_inf', 'forced_skips', 'clip_coef', 'grad_norm', 'reserved'],
+                   'skipped_steps', 'status', 'late_inf', 'forced_skips', 'clip_coef', 'grad_norm', 'cur_set', 'spec_state',
+                   'repair', 'saved_scale', 'saved_growth_step', 'saved_hysteresis_step', 'saved_step', 'reserved'],
         'ElxScalerCfg': ['dynamic', 'growth_factor', 'backoff_factor', 'min_scale', 'max_scale', 'growth_interval',
                          'hysteresis', 'max_norm'],
         'ElxHyper': ['lr', 'beta1', 'beta2', 'eps', 'weight_decay', 'adamw_mode', 'bias_correction', 'reserved'],

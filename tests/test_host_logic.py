@@ -209,3 +209,50 @@ def test_tensor_state_machine_equals_the_reference():
 def test_chunk_group_and_memory_pool_bookkeeping(world):
     import torch.multiprocessing as mp
     mp.spawn(W.group_worker, args=(world, 29730 + world), nprocs=world)
+
+
+def test_single_pass_step_bookkeeping_equals_the_two_phase_step(host_backend):
+    """Host-side logic of the single-pass step (two state sets, optimistic decision, commit or take-back, repair)
+    on the host-memory shim: over applied, overflowing and already-flagged steps the control block, the masters of
+    the current set and the working copies equal those of the probe-then-update step."""
+    from elixir_b200 import kernels as K
+    from elixir_b200.engine import ChunkStepEngine
+    from elixir_b200.scaler import DynamicGradScaler
+
+    def build(single_pass):
+        torch.manual_seed(0)
+        eng = ChunkStepEngine('cpu', torch.float16, DynamicGradScaler(initial_scale=64.0, hysteresis=1, growth_interval=2))
+        for n, nv in ((9000, 9000), (5000, 3000), (4096, 0)):
+            p, _, _, lowp = _shard(n)
+            eng.add_shard(p, lowp, nv, [(0, nv // 2, 0), (nv // 2, nv, 1)] if nv else [])
+        eng.finalize()
+        eng.set_hyper([K.hyper(weight_decay=0.01), K.hyper(lr=3e-3)])
+        if single_pass:
+            eng.enable_single_pass()
+        return eng
+
+    a, b = build(False), build(True)
+    for step in range(7):
+        gen = torch.Generator().manual_seed(100 + step)
+        for k in range(a.n_chunks):
+            g = (torch.randn(a.shards[k][3].numel(), generator=gen) * 1e-3 * 64).half()
+            if step in (2, 5) and k == 1:
+                g[10] = float('inf')
+            a.shards[k][3].copy_(g)
+            b.shards[k][3].copy_(g)
+        if step == 4:    # an overflow already known before the step (a probe with no step after it)
+            a.ctl.found_inf.fill_(1)
+            b.ctl.found_inf.fill_(1)
+        a.probe()
+        a.step()
+        b.step_single_pass()
+        ca, cb = a.read_control(), b.read_control()
+        for field in ('scale', 'growth_step', 'hysteresis_step', 'step', 'skip', 'skipped_steps', 'found_inf', 'status'):
+            assert getattr(ca, field) == getattr(cb, field), (step, field)
+        assert bool(cb.skip) == (step in (2, 4, 5))
+        assert cb.repair == int(step in (2, 5)) and cb.spec_state == 0
+        assert b.chunk_flags.tolist() == [0, 0, 0]
+        for sa, sb in zip(a.shards, b.current_shards()):
+            for x, y in zip(sa[:4], sb[:4]):
+                assert torch.equal(x, y), step
+    assert b.read_control().cur_set == 4 % 2    # four applied steps: the sets changed roles four times

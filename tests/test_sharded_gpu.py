@@ -213,6 +213,121 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False
     dist.destroy_process_group()
 
 
+def _mm_worker(rank, world, port, dtype_name='float16'):
+    """The single-pass sharded step: reduce-scatter, update and all-gather in one kernel through the NVLink switch
+    (multimem.ld_reduce / multimem.st on symmetric memory).  The switch adds the ranks' values in an order of its
+    own, so the gradients here are multiples of a power of two small enough for every partial sum to be exact:
+    the expected average is then the same number whatever the order, and the comparison with the oracle is as
+    strict as for the other paths."""
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
+                      MASTER_PORT=str(port))
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, 'tests'))
+    import torch.distributed as dist
+    from _util import bits_equal, close_1e6
+    from elixir_b200 import kernels as K
+    from elixir_b200.engine import ChunkStepEngine
+    from elixir_b200.scaler import DynamicGradScaler
+    from oracle import oracle as orc
+    torch.cuda.set_device(rank)
+    dev = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    dtype, scale = getattr(torch, dtype_name), 256.0
+    quantum, limit = (2.0**-6, 31.0) if dtype == torch.float16 else (2.0**-3, 15.0)
+    chunk_sizes = [world * 4096 * 40, world * (4096 + 16), world * 4096 * 5, world * 24]
+    used = [chunk_sizes[0], chunk_sizes[1], chunk_sizes[2] // 2 + 7, 9]
+    engine = ChunkStepEngine(dev, dtype, DynamicGradScaler(initial_scale=scale, hysteresis=1, growth_interval=3),
+                             process_group=dist.group.WORLD)
+    host = orc.ChunkSet(dtype)
+    host_ctl = orc.new_ctl(scale)
+    hypers = [K.hyper(weight_decay=0.01)]
+    host_state = []
+    for c, (C, u) in enumerate(zip(chunk_sizes, used)):
+        S = C // world
+        gen = torch.Generator().manual_seed(c)
+        full = torch.randn(C, generator=gen) * 0.02
+        full[u:] = 0
+        mine = full[rank * S:(rank + 1) * S].clone()
+        nv = max(0, min(S, u - rank * S))
+        lowp = torch.zeros(S, dtype=dtype)
+        host.add_chunk(mine, torch.zeros(S), torch.zeros(S), lowp, nv, [(0, nv, 0)] if nv else [])
+        host_state.append((mine, lowp, nv))
+        engine.add_shard(mine.to(dev), torch.zeros(S, dtype=dtype, device=dev), nv, [(0, nv, 0)] if nv else [])
+    engine.finalize()
+    engine.set_hyper(hypers)
+    engine.enable_single_pass()
+    engine.enable_multicast(chunk_sizes, timeout_ms=5000)
+    def one_step(step):
+        per_rank = []
+        for c, C in enumerate(chunk_sizes):
+            rank_grads = []
+            for r in range(world):
+                gen = torch.Generator().manual_seed(1000 * step + 10 * c + r)
+                g = torch.round((torch.randn(C, generator=gen) * 4).clamp(-limit, limit) / quantum) * quantum
+                g = g.to(dtype)
+                if step == 2 and c == 1 and r == world - 1:
+                    g[5] = float('inf')    # lands in rank 0's shard only
+                rank_grads.append(g)
+            per_rank.append(rank_grads)
+            engine.grad_block(c).copy_(rank_grads[rank])
+        engine.step_sharded_single_pass()
+        torch.cuda.synchronize()
+        for c, C in enumerate(chunk_sizes):
+            S = C // world
+            host_state[c][1].copy_(orc.reduce_avg_f32acc([g[rank * S:(rank + 1) * S].contiguous() for g in per_rank[c]]))
+        any_inf = step == 2
+        if any_inf:
+            host_ctl.found_inf = 1    # agreement: every rank skips
+        skipped = host.step(host_ctl, engine.scaler.cfg, hypers, probe=True, f64=True)
+        ctl = engine.read_control()
+        assert ctl.status == 0, (step, rank, ctl.status)
+        assert bool(ctl.skip) == skipped == any_inf, (step, rank)
+        assert (ctl.scale, ctl.step, ctl.repair) == (host_ctl.scale, host_ctl.step, int(any_inf))
+        shards = engine.current_shards()
+        for c, C in enumerate(chunk_sizes):
+            S = C // world
+            ok, ratio = close_1e6(shards[c][0], host_state[c][0].double(), rtol=2e-6)
+            assert ok, (step, rank, c, ratio)
+            want16 = torch.empty(S, dtype=dtype)
+            orc.cast(shards[c][0].cpu(), want16)
+            assert bits_equal(shards[c][3], want16), (step, rank, c)
+
+    def agree(failure):
+        verdict = torch.tensor([0 if failure is None else 1], device=dev)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MAX)
+        return bool(verdict.item())
+
+    # A rank that fails must not leave while the others still use memory bound to the multicast object: every
+    # rank learns of a failure between steps, all stop together, and the error is raised after an orderly teardown.
+    failure = None
+    for step in range(5):
+        try:
+            one_step(step)    # no host-side collective inside: a rank that raises cannot strand the others in one
+        except Exception as exc:    # noqa: BLE001
+            failure = f'{type(exc).__name__}: {exc}'
+        if agree(failure):
+            break
+        shards = engine.current_shards()
+        for c in range(len(chunk_sizes)):    # the gathered block holds every rank's refreshed shard
+            others = [torch.empty_like(shards[c][3]) for _ in range(world)]
+            dist.all_gather(others, shards[c][3])
+            if not bits_equal(engine.gather_block(c), torch.cat(others)):
+                failure = failure or f'step {step} rank {rank} chunk {c}: gathered block differs from the shards'
+        if agree(failure):
+            break
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+    assert failure is None, failure
+
+
+@pytest.mark.parametrize('world,dtype_name', [(2, 'float16'), (2, 'bfloat16'), (4, 'float16'), (8, 'float16')])
+def test_sharded_single_pass_step_through_the_switch(world, dtype_name):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f'needs {world} GPUs')
+    mp.spawn(_mm_worker, args=(world, 29900 + world + (10 if dtype_name == 'bfloat16' else 0), dtype_name), nprocs=world)
+
+
 @pytest.mark.parametrize('world', [2, 4])
 def test_sharded_step_staged_copy_engines(world):
     """The same step with the copy engines moving the slices (local staging + reduce kernel on local memory,

@@ -1,4 +1,4 @@
-"""The out-of-place update (elx_adam_multi_shadow) and the speculative host-buffer step built on it: same
+"""The out-of-place update (elx_adam_multi_shadow) and the host-buffer form of the single-pass step: same
 results as the step that waits for every gradient, bit for bit, including the step in which an overflow turns
 up after earlier chunks were already updated."""
 import pytest
@@ -33,7 +33,7 @@ def test_out_of_place_update_equals_in_place_and_leaves_its_input_alone(cuda, dt
     hypers = [K.hyper(lr=1e-3, weight_decay=0.01), K.hyper(lr=3e-3, betas=(0.8, 0.95), weight_decay=0.0, adamw_mode=False)]
     a, b = _engine(cuda, dtype), _engine(cuda, dtype)
     b.enable_speculation()
-    twin_table, twin_shards = b._twin
+    twin_table, twin_shards = b._sets[1]
     for eng in (a, b):
         eng.set_hyper(hypers)
         eng.probe()
@@ -78,7 +78,7 @@ def test_speculative_host_step_equals_the_step_that_waits(cuda, dtype):
         assert cw.status == 0 and cs.status == 0
         for field in ('scale', 'found_inf', 'growth_step', 'hysteresis_step', 'step', 'skip', 'div_scale', 'late_inf'):
             assert getattr(cw, field) == getattr(cs, field), (step, field)
-        for sw, ss, ow, os_ in zip(waits.shards, spec.shards, outs_w, outs_s):
+        for sw, ss, ow, os_ in zip(waits.shards, spec.current_shards(), outs_w, outs_s):
             for x, y in zip(sw[:4], ss[:4]):
                 assert bits_equal(x, y), step
             assert bits_equal(ow, os_), step
@@ -90,5 +90,5 @@ def test_speculation_is_refused_where_it_cannot_hold(cuda):
     eng = ChunkStepEngine(cuda, torch.float16, max_norm=1.0)    # the clip factor needs every gradient first
     eng.add_shard(torch.zeros(4096, device=cuda), torch.zeros(4096, dtype=torch.float16, device=cuda), 4096, [(0, 4096, 0)])
     eng.finalize()
-    with pytest.raises(RuntimeError, match='speculative'):
+    with pytest.raises(RuntimeError, match='single-pass'):
         eng.enable_speculation()
