@@ -767,6 +767,99 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
 
 
 # ------------------------------------------------------------------------------------------------------
+# residency modes of the wrapper (a secondary measurement: one training iteration, not the contract line)
+# ------------------------------------------------------------------------------------------------------
+
+
+def run_residency(args):
+    """``--workload residency``: time one training iteration (forward, backward, optimizer step) of a stack of MLP
+    blocks behind ``ElixirModule`` / ``ElixirOptimizer`` under the three ways of keeping chunks resident — ``all``: a
+    replica-cache block per chunk; ``fifo``: ``--blocks`` blocks, chunks fetched sub-module by sub-module on the main
+    stream; ``prefetch``: the same blocks, Belady's rule on the learnt access trace, gathers ahead and reduces on
+    side streams.  One chunk holds one block of the stack.  Prints one JSON line per mode (rank 0): milliseconds per
+    iteration (CUDA events, max over ranks), peak device memory, fetch counters.  Synthetic data, random weights."""
+    import gc
+    import torch.distributed as dist
+    import torch.nn as nn
+    from elixir_b200.optim import HybridAdam
+    from elixir_b200.wrapper import ElixirModule, ElixirOptimizer, simple_plan
+
+    class Block(nn.Module):
+
+        def __init__(self, hidden):
+            super().__init__()
+            self.up = nn.Linear(hidden, 4 * hidden)
+            self.down = nn.Linear(4 * hidden, hidden)
+
+        def forward(self, x):
+            return x + self.down(torch.nn.functional.gelu(self.up(x)))
+
+    class Stack(nn.Module):
+
+        def __init__(self, layers, hidden):
+            super().__init__()
+            self.blocks = nn.ModuleList(Block(hidden) for _ in range(layers))
+
+        def forward(self, x):
+            for block in self.blocks:
+                x = block(x)
+            return x.float().pow(2).mean()
+
+    rank, world = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1))
+    device = torch.device('cuda', int(os.environ.get('LOCAL_RANK', 0)))
+    torch.cuda.set_device(device)
+    os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+    os.environ.setdefault('MASTER_PORT', '29577')
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=device)
+    group = dist.group.WORLD
+    for mode in ('all', 'fifo', 'prefetch'):
+        torch.manual_seed(0)
+        with torch.device(device):
+            model = Stack(args.layers, args.hidden).to(torch.float16)
+        per_block = sum(p.numel() for p in model.blocks[0].parameters())
+        blocks = None if mode == 'all' else args.blocks
+        sr = simple_plan(model, world, unified_dtype=torch.float16, shard_device=device, chunk_size=per_block,
+                         public_block_number=blocks)
+        emodel = ElixirModule(model, sr, group, prefetch=(mode != 'fifo'), dtype=torch.float16)
+        eoptim = ElixirOptimizer(emodel, HybridAdam(model.parameters(), lr=1e-4), initial_scale=1024.0)
+        x = torch.randn(args.tokens, args.hidden, device=device, dtype=torch.float16)
+        torch.cuda.reset_peak_memory_stats(device)
+        rcache_gb = sr.chunk_group.rcache.public_space / 1e9
+
+        def iteration():
+            eoptim.zero_grad()
+            eoptim.backward(emodel(x))
+            eoptim.step()
+
+        for _ in range(args.warmup):
+            iteration()
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(args.steps):
+            iteration()
+        stop.record()
+        torch.cuda.synchronize(device)
+        ms = torch.tensor([start.elapsed_time(stop) / args.steps], device=device)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX, group=group)
+        eoptim.engine.check_status()
+        if rank == 0:
+            print(json.dumps(dict(workload='residency', mode=mode, ms_per_iteration=round(float(ms), 3), world=world,
+                                  layers=args.layers, hidden=args.hidden, tokens=args.tokens, chunk_elems=per_block,
+                                  chunks=len(emodel.param_chunks),
+                                  blocks=len(emodel.param_chunks) if blocks is None else blocks,
+                                  replica_cache_gb=round(rcache_gb, 2),
+                                  peak_mem_gb=round(torch.cuda.max_memory_allocated(device) / 1e9, 2),
+                                  fetch=dict(emodel.fetcher.stats) if emodel.scheduled else None)), flush=True)
+        del emodel, eoptim, model, sr, iteration, x
+        gc.collect()    # module <-> hook cycles keep the chunks alive otherwise
+        torch.cuda.empty_cache()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------------------
 # CPU arms
 # ------------------------------------------------------------------------------------------------------
 
@@ -902,8 +995,13 @@ def main():
                     help='N > 1: p2p = pull reduce-scatter and push all-gather kernels over peer-mapped NVLink memory; '
                     'mm = ONE kernel per step that reduces, updates and gathers tile by tile through the NVLink switch '
                     '(multimem); staged = copy engines; nccl = NCCL on side streams; auto = mm from 8 ranks on, else p2p')
-    ap.add_argument('--workload', default='auto', choices=['auto', 'opt66b_bf16'],
-                    help='N > 1: auto = OPT-13B-shaped fp16 chunk set; opt66b_bf16 = OPT-66B-shaped bf16 chunk set (8 GPUs)')
+    ap.add_argument('--workload', default='auto', choices=['auto', 'opt66b_bf16', 'residency'],
+                    help='N > 1: auto = OPT-13B-shaped fp16 chunk set; opt66b_bf16 = OPT-66B-shaped bf16 chunk set (8 GPUs); '
+                    'residency = one training iteration of an MLP stack through the wrapper under three residency modes')
+    ap.add_argument('--layers', type=int, default=12, help='residency workload: blocks of the stack (one chunk each)')
+    ap.add_argument('--hidden', type=int, default=4096, help='residency workload: hidden size')
+    ap.add_argument('--tokens', type=int, default=8192, help='residency workload: rows of the input')
+    ap.add_argument('--blocks', type=int, default=3, help='residency workload: replica-cache blocks of the two scheduled modes')
     ap.add_argument('--chunk-elems', type=int, default=0, help='override the chunk size in elements (profiling cases)')
     ap.add_argument('--params', type=int, default=0, help='override the parameter count (smoke runs of a workload)')
     ap.add_argument('--pool', type=int, default=0,
@@ -932,7 +1030,9 @@ def main():
     args = ap.parse_args()
     if args.collective == 'auto':
         args.collective = 'mm' if args.gpus >= 8 and args.workload == 'auto' and not args.pool else 'p2p'
-    if args.impl == 'reference':
+    if args.workload == 'residency':
+        run_residency(args)
+    elif args.impl == 'reference':
         run_reference(args)
     else:
         if args.warmup < 3:

@@ -200,6 +200,7 @@ class ElixirOptimizer:
     def loss_scale(self) -> float:
         """Current loss scale as a Python float.  Synchronises (the reference does too, ``:185-187``);
         ``backward`` does not use it."""
+        self.engine.check_status()    # the host waits for the device here anyway: report what the kernels flagged
         return float(self.grad_scaler.scale.item())
 
     def _check_overflow(self) -> bool:
@@ -285,6 +286,7 @@ class ElixirOptimizer:
         """This rank's flat optimizer state: one (exp_avg, exp_avg_sq) pair per chunk shard plus the control
         block fields.  The reference saves none of this (its scaler state is lost on restart)."""
         self._quiesce_host_shards()
+        self.engine.check_status()
         if not self.scaled_optimizer:
             return dict(scaler=self.grad_scaler.state_dict(), optim=self.optim.state_dict())
         self._refresh_step_counts()

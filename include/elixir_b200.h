@@ -330,6 +330,10 @@ int elx_adam_multi_hostmem(const ElxChunkDesc* descs, int first, int count, int6
  * the reference's rule that one overflow skips every parameter (optimizer.py:194-203) then still holds.
  * Always runs the bulk-copy variant.  A skipped step (ctl->skip) refreshes the working copy from descs as
  * elx_adam_multi does and writes nothing to the shadow set.
+ * The arrays of both tables must be device memory: this entry point, elx_adam_multi_push and the single-pass
+ * entry points always move tiles with bulk copies, which are kept to device memory (shards in mapped host
+ * memory go through elx_adam_multi_hostmem); the library cannot tell where an array lives from a table in device
+ * memory, so the caller has to keep to this.
  */
 int elx_adam_multi_shadow(const ElxChunkDesc* descs, const ElxChunkDesc* shadow, int first, int count,
                           int64_t n_tiles, int dtype, const ElxSeg* segs, const ElxHyper* hyper,

@@ -1,4 +1,5 @@
-"""The BASELINE configurations as parity cases (the single-GPU ones; sharded ones: test_sharded_gpu.py).
+"""The benchmark configurations of this path as parity cases (the single-GPU ones; sharded ones:
+test_sharded_gpu.py).
 
 config 1  4 chunks x 4 194 304 elements, fp16 gradients N(0,1e-3)*64, Adam lr 1e-3 b(0.9,0.999) eps 1e-8 wd 0,
           10 steps, seed 0 — full size, every step against the CPU oracle.

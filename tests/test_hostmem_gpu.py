@@ -158,6 +158,15 @@ def test_wrapper_with_shards_in_host_memory_trains_identically(cuda, blocks):
     assert host_opt.engine.read_control().status == 0
     for a, b in zip(dev.param_chunks, host.param_chunks):
         assert bits_equal(a.shard, b.shard) and bits_equal(a.paired_chunk.shard, b.paired_chunk.shard)
+    # the chunk-level norm (Chunk.set_l2_norm, elixir/chunk/core/chunk.py:218-221) also works on a shard in host
+    # memory: result and scratch live on the device that runs the kernel
+    for a, b in zip(dev.param_chunks, host.param_chunks):
+        for chunk in (a, b):
+            chunk.l2_norm = None
+            chunk.set_l2_norm(chunk.shard[:chunk.valid_end])
+        assert a.l2_norm == b.l2_norm
+        want = float(b.shard[:b.valid_end].float().pow(2).sum())
+        assert abs(b.l2_norm - want) <= 1e-5 * max(want, 1e-30)
     sa, sb = dev_opt.state_dict(), host_opt.state_dict()
     for x, y in zip(sa['shards'], sb['shards']):
         assert bits_equal(x['exp_avg'], y['exp_avg']) and bits_equal(x['exp_avg_sq'], y['exp_avg_sq'])

@@ -4,7 +4,7 @@
 * probe / sum of squares: against torch.isinf|isnan and float().norm(2)**2 — the expressions the
   reference uses (elixir/chunk/core/chunk.py:214-221).
 * Adam / AdamW arithmetic: against torch.optim.Adam / AdamW evaluated in float64 from the same state
-  (the fallback BASELINE names for the unavailable ColossalAI optimizers).
+  (the stand-in for the ColossalAI optimizers, which cannot be installed offline).
 * rank-average reduce: against the reference's sequence (divide in the chunk dtype, then sum).
 """
 import pytest
