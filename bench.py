@@ -353,6 +353,14 @@ def run_ours(args):
         chunk, workload = args.chunk_elems, workload + f'_chunk{args.chunk_elems}'
     n_chunks, used = chunk_layout(total, chunk, world)
     shard = chunk // world
+    if world > 1 and args.collective == 'mm':
+        # two sets of master and moments (26 B per element with the working copy) next to the two slabs of
+        # replicated blocks: refuse cleanly, before anything is allocated, where that does not fit
+        need = n_chunks * shard * 26 + 2 * n_chunks * chunk * 2
+        free, _ = torch.cuda.mem_get_info(device)
+        if need > 0.95 * free:
+            raise SystemExit(f'bench: --collective mm needs {need / 1e9:.0f} GB per GPU at {world} ranks for this workload '
+                             f'({free / 1e9:.0f} GB free); use --collective p2p')
 
     if dtype == torch.bfloat16:
         from elixir_b200.scaler import ConstantGradScaler

@@ -776,8 +776,10 @@ int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
         }
         opted_in[dev] = true;
     }
-    const int grid = grid_for(a.n_tiles, 1);
+    int grid = grid_for(a.n_tiles, 1);
     if (grid < 0) return grid;
+    // fewer CTAs than SMs leave the other SMs to a kernel on another stream (the pull of the next chunk)
+    if (g_tune.adam_tma_ctas > 0 && g_tune.adam_tma_ctas < grid) grid = g_tune.adam_tma_ctas;
     adam_tma_kernel<DT, MATH, MM><<<grid, kTmaThreads, smem, s>>>(a);
     return record_cuda(cudaGetLastError());
 }
@@ -871,7 +873,7 @@ static int single_pass_common(const ElxChunkDesc* descs, const ElxChunkDesc* sha
         if (!aligned(block_off, 8)) return ELX_ERR_ALIGN;
         int rc = peer_table_ok(*gather);
         if (rc != ELX_OK) return rc;
-        if (!repair) {
+        if (!repair && (grads_mc || gather_mc)) {
             // the gradient of a shard is the sum over the ranks' slabs: both views of the slabs are needed
             if (!grads || !grads_mc || !gather_mc) return ELX_ERR_NULL;
             rc = peer_table_ok(*grads);
@@ -901,7 +903,7 @@ static int single_pass_common(const ElxChunkDesc* descs, const ElxChunkDesc* sha
     if (sharded) {
         a.push = *gather;
         a.push_off = block_off;
-        if (!repair) {
+        if (!repair && grads_mc) {
             a.grads = *grads;
             a.mc_grads = static_cast<const char*>(grads_mc);
             a.mc_gather = static_cast<char*>(gather_mc);

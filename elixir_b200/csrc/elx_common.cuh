@@ -50,6 +50,8 @@ struct Tuning {
     int adam_variant = 1;         // 0 = direct global accesses, 1 = bulk-copy (TMA) pipeline
     int pull_ctas_per_sm = 0;
     int pull_variant = 1;         // 0 = per-lane loads, 1 = bulk-copy staging (16-bit chunks, W in {2, 4, 8})
+    int adam_tma_ctas = 0;        // grid of the bulk-copy update kernel, 0 = one CTA per SM
+    int pull_tma_ctas = 0;        // grid of the bulk-copy pull kernel, 0 = one CTA per SM
 };
 extern Tuning g_tune;
 

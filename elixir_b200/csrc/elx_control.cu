@@ -242,6 +242,8 @@ int elx_set_tuning(const char* name, int value) {
         {"adam_variant", &g_tune.adam_variant, def.adam_variant, 0, 1},
         {"pull_ctas_per_sm", &g_tune.pull_ctas_per_sm, def.pull_ctas_per_sm, 0, 32},
         {"pull_variant", &g_tune.pull_variant, def.pull_variant, 0, 1},
+        {"adam_tma_ctas", &g_tune.adam_tma_ctas, def.adam_tma_ctas, 0, 1024},
+        {"pull_tma_ctas", &g_tune.pull_tma_ctas, def.pull_tma_ctas, 0, 1024},
     };
     for (const Knob& k : knobs) {
         if (strcmp(name, k.name) != 0) continue;

@@ -334,8 +334,9 @@ int launch_pull_tma(const PullArgs& a, cudaStream_t s) {
             }
             opted_in[dev] = true;
         }
-        const int grid = grid_for(a.n_tiles, 1);
+        int grid = grid_for(a.n_tiles, 1);
         if (grid < 0) return grid;
+        if (g_tune.pull_tma_ctas > 0 && g_tune.pull_tma_ctas < grid) grid = g_tune.pull_tma_ctas;
         pull_reduce_tma_kernel<DT, kWorld><<<grid, kPullThreads, smem, s>>>(a);
         return record_cuda(cudaGetLastError());
     }

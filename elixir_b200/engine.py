@@ -702,6 +702,47 @@ class ChunkStepEngine:
                     dst.copy_(self.shards[k][3], non_blocking=True)
                 main.synchronize()
 
+    def step_sharded_overlapped(self, pull_ctas: int = 36):
+        """The peer-mapped sharded step (``enable_p2p`` slabs) with the reduction of later chunks running WHILE
+        earlier chunks are updated — possible because the update goes out of place (``enable_single_pass``) and is
+        adopted only after every chunk turned out clean:
+
+            barrier                      every rank's gradient blocks are written
+            elx_step_begin_optimistic
+            side stream:  pull(0) pull(1) pull(2) ...          (reduce-scatter + probe, ``pull_ctas`` CTAs)
+            main stream:       update+push(0) update+push(1) ...   (single-pass kernel on the remaining SMs)
+            barrier + agree, elx_step_commit, elx_adam_multi_repair, barrier
+
+        Worth it where the two phases are bound by different things (two ranks: the pull by the links, the update by
+        HBM); where both are link-bound the links are already busy in both directions in either phase."""
+        (t0, _), (t1, _) = self._sets
+        t1.set_hyper_from(t0)
+        main = torch.cuda.current_stream(self.device)
+        side = self._side_streams()[0]
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.peer_barrier(self.ctl)
+        kernels.step_begin_optimistic(self.ctl, self.scaler.cfg, self.chunk_flags)
+        side.wait_stream(main)
+        kernels.set_tuning(pull_tma_ctas=pull_ctas, adam_tma_ctas=max(1, sms - pull_ctas))
+        try:
+            pulled = []
+            with torch.cuda.stream(side):
+                for k in range(self.n_chunks):
+                    kernels.pull_reduce_multi(self.table, self.grad_slab.table, self.block_off, self.ctl,
+                                              chunk_flags=self.chunk_flags, first=k, count=1)
+                    pulled.append(side.record_event())
+            for k in range(self.n_chunks):
+                main.wait_event(pulled[k])
+                kernels.adam_multi_single_pass(t0, t1, self.ctl, self.chunk_flags, first=k, count=1,
+                                               grads_table=self.grad_slab.table, gather_table=self.gather_slab.table,
+                                               block_off=self.block_off)
+        finally:
+            kernels.set_tuning(pull_tma_ctas=-1, adam_tma_ctas=-1)
+        self.peer_barrier(self.ctl, exchange_overflow=True)
+        kernels.step_commit(self.ctl, self.scaler.cfg, self.chunk_flags)
+        kernels.adam_multi_repair(t0, t1, self.ctl, gather_table=self.gather_slab.table, block_off=self.block_off)
+        self.peer_barrier(self.ctl)
+
     # ------------------------------------------------------------------ single-pass step with host buffers
 
     def enable_speculation(self):

@@ -178,6 +178,9 @@ const char* elx_last_cuda_error(void);
  *   "pull_ctas_per_sm"   cap on the grid of the pull reduce-scatter kernel, 0 = every resident CTA
  *   "pull_variant"       0 = per-lane peer loads, 1 = bulk-copy staging through shared memory (16-bit
  *                        chunks and groups of 2, 4 or 8 ranks; other cases use variant 0)
+ *   "adam_tma_ctas"      grid of the bulk-copy update kernel, 0 = one CTA per SM; with "pull_tma_ctas" (the
+ *                        same for the bulk-copy pull kernel) it splits the SMs between an update and a pull
+ *                        that run at the same time on two streams
  *   "math_mode"          1 = IEEE division and square root in the update, 2 = reciprocal
  *                        multiplies and approximate division (both within 1e-6 relative) */
 int elx_set_tuning(const char* name, int value);
@@ -377,7 +380,10 @@ int elx_adam_multi_shadow(const ElxChunkDesc* descs, const ElxChunkDesc* shadow,
  * would not is treated as an overflow (a skipped step and a scale back-off), where the reference, which divides
  * before it sums, would have applied the step.  grads / gather are the same slabs as peer tables (for ragged
  * tiles, which use plain peer accesses); block_off as for elx_adam_multi_push.  All NULL / world 0: one rank,
- * gradients read from grad_src / grad_param.
+ * gradients read from grad_src / grad_param.  gather given without the multicast addresses: the gradients are
+ * read from the shard (where elx_pull_reduce_multi left the rank average) and the working copy is pushed to the
+ * gather blocks with plain bulk stores, as elx_adam_multi_push does -- the out-of-place form of that entry
+ * point, which lets the update of one chunk run while later chunks are still being reduced.
  */
 int elx_step_begin_optimistic(ElxCtl* ctl, ElxScalerCfg cfg, uint32_t* chunk_flags, int n_chunk_flags,
                               void* stream);

@@ -103,7 +103,7 @@ def _worker(rank, world, port):
     dist.destroy_process_group()
 
 
-def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False, pull_variant=1):
+def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False, pull_variant=1, overlapped=False):
     """The NVLink path: pull reduce-scatter + probe, overflow agreement inside the barrier, fused update with
     push all-gather — no NCCL collective in the step."""
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
@@ -149,6 +149,8 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False
     K.set_tuning(pull_variant=pull_variant)
     if staged:
         engine.enable_staging(pool=2)
+    if overlapped:
+        engine.enable_single_pass()
 
     def fill(step):
         per_rank = []
@@ -185,9 +187,12 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False
         per_rank = fill(step)
         if staged:
             engine.step_sharded_staged()
+        elif overlapped:
+            engine.step_sharded_overlapped(pull_ctas=40)
         else:
             engine.step_sharded_p2p()
         torch.cuda.synchronize()
+        shards = engine.current_shards()
         for c, C in enumerate(chunk_sizes):
             S = C // world
             host_state[c][1].copy_(orc.reduce_avg_f32acc([g[rank * S:(rank + 1) * S].contiguous()
@@ -202,9 +207,9 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False
         assert (ctl.scale, ctl.step) == (host_ctl.scale, host_ctl.step)
         for c, C in enumerate(chunk_sizes):
             S = C // world
-            ok, ratio = close_1e6(engine.shards[c][0], host_state[c][0].double(), rtol=2e-6)
+            ok, ratio = close_1e6(shards[c][0], host_state[c][0].double(), rtol=2e-6)
             assert ok, (step, rank, c, ratio)
-            mine16 = engine.shards[c][3]
+            mine16 = shards[c][3]
             others = [torch.empty_like(mine16) for _ in range(world)]
             dist.all_gather(others, mine16)
             if not pool or c + pool >= len(chunk_sizes):    # a pooled gather block holds its LAST chunk
@@ -344,6 +349,14 @@ def test_sharded_step_p2p_per_lane_pull(world, dtype_name):
     if torch.cuda.device_count() < world:
         pytest.skip(f'needs {world} GPUs')
     mp.spawn(_p2p_worker, args=(world, 29880 + world, dtype_name, None, False, 0), nprocs=world)
+
+
+def test_sharded_step_with_the_reduction_overlapping_the_update():
+    """Out-of-place update, so chunk k may be updated while chunk k + 1 is still being reduced on another stream
+    (the SMs split between the two kernels): same oracle, same bits as the two-phase step."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    mp.spawn(_p2p_worker, args=(2, 29865, 'float16', None, False, 1, True), nprocs=2)
 
 
 def test_sharded_step_p2p_pooled_blocks():
