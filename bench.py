@@ -722,6 +722,7 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
     grads = [host_in[c % pool] for c in range(n_chunks)]
     outs = [host_out[c % pool] for c in range(n_chunks)]
     conservative_ms = None
+    engine.normalize_sets()    # after single-pass steps: the in-place legs below work on the live state set
     if world == 1:
         # first the step that waits for the last gradient before it updates anything, then the speculative one
         # (updates into a second set of master/moment arrays while gradients still arrive; adopted unless an
