@@ -214,7 +214,7 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
             engine.enable_single_pass()
             engine.enable_multicast(chunk_sizes, timeout_ms=5000)
             gather = [engine.gather_block(c) for c in range(len(chunk_sizes))]
-        elif collective in ('p2p', 'staged'):
+        elif collective in ('p2p', 'p2p-overlap', 'staged'):
             engine.enable_p2p(chunk_sizes, timeout_ms=5000)
             if collective == 'staged':
                 engine.enable_staging(pool=2)
@@ -238,7 +238,7 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
                         g[5] = float('inf')    # lands in rank 0's shard only
                     rank_grads.append(g)
                 per_rank.append(rank_grads)
-                if collective in ('p2p', 'staged', 'mm'):
+                if collective in ('p2p', 'p2p-overlap', 'staged', 'mm'):
                     engine.grad_block(c).copy_(rank_grads[rank])
                 else:
                     blocks.append(rank_grads[rank].to(device))
@@ -246,7 +246,7 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
             for c, C in enumerate(chunk_sizes):
                 S = C // world
                 mine = [g[rank * S:(rank + 1) * S].contiguous() for g in per_rank[c]]
-                if collective in ('p2p', 'staged', 'mm'):
+                if collective in ('p2p', 'p2p-overlap', 'staged', 'mm'):
                     reduced.append(orc.reduce_avg_f32acc(mine))    # rank-order fp32 accumulation, one rounding
                 else:
                     out = torch.empty(S, dtype=dtype, device=device)
@@ -259,6 +259,8 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
                         failure = failure or f'{dtype} step {step} chunk {c}: NCCL average off the divide-then-sum value'
             if collective == 'p2p':
                 engine.step_sharded_p2p()
+            elif collective == 'p2p-overlap':
+                engine.step_sharded_probe_first(pull_ctas=40)
             elif collective == 'mm':
                 engine.step_sharded_single_pass()
             elif collective == 'staged':
@@ -405,7 +407,7 @@ def run_ours(args):
                 gen = torch.Generator(device=device).manual_seed(args.seed + 7919 * (c + 1))
                 grad_blocks.append(synth_grad(shard, device, gen, scale, sigma, dtype))
         gather_blocks = None
-    elif args.collective in ('p2p', 'staged', 'mm'):
+    elif args.collective in ('p2p', 'p2p-overlap', 'staged', 'mm'):
         # NVLink path: every chunk owns a block in the peer-mapped gradient and gather slabs
         if args.collective == 'mm':
             engine.enable_multicast([chunk] * n_chunks)
@@ -473,6 +475,8 @@ def run_ours(args):
             engine.end_step()
         elif args.collective == 'p2p':
             engine.step_sharded_p2p()
+        elif args.collective == 'p2p-overlap':
+            engine.step_sharded_probe_first(pull_ctas=args.pull_ctas)
         elif args.collective == 'mm':
             engine.step_sharded_single_pass()
         elif args.collective == 'staged':
@@ -542,6 +546,9 @@ def run_ours(args):
             'collectives': 'none (1 GPU)' if world == 1 else
                            ('fused into the kernels over peer-mapped NVLink memory (pull reduce-scatter + probe, '
                             'Adam + push all-gather)' if args.collective == 'p2p' else
+                            'the same two kernels chunk by chunk on two streams, the update of a chunk running while the next '
+                            'one is reduced; the overflow decision is taken first, from a probe of every rank\'s own gradient '
+                            'blocks' if args.collective == 'p2p-overlap' else
                             'ONE kernel per step through the NVLink switch: per tile the sum of all ranks\' gradients '
                             '(multimem.ld_reduce), Adam out of place with inf/nan detection, working copy to all ranks '
                             '(multimem.st); symmetric memory' if args.collective == 'mm' else
@@ -626,6 +633,16 @@ def run_ours(args):
                      'bytes per collective) so that the variants compare; the switch-side sum moves fewer bytes than that')
             result['gpu_launches'] = args.steps * 7
             result['phases_ms'] = mm_phases(engine)
+        elif args.collective == 'p2p-overlap':
+            # one pipelined phase behind the probe of the inputs: bounded by the slower of the links (both collectives
+            # share them) and HBM (probe of the own blocks 2 B x C, pull 4 B and update + push 30 B per own element)
+            probe_ms = n_chunks * chunk * 2 / (peak * 1e9) * 1e3
+            hbm_ms = engine.n_elements() * (4 + BYTES_PER_ELEM + 2) / (peak * 1e9) * 1e3
+            result['roofline'].update(
+                target_ms=probe_ms + max(2 * link_ms, hbm_ms), frac_of_target=(probe_ms + max(2 * link_ms, hbm_ms)) / ms_per_step,
+                target_note='probe of the own gradient blocks at the HBM rate + max(NVLink time of both collectives at 900 GB/s, '
+                            'HBM time of pull + update + push)')
+            result['gpu_launches'] = args.steps * (2 * n_chunks + 5)
         elif args.collective == 'p2p' and args.pool:
             result['gpu_launches'] = args.steps * (3 * n_chunks + 3)
         elif args.collective == 'p2p':
@@ -736,7 +753,7 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
             conservative_ms = timed(plain, max(1, min(args.steps, args.e2e_steps))) / max(1, min(args.steps, args.e2e_steps))
             engine.enable_speculation()
             fn = lambda: engine.step_from_host(grads, outs, speculative=True)    # noqa: E731
-    elif args.collective == 'p2p':
+    elif args.collective in ('p2p', 'p2p-overlap'):
         # chunk by chunk: block k filled from the host while earlier chunks are pulled, shard k copied out behind
         # its update while later chunks are updated and pushed
         fn = lambda: engine.step_sharded_p2p(host_grads=grads, host_params=outs)    # noqa: E731
@@ -763,7 +780,7 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
         'h2d_bytes_per_step': n_chunks * in_elems * 2 * world, 'd2h_bytes_per_step': n_chunks * shard * 2 * world,
         'conservative_ms_per_step': conservative_ms,
         'api': ('ChunkStepEngine.step_from_host' + ('' if conservative_ms is None else '(speculative=True)')) if world == 1 else
-               ('ChunkStepEngine.step_sharded_p2p(host_grads=, host_params=)' if args.collective == 'p2p' else
+               ('ChunkStepEngine.step_sharded_p2p(host_grads=, host_params=)' if args.collective in ('p2p', 'p2p-overlap') else
                 'ChunkStepEngine.step_sharded_single_pass(host_grads=, host_params=)' if args.collective == 'mm' else
                 'H2D into the gradient slab + ChunkStepEngine.step_sharded_staged + D2H of the shards'
                 if args.collective == 'staged' else 'ChunkStepEngine.step_sharded(host_grads=, host_params=)'),
@@ -1000,10 +1017,12 @@ def main():
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--seed', type=int, default=0)
-    ap.add_argument('--collective', default='auto', choices=['auto', 'p2p', 'mm', 'staged', 'nccl'],
+    ap.add_argument('--collective', default='auto', choices=['auto', 'p2p', 'p2p-overlap', 'mm', 'staged', 'nccl'],
                     help='N > 1: p2p = pull reduce-scatter and push all-gather kernels over peer-mapped NVLink memory; '
                     'mm = ONE kernel per step that reduces, updates and gathers tile by tile through the NVLink switch '
-                    '(multimem); staged = copy engines; nccl = NCCL on side streams; auto = mm from 8 ranks on, else p2p')
+                    '(multimem); p2p-overlap = the p2p kernels with the decision taken on the inputs first, so that the update '
+                    'of a chunk runs while the next one is reduced; staged = copy engines; nccl = NCCL on side streams; '
+                    'auto = mm from 8 ranks on, else p2p')
     ap.add_argument('--workload', default='auto', choices=['auto', 'opt66b_bf16', 'residency'],
                     help='N > 1: auto = OPT-13B-shaped fp16 chunk set; opt66b_bf16 = OPT-66B-shaped bf16 chunk set (8 GPUs); '
                     'residency = one training iteration of an MLP stack through the wrapper under three residency modes')
@@ -1026,6 +1045,8 @@ def main():
                     'capture, to be reported as roofline.traffic')
     ap.add_argument('--land-streams', type=int, default=2,
                     help='N = 1: side streams the per-chunk landing launches alternate on')
+    ap.add_argument('--pull-ctas', type=int, default=36,
+                    help='p2p-overlap: CTAs of the pull kernel; the update kernel gets the remaining SMs')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-parity-check', action='store_true',
                     help='N > 1: skip the small sharded case that is checked against the CPU oracle before the warm-up')

@@ -327,7 +327,7 @@ class ChunkStepEngine:
         self._p2p_sizes = list(chunk_sizes)
         self._p2p_offsets = offsets
         self.block_off = torch.tensor(offsets, dtype=torch.int64, device=self.device)
-        self.grad_slab = PeerBuffer(total, self.dtype, self.device, self.group)
+        self.grad_slab = PeerBuffer(total, self.dtype, self.device, self.group, zero=True)    # finite padding
         self.gather_slab = PeerBuffer(total, self.dtype, self.device, self.group)
         self.peer_barrier = PeerBarrier(self.device, self.group, timeout_ms)
         return self
@@ -430,6 +430,51 @@ class ChunkStepEngine:
             kernels.adam_multi_push(self.table, self.ctl, self.gather_slab.table, self.block_off)
         if host_params is not None:
             main.wait_stream(d2h)
+        self.peer_barrier(self.ctl)
+
+    def step_sharded_probe_first(self, pull_ctas: int = 36):
+        """The peer-mapped sharded step with the decision taken BEFORE the reduction, so that the in-place update of
+        chunk k can run while chunk k + 1 is still being reduced on a second stream (the SMs split between the two
+        kernels).  It rests on one property of the pull reduce-scatter — the rank average, accumulated in fp32 and
+        rounded once, is non-finite exactly when one of its inputs is — so the overflow word can be formed from
+        the INPUTS: every rank probes its own gradient slab (one launch, HBM speed), and the barrier ORs the words.
+
+            barrier                  every rank's gradient blocks are written
+            probe of the own slab    elx_grad_check over all blocks of this rank
+            barrier + agree          found_inf OR-ed over the ranks
+            decision                 elx_step_begin
+            side stream:  pull(0) pull(1) pull(2) ...                     (``pull_ctas`` CTAs)
+            main stream:       update+push(0) update+push(1) ...          (the remaining SMs)
+            barrier                  every rank's pushes have landed
+
+        Same results as ``step_sharded_p2p`` (tested bit for bit); the per-chunk overflow words are not filled in
+        (only the global decision exists).  Pays where the two phases are bound by different things — two ranks:
+        the pull by the links, the update by HBM.  Needs slabs whose padding is finite (``enable_p2p`` zeroes
+        them) and one block per chunk."""
+        if getattr(self, '_p2p_pool', 0) or self.clipping:
+            raise RuntimeError('step_sharded_probe_first needs a block per chunk and no gradient clipping')
+        main = torch.cuda.current_stream(self.device)
+        side = self._side_streams()[0]
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.peer_barrier(self.ctl)
+        kernels.grad_check(self.grad_slab.local, ctl=self.ctl)
+        self.peer_barrier(self.ctl, exchange_overflow=True)
+        kernels.step_begin(self.ctl, self.scaler.cfg, None, self.chunk_flags)
+        side.wait_stream(main)
+        kernels.set_tuning(pull_tma_ctas=pull_ctas, adam_tma_ctas=max(1, sms - pull_ctas))
+        try:
+            pulled = []
+            with torch.cuda.stream(side):
+                for k in range(self.n_chunks):
+                    # no control block: the decision of this step is taken, and what this probe would raise
+                    # must not leak into the next one
+                    kernels.pull_reduce_multi(self.table, self.grad_slab.table, self.block_off, None, first=k, count=1)
+                    pulled.append(side.record_event())
+            for k in range(self.n_chunks):
+                main.wait_event(pulled[k])
+                kernels.adam_multi_push(self.table, self.ctl, self.gather_slab.table, self.block_off, first=k, count=1)
+        finally:
+            kernels.set_tuning(pull_tma_ctas=-1, adam_tma_ctas=-1)
         self.peer_barrier(self.ctl)
 
     def enable_staging(self, pool: int = 4):

@@ -103,7 +103,8 @@ def _worker(rank, world, port):
     dist.destroy_process_group()
 
 
-def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False, pull_variant=1, overlapped=False):
+def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False, pull_variant=1, overlapped=False,
+                probe_first=False):
     """The NVLink path: pull reduce-scatter + probe, overflow agreement inside the barrier, fused update with
     push all-gather — no NCCL collective in the step."""
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
@@ -189,6 +190,8 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False
             engine.step_sharded_staged()
         elif overlapped:
             engine.step_sharded_overlapped(pull_ctas=40)
+        elif probe_first:
+            engine.step_sharded_probe_first(pull_ctas=40)
         else:
             engine.step_sharded_p2p()
         torch.cuda.synchronize()
@@ -357,6 +360,17 @@ def test_sharded_step_with_the_reduction_overlapping_the_update():
     if torch.cuda.device_count() < 2:
         pytest.skip('needs 2 GPUs')
     mp.spawn(_p2p_worker, args=(2, 29865, 'float16', None, False, 1, True), nprocs=2)
+
+
+@pytest.mark.parametrize('world,dtype_name', [(2, 'float16'), (2, 'bfloat16'), (4, 'float16')])
+def test_sharded_step_decided_on_the_inputs_with_the_reduction_overlapping_the_update(world, dtype_name):
+    """The overflow word formed from every rank's own gradient blocks before the reduction (the fp32-accumulated
+    average is non-finite exactly when an input is), so that the in-place update of chunk k runs while chunk
+    k + 1 is still being reduced: same oracle, same bits as the two-phase step."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f'needs {world} GPUs')
+    mp.spawn(_p2p_worker, args=(world, 29920 + world + (10 if dtype_name == 'bfloat16' else 0), dtype_name, None, False, 1,
+                                False, True), nprocs=world)
 
 
 def test_sharded_step_p2p_pooled_blocks():
