@@ -256,3 +256,25 @@ def test_single_pass_step_bookkeeping_equals_the_two_phase_step(host_backend):
             for x, y in zip(sa[:4], sb[:4]):
                 assert torch.equal(x, y), step
     assert b.read_control().cur_set == 4 % 2    # four applied steps: the sets changed roles four times
+    # one more applied step leaves set 1 current; normalize_sets makes the live state "set 0" again, after which
+    # the in-place step continues from it exactly as the reference engine does
+    for eng in (a, b):
+        for k in range(eng.n_chunks):
+            eng.shards[k][3].fill_(0.01)
+    a.probe()
+    a.step()
+    b.step_single_pass()
+    assert b.read_control().cur_set == 1
+    b.normalize_sets()
+    assert b.read_control().cur_set == 0
+    for sa, sb in zip(a.shards, b.shards):
+        for x, y in zip(sa[:4], sb[:4]):
+            assert torch.equal(x, y)
+    for eng in (a, b):
+        for k in range(eng.n_chunks):
+            eng.shards[k][3].fill_(-0.02)
+        eng.probe()
+        eng.step()
+    for sa, sb in zip(a.shards, b.shards):
+        for x, y in zip(sa[:4], sb[:4]):
+            assert torch.equal(x, y)
