@@ -104,7 +104,7 @@ def _worker(rank, world, port):
 
 
 def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False, pull_variant=1, overlapped=False,
-                probe_first=False):
+                probe_first=False, host_buffers=False):
     """The NVLink path: pull reduce-scatter + probe, overflow agreement inside the barrier, fused update with
     push all-gather — no NCCL collective in the step."""
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
@@ -153,7 +153,10 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False
     if overlapped:
         engine.enable_single_pass()
 
-    def fill(step):
+    host_in = [torch.empty(C, dtype=dtype).pin_memory() for C in chunk_sizes] if host_buffers else None
+    host_out = [torch.empty(C // world, dtype=dtype).pin_memory() for C in chunk_sizes] if host_buffers else None
+
+    def fill(step, into_blocks=not host_buffers):
         per_rank = []
         for c, C in enumerate(chunk_sizes):
             rank_grads = []
@@ -168,11 +171,18 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False
                     g[5] = float('inf')    # lands in rank 0's shard only
                 rank_grads.append(g)
             per_rank.append(rank_grads)
-            engine.grad_block(c).copy_(rank_grads[rank])
+            if into_blocks:
+                engine.grad_block(c).copy_(rank_grads[rank])
+            else:
+                host_in[c].copy_(rank_grads[rank])
+        if not into_blocks:
+            for c in range(len(chunk_sizes)):
+                if pool and c >= pool:
+                    host_in[c].copy_(host_in[c - pool])
         return per_rank
 
     # the pull alone: bit-exact against the oracle's fp32-accumulated average
-    per_rank = fill(0)
+    per_rank = fill(0, into_blocks=True)
     engine.peer_barrier(engine.ctl)
     K.pull_reduce_multi(engine.table, engine.grad_slab.table, engine.block_off, engine.ctl,
                         chunk_flags=engine.chunk_flags)
@@ -188,6 +198,8 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False
         per_rank = fill(step)
         if staged:
             engine.step_sharded_staged()
+        elif host_buffers:
+            engine.step_sharded_p2p(host_grads=host_in, host_params=host_out)
         elif overlapped:
             engine.step_sharded_overlapped(pull_ctas=40)
         elif probe_first:
@@ -217,11 +229,13 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False
             dist.all_gather(others, mine16)
             if not pool or c + pool >= len(chunk_sizes):    # a pooled gather block holds its LAST chunk
                 assert bits_equal(engine.gather_block(c), torch.cat(others)), (step, rank, c)
+            if host_buffers:
+                assert bits_equal(host_out[c], mine16), (step, rank, c)
     dist.barrier()
     dist.destroy_process_group()
 
 
-def _mm_worker(rank, world, port, dtype_name='float16'):
+def _mm_worker(rank, world, port, dtype_name='float16', host_buffers=False):
     """The single-pass sharded step: reduce-scatter, update and all-gather in one kernel through the NVLink switch
     (multimem.ld_reduce / multimem.st on symmetric memory).  The switch adds the ranks' values in an order of its
     own, so the gradients here are multiples of a power of two small enough for every partial sum to be exact:
@@ -265,6 +279,8 @@ def _mm_worker(rank, world, port, dtype_name='float16'):
     engine.set_hyper(hypers)
     engine.enable_single_pass()
     engine.enable_multicast(chunk_sizes, timeout_ms=5000)
+    host_in = [torch.empty(C, dtype=dtype).pin_memory() for C in chunk_sizes] if host_buffers else None
+    host_out = [torch.empty(C // world, dtype=dtype).pin_memory() for C in chunk_sizes] if host_buffers else None
     def one_step(step):
         per_rank = []
         for c, C in enumerate(chunk_sizes):
@@ -277,8 +293,11 @@ def _mm_worker(rank, world, port, dtype_name='float16'):
                     g[5] = float('inf')    # lands in rank 0's shard only
                 rank_grads.append(g)
             per_rank.append(rank_grads)
-            engine.grad_block(c).copy_(rank_grads[rank])
-        engine.step_sharded_single_pass()
+            (host_in[c] if host_buffers else engine.grad_block(c)).copy_(rank_grads[rank])
+        if host_buffers:    # blocks filled from pinned memory chunk by chunk, shards copied out behind their update
+            engine.step_sharded_single_pass(host_grads=host_in, host_params=host_out)
+        else:
+            engine.step_sharded_single_pass()
         torch.cuda.synchronize()
         for c, C in enumerate(chunk_sizes):
             S = C // world
@@ -299,6 +318,8 @@ def _mm_worker(rank, world, port, dtype_name='float16'):
             want16 = torch.empty(S, dtype=dtype)
             orc.cast(shards[c][0].cpu(), want16)
             assert bits_equal(shards[c][3], want16), (step, rank, c)
+            if host_buffers:    # also after the overflow step, when the rebuilt working copies are sent again
+                assert bits_equal(host_out[c], want16), (step, rank, c)
 
     def agree(failure):
         verdict = torch.tensor([0 if failure is None else 1], device=dev)
@@ -336,6 +357,12 @@ def test_sharded_single_pass_step_through_the_switch(world, dtype_name):
     mp.spawn(_mm_worker, args=(world, 29900 + world + (10 if dtype_name == 'bfloat16' else 0), dtype_name), nprocs=world)
 
 
+def test_sharded_single_pass_step_fed_from_host_buffers():
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    mp.spawn(_mm_worker, args=(2, 29935, 'float16', True), nprocs=2)
+
+
 @pytest.mark.parametrize('world', [2, 4])
 def test_sharded_step_staged_copy_engines(world):
     """The same step with the copy engines moving the slices (local staging + reduce kernel on local memory,
@@ -371,6 +398,16 @@ def test_sharded_step_decided_on_the_inputs_with_the_reduction_overlapping_the_u
         pytest.skip(f'needs {world} GPUs')
     mp.spawn(_p2p_worker, args=(world, 29920 + world + (10 if dtype_name == 'bfloat16' else 0), dtype_name, None, False, 1,
                                 False, True), nprocs=world)
+
+
+@pytest.mark.parametrize('pool', [None, 2])
+def test_sharded_step_p2p_fed_from_host_buffers(pool):
+    """Gradient blocks filled from pinned host memory chunk by chunk while earlier chunks are reduced, refreshed
+    shards copied out behind their update; with a pool of two blocks a block is refilled only once every rank is
+    done reading its previous tenant."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    mp.spawn(_p2p_worker, args=(2, 29940 + (pool or 0), 'float16', pool, False, 1, False, False, True), nprocs=2)
 
 
 def test_sharded_step_p2p_pooled_blocks():
