@@ -21,7 +21,10 @@ def _ctl_tuple(c):
     return (c.scale, c.found_inf, c.growth_step, c.hysteresis_step, c.step, c.skip, c.div_scale, c.skipped_steps)
 
 
-def test_config1_ten_steps_full_size(cuda, oracle):
+@pytest.mark.parametrize('single_pass', [False, True])
+def test_config1_ten_steps_full_size(cuda, oracle, single_pass):
+    """single_pass: the step as ONE launch that detects inf/nan itself and updates out of place between two state
+    sets, reading the gradients from blocks of their own (what bench.py times on one GPU)."""
     from elixir_b200 import kernels as K
     from elixir_b200.engine import ChunkStepEngine
     from elixir_b200.scaler import DynamicGradScaler
@@ -31,32 +34,43 @@ def test_config1_ten_steps_full_size(cuda, oracle):
     host = oracle.ChunkSet(torch.float16)
     host_ctl = oracle.new_ctl(scale)
     gen = torch.Generator().manual_seed(0)
-    hs = []
+    hs, blocks = [], []
     for c in range(n_chunks):
         master = torch.randn(n, generator=gen) * 0.02
         lowp = torch.zeros(n, dtype=torch.float16)
         hm = (master.clone(), torch.zeros(n), torch.zeros(n), lowp)
         host.add_chunk(*hm, n, [(0, n, 0)])
         hs.append(hm)
-        engine.add_shard(master.to(cuda), torch.zeros(n, dtype=torch.float16, device=cuda), n, [(0, n, 0)])
+        block = torch.zeros(n, dtype=torch.float16, device=cuda) if single_pass else None
+        blocks.append(block)
+        engine.add_shard(master.to(cuda), torch.zeros(n, dtype=torch.float16, device=cuda), n, [(0, n, 0)], grad_src=block)
     engine.finalize()
     engine.set_hyper(hyper)
+    if single_pass:
+        engine.enable_single_pass()
     for step in range(10):
         for c in range(n_chunks):
             g = (torch.randn(n, generator=gen) * 1e-3 * scale).half()
             hs[c][3].copy_(g)
-            engine.land(c, g.to(cuda))
-        engine.step()
+            if single_pass:
+                blocks[c].copy_(g)
+            else:
+                engine.land(c, g.to(cuda))
+        if single_pass:
+            engine.step_single_pass()
+        else:
+            engine.step()
         assert not host.step(host_ctl, engine.scaler.cfg, hyper, probe=True, f64=True)
         assert _ctl_tuple(engine.read_control()) == _ctl_tuple(host_ctl)
+        shards = engine.current_shards()
         for c in range(n_chunks):
-            for name, got, want in zip(('master', 'exp_avg', 'exp_avg_sq'), engine.shards[c][:3], hs[c][:3]):
+            for name, got, want in zip(('master', 'exp_avg', 'exp_avg_sq'), shards[c][:3], hs[c][:3]):
                 ok, ratio = close_1e6(got, want.double())
                 assert ok, (step, c, name, ratio)
             want16 = torch.empty(n, dtype=torch.float16)
-            oracle.cast(engine.shards[c][0].cpu(), want16)
-            assert bits_equal(engine.shards[c][3], want16)
-            assert lowp_within_1ulp(engine.shards[c][3], hs[c][3], hs[c][0])[0]
+            oracle.cast(shards[c][0].cpu(), want16)
+            assert bits_equal(shards[c][3], want16)
+            assert lowp_within_1ulp(shards[c][3], hs[c][3], hs[c][0])[0]
     assert engine.read_control().status == 0 and engine.read_control().step == 10
 
 
@@ -69,8 +83,9 @@ def _inject(g, gen, rate):
     return out, int(mask.sum().item())
 
 
+@pytest.mark.parametrize('single_pass', [False, True])
 @pytest.mark.parametrize('hysteresis,growth_interval', [(1, 1000), (2, 1000), (1, 5), (2, 5)])
-def test_config4_overflow_trajectory_16m_elementwise(cuda, oracle, hysteresis, growth_interval):
+def test_config4_overflow_trajectory_16m_elementwise(cuda, oracle, hysteresis, growth_interval, single_pass):
     from elixir_b200 import kernels as K
     from elixir_b200.engine import ChunkStepEngine
     from elixir_b200.scaler import DynamicGradScaler
@@ -92,6 +107,8 @@ def test_config4_overflow_trajectory_16m_elementwise(cuda, oracle, hysteresis, g
         engine.add_shard(master.to(cuda), torch.zeros(n, dtype=torch.float16, device=cuda), n, [(0, n, 0)])
     engine.finalize()
     engine.set_hyper(hyper)
+    if single_pass:
+        engine.enable_single_pass()
     skipped_steps = []
     for step in range(20):
         for c in range(n_chunks):
@@ -99,17 +116,24 @@ def test_config4_overflow_trajectory_16m_elementwise(cuda, oracle, hysteresis, g
             if step in bad_steps:
                 g, count = _inject(g, gen, 1e-6 if c else 2e-6)
             hs[c][3].copy_(g)
-            engine.land(c, g.to(cuda))
-        flags = engine.chunk_flags.tolist()
-        assert flags == [int(oracle.probe(hs[c][3])) for c in range(n_chunks)]
-        engine.step()
+            if single_pass:
+                engine.shards[c][3].copy_(g)    # no probe beforehand: the update kernel finds what there is to find
+            else:
+                engine.land(c, g.to(cuda))
+        if single_pass:
+            engine.step_single_pass()
+        else:
+            flags = engine.chunk_flags.tolist()
+            assert flags == [int(oracle.probe(hs[c][3])) for c in range(n_chunks)]
+            engine.step()
         skipped = host.step(host_ctl, engine.scaler.cfg, hyper, probe=True, f64=True)
         assert _ctl_tuple(engine.read_control()) == _ctl_tuple(host_ctl), step
         if skipped:
             skipped_steps.append(step)
         if step % 5 == 4 or skipped:
+            shards = engine.current_shards()
             for c in range(n_chunks):
-                for got, want in zip(engine.shards[c][:3], hs[c][:3]):
+                for got, want in zip(shards[c][:3], hs[c][:3]):
                     assert close_1e6(got, want.double())[0], (step, c)
     assert set(skipped_steps) <= bad_steps and len(skipped_steps) >= 1
     assert engine.read_control().status == 0
