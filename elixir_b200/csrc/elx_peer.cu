@@ -143,11 +143,13 @@ __global__ void __launch_bounds__(256) pull_reduce_kernel(const __grid_constant_
 // multicast) into a shared-memory stage two tiles ahead; the warps sum the slices out of shared memory
 // in rank order, store the shard tile and probe it.  Larger NVLink requests than per-lane loads, and the
 // link stays busy while a tile is being summed.
-// three stages of W slices of 8 KB each (a deeper ring measured slower: 12 stages at W = 2 took 20.2 ms
-// against 19.3 ms for the step's pull phase)
-template <int kWorld>
+// Ring depth.  With one CTA on every SM three stages of W slices of 8 KB each are enough (a deeper ring measured
+// slower there: 12 stages at W = 2 took 20.2 ms against 19.3 ms for the step's pull phase).  When the pull runs
+// on a few SMs beside an update kernel ("pull_tma_ctas"), three stages keep only 24 KB of remote data in flight
+// per SM, about 7 GB/s each; the deep ring fills the shared memory (192 KB: 12 stages at W = 2, 6 at W = 4).
+template <int kWorld, bool kDeep>
 struct PullRing {
-    static constexpr int kStages = 3;
+    static constexpr int kStages = kDeep ? (kWorld == 2 ? 12 : kWorld == 4 ? 6 : 3) : 3;
 };
 constexpr int kPullThreads = 256;
 
@@ -160,10 +162,10 @@ struct PullSlot {
     int kind;             // 1 = staged in shared memory, 2 = ragged (direct loads), 3 = bad descriptor
 };
 
-template <int DT, int kWorld>
+template <int DT, int kWorld, bool kDeep>
 __global__ void __launch_bounds__(kPullThreads, 1) pull_reduce_tma_kernel(const __grid_constant__ PullArgs a) {
     static_assert(DT != ELX_F32, "the staged pull is for 16-bit chunks");
-    constexpr int kPullStages = PullRing<kWorld>::kStages;
+    constexpr int kPullStages = PullRing<kWorld, kDeep>::kStages;
     using T = typename Lp<DT>::T;
     constexpr int kSliceBytes = kTile * 2;
     constexpr int kStageBytes = kWorld * kSliceBytes;
@@ -312,12 +314,12 @@ __global__ void __launch_bounds__(kPullThreads, 1) pull_reduce_tma_kernel(const 
     if (ballot_desc && lane == 0 && a.ctl) atomicOr(&a.ctl->status, ELX_STAT_BAD_DESC);
 }
 
-template <int DT, int kWorld>
+template <int DT, int kWorld, bool kDeep = false>
 int launch_pull_tma(const PullArgs& a, cudaStream_t s) {
     if constexpr (DT == ELX_F32) {
         return ELX_ERR_DTYPE;
     } else {
-        constexpr int smem = PullRing<kWorld>::kStages * kWorld * kTile * 2;
+        constexpr int smem = PullRing<kWorld, kDeep>::kStages * kWorld * kTile * 2;
         static bool opted_in[64];
         int dev = -1;
         if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
@@ -325,7 +327,7 @@ int launch_pull_tma(const PullArgs& a, cudaStream_t s) {
             return ELX_ERR_NODEVICE;
         }
         if (!opted_in[dev]) {
-            const cudaError_t attr = cudaFuncSetAttribute(pull_reduce_tma_kernel<DT, kWorld>,
+            const cudaError_t attr = cudaFuncSetAttribute(pull_reduce_tma_kernel<DT, kWorld, kDeep>,
                                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
             if (attr != cudaSuccess) {
                 const int rc = record_cuda(attr);
@@ -337,7 +339,7 @@ int launch_pull_tma(const PullArgs& a, cudaStream_t s) {
         int grid = grid_for(a.n_tiles, 1);
         if (grid < 0) return grid;
         if (g_tune.pull_tma_ctas > 0 && g_tune.pull_tma_ctas < grid) grid = g_tune.pull_tma_ctas;
-        pull_reduce_tma_kernel<DT, kWorld><<<grid, kPullThreads, smem, s>>>(a);
+        pull_reduce_tma_kernel<DT, kWorld, kDeep><<<grid, kPullThreads, smem, s>>>(a);
         return record_cuda(cudaGetLastError());
     }
 }
@@ -354,9 +356,10 @@ int launch_pull_inst(const PullArgs& a, cudaStream_t s) {
 template <int DT>
 int launch_pull(const PullArgs& a, cudaStream_t s) {
     if (g_tune.pull_variant == 1 && DT != ELX_F32) {
+        const bool deep = g_tune.pull_tma_ctas > 0;   // few CTAs: each one keeps more data in flight
         switch (a.grads.world) {
-            case 2: return launch_pull_tma<DT, 2>(a, s);
-            case 4: return launch_pull_tma<DT, 4>(a, s);
+            case 2: return deep ? launch_pull_tma<DT, 2, true>(a, s) : launch_pull_tma<DT, 2>(a, s);
+            case 4: return deep ? launch_pull_tma<DT, 4, true>(a, s) : launch_pull_tma<DT, 4>(a, s);
             case 8: return launch_pull_tma<DT, 8>(a, s);
         }
     }
