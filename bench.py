@@ -322,10 +322,28 @@ def run_ours(args):
 
     parity = None
     if world > 1 and not args.no_parity_check:
-        ok, cases, failure = sharded_parity_check(args.collective, world, rank, device, group, args.seed)
-        parity = {'ok': ok, 'world': world, 'cases': cases, 'collective': args.collective,
-                  'what': 'small ragged chunk set, 5 steps (1 skipped by an inf in one rank\'s shard), fp16 and bf16, '
-                          'against the CPU oracle on every rank'}
+        what = ('small ragged chunk set, 5 steps (1 skipped by an inf in one rank\'s shard), fp16 and bf16, against the CPU '
+                'oracle on every rank')
+        note = None
+        if args.collective_was_auto and args.collective == 'mm':
+            # the switch-side path needs multicast support of GPUs, driver and torch: where its self-check does not
+            # come out clean the benchmark falls back to the peer-mapped kernels instead of giving up
+            try:
+                ok, cases, failure = sharded_parity_check('mm', world, rank, device, group, args.seed)
+            except Exception as exc:    # noqa: BLE001
+                ok, cases, failure = False, 0, f'{type(exc).__name__}: {exc}'
+            agreed = torch.tensor([1 if ok else 0], device=device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            if not agreed.item():
+                note = f'--collective auto: the switch-side path did not pass its self-check here ({failure}); using p2p'
+                if rank == 0:
+                    print('bench: ' + note, file=sys.stderr)
+                args.collective = 'p2p'
+        if note is not None or not (args.collective_was_auto and args.collective == 'mm'):
+            ok, cases, failure = sharded_parity_check(args.collective, world, rank, device, group, args.seed)
+        parity = {'ok': ok, 'world': world, 'cases': cases, 'collective': args.collective, 'what': what}
+        if note:
+            parity['note'] = note
         if not ok:
             if failure:
                 print(f'bench: parity check failed on rank {rank}: {failure}', file=sys.stderr)
@@ -360,7 +378,9 @@ def run_ours(args):
         # replicated blocks: refuse cleanly, before anything is allocated, where that does not fit
         need = n_chunks * shard * 26 + 2 * n_chunks * chunk * 2
         free, _ = torch.cuda.mem_get_info(device)
-        if need > 0.95 * free:
+        if need > 0.95 * free and args.collective_was_auto:
+            args.collective = 'p2p'    # (the self-check above ran on the switch-side path; the timed step is p2p)
+        elif need > 0.95 * free:
             raise SystemExit(f'bench: --collective mm needs {need / 1e9:.0f} GB per GPU at {world} ranks for this workload '
                              f'({free / 1e9:.0f} GB free); use --collective p2p')
 
@@ -1058,7 +1078,8 @@ def main():
                     "'host-streamed': the same state moved by the copy engines through device staging sets (N=1 only)")
     ap.add_argument('--e2e-steps', type=int, default=10)
     args = ap.parse_args()
-    if args.collective == 'auto':
+    args.collective_was_auto = args.collective == 'auto'
+    if args.collective_was_auto:
         args.collective = 'mm' if args.gpus >= 8 and args.workload == 'auto' and not args.pool else 'p2p'
     if args.workload == 'residency':
         run_residency(args)
