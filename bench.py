@@ -214,7 +214,7 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
             engine.enable_single_pass()
             engine.enable_multicast(chunk_sizes, timeout_ms=5000)
             gather = [engine.gather_block(c) for c in range(len(chunk_sizes))]
-        elif collective in ('p2p', 'p2p-overlap', 'staged'):
+        elif collective in ('p2p', 'p2p-fused', 'p2p-overlap', 'staged'):
             engine.enable_p2p(chunk_sizes, timeout_ms=5000)
             if collective == 'staged':
                 engine.enable_staging(pool=2)
@@ -238,7 +238,7 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
                         g[5] = float('inf')    # lands in rank 0's shard only
                     rank_grads.append(g)
                 per_rank.append(rank_grads)
-                if collective in ('p2p', 'p2p-overlap', 'staged', 'mm'):
+                if collective in ('p2p', 'p2p-fused', 'p2p-overlap', 'staged', 'mm'):
                     engine.grad_block(c).copy_(rank_grads[rank])
                 else:
                     blocks.append(rank_grads[rank].to(device))
@@ -246,7 +246,7 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
             for c, C in enumerate(chunk_sizes):
                 S = C // world
                 mine = [g[rank * S:(rank + 1) * S].contiguous() for g in per_rank[c]]
-                if collective in ('p2p', 'p2p-overlap', 'staged', 'mm'):
+                if collective in ('p2p', 'p2p-fused', 'p2p-overlap', 'staged', 'mm'):
                     reduced.append(orc.reduce_avg_f32acc(mine))    # rank-order fp32 accumulation, one rounding
                 else:
                     out = torch.empty(S, dtype=dtype, device=device)
@@ -261,6 +261,8 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
                 engine.step_sharded_p2p()
             elif collective == 'p2p-overlap':
                 engine.step_sharded_probe_first(pull_ctas=40)
+            elif collective == 'p2p-fused':
+                engine.step_sharded_pull_push()
             elif collective == 'mm':
                 engine.step_sharded_single_pass()
             elif collective == 'staged':
@@ -427,7 +429,7 @@ def run_ours(args):
                 gen = torch.Generator(device=device).manual_seed(args.seed + 7919 * (c + 1))
                 grad_blocks.append(synth_grad(shard, device, gen, scale, sigma, dtype))
         gather_blocks = None
-    elif args.collective in ('p2p', 'p2p-overlap', 'staged', 'mm'):
+    elif args.collective in ('p2p', 'p2p-fused', 'p2p-overlap', 'staged', 'mm'):
         # NVLink path: every chunk owns a block in the peer-mapped gradient and gather slabs
         if args.collective == 'mm':
             engine.enable_multicast([chunk] * n_chunks)
@@ -497,6 +499,8 @@ def run_ours(args):
             engine.step_sharded_p2p()
         elif args.collective == 'p2p-overlap':
             engine.step_sharded_probe_first(pull_ctas=args.pull_ctas)
+        elif args.collective == 'p2p-fused':
+            engine.step_sharded_pull_push()
         elif args.collective == 'mm':
             engine.step_sharded_single_pass()
         elif args.collective == 'staged':
@@ -566,6 +570,10 @@ def run_ours(args):
             'collectives': 'none (1 GPU)' if world == 1 else
                            ('fused into the kernels over peer-mapped NVLink memory (pull reduce-scatter + probe, '
                             'Adam + push all-gather)' if args.collective == 'p2p' else
+                            'both collectives inside the in-place update kernel over peer-mapped NVLink memory (per tile: bulk loads '
+                            'of every rank\'s gradient slice, rank average, Adam, bulk stores to every rank\'s gather block); '
+                            'the overflow decision is taken first, from a probe of every rank\'s own gradient blocks'
+                            if args.collective == 'p2p-fused' else
                             'the same two kernels chunk by chunk on two streams, the update of a chunk running while the next '
                             'one is reduced; the overflow decision is taken first, from a probe of every rank\'s own gradient '
                             'blocks' if args.collective == 'p2p-overlap' else
@@ -653,6 +661,18 @@ def run_ours(args):
                      'bytes per collective) so that the variants compare; the switch-side sum moves fewer bytes than that')
             result['gpu_launches'] = args.steps * 7
             result['phases_ms'] = mm_phases(engine)
+        elif args.collective == 'p2p-fused':
+            # one kernel behind the probe of the inputs: bounded by the slower of the links (both collectives share
+            # them) and HBM (own gradient slice 2 B, master and moments 24 B, working copy 2 B, own gather slot 2 B
+            # per own element, plus what the peers read from this rank's blocks and write into its gather blocks)
+            probe_ms = n_chunks * chunk * 2 / (peak * 1e9) * 1e3
+            hbm_ms = engine.n_elements() * (30 + 4 * (world - 1)) / (peak * 1e9) * 1e3
+            result['roofline'].update(
+                target_ms=probe_ms + max(2 * link_ms, hbm_ms), frac_of_target=(probe_ms + max(2 * link_ms, hbm_ms)) / ms_per_step,
+                target_note='probe of the own gradient blocks at the HBM rate + one kernel: max(NVLink time of both collectives '
+                            'at 900 GB/s, HBM time)')
+            result['gpu_launches'] = args.steps * 7
+            result['phases_ms'] = fused_phases(engine)
         elif args.collective == 'p2p-overlap':
             # one pipelined phase behind the probe of the inputs: bounded by the slower of the links (both collectives
             # share them) and HBM (probe of the own blocks 2 B x C, pull 4 B and update + push 30 B per own element)
@@ -723,6 +743,24 @@ def mm_phases(engine):
     return {'reduce_adam_gather_one_kernel': ev[0].elapsed_time(ev[1])}
 
 
+def fused_phases(engine):
+    """CUDA-event times of the probe of the inputs and of the one fused kernel of an (untimed) p2p-fused step."""
+    from elixir_b200 import kernels as K
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    engine.peer_barrier(engine.ctl)
+    ev[0].record()
+    K.grad_check(engine.grad_slab.local, ctl=engine.ctl)
+    ev[1].record()
+    engine.peer_barrier(engine.ctl, exchange_overflow=True)
+    K.step_begin(engine.ctl, engine.scaler.cfg, None, engine.chunk_flags)
+    ev[2].record()
+    K.adam_multi_pull_push(engine.table, engine.ctl, engine.grad_slab.table, engine.gather_slab.table, engine.block_off)
+    ev[3].record()
+    engine.peer_barrier(engine.ctl)
+    torch.cuda.synchronize()
+    return {'probe_of_own_gradient_blocks': ev[0].elapsed_time(ev[1]), 'reduce_adam_gather_one_kernel': ev[2].elapsed_time(ev[3])}
+
+
 def p2p_phases(engine):
     """CUDA-event time of the two fused kernels of one (untimed) NVLink step, barriers included in neither."""
     from elixir_b200 import kernels as K
@@ -773,7 +811,7 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
             conservative_ms = timed(plain, max(1, min(args.steps, args.e2e_steps))) / max(1, min(args.steps, args.e2e_steps))
             engine.enable_speculation()
             fn = lambda: engine.step_from_host(grads, outs, speculative=True)    # noqa: E731
-    elif args.collective in ('p2p', 'p2p-overlap'):
+    elif args.collective in ('p2p', 'p2p-fused', 'p2p-overlap'):
         # chunk by chunk: block k filled from the host while earlier chunks are pulled, shard k copied out behind
         # its update while later chunks are updated and pushed
         fn = lambda: engine.step_sharded_p2p(host_grads=grads, host_params=outs)    # noqa: E731
@@ -800,7 +838,7 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
         'h2d_bytes_per_step': n_chunks * in_elems * 2 * world, 'd2h_bytes_per_step': n_chunks * shard * 2 * world,
         'conservative_ms_per_step': conservative_ms,
         'api': ('ChunkStepEngine.step_from_host' + ('' if conservative_ms is None else '(speculative=True)')) if world == 1 else
-               ('ChunkStepEngine.step_sharded_p2p(host_grads=, host_params=)' if args.collective in ('p2p', 'p2p-overlap') else
+               ('ChunkStepEngine.step_sharded_p2p(host_grads=, host_params=)' if args.collective in ('p2p', 'p2p-fused', 'p2p-overlap') else
                 'ChunkStepEngine.step_sharded_single_pass(host_grads=, host_params=)' if args.collective == 'mm' else
                 'H2D into the gradient slab + ChunkStepEngine.step_sharded_staged + D2H of the shards'
                 if args.collective == 'staged' else 'ChunkStepEngine.step_sharded(host_grads=, host_params=)'),
@@ -1037,12 +1075,13 @@ def main():
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--seed', type=int, default=0)
-    ap.add_argument('--collective', default='auto', choices=['auto', 'p2p', 'p2p-overlap', 'mm', 'staged', 'nccl'],
+    ap.add_argument('--collective', default='auto', choices=['auto', 'p2p', 'p2p-fused', 'p2p-overlap', 'mm', 'staged', 'nccl'],
                     help='N > 1: p2p = pull reduce-scatter and push all-gather kernels over peer-mapped NVLink memory; '
                     'mm = ONE kernel per step that reduces, updates and gathers tile by tile through the NVLink switch '
-                    '(multimem); p2p-overlap = the p2p kernels with the decision taken on the inputs first, so that the update '
+                    '(multimem); p2p-fused = both collectives inside the in-place update kernel over peer-mapped memory, the '
+                    'decision taken on the inputs first (two ranks); p2p-overlap = the p2p kernels with the decision taken on the inputs first, so that the update '
                     'of a chunk runs while the next one is reduced; staged = copy engines; nccl = NCCL on side streams; '
-                    'auto = mm from 8 ranks on, else p2p')
+                    'auto = mm from 8 ranks on, p2p-fused at 2 ranks, else p2p')
     ap.add_argument('--workload', default='auto', choices=['auto', 'opt66b_bf16', 'residency'],
                     help='N > 1: auto = OPT-13B-shaped fp16 chunk set; opt66b_bf16 = OPT-66B-shaped bf16 chunk set (8 GPUs); '
                     'residency = one training iteration of an MLP stack through the wrapper under three residency modes')

@@ -158,6 +158,7 @@ PROTOTYPES = {
     'elx_pull_reduce_multi': (_i, [_p, _i, _i, _i64, _i, ElxPeerTable, _p, _p, _p, _p, _p]),
     'elx_copy_async': (_i, [_p, _p, _i64, _p]),
     'elx_adam_multi_push': (_i, [_p, _i, _i, _i64, _i, _p, _p, _i, _p, ElxPeerTable, _p, _p]),
+    'elx_adam_multi_pull_push': (_i, [_p, _i, _i, _i64, _i, _p, _p, _i, _p, ElxPeerTable, ElxPeerTable, _p, _p]),
     'elx_adam_chunk': (_i, [_p, _p, _p, _p, _i, _i64, _i64, ElxHyper, _p, _p]),
     'elx_cast_copyback': (_i, [_p, _p, _i, _i64, _p]),
 }

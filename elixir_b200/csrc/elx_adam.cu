@@ -89,7 +89,8 @@ struct AdamArgs {
     // collectives through the switch: multicast addresses of all ranks' gradient / gather slabs (null = none)
     const char* mc_grads;
     char* mc_gather;
-    ElxPeerTable grads;        // the gradient slabs as plain peer addresses (ragged tiles)
+    ElxPeerTable grads;        // the gradient slabs as plain peer addresses (ragged tiles; all tiles when `pull`)
+    int pull;                  // 1: the gradient of a tile is the rank average of the slabs, fetched in this kernel
     // single-shard form: the three tables travel in the kernel parameters
     ElxChunkDesc one_desc;
     ElxSeg one_seg;
@@ -442,10 +443,17 @@ __device__ __forceinline__ void mm_st8(void* mc, uint2 v) {
 
 // MM: the gradient tile is the switch-side sum over all ranks' gradient slabs and the refreshed working copy
 // is multicast to all ranks' gather slabs (16-bit chunks only).
-template <int DT, int MATH, bool MM>
+// PW > 1: the gradient tile is the rank average of PW ranks' gradient slabs, fetched here with PW plain
+// (non-multicast) bulk loads per tile -- the own slice into the stage's low-precision slot, the peers' slices
+// into PW - 1 staging slots behind the stage -- and summed by the threads exactly as the pull kernel sums
+// (fp32, rank order, one rounding to the chunk dtype).  16-bit chunks; shared memory allows PW = 2.
+template <int DT, int MATH, bool MM, int PW>
 __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_constant__ AdamArgs a) {
     using Stage = TmaStage<DT>;
     static_assert(!MM || DT != ELX_F32, "the multicast form is for 16-bit chunks");
+    static_assert(PW == 0 || (PW > 1 && !MM && DT != ELX_F32), "the pulling form is for 16-bit chunks, without multicast");
+    constexpr int kPeerSlots = PW > 1 ? PW - 1 : 0;
+    constexpr int kStageBytes = Stage::kBytes + kPeerSlots * Stage::kLowpBytes;
     extern __shared__ __align__(128) unsigned char s_dyn[];
     __shared__ GroupK s_group[kMaxGroups];
     __shared__ TileSlot s_slot[kTmaStages];
@@ -488,8 +496,9 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
 
     const int64_t tile_lo = src[a.first].tile_begin;
     const int64_t my_tiles = blockIdx.x < a.n_tiles ? (a.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const float inv_w = MM ? 1.0f / static_cast<float>(a.push.world) : 1.0f;
-    constexpr uint32_t kLoadBytes = MM ? 3 * Stage::kF32Bytes : Stage::kBytes;   // MM: no gradient tile from HBM
+    const float inv_w = (MM || PW > 1) ? 1.0f / static_cast<float>(a.push.world) : 1.0f;
+    // MM: no gradient tile from HBM; PW: the peers' slices come in beside the stage
+    constexpr uint32_t kLoadBytes = MM ? 3 * Stage::kF32Bytes : kStageBytes;
     ProducerCursor pc;
     float nan_acc = 0.0f;
     bool bad_desc = false;
@@ -502,17 +511,28 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         classify_tile<DT>(a, src, dst, segs, spec, tile_lo + blockIdx.x + k * gridDim.x, pc, slot);
         s_slot[s] = slot;
         if (slot.kind == kTileBulk) {
-            unsigned char* base = s_dyn + static_cast<size_t>(s) * Stage::kBytes;
+            unsigned char* base = s_dyn + static_cast<size_t>(s) * kStageBytes;
             mbar_arrive_expect_tx(&s_full[s], kLoadBytes);
-            if (!MM)
+            if constexpr (PW > 1) {
+                // slice of every rank's gradient block that belongs to this tile: the own one into the stage's
+                // low-precision slot, the others (over NVLink) into the slots behind the stage
+#pragma unroll
+                for (int i = 0; i < PW; ++i) {
+                    const int j = (a.grads.rank + i) % PW;
+                    unsigned char* dst = i == 0 ? base : base + Stage::kBytes + (i - 1) * Stage::kLowpBytes;
+                    bulk_g2s(dst, static_cast<const char*>(a.grads.base[j]) + slot.push_elem * Lp<DT>::kBytes,
+                             Stage::kLowpBytes, &s_full[s]);
+                }
+            } else if (!MM) {
                 bulk_g2s(base, static_cast<const char*>(slot.gsrc) + slot.e0 * Lp<DT>::kBytes, Stage::kLowpBytes,
                          &s_full[s]);
+            }
             bulk_g2s(base + Stage::kLowpBytes, slot.master + slot.e0, Stage::kF32Bytes, &s_full[s]);
             bulk_g2s(base + Stage::kLowpBytes + Stage::kF32Bytes, slot.exp_avg + slot.e0, Stage::kF32Bytes, &s_full[s]);
             bulk_g2s(base + Stage::kLowpBytes + 2 * Stage::kF32Bytes, slot.exp_avg_sq + slot.e0, Stage::kF32Bytes,
                      &s_full[s]);
         } else if (slot.kind == kTileRefresh) {
-            unsigned char* base = s_dyn + static_cast<size_t>(s) * Stage::kBytes;
+            unsigned char* base = s_dyn + static_cast<size_t>(s) * kStageBytes;
             mbar_arrive_expect_tx(&s_full[s], Stage::kF32Bytes);
             bulk_g2s(base + Stage::kLowpBytes, slot.master + slot.e0, Stage::kF32Bytes, &s_full[s]);
         } else {
@@ -551,7 +571,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         __syncthreads();
         if (s_abort) break;
         const TileSlot slot = s_slot[s];   // into registers: measured 1.3 % faster than reading the fields from shared memory
-        unsigned char* base = s_dyn + static_cast<size_t>(s) * Stage::kBytes;
+        unsigned char* base = s_dyn + static_cast<size_t>(s) * kStageBytes;
         if constexpr (MM) fetch(k + 1, g_next);   // slot k + 1 was published before the barrier above
 
         if (slot.kind == kTileBulk) {
@@ -571,14 +591,33 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                     const float4 gg = *reinterpret_cast<const float4*>(base + static_cast<size_t>(e) * 4);
                     g[0] = gg.x; g[1] = gg.y; g[2] = gg.z; g[3] = gg.w;
                 } else {
-                    uint2 gg;
-                    if constexpr (MM) gg = g_now[h];
-                    else gg = *reinterpret_cast<const uint2*>(base + static_cast<size_t>(e) * 2);
-                    const float2 a0 = Lp<DT>::unpack2(gg.x), a1 = Lp<DT>::unpack2(gg.y);
-                    g[0] = a0.x; g[1] = a0.y; g[2] = a1.x; g[3] = a1.y;
-                    if constexpr (MM) {
+                    if constexpr (PW > 1) {
+                        // rank average as the pull kernel forms it: fp32, rank order, rounded once to the chunk dtype
+                        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) g[j] *= inv_w;   // the switch summed; the step wants the average
+                        for (int j = 0; j < PW; ++j) {
+                            const int i = (j - a.grads.rank + PW) % PW;   // which slot holds rank j's slice
+                            const unsigned char* slice = i == 0 ? base : base + Stage::kBytes + (i - 1) * Stage::kLowpBytes;
+                            const uint2 w = *reinterpret_cast<const uint2*>(slice + static_cast<size_t>(e) * 2);
+                            const float2 a0 = Lp<DT>::unpack2(w.x), a1 = Lp<DT>::unpack2(w.y);
+                            acc[0] = fmaf(a0.x, inv_w, acc[0]);
+                            acc[1] = fmaf(a0.y, inv_w, acc[1]);
+                            acc[2] = fmaf(a1.x, inv_w, acc[2]);
+                            acc[3] = fmaf(a1.y, inv_w, acc[3]);
+                        }
+                        const float2 r0 = Lp<DT>::unpack2(Lp<DT>::pack2(acc[0], acc[1]));
+                        const float2 r1 = Lp<DT>::unpack2(Lp<DT>::pack2(acc[2], acc[3]));
+                        g[0] = r0.x; g[1] = r0.y; g[2] = r1.x; g[3] = r1.y;
+                    } else {
+                        uint2 gg;
+                        if constexpr (MM) gg = g_now[h];
+                        else gg = *reinterpret_cast<const uint2*>(base + static_cast<size_t>(e) * 2);
+                        const float2 a0 = Lp<DT>::unpack2(gg.x), a1 = Lp<DT>::unpack2(gg.y);
+                        g[0] = a0.x; g[1] = a0.y; g[2] = a1.x; g[3] = a1.y;
+                        if constexpr (MM) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) g[j] *= inv_w;   // the switch summed; the step wants the average
+                        }
                     }
                 }
                 float pp[4] = {p.x, p.y, p.z, p.w}, mm[4] = {m.x, m.y, m.z, m.w}, vv[4] = {v.x, v.y, v.z, v.w};
@@ -633,6 +672,13 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                             acc += Lp<DT>::to_float(
                                 static_cast<const typename Lp<DT>::T*>(a.grads.base[j])[slot.push_elem + (e - slot.e0)]);
                         g = Lp<DT>::to_float(Lp<DT>::from_float(acc)) * inv_w;
+                    } else if constexpr (PW > 1) {
+                        float acc = 0.0f;
+                        for (int j = 0; j < PW; ++j)
+                            acc = fmaf(Lp<DT>::to_float(static_cast<const typename Lp<DT>::T*>(
+                                           a.grads.base[j])[slot.push_elem + (e - slot.e0)]),
+                                       inv_w, acc);
+                        g = Lp<DT>::to_float(Lp<DT>::from_float(acc));
                     } else {
                         g = Lp<DT>::to_float(gin[e]);
                     }
@@ -756,9 +802,9 @@ int launch_adam_minb(const AdamArgs& a, cudaStream_t s) {
     return launch_adam_inst<DT, EPT, MATH, 2>(a, s);
 }
 
-template <int DT, int MATH, bool MM = false>
+template <int DT, int MATH, bool MM = false, int PW = 0>
 int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
-    constexpr int smem = kTmaStages * TmaStage<DT>::kBytes;
+    constexpr int smem = kTmaStages * (TmaStage<DT>::kBytes + (PW > 1 ? (PW - 1) * TmaStage<DT>::kLowpBytes : 0));
     // the opt-in to more than 48 KB of dynamic shared memory is per device: once for each ordinal
     static bool opted_in[64];
     int dev = -1;
@@ -768,7 +814,7 @@ int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
     }
     if (!opted_in[dev]) {
         const cudaError_t attr =
-            cudaFuncSetAttribute(adam_tma_kernel<DT, MATH, MM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            cudaFuncSetAttribute(adam_tma_kernel<DT, MATH, MM, PW>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (attr != cudaSuccess) {
             const int rc = record_cuda(attr);
             (void)cudaGetLastError();
@@ -780,7 +826,7 @@ int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
     if (grid < 0) return grid;
     // fewer CTAs than SMs leave the other SMs to a kernel on another stream (the pull of the next chunk)
     if (g_tune.adam_tma_ctas > 0 && g_tune.adam_tma_ctas < grid) grid = g_tune.adam_tma_ctas;
-    adam_tma_kernel<DT, MATH, MM><<<grid, kTmaThreads, smem, s>>>(a);
+    adam_tma_kernel<DT, MATH, MM, PW><<<grid, kTmaThreads, smem, s>>>(a);
     return record_cuda(cudaGetLastError());
 }
 
@@ -790,6 +836,12 @@ int launch_adam_dt(const AdamArgs& a, cudaStream_t s) {
     if (a.mc_grads) {
         if constexpr (DT == ELX_F32) return ELX_ERR_DTYPE;   // the switch-side sum is used for 16-bit chunks
         else return precise ? launch_adam_tma<DT, 1, true>(a, s) : launch_adam_tma<DT, 2, true>(a, s);
+    }
+    if (a.pull) {
+        // gradients pulled from the ranks' slabs inside the update kernel: what shared memory has room for
+        if constexpr (DT == ELX_F32) return ELX_ERR_DTYPE;
+        else if (a.push.world == 2) return precise ? launch_adam_tma<DT, 1, false, 2>(a, s) : launch_adam_tma<DT, 2, false, 2>(a, s);
+        else return ELX_ERR_CAPACITY;
     }
     if ((g_tune.adam_variant == 1 && !a.force_direct) || a.push.world > 0 || a.shadow)
         return precise ? launch_adam_tma<DT, 1>(a, s) : launch_adam_tma<DT, 2>(a, s);
@@ -954,6 +1006,41 @@ int elx_adam_multi_push(const ElxChunkDesc* descs, int first, int count, int64_t
     a.n_tiles = n_tiles;
     a.push = gather;
     a.push_off = block_off;
+    return launch_adam(a, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int elx_adam_multi_pull_push(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                             const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl, ElxPeerTable grads,
+                             ElxPeerTable gather, const int64_t* block_off, void* stream) {
+    if (!descs || !ctl || !block_off) return ELX_ERR_NULL;
+    if (n_groups > 0 && (!segs || !hyper)) return ELX_ERR_NULL;
+    if (dtype != ELX_F16 && dtype != ELX_BF16) return ELX_ERR_DTYPE;
+    if (first < 0 || count < 0 || n_tiles < 0 || n_groups < 0) return ELX_ERR_SIZE;
+    if (n_groups > kMaxGroups) return ELX_ERR_CAPACITY;
+    int rc = peer_table_ok(gather);
+    if (rc != ELX_OK) return rc;
+    rc = peer_table_ok(grads);
+    if (rc != ELX_OK) return rc;
+    if (grads.world != gather.world || grads.rank != gather.rank) return ELX_ERR_ARG;
+    if (gather.world != 2) return ELX_ERR_CAPACITY;
+    if (!aligned(descs, 8) || !aligned(ctl, 16) || !aligned(block_off, 8) || (segs && !aligned(segs, 8)) ||
+        (hyper && !aligned(hyper, 4)))
+        return ELX_ERR_ALIGN;
+    if (count == 0 || n_tiles == 0) return ELX_OK;
+    AdamArgs a;
+    memset(&a, 0, sizeof(a));
+    a.descs = descs;
+    a.segs = segs;
+    a.hyper = hyper;
+    a.ctl = ctl;
+    a.first = first;
+    a.count = count;
+    a.n_groups = n_groups;
+    a.n_tiles = n_tiles;
+    a.push = gather;
+    a.push_off = block_off;
+    a.grads = grads;
+    a.pull = 1;
     return launch_adam(a, dtype, static_cast<cudaStream_t>(stream));
 }
 

@@ -432,6 +432,28 @@ class ChunkStepEngine:
             main.wait_stream(d2h)
         self.peer_barrier(self.ctl)
 
+    def step_sharded_pull_push(self):
+        """The peer-mapped sharded step with BOTH collectives inside the update kernel (two ranks): per tile the
+        kernel fetches the slice of every rank's gradient block with bulk loads, averages it as the pull kernel
+        does, updates in place and bulk-stores the refreshed tile to every rank's gather block, so the link-bound
+        fetch of the next tiles runs under the HBM-bound update of the current one and the reduced gradient never
+        touches memory.  The decision is taken first, from a probe of every rank's OWN gradient slab (see
+        ``step_sharded_probe_first`` for why that is the same decision):
+
+            barrier, probe of the own slab, barrier + agree, elx_step_begin
+            elx_adam_multi_pull_push     one launch over all chunks
+            barrier
+
+        Same results as ``step_sharded_p2p``, bit for bit (tested); the per-chunk overflow words are not filled in."""
+        if getattr(self, '_p2p_pool', 0) or self.clipping:
+            raise RuntimeError('step_sharded_pull_push needs a block per chunk and no gradient clipping')
+        self.peer_barrier(self.ctl)
+        kernels.grad_check(self.grad_slab.local, ctl=self.ctl)
+        self.peer_barrier(self.ctl, exchange_overflow=True)
+        kernels.step_begin(self.ctl, self.scaler.cfg, None, self.chunk_flags)
+        kernels.adam_multi_pull_push(self.table, self.ctl, self.grad_slab.table, self.gather_slab.table, self.block_off)
+        self.peer_barrier(self.ctl)
+
     def step_sharded_probe_first(self, pull_ctas: int = 36):
         """The peer-mapped sharded step with the decision taken BEFORE the reduction, so that the in-place update of
         chunk k can run while chunk k + 1 is still being reduced on a second stream (the SMs split between the two

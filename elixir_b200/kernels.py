@@ -612,6 +612,24 @@ def adam_multi_push(table: ChunkTable, ctl: ControlBlock, gather_table, block_of
             'elx_adam_multi_push')
 
 
+def adam_multi_pull_push(table: ChunkTable, ctl: ControlBlock, grads_table, gather_table, block_off: torch.Tensor,
+                         first: int = 0, count: Optional[int] = None):
+    """Reduce-scatter, in-place update and all-gather in one launch over peer-mapped slabs
+    (``elx_adam_multi_pull_push``); the decision must already exist."""
+    count = table.n_chunks - first if count is None else count
+    if table.host_resident:
+        raise RuntimeError('the update fused with both collectives runs on device-resident shards only')
+    _check_tensor(block_off, 'block_off', torch.int64)
+    if block_off.numel() < table.n_chunks:
+        raise ValueError('block_off is shorter than the table')
+    with _DeviceGuard(table.descs_dev):
+        _lib.check(
+            _lib.get().elx_adam_multi_pull_push(_ptr(table.descs_dev), first, count, table.tiles(first, count), table.code,
+                                                _ptr(table.segs_dev), _ptr(table.hyper_dev), table.n_groups, ctl.ptr,
+                                                grads_table, gather_table, _ptr(block_off), _stream(table.descs_dev)),
+            'elx_adam_multi_pull_push')
+
+
 def copy_async(dst_ptr: int, src_ptr: int, nbytes: int, stream: torch.cuda.Stream):
     """One copy-engine transfer between raw device addresses (local or peer-mapped) on ``stream``."""
     _lib.check(_lib.get().elx_copy_async(ctypes.c_void_p(dst_ptr), ctypes.c_void_p(src_ptr), nbytes,

@@ -467,6 +467,23 @@ int elx_adam_multi_push(const ElxChunkDesc* descs, int first, int count, int64_t
                         ElxPeerTable gather, const int64_t* block_off, void* stream);
 
 /*
+ * elx_adam_multi_push with the reduce-scatter inside as well: the gradient of a tile is not read from the shard
+ * but fetched from every rank's gradient slab (grads.base[j] + block_off[c] + rank * n_shard, the slice
+ * elx_pull_reduce_multi would read) with plain bulk loads into shared memory and averaged there exactly as
+ * elx_pull_reduce_multi averages (fp32, rank order, one rounding to the chunk dtype), so that the links are busy
+ * while the previous tile is being updated and the reduced gradient never touches memory: Chunk.reduce, the update
+ * and __update_replica (chunk.py:282-315, 475-482; optimizer.py:115-135, 216) in one launch, in place.
+ * An update in place needs the decision first: call it after elx_step_begin, with ctl->found_inf formed from the
+ * INPUTS (elx_grad_check over this rank's own gradient slab, then elx_peer_barrier with exchange_overflow) --
+ * the fp32-accumulated average is non-finite exactly when one of its inputs is.
+ * 16-bit chunks; groups of two ranks (ELX_ERR_CAPACITY otherwise: the peers' slices of three tiles in flight have
+ * to fit in shared memory beside the update's own stages).
+ */
+int elx_adam_multi_pull_push(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                             const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl,
+                             ElxPeerTable grads, ElxPeerTable gather, const int64_t* block_off, void* stream);
+
+/*
  * Single-shard convenience form with the hyper-parameters by value and one implicit segment
  * [0, n_valid).  Same arithmetic as elx_adam_multi.  Pointers need only be aligned to their
  * element size; the vector path is used when all of them are 32-byte aligned.

@@ -379,6 +379,13 @@ int elx_adam_multi_push(const ElxChunkDesc* descs, int first, int count, int64_t
     (void)ctl; (void)gather; (void)block_off; (void)stream;
     return ELX_ERR_NODEVICE;
 }
+int elx_adam_multi_pull_push(const ElxChunkDesc* descs, int first, int count, int64_t n_tiles, int dtype,
+                             const ElxSeg* segs, const ElxHyper* hyper, int n_groups, ElxCtl* ctl, ElxPeerTable grads,
+                             ElxPeerTable gather, const int64_t* block_off, void* stream) {
+    (void)descs; (void)first; (void)count; (void)n_tiles; (void)dtype; (void)segs; (void)hyper; (void)n_groups;
+    (void)ctl; (void)grads; (void)gather; (void)block_off; (void)stream;
+    return ELX_ERR_NODEVICE;
+}
 int elx_ipc_open(const void* handle, void** base) {
     (void)handle; (void)base;
     return ELX_ERR_NODEVICE;

@@ -104,7 +104,7 @@ def _worker(rank, world, port):
 
 
 def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False, pull_variant=1, overlapped=False,
-                probe_first=False, host_buffers=False):
+                probe_first=False, host_buffers=False, pull_push=False):
     """The NVLink path: pull reduce-scatter + probe, overflow agreement inside the barrier, fused update with
     push all-gather — no NCCL collective in the step."""
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
@@ -204,6 +204,8 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False
             engine.step_sharded_overlapped(pull_ctas=40)
         elif probe_first:
             engine.step_sharded_probe_first(pull_ctas=40)
+        elif pull_push:
+            engine.step_sharded_pull_push()
         else:
             engine.step_sharded_p2p()
         torch.cuda.synchronize()
@@ -408,6 +410,17 @@ def test_sharded_step_p2p_fed_from_host_buffers(pool):
     if torch.cuda.device_count() < 2:
         pytest.skip('needs 2 GPUs')
     mp.spawn(_p2p_worker, args=(2, 29940 + (pool or 0), 'float16', pool, False, 1, False, False, True), nprocs=2)
+
+
+@pytest.mark.parametrize('dtype_name', ['float16', 'bfloat16'])
+def test_sharded_step_with_both_collectives_inside_the_update_kernel(dtype_name):
+    """Two ranks: per tile the update kernel fetches both ranks' gradient slices, averages them as the pull kernel
+    does, updates in place and stores the refreshed tile to both gather blocks; the decision comes from a probe of
+    the inputs.  Same oracle, same bits as the two-phase step."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    mp.spawn(_p2p_worker, args=(2, 29950 + (1 if dtype_name == 'bfloat16' else 0), dtype_name, None, False, 1, False, False,
+                                False, True), nprocs=2)
 
 
 def test_sharded_step_p2p_pooled_blocks():
