@@ -327,21 +327,23 @@ def run_ours(args):
         what = ('small ragged chunk set, 5 steps (1 skipped by an inf in one rank\'s shard), fp16 and bf16, against the CPU '
                 'oracle on every rank')
         note = None
-        if args.collective_was_auto and args.collective == 'mm':
-            # the switch-side path needs multicast support of GPUs, driver and torch: where its self-check does not
-            # come out clean the benchmark falls back to the peer-mapped kernels instead of giving up
+        preferred = args.collective_was_auto and args.collective != 'p2p'
+        if preferred:
+            # the variant --collective auto prefers at this size has requirements of its own (the switch-side path:
+            # multicast support of GPUs, driver and torch): where its self-check does not come out clean the
+            # benchmark falls back to the two peer-mapped kernels instead of giving up
             try:
-                ok, cases, failure = sharded_parity_check('mm', world, rank, device, group, args.seed)
+                ok, cases, failure = sharded_parity_check(args.collective, world, rank, device, group, args.seed)
             except Exception as exc:    # noqa: BLE001
                 ok, cases, failure = False, 0, f'{type(exc).__name__}: {exc}'
             agreed = torch.tensor([1 if ok else 0], device=device)
             dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
             if not agreed.item():
-                note = f'--collective auto: the switch-side path did not pass its self-check here ({failure}); using p2p'
+                note = f'--collective auto: {args.collective} did not pass its self-check here ({failure}); using p2p'
                 if rank == 0:
                     print('bench: ' + note, file=sys.stderr)
                 args.collective = 'p2p'
-        if note is not None or not (args.collective_was_auto and args.collective == 'mm'):
+        if note is not None or not preferred:
             ok, cases, failure = sharded_parity_check(args.collective, world, rank, device, group, args.seed)
         parity = {'ok': ok, 'world': world, 'cases': cases, 'collective': args.collective, 'what': what}
         if note:
