@@ -1121,7 +1121,8 @@ def main():
     args = ap.parse_args()
     args.collective_was_auto = args.collective == 'auto'
     if args.collective_was_auto:
-        args.collective = 'mm' if args.gpus >= 8 and args.workload == 'auto' and not args.pool else 'p2p'
+        plain = args.workload == 'auto' and not args.pool    # a block per chunk, fp16, no pooled slabs
+        args.collective = 'mm' if plain and args.gpus >= 8 else 'p2p-fused' if plain and args.gpus == 2 else 'p2p'
     if args.workload == 'residency':
         run_residency(args)
     elif args.impl == 'reference':
