@@ -195,7 +195,10 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
         used = [chunk_sizes[0], chunk_sizes[1], chunk_sizes[2] // 2 + 7, 9]
         engine = ChunkStepEngine(device, dtype, DynamicGradScaler(initial_scale=scale, hysteresis=1, growth_interval=3),
                                  process_group=group)
-        host, host_ctl, host_state = orc.ChunkSet(dtype), orc.new_ctl(scale), []
+        # switch-side sum: the oracle steps on the averaged gradients as fp32 values (float(sum) / W, what the kernel feeds
+        # to Adam); otherwise on the reduced low-precision shard
+        host_dtype = torch.float32 if collective == 'mm' else dtype
+        host, host_ctl, host_state = orc.ChunkSet(host_dtype), orc.new_ctl(scale), []
         hypers = [K.hyper(weight_decay=0.01)]
         for c, (C, u) in enumerate(zip(chunk_sizes, used)):
             S = C // world
@@ -204,7 +207,7 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
             full[u:] = 0
             mine = full[rank * S:(rank + 1) * S].clone()
             nv = max(0, min(S, u - rank * S))
-            lowp = torch.zeros(S, dtype=dtype)
+            lowp = torch.zeros(S, dtype=host_dtype)
             host.add_chunk(mine, torch.zeros(S), torch.zeros(S), lowp, nv, [(0, nv, 0)] if nv else [])
             host_state.append((mine, lowp))
             engine.add_shard(mine.to(device), torch.zeros(S, dtype=dtype, device=device), nv, [(0, nv, 0)] if nv else [])
@@ -227,13 +230,7 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
                 rank_grads = []
                 for r in range(world):
                     gen = torch.Generator().manual_seed(seed + 1000 * step + 10 * c + r)
-                    if collective == 'mm':
-                        # the switch adds in an order of its own: multiples of a power of two, small enough for
-                        # every partial sum to be exact, make the expected average independent of that order
-                        quantum, limit = (2.0**-6, 31.0) if dtype == torch.float16 else (2.0**-3, 15.0)
-                        g = (torch.round((torch.randn(C, generator=gen) * 4).clamp(-limit, limit) / quantum) * quantum).to(dtype)
-                    else:
-                        g = (torch.randn(C, generator=gen) * 1e-3 * host_ctl.scale).to(dtype)
+                    g = (torch.randn(C, generator=gen) * 1e-3 * host_ctl.scale).to(dtype)
                     if step == 2 and c == 1 and r == world - 1:
                         g[5] = float('inf')    # lands in rank 0's shard only
                     rank_grads.append(g)
@@ -243,10 +240,27 @@ def sharded_parity_check(collective, world, rank, device, group, seed):
                 else:
                     blocks.append(rank_grads[rank].to(device))
             reduced = []
+            if collective == 'mm':
+                # the switch's sum has an arithmetic of its own, as NCCL's order is its own: parity of the step is defined
+                # GIVEN the reduced gradients, captured here with the same switch operation before the step consumes them
+                torch.cuda.synchronize()
+                dist.barrier(group=group)
+                sums = [t.cpu() for t in engine.switch_reduced_gradients()]
+                torch.cuda.synchronize()
+                dist.barrier(group=group)
             for c, C in enumerate(chunk_sizes):
                 S = C // world
                 mine = [g[rank * S:(rank + 1) * S].contiguous() for g in per_rank[c]]
-                if collective in ('p2p', 'p2p-fused', 'p2p-overlap', 'staged', 'mm'):
+                if collective == 'mm':
+                    exact = torch.stack([m.double() for m in mine]).sum(0)
+                    finite = torch.isfinite(exact)
+                    ulp = 2.0**-10 if dtype == torch.float16 else 2.0**-7
+                    bound = world * ulp * torch.stack([m.double().abs() for m in mine]).sum(0)
+                    if not torch.equal(torch.isfinite(sums[c].double()), finite) or \
+                            not bool(((sums[c].double() - exact).abs()[finite] <= bound[finite]).all()):
+                        failure = failure or f'{dtype} step {step} chunk {c}: switch-side sum off the exact sum by more than its roundings'
+                    reduced.append(sums[c].float() * (1.0 / world))
+                elif collective in ('p2p', 'p2p-fused', 'p2p-overlap', 'staged'):
                     reduced.append(orc.reduce_avg_f32acc(mine))    # rank-order fp32 accumulation, one rounding
                 else:
                     out = torch.empty(S, dtype=dtype, device=device)

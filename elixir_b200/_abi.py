@@ -156,6 +156,7 @@ PROTOTYPES = {
     'elx_peek_u32': (_i, [_p, C.POINTER(C.c_uint32)]),
     'elx_peer_barrier': (_i, [ElxPeerTable, C.c_uint32, _p, _i, _i, _p]),
     'elx_pull_reduce_multi': (_i, [_p, _i, _i, _i64, _i, ElxPeerTable, _p, _p, _p, _p, _p]),
+    'elx_multimem_reduce': (_i, [_p, _p, _i, _i64, _p]),
     'elx_copy_async': (_i, [_p, _p, _i64, _p]),
     'elx_adam_multi_push': (_i, [_p, _i, _i, _i64, _i, _p, _p, _i, _p, ElxPeerTable, _p, _p]),
     'elx_adam_multi_pull_push': (_i, [_p, _i, _i, _i64, _i, _p, _p, _i, _p, ElxPeerTable, ElxPeerTable, _p, _p]),

@@ -437,6 +437,16 @@ __device__ __forceinline__ uint2 mm_ld_reduce8(const void* mc) {
     }
     return r;
 }
+template <int DT>
+__device__ __forceinline__ uint32_t mm_ld_reduce4(const void* mc) {
+    uint32_t r;
+    if constexpr (DT == ELX_BF16) {
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.bf16x2 %0, [%1];" : "=r"(r) : "l"(mc) : "memory");
+    } else {
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.f16x2 %0, [%1];" : "=r"(r) : "l"(mc) : "memory");
+    }
+    return r;
+}
 __device__ __forceinline__ void mm_st8(void* mc, uint2 v) {
     asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1,%2};" ::"l"(mc), "r"(v.x), "r"(v.y) : "memory");
 }
@@ -666,12 +676,12 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                 float g = 0.0f;
                 if (e < slot.n_valid) {
                     if constexpr (MM) {
-                        // the same value the switch would return: rank-order fp32 sum, one rounding, then 1/W
-                        float acc = 0.0f;
-                        for (int j = 0; j < a.grads.world; ++j)
-                            acc += Lp<DT>::to_float(
-                                static_cast<const typename Lp<DT>::T*>(a.grads.base[j])[slot.push_elem + (e - slot.e0)]);
-                        g = Lp<DT>::to_float(Lp<DT>::from_float(acc)) * inv_w;
+                        // the switch's own sum here too (its arithmetic is not the rank-order fp32 sum rounded once):
+                        // the aligned pair that holds the element, one of its halves
+                        const int64_t idx = slot.push_elem + (e - slot.e0);
+                        const uint32_t pair = mm_ld_reduce4<DT>(a.mc_grads + (idx & ~static_cast<int64_t>(1)) * 2);
+                        const float2 both = Lp<DT>::unpack2(pair);
+                        g = ((idx & 1) ? both.y : both.x) * inv_w;
                     } else if constexpr (PW > 1) {
                         float acc = 0.0f;
                         for (int j = 0; j < PW; ++j)

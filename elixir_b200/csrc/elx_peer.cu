@@ -371,6 +371,24 @@ int launch_pull(const PullArgs& a, cudaStream_t s) {
     return launch_pull_inst<DT, 0>(a, s);
 }
 
+// dst[i] = sum over the ranks of element i, as the NVLink switch forms it (16-bit elements, 16 bytes per access).
+template <int DT>
+__global__ void __launch_bounds__(512) multimem_reduce_kernel(const char* __restrict__ src_mc, char* __restrict__ dst,
+                                                              int64_t n16) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride) {
+        U4 r;
+        if constexpr (DT == ELX_BF16) {
+            asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(r.x[0]), "=r"(r.x[1]), "=r"(r.x[2]), "=r"(r.x[3]) : "l"(src_mc + i * 16) : "memory");
+        } else {
+            asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(r.x[0]), "=r"(r.x[1]), "=r"(r.x[2]), "=r"(r.x[3]) : "l"(src_mc + i * 16) : "memory");
+        }
+        st128(dst + i * 16, r);
+    }
+}
+
 // Flag region of one rank (peer-mapped): for each parity of the epoch and each sender, {epoch, word}.
 // A rank can run at most one barrier ahead of a peer, so two parities are enough.
 __device__ __forceinline__ uint32_t* flag_slot(void* region, uint32_t epoch, int sender) {
@@ -542,6 +560,23 @@ int elx_peer_barrier(ElxPeerTable flags, uint32_t epoch, ElxCtl* ctl, int exchan
     if (timeout_ms <= 0 || epoch == 0) return ELX_ERR_ARG;
     peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, epoch, ctl, exchange_overflow,
                                                                       static_cast<uint64_t>(timeout_ms) * 1000000ull);
+    return record_cuda(cudaGetLastError());
+}
+
+int elx_multimem_reduce(const void* src_mc, void* dst, int dtype, int64_t n, void* stream) {
+    if (!src_mc || !dst) return ELX_ERR_NULL;
+    if (dtype != ELX_F16 && dtype != ELX_BF16) return ELX_ERR_DTYPE;
+    if (n < 0 || (n & 7) != 0) return ELX_ERR_SIZE;
+    if (!aligned(src_mc, 16) || !aligned(dst, 16)) return ELX_ERR_ALIGN;
+    if (n == 0) return ELX_OK;
+    const int64_t n16 = n / 8;
+    const int grid = grid_for((n16 + 511) / 512, 2);
+    if (grid < 0) return grid;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == ELX_F16)
+        multimem_reduce_kernel<ELX_F16><<<grid, 512, 0, s>>>(static_cast<const char*>(src_mc), static_cast<char*>(dst), n16);
+    else
+        multimem_reduce_kernel<ELX_BF16><<<grid, 512, 0, s>>>(static_cast<const char*>(src_mc), static_cast<char*>(dst), n16);
     return record_cuda(cudaGetLastError());
 }
 

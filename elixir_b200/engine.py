@@ -709,6 +709,20 @@ class ChunkStepEngine:
         self.peer_barrier = PeerBarrier(self.device, self.group, timeout_ms)
         return self
 
+    def switch_reduced_gradients(self) -> List[torch.Tensor]:
+        """What ``step_sharded_single_pass`` will consume, made visible: for every chunk the SUM over the ranks of
+        this rank's slice of the gradient blocks as the NVLink switch forms it (the kernel multiplies it by 1/W).
+        For checks and tests; the step itself never stores these values.  Every rank's blocks must be written and
+        the shard sizes multiples of 8."""
+        out = []
+        itemsize = self.grad_slab.local.element_size()
+        for k, shard in enumerate(self.shards):
+            n = shard[0].numel()
+            dst = torch.empty(n, dtype=self.dtype, device=self.device)
+            kernels.multimem_reduce(dst, self.grad_slab.mc_ptr + (self._p2p_offsets[k] + self.grad_slab.rank * n) * itemsize)
+            out.append(dst)
+        return out
+
     def step_sharded_single_pass(self, host_grads: Optional[Sequence[torch.Tensor]] = None,
                                  host_params: Optional[Sequence[torch.Tensor]] = None):
         """The sharded step with reduce-scatter, update and all-gather in ONE kernel, tile by tile, through the

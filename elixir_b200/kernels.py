@@ -630,6 +630,15 @@ def adam_multi_pull_push(table: ChunkTable, ctl: ControlBlock, grads_table, gath
             'elx_adam_multi_pull_push')
 
 
+def multimem_reduce(dst: torch.Tensor, src_mc: int):
+    """``dst[i]`` = the sum over all ranks of element i behind the multicast address ``src_mc``, as the NVLink
+    switch forms it (``elx_multimem_reduce``)."""
+    _check_tensor(dst, 'dst')
+    with _DeviceGuard(dst):
+        _lib.check(_lib.get().elx_multimem_reduce(ctypes.c_void_p(src_mc), _ptr(dst), dtype_code(dst.dtype), dst.numel(),
+                                                  _stream(dst)), 'elx_multimem_reduce')
+
+
 def copy_async(dst_ptr: int, src_ptr: int, nbytes: int, stream: torch.cuda.Stream):
     """One copy-engine transfer between raw device addresses (local or peer-mapped) on ``stream``."""
     _lib.check(_lib.get().elx_copy_async(ctypes.c_void_p(dst_ptr), ctypes.c_void_p(src_ptr), nbytes,

@@ -450,6 +450,16 @@ int elx_pull_reduce_multi(const ElxChunkDesc* descs, int first, int count, int64
                           ElxPeerTable grads, const int64_t* block_off, const int64_t* stage_off,
                           uint32_t* chunk_flags, ElxCtl* ctl, void* stream);
 
+/*
+ * dst[i] = the sum over all ranks of element i of the buffers behind the multicast address src_mc, formed by the
+ * NVLink switch (multimem.ld_reduce with fp32 accumulation, returned in `dtype`, ELX_F16 or ELX_BF16): the
+ * reduce-scatter of Chunk.reduce (chunk.py:299-303) without the division, for a caller that wants the reduced slice in
+ * memory -- the single-pass kernel consumes the same values without storing them, and the parity tests use this entry
+ * point to see them.  For more than two ranks the switch's result is not the rank-order fp32 sum rounded once: it can
+ * differ from it in the last bit of the 16-bit format.  n a multiple of 8; src_mc and dst 16-byte aligned.
+ */
+int elx_multimem_reduce(const void* src_mc, void* dst, int dtype, int64_t n, void* stream);
+
 /* One asynchronous device-to-device copy on `stream` (cudaMemcpyAsync, any mix of local and peer-mapped
  * addresses): the copy engines move whole slices over NVLink at a higher rate than SM-issued accesses.
  * Used by the staged form of the sharded step: the other ranks' slices are first copied into local

@@ -386,6 +386,10 @@ int elx_adam_multi_pull_push(const ElxChunkDesc* descs, int first, int count, in
     (void)ctl; (void)grads; (void)gather; (void)block_off; (void)stream;
     return ELX_ERR_NODEVICE;
 }
+int elx_multimem_reduce(const void* src_mc, void* dst, int dtype, int64_t n, void* stream) {
+    (void)src_mc; (void)dst; (void)dtype; (void)n; (void)stream;
+    return ELX_ERR_NODEVICE;
+}
 int elx_ipc_open(const void* handle, void** base) {
     (void)handle; (void)base;
     return ELX_ERR_NODEVICE;

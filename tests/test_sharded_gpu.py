@@ -239,10 +239,11 @@ def _p2p_worker(rank, world, port, dtype_name='float16', pool=None, staged=False
 
 def _mm_worker(rank, world, port, dtype_name='float16', host_buffers=False):
     """The single-pass sharded step: reduce-scatter, update and all-gather in one kernel through the NVLink switch
-    (multimem.ld_reduce / multimem.st on symmetric memory).  The switch adds the ranks' values in an order of its
-    own, so the gradients here are multiples of a power of two small enough for every partial sum to be exact:
-    the expected average is then the same number whatever the order, and the comparison with the oracle is as
-    strict as for the other paths."""
+    (multimem.ld_reduce / multimem.st on symmetric memory).  The switch forms the sum of the ranks' values with an
+    arithmetic of its own (for more than two ranks not the rank-order fp32 sum rounded once), exactly as NCCL's
+    order is its own, so parity of the step is defined GIVEN the reduced gradients: they are captured first with
+    ``elx_multimem_reduce`` (the same switch operation, stored instead of consumed), checked against the exact
+    average to the rounding of the 16-bit format, and the oracle then steps on them."""
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR='127.0.0.1',
                       MASTER_PORT=str(port))
     sys.path.insert(0, ROOT)
@@ -257,12 +258,12 @@ def _mm_worker(rank, world, port, dtype_name='float16', host_buffers=False):
     dev = torch.device('cuda', rank)
     dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
     dtype, scale = getattr(torch, dtype_name), 256.0
-    quantum, limit = (2.0**-6, 31.0) if dtype == torch.float16 else (2.0**-3, 15.0)
+    ulp = 2.0**-10 if dtype == torch.float16 else 2.0**-7
     chunk_sizes = [world * 4096 * 40, world * (4096 + 16), world * 4096 * 5, world * 24]
     used = [chunk_sizes[0], chunk_sizes[1], chunk_sizes[2] // 2 + 7, 9]
     engine = ChunkStepEngine(dev, dtype, DynamicGradScaler(initial_scale=scale, hysteresis=1, growth_interval=3),
                              process_group=dist.group.WORLD)
-    host = orc.ChunkSet(dtype)
+    host = orc.ChunkSet(torch.float32)    # the oracle steps on the averaged gradients as fp32 values: float(sum) / W
     host_ctl = orc.new_ctl(scale)
     hypers = [K.hyper(weight_decay=0.01)]
     host_state = []
@@ -273,9 +274,9 @@ def _mm_worker(rank, world, port, dtype_name='float16', host_buffers=False):
         full[u:] = 0
         mine = full[rank * S:(rank + 1) * S].clone()
         nv = max(0, min(S, u - rank * S))
-        lowp = torch.zeros(S, dtype=dtype)
-        host.add_chunk(mine, torch.zeros(S), torch.zeros(S), lowp, nv, [(0, nv, 0)] if nv else [])
-        host_state.append((mine, lowp, nv))
+        grad32 = torch.zeros(S)
+        host.add_chunk(mine, torch.zeros(S), torch.zeros(S), grad32, nv, [(0, nv, 0)] if nv else [])
+        host_state.append((mine, grad32, nv))
         engine.add_shard(mine.to(dev), torch.zeros(S, dtype=dtype, device=dev), nv, [(0, nv, 0)] if nv else [])
     engine.finalize()
     engine.set_hyper(hypers)
@@ -283,27 +284,42 @@ def _mm_worker(rank, world, port, dtype_name='float16', host_buffers=False):
     engine.enable_multicast(chunk_sizes, timeout_ms=5000)
     host_in = [torch.empty(C, dtype=dtype).pin_memory() for C in chunk_sizes] if host_buffers else None
     host_out = [torch.empty(C // world, dtype=dtype).pin_memory() for C in chunk_sizes] if host_buffers else None
+
     def one_step(step):
         per_rank = []
         for c, C in enumerate(chunk_sizes):
             rank_grads = []
             for r in range(world):
                 gen = torch.Generator().manual_seed(1000 * step + 10 * c + r)
-                g = torch.round((torch.randn(C, generator=gen) * 4).clamp(-limit, limit) / quantum) * quantum
-                g = g.to(dtype)
+                g = (torch.randn(C, generator=gen) * 1e-3 * host_ctl.scale).to(dtype)
                 if step == 2 and c == 1 and r == world - 1:
                     g[5] = float('inf')    # lands in rank 0's shard only
                 rank_grads.append(g)
             per_rank.append(rank_grads)
-            (host_in[c] if host_buffers else engine.grad_block(c)).copy_(rank_grads[rank])
+            engine.grad_block(c).copy_(rank_grads[rank])
+            if host_buffers:
+                host_in[c].copy_(rank_grads[rank])
+        # every rank's blocks are in place; what the switch makes of them, seen before the step consumes it
+        torch.cuda.synchronize()
+        dist.barrier()
+        sums = [t.cpu() for t in engine.switch_reduced_gradients()]
+        torch.cuda.synchronize()
+        dist.barrier()
+        for c, C in enumerate(chunk_sizes):
+            S = C // world
+            exact = torch.stack([g[rank * S:(rank + 1) * S].double() for g in per_rank[c]]).sum(0)
+            got = sums[c].double()
+            finite = torch.isfinite(exact)
+            assert torch.equal(torch.isfinite(got), finite), (step, rank, c)
+            # a few roundings to the 16-bit format on the way, each at most one unit in the last place of a partial sum
+            bound = world * ulp * torch.stack([g[rank * S:(rank + 1) * S].double().abs() for g in per_rank[c]]).sum(0)
+            assert bool(((got - exact).abs()[finite] <= bound[finite]).all()), (step, rank, c)
+            host_state[c][1].copy_(sums[c].float() * (1.0 / world))    # exact in fp32: what the kernel feeds to Adam
         if host_buffers:    # blocks filled from pinned memory chunk by chunk, shards copied out behind their update
             engine.step_sharded_single_pass(host_grads=host_in, host_params=host_out)
         else:
             engine.step_sharded_single_pass()
         torch.cuda.synchronize()
-        for c, C in enumerate(chunk_sizes):
-            S = C // world
-            host_state[c][1].copy_(orc.reduce_avg_f32acc([g[rank * S:(rank + 1) * S].contiguous() for g in per_rank[c]]))
         any_inf = step == 2
         if any_inf:
             host_ctl.found_inf = 1    # agreement: every rank skips
@@ -333,7 +349,7 @@ def _mm_worker(rank, world, port, dtype_name='float16', host_buffers=False):
     failure = None
     for step in range(5):
         try:
-            one_step(step)    # no host-side collective inside: a rank that raises cannot strand the others in one
+            one_step(step)    # its two host-side barriers come before anything that can raise
         except Exception as exc:    # noqa: BLE001
             failure = f'{type(exc).__name__}: {exc}'
         if agree(failure):
