@@ -1097,7 +1097,7 @@ def main():
                     '(multimem); p2p-fused = both collectives inside the in-place update kernel over peer-mapped memory, the '
                     'decision taken on the inputs first (two ranks); p2p-overlap = the p2p kernels with the decision taken on the inputs first, so that the update '
                     'of a chunk runs while the next one is reduced; staged = copy engines; nccl = NCCL on side streams; '
-                    'auto = mm from 8 ranks on, p2p-fused at 2 ranks, else p2p')
+                    'auto = mm from 4 ranks on (where its two state sets fit), p2p-fused at 2 ranks, else p2p')
     ap.add_argument('--workload', default='auto', choices=['auto', 'opt66b_bf16', 'residency'],
                     help='N > 1: auto = OPT-13B-shaped fp16 chunk set; opt66b_bf16 = OPT-66B-shaped bf16 chunk set (8 GPUs); '
                     'residency = one training iteration of an MLP stack through the wrapper under three residency modes')
@@ -1136,7 +1136,7 @@ def main():
     args.collective_was_auto = args.collective == 'auto'
     if args.collective_was_auto:
         plain = args.workload == 'auto' and not args.pool    # a block per chunk, fp16, no pooled slabs
-        args.collective = 'mm' if plain and args.gpus >= 8 else 'p2p-fused' if plain and args.gpus == 2 else 'p2p'
+        args.collective = 'mm' if plain and args.gpus >= 4 else 'p2p-fused' if plain and args.gpus == 2 else 'p2p'
     if args.workload == 'residency':
         run_residency(args)
     elif args.impl == 'reference':
