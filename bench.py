@@ -580,7 +580,8 @@ def run_ours(args):
             'grad_dtype': 'bf16' if dtype == torch.bfloat16 else 'fp16',
             'optimizer': f'AdamW lr1e-3 b(0.9,0.999) eps1e-8 wd{wd}',
             'loss_scale': scale,
-            'l2_policy': 'inputs larger than L2 (state per GPU %.1f GB)' % (engine.n_elements() * 14 / 1e9),
+            'l2_policy': 'inputs larger than L2 (state per GPU %.1f GB)' % (
+                engine.n_elements() * (26 if engine._sets is not None else 14) / 1e9),
             'layout': 'flat packing, tensors may straddle chunks',
             'block_pool': args.pool or n_chunks,
             'collectives': 'none (1 GPU)' if world == 1 else
