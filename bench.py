@@ -3,21 +3,30 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 N = 1: the GPT-2-XL-shaped chunk set (1 557 611 200 parameters in 64 MiB fp16 chunks, fp32 master and
-moments, AdamW wd 0.01, gradients ~ N(0, 1e-3) * 2^16).  One step = ONE inf/nan probe launch over the
-gradient blocks of all chunks (read where the backward pass left them), the device-side decision /
-loss-scaler update, then ONE fused unscale + AdamW + fp16 copy-back launch over all chunks that reads the
-gradients from the same blocks and writes the working copies into the shards.  ``--landing copy`` times the
-older form instead, in which every block is first copied into its shard (fused with the probe).
-N > 1 (under torchrun): the OPT-13B-shaped chunk set sharded over the ranks; one step = reduce-scatter (rank
-average) fused with the probe, the decision, then the fused update with the all-gather: by default inside
-the kernels over peer-mapped NVLink memory (``--collective p2p``), or copy-engine staged (``staged``) or over
-NCCL on side streams (``nccl``).  ``--workload opt66b_bf16``: the OPT-66B-shaped bf16 set.
+moments, AdamW wd 0.01, gradients ~ N(0, 1e-3) * 2^16).  One step = the single-pass step: the device-side
+decision taken on the assumption of no overflow, ONE launch over all chunks that unscales, detects inf/nan,
+runs AdamW out of place between two sets of master/moment arrays and writes the fp16 working copies (gradients
+read from the blocks where the backward pass left them), then the device-side commit (the sets change roles, or
+the update is dropped and the step becomes a skip).  ``--step probe-update`` times the two-pass form instead (one
+probe launch over all gradient blocks, decision, update in place), ``--landing copy`` the older form in which
+every block is first copied into its shard (fused with the probe).
+N > 1 (under torchrun): the OPT-13B-shaped chunk set sharded over the ranks; one step = rank average of the
+gradient blocks (reduce-scatter), decision, update of the rank's shards, all-gather of the refreshed working
+copies.  ``--collective auto`` (default) runs the fastest measured form for the group size, behind a self-check
+against the CPU oracle: at 2 ranks the in-place update kernel with both collectives inside over peer-mapped NVLink
+memory (``p2p-fused``), from 4 ranks on ONE kernel that reduces, updates and gathers tile by tile through the
+NVLink switch (``mm``); otherwise, and as fall-back, the pull reduce-scatter kernel and the update + push
+all-gather kernel (``p2p``).  Also: ``p2p-overlap``, copy-engine staged (``staged``), NCCL on side streams
+(``nccl``).  ``--workload opt66b_bf16``: the OPT-66B-shaped bf16 set; ``--workload residency``: one training
+iteration through the wrapper under three residency modes.
 
 Prints ONE JSON line (rank 0).  ``value`` is whole-job parameters per second with all inputs resident
-in HBM; ``e2e`` is the same step through ``ChunkStepEngine.step_from_host`` with pinned host buffers on
-both ends (gradients in, updated low-precision parameters out); at N = 1 it is the speculative form of
-that call (updates start while gradients still arrive and are dropped if an overflow turns up), with the
-plain form's time beside it.  ``--shards host`` / ``host-streamed`` (N = 1): the optimizer state kept in
+in HBM; ``e2e`` is the same step through an engine method that takes pinned host buffers on both ends
+(gradients in, updated low-precision parameters out: ``step_from_host`` at N = 1, ``step_sharded_p2p`` /
+``step_sharded_single_pass`` with ``host_grads=`` / ``host_params=`` at N > 1); at N = 1 it is the single-pass
+form (updates start while gradients still arrive and are dropped if an overflow turns up), with the plain
+form's time beside it.  At N > 1 the line carries ``parity_check``: a small sharded case run through the same
+engine method and compared with the CPU oracle on every rank before the warm-up.  ``--shards host`` / ``host-streamed`` (N = 1): the optimizer state kept in
 pinned host memory.  ``--impl reference`` times the
 reference's CPU Adam path (torch.optim.AdamW on the host cores — ColossalAI's CPUAdam is not installable
 offline — next to the C oracle with all threads) on a bounded sample of the same workload.
