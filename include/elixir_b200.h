@@ -179,8 +179,9 @@ const char* elx_last_cuda_error(void);
  *   "pull_variant"       0 = per-lane peer loads, 1 = bulk-copy staging through shared memory (16-bit
  *                        chunks and groups of 2, 4 or 8 ranks; other cases use variant 0)
  *   "adam_tma_ctas"      grid of the bulk-copy update kernel, 0 = one CTA per SM; with "pull_tma_ctas" (the
- *                        same for the bulk-copy pull kernel) it splits the SMs between an update and a pull
- *                        that run at the same time on two streams
+ *                        same for the bulk-copy pull kernel, which then also uses a deeper shared-memory ring,
+ *                        since few CTAs have to keep more data in flight each) it splits the SMs between an
+ *                        update and a pull that run at the same time on two streams
  *   "math_mode"          1 = IEEE division and square root in the update, 2 = reciprocal
  *                        multiplies and approximate division (both within 1e-6 relative) */
 int elx_set_tuning(const char* name, int value);
