@@ -34,6 +34,7 @@ offline — next to the C oracle with all threads) on a bounded sample of the sa
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -52,6 +53,29 @@ CHUNK_1GPU = 32 * 1024 * 1024    # 64 MiB of fp16
 CHUNK_SHARDED = 256 * 1024 * 1024    # 512 MiB of fp16
 BYTES_PER_ELEM = 28    # updated element: g 2 + p/m/v 12 read, p/m/v 12 + p16 2 written
 BYTES_PER_PAD_ELEM = 6    # element past valid_end: master read, working copy written
+
+
+# ncu captures of the update kernel on a small case (larger than L2), summarised as text; the row that gives the DRAM
+# bytes per element is read from there
+TRAFFIC_PROFILES = {'single-pass': 'adam_tma_kernel_single_pass_small_case_ncu.md',
+                    'probe-update': 'adam_tma_kernel_small_case_ncu.md'}
+
+
+def captured_traffic_per_element(step):
+    """(dram read + write bytes per element of the small-case ncu capture, the summary's file name), or (None, None)
+    when the summary or its row is missing."""
+    name = TRAFFIC_PROFILES.get(step)
+    try:
+        with open(os.path.join(ROOT, 'profiles', name)) as f:
+            text = f.read()
+    except (OSError, TypeError):
+        return None, None
+    m = re.search(r'^\|\s*traffic per element\s*\|\s*([\d ,.]+)MB\s*/\s*([\d ,]+)=', text, re.M)
+    if not m:
+        return None, None
+    mbytes = float(m.group(1).replace(' ', '').replace(',', ''))
+    elems = int(m.group(2).replace(' ', '').replace(',', ''))
+    return mbytes * 1e6 / elems, name
 
 
 def load_peaks():
@@ -622,14 +646,24 @@ def run_ours(args):
         # algorithmic bytes of one update launch: 28 per updated element, 6 per element past valid_end
         algo_bytes = BYTES_PER_ELEM * n_valid_total + BYTES_PER_PAD_ELEM * (n_elems - n_valid_total)
         achieved = algo_bytes / (adam_ms * 1e-3) / 1e9
+        # DRAM traffic of one launch: counted by ncu on a small case of the same kernel (the full-size launch is not
+        # captured), scaled by the algorithmic bytes, which is what the traffic is proportional to
+        per_elem, traffic_source = captured_traffic_per_element(args.step)
+        if args.ncu_traffic_bytes:
+            traffic, traffic_source = args.ncu_traffic_bytes, 'command line (--ncu-traffic-bytes)'
+        elif per_elem is not None and args.shards == 'device' and args.landing == 'none':
+            traffic = per_elem / BYTES_PER_ELEM * algo_bytes
+            traffic_source = (f'profiles/{traffic_source}: {per_elem:.2f} B per element on the captured small case, '
+                              'scaled to this launch by its algorithmic bytes')
+        else:
+            traffic, traffic_source = None, None
         result['roofline'] = {
             'bound': 'hbm', 'kernel': 'adam_tma_kernel', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s',
             'frac': achieved / peak, 'peak_kind': peak_kind, 'ms_per_launch': adam_ms,
             'elements_per_launch': n_elems, 'updated_elements_per_launch': n_valid_total,
             'algorithmic_bytes_per_launch': algo_bytes,
             'bytes_per_element': {'updated': BYTES_PER_ELEM, 'past_valid_end': BYTES_PER_PAD_ELEM},
-            # DRAM bytes of one launch as an ncu capture of this command counted them, when given on the command line
-            'traffic': args.ncu_traffic_bytes or None,
+            'traffic': traffic, 'traffic_source': traffic_source,
             'frac_of_8TBs_nominal': achieved / 8000.0,
         }
         result['adam_gparams_per_s'] = n_elems / (adam_ms * 1e-3) / 1e9
