@@ -607,6 +607,7 @@ def run_ours(args):
         'data': 'synthetic',
         'config': {
             'workload': workload,
+            **({'tuning': list(args.tune)} if args.tune else {}),
             'params': total,
             'chunk_elems': chunk,
             'n_chunks': n_chunks,
@@ -1176,6 +1177,8 @@ def main():
                     help="'host': optimizer state in pinned host memory, updated in place over PCIe by the kernel; "
                     "'host-streamed': the same state moved by the copy engines through device staging sets (N=1 only)")
     ap.add_argument('--e2e-steps', type=int, default=10)
+    ap.add_argument('--tune', action='append', default=[], metavar='KNOB=VALUE',
+                    help='launch-shape knob of the library (elx_set_tuning), for experiments; results do not depend on them')
     args = ap.parse_args()
     args.collective_was_auto = args.collective == 'auto'
     if args.collective_was_auto:
@@ -1189,6 +1192,9 @@ def main():
         if args.warmup < 3:
             print('bench: warm-up raised to 3', file=sys.stderr)
             args.warmup = 3
+        if args.tune:
+            from elixir_b200 import kernels
+            kernels.set_tuning(**{k: int(v) for k, v in (item.split('=', 1) for item in args.tune)})
         run_ours(args)
 
 

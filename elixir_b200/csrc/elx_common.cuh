@@ -46,12 +46,14 @@ struct Tuning {
     int adam_ctas_per_sm = 0;
     int probe_ctas_per_sm = 0;
     int probe_unroll = 4;
+    int probe_variant = 1;        // single-array probe: 0 = loads, 1 = bulk-copy ring for long arrays, 2 = ring always
     int math_mode = 1;
     int adam_variant = 1;         // 0 = direct global accesses, 1 = bulk-copy (TMA) pipeline
     int pull_ctas_per_sm = 0;
     int pull_variant = 1;         // 0 = per-lane loads, 1 = bulk-copy staging (16-bit chunks, W in {2, 4, 8})
     int adam_tma_ctas = 0;        // grid of the bulk-copy update kernel, 0 = one CTA per SM
     int pull_tma_ctas = 0;        // grid of the bulk-copy pull kernel, 0 = one CTA per SM
+    int adam_tma_stages = 0;      // ring depth of the bulk-copy update kernel: 0 = the deepest that fits, 3 = three
 };
 extern Tuning g_tune;
 

@@ -238,12 +238,14 @@ int elx_set_tuning(const char* name, int value) {
         {"adam_ctas_per_sm", &g_tune.adam_ctas_per_sm, def.adam_ctas_per_sm, 0, 32},
         {"probe_ctas_per_sm", &g_tune.probe_ctas_per_sm, def.probe_ctas_per_sm, 0, 32},
         {"probe_unroll", &g_tune.probe_unroll, def.probe_unroll, 4, 8},
+        {"probe_variant", &g_tune.probe_variant, def.probe_variant, 0, 2},
         {"math_mode", &g_tune.math_mode, def.math_mode, 1, 2},
         {"adam_variant", &g_tune.adam_variant, def.adam_variant, 0, 1},
         {"pull_ctas_per_sm", &g_tune.pull_ctas_per_sm, def.pull_ctas_per_sm, 0, 32},
         {"pull_variant", &g_tune.pull_variant, def.pull_variant, 0, 1},
         {"adam_tma_ctas", &g_tune.adam_tma_ctas, def.adam_tma_ctas, 0, 1024},
         {"pull_tma_ctas", &g_tune.pull_tma_ctas, def.pull_tma_ctas, 0, 1024},
+        {"adam_tma_stages", &g_tune.adam_tma_stages, def.adam_tma_stages, 0, 3},
     };
     for (const Knob& k : knobs) {
         if (strcmp(name, k.name) != 0) continue;
@@ -254,6 +256,7 @@ int elx_set_tuning(const char* name, int value) {
         if (value < k.lo || value > k.hi) return ELX_ERR_ARG;
         if (k.slot == &g_tune.adam_threads && value != 256 && value != 512) return ELX_ERR_ARG;
         if (k.slot == &g_tune.probe_unroll && value != 4 && value != 8) return ELX_ERR_ARG;
+        if (k.slot == &g_tune.adam_tma_stages && value != 0 && value != 3) return ELX_ERR_ARG;
         *k.slot = value;
         return ELX_OK;
     }

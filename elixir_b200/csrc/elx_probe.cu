@@ -198,6 +198,154 @@ __global__ void __launch_bounds__(256) norm_finalize(const __grid_constant__ Nor
     if (threadIdx.x == 0 && a.total_l2sq) *a.total_l2sq = static_cast<float>(total);
 }
 
+// ------------------------------------------------------------------------------------------------
+// probe of one long contiguous array through a bulk-copy ring
+// ------------------------------------------------------------------------------------------------
+//
+// The load/store probe above keeps 96 KB per SM in flight (3 CTAs x 256 threads x 128 B) and its rate grows
+// with the resident CTAs (1.8 / 3.5 / 4.9 TB/s for 1 / 2 / 3 CTAs per SM): it is bound by bytes in flight, and
+// registers are what limits those.  Here ONE CTA per SM keeps a ring of 6 x 32 KB in shared memory filled by
+// cp.async.bulk (no registers held by data in flight); the CTA tests each stage from shared memory.  Probe only:
+// no copy, no norm.  The array must start on a 16-byte boundary; a last piece shorter than 16 bytes is read
+// with plain loads.
+
+constexpr int kBulkProbeStages = 6;
+constexpr int kBulkProbeStageBytes = 32768;
+constexpr int kBulkProbeSmem = kBulkProbeStages * kBulkProbeStageBytes;
+
+struct BulkProbeArgs {
+    const unsigned char* src;
+    int64_t bytes;      // probed bytes (n_valid elements)
+    uint32_t* flag;     // may be null
+    ElxCtl* ctl;        // may be null
+};
+
+template <int DT>
+__global__ void __launch_bounds__(kProbeThreads, 1) probe_bulk_kernel(const __grid_constant__ BulkProbeArgs a) {
+    using T = typename Lp<DT>::T;
+    constexpr int kVecPerThread = kBulkProbeStageBytes / (kProbeThreads * 16);   // 8
+    extern __shared__ __align__(128) unsigned char s_dyn[];
+    __shared__ __align__(8) uint64_t s_full[kBulkProbeStages];
+    __shared__ int s_abort;
+
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kBulkProbeStages; ++s) mbar_init(&s_full[s], 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int64_t n_units = (a.bytes + kBulkProbeStageBytes - 1) / kBulkProbeStageBytes;
+    const int64_t my_units = blockIdx.x < n_units ? (n_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    auto unit_offset = [&](int64_t k) { return (blockIdx.x + k * gridDim.x) * static_cast<int64_t>(kBulkProbeStageBytes); };
+    auto unit_bytes = [&](int64_t k) {
+        const int64_t rest = a.bytes - unit_offset(k);
+        return static_cast<uint32_t>(rest < kBulkProbeStageBytes ? rest : kBulkProbeStageBytes);
+    };
+    auto produce = [&](int64_t k) {    // thread 0 only
+        const int s = static_cast<int>(k % kBulkProbeStages);
+        const uint32_t len16 = unit_bytes(k) & ~15u;
+        if (len16) {
+            mbar_arrive_expect_tx(&s_full[s], len16);
+            bulk_g2s(s_dyn + static_cast<size_t>(s) * kBulkProbeStageBytes, a.src + unit_offset(k), len16, &s_full[s]);
+        } else {
+            mbar_arrive(&s_full[s]);
+        }
+    };
+
+    if (threadIdx.x == 0) {
+        for (int64_t k = 0; k < my_units && k < kBulkProbeStages; ++k) produce(k);
+    }
+
+    uint32_t bad = 0;
+    int64_t k = 0;
+    for (; k < my_units; ++k) {
+        const int s = static_cast<int>(k % kBulkProbeStages);
+        const uint32_t parity = static_cast<uint32_t>((k / kBulkProbeStages) & 1);
+        if (!mbar_wait_bounded(&s_full[s], parity)) s_abort = 1;
+        __syncthreads();
+        if (s_abort) break;
+        const unsigned char* base = s_dyn + static_cast<size_t>(s) * kBulkProbeStageBytes;
+        const uint32_t len = unit_bytes(k);
+        if (len == kBulkProbeStageBytes) {
+            // consecutive threads read consecutive 16-byte pieces: conflict-free 128-bit shared reads
+#pragma unroll
+            for (int h = 0; h < kVecPerThread; ++h) {
+                const uint4 w = *reinterpret_cast<const uint4*>(base + (h * kProbeThreads + threadIdx.x) * 16);
+                bad |= Lp<DT>::nonfinite_word(w.x) | Lp<DT>::nonfinite_word(w.y) | Lp<DT>::nonfinite_word(w.z) |
+                       Lp<DT>::nonfinite_word(w.w);
+            }
+        } else {
+            const uint32_t len16 = len & ~15u;
+            for (uint32_t off = threadIdx.x * 16; off < len16; off += kProbeThreads * 16) {
+                const uint4 w = *reinterpret_cast<const uint4*>(base + off);
+                bad |= Lp<DT>::nonfinite_word(w.x) | Lp<DT>::nonfinite_word(w.y) | Lp<DT>::nonfinite_word(w.z) |
+                       Lp<DT>::nonfinite_word(w.w);
+            }
+            // the last elements, fewer than 16 bytes of them, straight from global memory
+            const uint32_t tail_elems = (len - len16) / Lp<DT>::kBytes;
+            if (threadIdx.x < tail_elems) {
+                const T x = reinterpret_cast<const T*>(a.src + unit_offset(k) + len16)[threadIdx.x];
+                if (Lp<DT>::nonfinite(x)) bad = 1;
+            }
+        }
+        __syncthreads();   // the stage has been read by every warp
+        if (threadIdx.x == 0 && k + kBulkProbeStages < my_units) produce(k + kBulkProbeStages);
+    }
+    const unsigned any_bad = __ballot_sync(0xFFFFFFFFu, bad != 0);
+    if (any_bad && lane == 0) {
+        if (a.flag) atomicOr(a.flag, 1u);
+        if (a.ctl) atomicOr(&a.ctl->found_inf, 1u);
+    }
+    if (threadIdx.x == 0 && s_abort) {
+        // gave up on unit k: loads already issued for later units still target this CTA's shared memory
+        for (int64_t j = k; j < my_units && j < k + kBulkProbeStages; ++j)
+            (void)mbar_wait_bounded(&s_full[j % kBulkProbeStages], static_cast<uint32_t>((j / kBulkProbeStages) & 1));
+        if (a.ctl) atomicOr(&a.ctl->status, ELX_STAT_TIMEOUT);
+        if (a.flag) atomicOr(a.flag, 1u);    // an array that was not read to the end does not count as clean
+        if (a.ctl) atomicOr(&a.ctl->found_inf, 1u);
+    }
+}
+
+template <int DT>
+int launch_probe_bulk_inst(const BulkProbeArgs& a, cudaStream_t s) {
+    static bool opted_in[64];
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        (void)cudaGetLastError();
+        return ELX_ERR_NODEVICE;
+    }
+    if (!opted_in[dev]) {
+        const cudaError_t attr =
+            cudaFuncSetAttribute(probe_bulk_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkProbeSmem);
+        if (attr != cudaSuccess) {
+            const int rc = record_cuda(attr);
+            (void)cudaGetLastError();
+            return rc;
+        }
+        opted_in[dev] = true;
+    }
+    const int64_t n_units = (a.bytes + kBulkProbeStageBytes - 1) / kBulkProbeStageBytes;
+    const int grid = grid_for(n_units, 1);
+    if (grid < 0) return grid;
+    probe_bulk_kernel<DT><<<grid, kProbeThreads, kBulkProbeSmem, s>>>(a);
+    return record_cuda(cudaGetLastError());
+}
+
+int launch_probe_bulk(const BulkProbeArgs& a, int dtype, cudaStream_t s) {
+    switch (dtype) {
+        case ELX_F16: return launch_probe_bulk_inst<ELX_F16>(a, s);
+        case ELX_BF16: return launch_probe_bulk_inst<ELX_BF16>(a, s);
+        case ELX_F32: return launch_probe_bulk_inst<ELX_F32>(a, s);
+    }
+    return ELX_ERR_DTYPE;
+}
+
+// Arrays from this size on take the bulk-copy probe (probe_variant 1); below it the ring's ramp-up and drain
+// outweigh what it gains.  probe_variant 2 sends every eligible array there (tests), 0 none.
+constexpr int64_t kBulkProbeMinBytes = int64_t(16) << 20;
+
 template <int DT, bool COPY, bool NORM, int UNROLL>
 int launch_probe_inst(const ProbeArgs& a, cudaStream_t s) {
     static const int resident = resident_ctas(probe_kernel<DT, COPY, NORM, UNROLL>, kProbeThreads);
@@ -253,6 +401,15 @@ int probe_single(const void* src, void* dst, int dtype, int64_t n_shard, int64_t
     if (n_tiles == 0) {
         if (l2sq) return record_cuda(cudaMemsetAsync(l2sq, 0, sizeof(float), s));
         return ELX_OK;
+    }
+    if (!copy && !l2sq && n_valid > 0 && aligned(src, 16) && g_tune.probe_variant != 0 &&
+        (g_tune.probe_variant == 2 || n_valid * dtype_bytes(dtype) >= kBulkProbeMinBytes)) {
+        BulkProbeArgs b;
+        b.src = static_cast<const unsigned char*>(src);
+        b.bytes = n_valid * dtype_bytes(dtype);
+        b.flag = flag;
+        b.ctl = ctl;
+        return launch_probe_bulk(b, dtype, s);
     }
     ProbeArgs a;
     memset(&a, 0, sizeof(a));

@@ -173,6 +173,9 @@ const char* elx_last_cuda_error(void);
  *   "adam_ctas_per_sm"   direct variant: cap on the persistent grid, 0 = every resident CTA
  *   "probe_ctas_per_sm"  the same for the probe kernels
  *   "probe_unroll"       4 or 8 tiles in flight per probe CTA
+ *   "probe_variant"      elx_grad_check without a norm: 0 = per-thread loads, 1 = a bulk-copy ring through
+ *                        shared memory for arrays of 16 MiB and more that start on a 16-byte boundary
+ *                        (default), 2 = the ring for every such array whatever its size
  *   "adam_variant"       0 = direct 256-bit global accesses, 1 = bulk-copy (TMA) pipeline through
  *                        shared memory
  *   "pull_ctas_per_sm"   cap on the grid of the pull reduce-scatter kernel, 0 = every resident CTA
@@ -182,6 +185,8 @@ const char* elx_last_cuda_error(void);
  *                        same for the bulk-copy pull kernel, which then also uses a deeper shared-memory ring,
  *                        since few CTAs have to keep more data in flight each) it splits the SMs between an
  *                        update and a pull that run at the same time on two streams
+ *   "adam_tma_stages"    ring depth of the bulk-copy update kernel: 0 = the deepest that fits in shared memory
+ *                        (four 56 KB stages for 16-bit chunks in IEEE mode, else three), 3 = three
  *   "math_mode"          1 = IEEE division and square root in the update, 2 = reciprocal
  *                        multiplies and approximate division (both within 1e-6 relative) */
 int elx_set_tuning(const char* name, int value);

@@ -102,6 +102,72 @@ def test_probe_largest_finite_values_do_not_flag(K, cuda):
 
 
 @pytest.mark.parametrize('dtype', DTYPES)
+def test_probe_through_the_bulk_copy_ring(K, oracle, cuda, dtype):
+    """The single-array probe has a second form for long arrays (a ring of bulk copies through shared memory);
+    ``probe_variant=2`` sends every size there.  Sizes around its 32 KiB stage, 16-byte piece and ring length, an
+    inf/nan at every kind of position, ``n_valid`` cutting the array, and the same answers as the loads form."""
+    size = torch.empty(0, dtype=dtype).element_size()
+    per_stage = 32768 // size
+    sizes = [1, 7, 8, 9, per_stage - 1, per_stage, per_stage + 1, 6 * per_stage, 6 * per_stage + 3,
+             148 * 6 * per_stage + 5 * per_stage + 11, 148 * 13 * per_stage - 1]
+    K.set_tuning(probe_variant=2)
+    try:
+        for n in sizes:
+            g = torch.ones(n, dtype=dtype, device=cuda)
+            flag = torch.zeros(1, dtype=torch.int32, device=cuda)
+            ctl = K.ControlBlock(cuda, 1.0)
+            K.grad_check(g, flag=flag, ctl=ctl)
+            assert flag.item() == 0 and ctl.read().found_inf == 0 and ctl.read().status == 0, n
+            spots = sorted({0, n - 1, n // 2, max(0, n - 8), max(0, n - 9), min(n - 1, per_stage), min(n - 1, per_stage - 1)})
+            for pos in spots:
+                for val in (float('inf'), float('nan')):
+                    g[pos] = val
+                    flag.zero_()
+                    K.grad_check(g, flag=flag)
+                    assert flag.item() == 1, (n, pos, val)
+                    # the same array cut just before the bad element is clean
+                    flag.zero_()
+                    K.grad_check(g, n_valid=pos, flag=flag)
+                    assert flag.item() == 0, (n, pos, 'cut')
+                    g[pos] = 1.0
+        # a view that starts off the 16-byte boundary goes to the loads form and gives the same answer
+        g = torch.ones(3 * per_stage + 9, dtype=dtype, device=cuda)
+        g[-1] = float('-inf')
+        flag = torch.zeros(1, dtype=torch.int32, device=cuda)
+        K.grad_check(g[1:], flag=flag)
+        assert flag.item() == 1
+        # random data against the oracle and against the loads form
+        gen = torch.Generator().manual_seed(5)
+        h = (torch.randn(5 * per_stage + 123, generator=gen) * 1e4).to(dtype)
+        want = oracle.probe(h)
+        hd = h.to(cuda)
+        got = []
+        for variant in (2, 0):
+            K.set_tuning(probe_variant=variant)
+            flag.zero_()
+            K.grad_check(hd, flag=flag)
+            got.append(bool(flag.item()))
+        assert got == [want, want]
+    finally:
+        K.set_tuning(probe_variant=-1)
+
+
+def test_probe_of_a_long_array_takes_the_ring_by_default(K, cuda):
+    """From 16 MiB on the ring is the default form: same answers on a 96 MiB array."""
+    n = 48 * (1 << 20) + 5
+    g = torch.zeros(n, dtype=torch.float16, device=cuda)
+    flag = torch.zeros(1, dtype=torch.int32, device=cuda)
+    K.grad_check(g, flag=flag)
+    assert flag.item() == 0
+    for pos in (0, n // 3, n - 1):
+        g[pos] = float('nan')
+        flag.zero_()
+        K.grad_check(g, flag=flag)
+        assert flag.item() == 1, pos
+        g[pos] = 0
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
 @pytest.mark.parametrize('n', [1, 4095, 4096, 70001, (1 << 22) + 17])
 def test_probe_l2_norm(K, oracle, cuda, dtype, n):
     gen = torch.Generator().manual_seed(n + 1)
@@ -528,8 +594,9 @@ def test_bulk_copy_pipeline_variant_is_bit_identical_to_direct(K, oracle, cuda, 
     hypers = [K.hyper(1e-3, (0.9, 0.999), 1e-8, 0.01, True), K.hyper(5e-4, (0.9, 0.98), 1e-6, 0.0, True),
               K.hyper(2e-3, (0.85, 0.99), 1e-8, 0.05, False)]
     outs = []
-    for variant in (0, 1):
-        K.set_tuning(adam_variant=variant)
+    # direct accesses; the ring at its default depth (four stages for 16-bit chunks); the ring with three stages
+    for variant, stages in ((0, -1), (1, -1), (1, 3)):
+        K.set_tuning(adam_variant=variant, adam_tma_stages=stages)
         try:
             table, _, dev_t, _ = _build_set(K, oracle, cuda, dtype, sizes, valid, seg_lists, 21, 512.0)
             table.set_hyper(hypers)
@@ -546,10 +613,11 @@ def test_bulk_copy_pipeline_variant_is_bit_identical_to_direct(K, oracle, cuda, 
             assert ctl.read().status == 0
             outs.append([[t.cpu() for t in ts] for ts in dev_t])
         finally:
-            K.set_tuning(adam_variant=-1)
-    for a, b in zip(*outs):
-        for x, y in zip(a, b):
-            assert bits_equal(x, y)
+            K.set_tuning(adam_variant=-1, adam_tma_stages=-1)
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            for x, y in zip(a, b):
+                assert bits_equal(x, y)
 
 
 def test_peer_barrier_wait_is_bounded(K, cuda):
