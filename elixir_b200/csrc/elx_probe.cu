@@ -342,6 +342,226 @@ int launch_probe_bulk(const BulkProbeArgs& a, int dtype, cudaStream_t s) {
     return ELX_ERR_DTYPE;
 }
 
+// The same ring over a table of chunks (elx_grad_check_multi without a norm).  A stage holds kTilesPerStage
+// consecutive tiles of the table's tile numbering.  Nearly every stage lies inside one chunk, below its valid_end
+// and on a 16-byte boundary: it is fetched by ONE bulk copy and tested as a whole (the producer decides that with
+// a few comparisons against its cached chunk).  The other stages (a chunk boundary, a ragged tail, a gradient
+// source off the 16-byte boundary) are described tile by tile: the aligned part of each tile is staged by a copy of
+// its own, the rest is read with plain loads.  Overflow words are raised per chunk.
+
+struct RingTile {
+    const unsigned char* src;   // first element of the tile in global memory
+    uint32_t valid_bytes;       // bytes of the tile that are probed (up to valid_end)
+    int chunk;                  // descriptor index, -1 = nothing to probe
+    int staged;                 // 1: the first valid_bytes & ~15 bytes are in the stage
+};
+
+template <int DT>
+__global__ void __launch_bounds__(kProbeThreads, 1) probe_ring_multi_kernel(const __grid_constant__ ProbeArgs a) {
+    using T = typename Lp<DT>::T;
+    constexpr int kTileBytes = kTile * Lp<DT>::kBytes;
+    constexpr int kTilesPerStage = kBulkProbeStageBytes / kTileBytes;   // 4 (16-bit) or 2 (fp32)
+    constexpr int kVecPerThread = kBulkProbeStageBytes / (kProbeThreads * 16);
+    extern __shared__ __align__(128) unsigned char s_dyn[];
+    __shared__ RingTile s_tile[kBulkProbeStages][kTilesPerStage];
+    __shared__ int s_whole[kBulkProbeStages];    // >= 0: the stage is one piece of this chunk; -1: see s_tile
+    __shared__ __align__(8) uint64_t s_full[kBulkProbeStages];
+    __shared__ int s_abort;
+
+    const ElxChunkDesc* __restrict__ descs = a.descs;
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kBulkProbeStages; ++s) mbar_init(&s_full[s], 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int64_t tile_lo = descs[a.first].tile_begin;
+    const int64_t n_units = (a.n_tiles + kTilesPerStage - 1) / kTilesPerStage;
+    const int64_t my_units = blockIdx.x < n_units ? (n_units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    // producer-side cache of the chunk the last tile fell into (thread 0 only), in scalars
+    int64_t pc_t0 = 0, pc_t1 = 0;        // its tile range
+    int64_t pc_full_t1 = 0;              // tiles [pc_t0, pc_full_t1) lie wholly below valid_end
+    int64_t pc_n_valid = 0;
+    const unsigned char* pc_base = nullptr;
+    int pc_index = -1;
+    bool pc_ok = false;                  // right dtype
+    bool pc_aligned = false;             // gradient source on a 16-byte boundary
+    bool bad_desc = false;
+
+    auto locate = [&](int64_t t) {       // thread 0 only
+        if (t >= pc_t0 && t < pc_t1) return;
+        int lo = a.first, hi = a.first + a.count - 1;
+        while (lo < hi) {
+            int mid = (lo + hi + 1) >> 1;
+            if (descs[mid].tile_begin <= t) lo = mid; else hi = mid - 1;
+        }
+        const ElxChunkDesc d = descs[lo];
+        pc_index = lo;
+        pc_t0 = d.tile_begin;
+        pc_t1 = pc_t0 + tiles_of(d.n_shard);
+        pc_n_valid = d.n_valid;
+        pc_full_t1 = pc_t0 + d.n_valid / kTile;
+        pc_base = static_cast<const unsigned char*>(grad_source(d));
+        pc_ok = d.dtype == DT;
+        pc_aligned = (reinterpret_cast<uintptr_t>(pc_base) & 15u) == 0;
+    };
+
+    auto produce = [&](int64_t k) {    // thread 0 only
+        const int s = static_cast<int>(k % kBulkProbeStages);
+        const int64_t it0 = (blockIdx.x + k * gridDim.x) * static_cast<int64_t>(kTilesPerStage);
+        const int64_t t0 = tile_lo + it0;
+        unsigned char* stage = s_dyn + static_cast<size_t>(s) * kBulkProbeStageBytes;
+        locate(t0);
+        if (it0 + kTilesPerStage <= a.n_tiles && t0 >= pc_t0 && t0 + kTilesPerStage <= pc_full_t1 && pc_ok && pc_aligned) {
+            s_whole[s] = pc_index;
+            mbar_arrive_expect_tx(&s_full[s], kBulkProbeStageBytes);
+            bulk_g2s(stage, pc_base + (t0 - pc_t0) * kTileBytes, kBulkProbeStageBytes, &s_full[s]);
+            return;
+        }
+        s_whole[s] = -1;
+        uint32_t tx = 0;
+#pragma unroll
+        for (int j = 0; j < kTilesPerStage; ++j) {
+            RingTile rt = {nullptr, 0u, -1, 0};
+            if (it0 + j < a.n_tiles) {
+                const int64_t t = t0 + j;
+                locate(t);
+                if (t >= pc_t0 && t < pc_t1 && pc_ok) {
+                    const int64_t e0 = (t - pc_t0) * kTile;
+                    const int64_t valid = pc_n_valid - e0;
+                    if (valid > 0) {
+                        rt.src = pc_base + e0 * Lp<DT>::kBytes;
+                        rt.valid_bytes = static_cast<uint32_t>((valid < kTile ? valid : kTile) * Lp<DT>::kBytes);
+                        rt.chunk = pc_index;
+                        rt.staged = pc_aligned && (rt.valid_bytes & ~15u) != 0;
+                        if (rt.staged) tx += rt.valid_bytes & ~15u;
+                    }
+                } else {
+                    bad_desc = true;
+                }
+            }
+            s_tile[s][j] = rt;
+        }
+        if (tx) {
+            mbar_arrive_expect_tx(&s_full[s], tx);
+#pragma unroll
+            for (int j = 0; j < kTilesPerStage; ++j) {
+                const RingTile rt = s_tile[s][j];
+                if (rt.staged) bulk_g2s(stage + j * kTileBytes, rt.src, rt.valid_bytes & ~15u, &s_full[s]);
+            }
+        } else {
+            mbar_arrive(&s_full[s]);   // nothing to load: the phase completes at once and publishes the tiles
+        }
+    };
+
+    if (threadIdx.x == 0) {
+        for (int64_t k = 0; k < my_units && k < kBulkProbeStages; ++k) produce(k);
+    }
+
+    auto raise = [&](uint32_t bad, int chunk) {
+        const unsigned any_bad = __ballot_sync(0xFFFFFFFFu, bad != 0);
+        if (any_bad && lane == 0) {
+            if (a.chunk_flags) atomicOr(&a.chunk_flags[chunk], 1u);
+            if (a.ctl) atomicOr(&a.ctl->found_inf, 1u);
+        }
+    };
+
+    int64_t k = 0;
+    for (; k < my_units; ++k) {
+        const int s = static_cast<int>(k % kBulkProbeStages);
+        const uint32_t parity = static_cast<uint32_t>((k / kBulkProbeStages) & 1);
+        if (!mbar_wait_bounded(&s_full[s], parity)) s_abort = 1;
+        __syncthreads();
+        if (s_abort) break;
+        const unsigned char* stage = s_dyn + static_cast<size_t>(s) * kBulkProbeStageBytes;
+        const int whole = s_whole[s];
+        if (whole >= 0) {
+            uint32_t bad = 0;
+            // consecutive threads read consecutive 16-byte pieces: conflict-free 128-bit shared reads
+#pragma unroll
+            for (int h = 0; h < kVecPerThread; ++h) {
+                const uint4 w = *reinterpret_cast<const uint4*>(stage + (h * kProbeThreads + threadIdx.x) * 16);
+                bad |= Lp<DT>::nonfinite_word(w.x) | Lp<DT>::nonfinite_word(w.y) | Lp<DT>::nonfinite_word(w.z) |
+                       Lp<DT>::nonfinite_word(w.w);
+            }
+            raise(bad, whole);
+        } else {
+            for (int j = 0; j < kTilesPerStage; ++j) {
+                const RingTile rt = s_tile[s][j];
+                if (rt.chunk < 0) continue;     // the same for every thread
+                uint32_t bad = 0;
+                uint32_t from_global = 0;       // byte offset from which the tile is read with plain loads
+                if (rt.staged) {
+                    const uint32_t len16 = rt.valid_bytes & ~15u;
+                    for (uint32_t off = threadIdx.x * 16; off < len16; off += kProbeThreads * 16) {
+                        const uint4 w = *reinterpret_cast<const uint4*>(stage + j * kTileBytes + off);
+                        bad |= Lp<DT>::nonfinite_word(w.x) | Lp<DT>::nonfinite_word(w.y) | Lp<DT>::nonfinite_word(w.z) |
+                               Lp<DT>::nonfinite_word(w.w);
+                    }
+                    from_global = len16;
+                }
+                const uint32_t n_rest = (rt.valid_bytes - from_global) / Lp<DT>::kBytes;
+                const T* rest = reinterpret_cast<const T*>(rt.src + from_global);
+                for (uint32_t e = threadIdx.x; e < n_rest; e += kProbeThreads)
+                    if (Lp<DT>::nonfinite(rest[e])) bad = 1;
+                raise(bad, rt.chunk);
+            }
+        }
+        __syncthreads();   // the stage and its records have been read by every warp
+        if (threadIdx.x == 0 && k + kBulkProbeStages < my_units) produce(k + kBulkProbeStages);
+    }
+    if (threadIdx.x == 0) {
+        if (s_abort) {
+            for (int64_t j = k; j < my_units && j < k + kBulkProbeStages; ++j)
+                (void)mbar_wait_bounded(&s_full[j % kBulkProbeStages], static_cast<uint32_t>((j / kBulkProbeStages) & 1));
+            // chunks that were not read to the end do not count as clean
+            if (a.ctl) {
+                atomicOr(&a.ctl->status, ELX_STAT_TIMEOUT);
+                atomicOr(&a.ctl->found_inf, 1u);
+            }
+            if (a.chunk_flags)
+                for (int i = 0; i < a.count; ++i) atomicOr(&a.chunk_flags[a.first + i], 1u);
+        }
+        if (bad_desc && a.ctl) atomicOr(&a.ctl->status, ELX_STAT_BAD_DESC);
+    }
+}
+
+template <int DT>
+int launch_probe_ring_multi_inst(const ProbeArgs& a, cudaStream_t s) {
+    static bool opted_in[64];
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        (void)cudaGetLastError();
+        return ELX_ERR_NODEVICE;
+    }
+    if (!opted_in[dev]) {
+        const cudaError_t attr = cudaFuncSetAttribute(probe_ring_multi_kernel<DT>,
+                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkProbeSmem);
+        if (attr != cudaSuccess) {
+            const int rc = record_cuda(attr);
+            (void)cudaGetLastError();
+            return rc;
+        }
+        opted_in[dev] = true;
+    }
+    constexpr int kTilesPerStage = kBulkProbeStageBytes / (kTile * Lp<DT>::kBytes);
+    const int grid = grid_for((a.n_tiles + kTilesPerStage - 1) / kTilesPerStage, 1);
+    if (grid < 0) return grid;
+    probe_ring_multi_kernel<DT><<<grid, kProbeThreads, kBulkProbeSmem, s>>>(a);
+    return record_cuda(cudaGetLastError());
+}
+
+int launch_probe_ring_multi(const ProbeArgs& a, int dtype, cudaStream_t s) {
+    switch (dtype) {
+        case ELX_F16: return launch_probe_ring_multi_inst<ELX_F16>(a, s);
+        case ELX_BF16: return launch_probe_ring_multi_inst<ELX_BF16>(a, s);
+        case ELX_F32: return launch_probe_ring_multi_inst<ELX_F32>(a, s);
+    }
+    return ELX_ERR_DTYPE;
+}
+
 // Arrays from this size on take the bulk-copy probe (probe_variant 1); below it the ring's ramp-up and drain
 // outweigh what it gains.  probe_variant 2 sends every eligible array there (tests), 0 none.
 constexpr int64_t kBulkProbeMinBytes = int64_t(16) << 20;
@@ -629,7 +849,10 @@ int elx_grad_check_multi(const ElxChunkDesc* descs, int first, int count, int64_
         a.first = first;
         a.count = count;
         a.n_tiles = n_tiles;
-        rc = launch_probe<false>(a, dtype, norm, s);
+        // without a norm: the bulk-copy ring from 16 MiB of tiles on (probe_variant 2: always, 0: never)
+        const bool ring = !norm && g_tune.probe_variant != 0 &&
+                          (g_tune.probe_variant == 2 || n_tiles * kTile * dtype_bytes(dtype) >= kBulkProbeMinBytes);
+        rc = ring ? launch_probe_ring_multi(a, dtype, s) : launch_probe<false>(a, dtype, norm, s);
         if (rc != ELX_OK) return rc;
     }
     if (norm) {

@@ -481,6 +481,74 @@ def _segments(n_valid, cuts, groups):
 
 
 @pytest.mark.parametrize('dtype', DTYPES)
+def test_table_probe_through_the_bulk_copy_ring(K, oracle, cuda, dtype):
+    """``elx_grad_check_multi`` without a norm has the ring form too (``probe_variant=2`` forces it at every size).
+    Chunks whose tiles share stages with their neighbours, ragged tails, ``valid_end`` inside a tile, an empty
+    chunk, a gradient source of its own that is off the 16-byte boundary: the per-chunk words and the control
+    block's word must say the same as the oracle's probe of every chunk, for an inf/nan at any kind of position,
+    and the same as the loads form."""
+    sizes = [9 * 4096, 5 * 4096 + 100, 4096, 3, 12 * 4096 + 7, 40 * 4096]
+    valid = [9 * 4096, 5 * 4096 + 100, 1000, 0, 7 * 4096 + 1, 40 * 4096 - 3]
+    table = K.ChunkTable(cuda, dtype)
+    grads = []
+    for c, (n, nv) in enumerate(zip(sizes, valid)):
+        p, m, v, g = make_chunk(n, dtype, seed=300 + c, scale=4.0)
+        dts = [t.to(cuda) for t in (p, m, v, g)]
+        kw = {}
+        if c == 4:    # gradients in a block of their own, starting one element off the vector alignment
+            store = torch.ones(n + 8, dtype=dtype, device=cuda)
+            kw['grad_src'] = store[1:n + 1]
+            dts.append(store)
+        table.add_chunk(dts[0], dts[1], dts[2], dts[3], n_valid=nv, segments=[(0, nv, 0)] if nv else [], **kw)
+        grads.append(kw.get('grad_src', dts[3]))
+    table.finalize()
+    flags = torch.zeros(table.n_chunks, dtype=torch.int32, device=cuda)
+
+    def probe(variant):
+        K.set_tuning(probe_variant=variant)
+        try:
+            flags.zero_()
+            ctl = K.ControlBlock(cuda, 1.0)
+            K.grad_check_multi(table, ctl, chunk_flags=flags)
+            c = ctl.read()
+            assert c.status == 0
+            return flags.tolist(), int(c.found_inf)
+        finally:
+            K.set_tuning(probe_variant=-1)
+
+    for g in grads:
+        g.fill_(1.0)
+    assert probe(2) == ([0] * len(sizes), 0)
+    for c, nv in enumerate(valid):
+        spots = sorted({p for p in (0, nv - 1, nv // 2, nv - 8, nv - 9, 4095, 4096, 4 * 4096 - 1, 4 * 4096) if 0 <= p < nv})
+        for pos in spots:
+            for val in (float('inf'), float('nan')):
+                grads[c][pos] = val
+                want = ([int(i == c) for i in range(len(sizes))], 1)
+                assert oracle.probe(grads[c].cpu(), nv)
+                assert probe(2) == want, (c, pos, val)
+                assert probe(0) == want
+                grads[c][pos] = 1.0
+        if nv < sizes[c]:    # the first element past valid_end does not count
+            grads[c][nv] = float('nan')
+            assert probe(2) == ([0] * len(sizes), 0), c
+            grads[c][nv] = 1.0
+    # a sub-range of the table
+    grads[1][7] = float('inf')
+    grads[5][11] = float('inf')
+    K.set_tuning(probe_variant=2)
+    try:
+        flags.zero_()
+        ctl = K.ControlBlock(cuda, 1.0)
+        K.grad_check_multi(table, ctl, chunk_flags=flags, first=2, count=3)
+        assert flags.tolist() == [0] * len(sizes) and ctl.read().found_inf == 0
+        K.grad_check_multi(table, ctl, chunk_flags=flags, first=1, count=5)
+        assert flags.tolist() == [0, 1, 0, 0, 0, 1] and ctl.read().found_inf == 1
+    finally:
+        K.set_tuning(probe_variant=-1)
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
 def test_adam_multi_segments_and_groups(K, oracle, cuda, dtype):
     sizes = [8 * 4096, 5 * 4096 + 100, 4096, 3, 12 * 4096]
     valid = [8 * 4096, 5 * 4096 + 100, 1000, 0, 7 * 4096 + 1]
