@@ -916,6 +916,63 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
 # ------------------------------------------------------------------------------------------------------
 
 
+def run_probe_rate(args):
+    """``--workload probe-rate``: the inf/nan probe alone, load/store form (``probe_variant`` 0) against the bulk-copy
+    ring (2), on one contiguous fp16 array of growing size (``elx_grad_check``) and on a table of 47 chunks of 32 Mi
+    elements (``elx_grad_check_multi``).  Minimum of 7 launches after 3 warm-up launches, CUDA events around each
+    launch.  One JSON line.  Synthetic data (zeros: the probe's work does not depend on the values)."""
+    from elixir_b200 import kernels as K
+    device = torch.device('cuda', 0)
+    torch.cuda.set_device(device)
+
+    def best_ms(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        return min(times)
+
+    ctl = K.ControlBlock(device)
+    n_chunks, chunk = 47, 32 * 1024 * 1024
+    flat = torch.zeros(int(25.77e9) // 2, dtype=torch.float16, device=device)
+    rows = []
+    try:
+        for gb in (0.016, 0.067, 0.268, 1.0, 3.15, 12.9, 25.77):
+            g = flat[:int(gb * 1e9) // 2]
+            row = {'form': 'one array', 'bytes': g.numel() * 2}
+            for variant, name in ((0, 'loads'), (2, 'ring')):
+                K.set_tuning(probe_variant=variant)
+                ms = best_ms(lambda: K.grad_check(g, ctl=ctl))
+                row[name] = {'ms': ms, 'TBs': g.numel() * 2 / ms / 1e9}
+            rows.append(row)
+        table = K.ChunkTable(device, torch.float16)
+        stub = torch.zeros(chunk, dtype=torch.float32, device=device)    # the probe never touches the fp32 arrays
+        for c in range(n_chunks):
+            table.add_chunk(stub, stub, stub, flat[c * chunk:(c + 1) * chunk], n_valid=chunk - (5 if c % 3 == 0 else 0),
+                            segments=[(0, chunk - 5, 0)])
+        table.finalize()
+        flags = torch.zeros(n_chunks, dtype=torch.int32, device=device)
+        row = {'form': f'table of {n_chunks} chunks', 'bytes': n_chunks * chunk * 2}
+        for variant, name in ((0, 'loads'), (2, 'ring')):
+            K.set_tuning(probe_variant=variant)
+            ms = best_ms(lambda: K.grad_check_multi(table, ctl, chunk_flags=flags))
+            row[name] = {'ms': ms, 'TBs': n_chunks * chunk * 2 / ms / 1e9}
+        rows.append(row)
+    finally:
+        K.set_tuning(probe_variant=-1)
+    c = ctl.read()
+    assert c.found_inf == 0 and c.status == 0 and int(flags.sum().item()) == 0
+    peak, peak_kind = load_peaks()
+    print(json.dumps({'workload': 'probe-rate', 'unit': 'TB/s', 'hbm_copy_peak_gbs': peak, 'peak_kind': peak_kind, 'rows': rows}))
+
+
 def run_residency(args):
     """``--workload residency``: time one training iteration (forward, backward, optimizer step) of a stack of MLP
     blocks behind ``ElixirModule`` / ``ElixirOptimizer`` under the three ways of keeping chunks resident — ``all``: a
@@ -1143,9 +1200,10 @@ def main():
                     'decision taken on the inputs first (two ranks); p2p-overlap = the p2p kernels with the decision taken on the inputs first, so that the update '
                     'of a chunk runs while the next one is reduced; staged = copy engines; nccl = NCCL on side streams; '
                     'auto = mm from 4 ranks on (where its two state sets fit), p2p-fused at 2 ranks, else p2p')
-    ap.add_argument('--workload', default='auto', choices=['auto', 'opt66b_bf16', 'residency'],
+    ap.add_argument('--workload', default='auto', choices=['auto', 'opt66b_bf16', 'residency', 'probe-rate'],
                     help='N > 1: auto = OPT-13B-shaped fp16 chunk set; opt66b_bf16 = OPT-66B-shaped bf16 chunk set (8 GPUs); '
-                    'residency = one training iteration of an MLP stack through the wrapper under three residency modes')
+                    'residency = one training iteration of an MLP stack through the wrapper under three residency modes; '
+                    'probe-rate = the inf/nan probe alone, load/store form against the bulk-copy ring (1 GPU)')
     ap.add_argument('--layers', type=int, default=12, help='residency workload: blocks of the stack (one chunk each)')
     ap.add_argument('--hidden', type=int, default=4096, help='residency workload: hidden size')
     ap.add_argument('--tokens', type=int, default=8192, help='residency workload: rows of the input')
@@ -1186,6 +1244,8 @@ def main():
         args.collective = 'mm' if plain and args.gpus >= 4 else 'p2p-fused' if plain and args.gpus == 2 else 'p2p'
     if args.workload == 'residency':
         run_residency(args)
+    elif args.workload == 'probe-rate':
+        run_probe_rate(args)
     elif args.impl == 'reference':
         run_reference(args)
     else:
