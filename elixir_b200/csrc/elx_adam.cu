@@ -108,7 +108,9 @@ __device__ __forceinline__ int64_t push_base_elem(const AdamArgs& a, int c, int6
 // CTA-collective; s_cur is a shared-memory cursor that cursor_reset() has initialised.
 template <int DT, int EPT>
 __device__ __forceinline__ bool copyback_tiles(const AdamArgs& a, const ElxChunkDesc* __restrict__ descs,
-                                               ChunkCursor& s_cur) {
+                                               ChunkCursor& s_cur, bool active, int n_active) {
+    // every thread of the CTA takes part in the chunk lookup (it synchronises the CTA); the first n_active
+    // threads, those with `active` set, move the data
     bool bad_desc = false;
     const int64_t tile_lo = descs[a.first].tile_begin;
     for (int64_t it = blockIdx.x; it < a.n_tiles; it += gridDim.x) {
@@ -117,6 +119,7 @@ __device__ __forceinline__ bool copyback_tiles(const AdamArgs& a, const ElxChunk
             bad_desc = true;
             continue;
         }
+        if (!active) continue;
         const int64_t e0 = (t - s_cur.t0) * kTile;
         const int64_t e1 = min(e0 + kTile, s_cur.d.n_shard);
         float* const master = s_cur.d.master;
@@ -130,7 +133,7 @@ __device__ __forceinline__ bool copyback_tiles(const AdamArgs& a, const ElxChunk
             for (int j = 0; j < world; ++j) store_lowp<DT, EPT>(a.push.base[j], pb + e0, p);
         } else {
             typename Lp<DT>::T* out = static_cast<typename Lp<DT>::T*>(lowp);
-            for (int64_t e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
+            for (int64_t e = e0 + threadIdx.x; e < e1; e += n_active) {
                 const typename Lp<DT>::T val = Lp<DT>::from_float(master[e]);
                 out[e] = val;
                 for (int j = 0; j < world; ++j) static_cast<typename Lp<DT>::T*>(a.push.base[j])[pb + e] = val;
@@ -172,7 +175,7 @@ __global__ void __launch_bounds__(kTile / EPT, MINB) adam_kernel(const __grid_co
     bool bad_desc = false;
 
     if (skip) {
-        bad_desc = copyback_tiles<DT, EPT>(a, descs, s_cur);
+        bad_desc = copyback_tiles<DT, EPT>(a, descs, s_cur, true, blockDim.x);
         if (__ballot_sync(0xFFFFFFFFu, bad_desc) && (threadIdx.x & 31) == 0) atomicOr(&ctl->status, ELX_STAT_BAD_DESC);
         return;
     }
@@ -278,26 +281,31 @@ __global__ void __launch_bounds__(kTile / EPT, MINB) adam_kernel(const __grid_co
 // Adam, bulk-copy pipelined variant
 // ------------------------------------------------------------------------------------------------
 //
-// Same arithmetic, different data movement: one elected thread streams whole tiles between HBM and
-// shared memory with cp.async.bulk (the TMA unit's untiled form), completion tracked by mbarriers,
-// so loads of the next tiles and stores of the previous one are in flight while the CTA's warps
-// compute on the current one out of shared memory.  One CTA per SM, a ring of S stages of one tile
-// each (16-bit gradients: 8 KB + 3 x 16 KB = 56 KB per stage; S = 4 where that fits, else 3).
+// Same arithmetic, different data movement: whole tiles stream between HBM and shared memory with
+// cp.async.bulk (the TMA unit's untiled form), completion tracked by mbarriers, so loads of the next tiles
+// and stores of the previous one are in flight while the CTA's warps compute on the current one out of
+// shared memory.  One CTA per SM: 16 computing warps plus one warp whose first lane -- the data mover --
+// issues every bulk copy; a ring of S stages of one tile each (16-bit gradients: 8 KB + 3 x 16 KB = 56 KB
+// per stage; S = 4 where that fits, else 3).
 //
-//   iteration k (stage s = k % S):
-//     all threads   wait full[s]; read g,p,m,v from the stage; update; write p,m,v,p16 back in place
-//                   fence.proxy.async; __syncthreads
-//     thread 0      4 bulk stores stage s -> HBM, commit; wait until the stores of iteration k-1 have
-//                   read their stage; arm full[(k+S-1) % S] and issue the 4 bulk loads of tile k+S-1 into it
+//   computing warps, tile k (stage s = k % S):
+//       wait full[s]; read g,p,m,v from the stage; update; write p,m,v,p16 back in place;
+//       fence.proxy.async; barrier among the computing warps; one arrival on done[s]
+//   data mover, tile k:
+//       wait done[s]; 4 bulk stores stage s -> HBM, commit; wait until the stores of tile k-1 have read
+//       their stage; classify tile k+S-1, publish its slot, arm full[(k+S-1) % S], issue its 4 bulk loads
 //
-// Measured on the GPT-2-XL chunk set, same GPU, back to back: 7.13 ms per launch with three stages, 6.97 ms
-// with four (more loads in flight while a tile is computed and the previous one drains).
+// The mover's bookkeeping (tile classification, descriptor and segment lookup, some hundred instructions per
+// tile) used to be done by thread 0 between two CTA-wide barriers, i.e. on every warp's path.  Measured on the
+// GPT-2-XL chunk set, same GPU, back to back: 7.17 ms per launch with thread 0 as the mover, 6.98 ms with the
+// warp of its own; before that, three stages against four: 7.13 ms against 6.97 ms.
 //
 // Ragged tiles (shard tail, segment boundary, unaligned pointers) bypass the pipeline and are updated
 // in place in global memory by the same scalar path as the direct kernel.  Every mbarrier wait is
 // bounded: on expiry the CTA raises ELX_STAT_TIMEOUT, stops issuing copies, drains and returns.
 
-constexpr int kTmaThreads = 512;
+constexpr int kTmaThreads = 512;                   // the warps that compute
+constexpr int kTmaBlock = kTmaThreads + 32;        // plus one warp whose first lane moves the data
 
 // Stages of the ring.  Three everywhere, except the default instantiations (16-bit chunks, IEEE arithmetic, no
 // peers' slices beside the stage): four 56 KB stages plus the kernel's static shared memory just fit into the
@@ -497,7 +505,7 @@ __device__ __forceinline__ void mm_st8(void* mc, uint2 v) {
 // into PW - 1 staging slots behind the stage -- and summed by the threads exactly as the pull kernel sums
 // (fp32, rank order, one rounding to the chunk dtype).  16-bit chunks; shared memory allows PW = 2.
 template <int DT, int MATH, bool MM, int PW, int STAGES>
-__global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_constant__ AdamArgs a) {
+__global__ void __launch_bounds__(kTmaBlock, 1) adam_tma_kernel(const __grid_constant__ AdamArgs a) {
     using Stage = TmaStage<DT>;
     static_assert(!MM || DT != ELX_F32, "the multicast form is for 16-bit chunks");
     static_assert(PW == 0 || (PW > 1 && !MM && DT != ELX_F32), "the pulling form is for 16-bit chunks, without multicast");
@@ -509,9 +517,12 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
     extern __shared__ __align__(128) unsigned char s_dyn[];
     __shared__ GroupStore s_group[kMaxGroups];
     __shared__ TileSlot s_slot[kTmaStages];
-    __shared__ __align__(8) uint64_t s_full[kTmaStages];
+    __shared__ __align__(8) uint64_t s_full[kTmaStages];   // the loads of a stage have landed (and its slot is published)
+    __shared__ __align__(8) uint64_t s_done[kTmaStages];   // the computing warps are through with a stage
     __shared__ int s_abort;
 
+    const bool mover = threadIdx.x == kTmaThreads;         // the one thread that issues every bulk copy
+    const bool computes = threadIdx.x < kTmaThreads;
     const ElxChunkDesc* __restrict__ descs = a.inline_tables ? &a.one_desc : a.descs;
     const ElxSeg* __restrict__ segs = a.inline_tables ? &a.one_seg : a.segs;
     const ElxHyper* __restrict__ hyper = a.inline_tables ? &a.one_hyper : a.hyper;
@@ -530,7 +541,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         // the ring is not used on this path: the cursor lives at its start
         ChunkCursor& s_cur = *reinterpret_cast<ChunkCursor*>(s_dyn);
         cursor_reset(s_cur);
-        const bool bad = copyback_tiles<DT, kTile / kTmaThreads>(a, src, s_cur);
+        const bool bad = copyback_tiles<DT, kTile / kTmaThreads>(a, src, s_cur, computes, kTmaThreads);
         if (__ballot_sync(0xFFFFFFFFu, bad) && (threadIdx.x & 31) == 0) atomicOr(&ctl->status, ELX_STAT_BAD_DESC);
         return;
     }
@@ -545,7 +556,10 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         else s_group[gi] = derived;
     }
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kTmaStages; ++s) mbar_init(&s_full[s], 1);
+        for (int s = 0; s < kTmaStages; ++s) {
+            mbar_init(&s_full[s], 1);
+            mbar_init(&s_done[s], 1);
+        }
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -597,7 +611,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         }
     };
 
-    if (threadIdx.x == 0) {
+    if (mover) {
         for (int64_t k = 0; k < my_tiles && k < kTmaStages - 1; ++k) produce(k);
     }
 
@@ -617,19 +631,30 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
     };
     if constexpr (MM) {
         __syncthreads();   // the first slots are published
-        fetch(0, g_now);
+        if (computes) fetch(0, g_now);
     }
 
+    // barrier of the computing warps alone (the data mover runs on its own clock)
+    auto sync_computing = [] { asm volatile("bar.sync 1, %0;" ::"n"(kTmaThreads) : "memory"); };
+
     int64_t k = 0;
+    if (computes) {
     for (; k < my_tiles; ++k) {
         const int s = static_cast<int>(k % kTmaStages);
         const uint32_t parity = static_cast<uint32_t>((k / kTmaStages) & 1);
         if (!mbar_wait_bounded(&s_full[s], parity)) s_abort = 1;
-        __syncthreads();
+        sync_computing();
         if (s_abort) break;
         const TileSlot slot = s_slot[s];   // into registers: measured 1.3 % faster than reading the fields from shared memory
         unsigned char* base = s_dyn + static_cast<size_t>(s) * kStageBytes;
-        if constexpr (MM) fetch(k + 1, g_next);   // slot k + 1 was published before the barrier above
+        if constexpr (MM) {
+            // the slot of tile k + 1 is published once its loads have been started; they were started three tiles ago
+            if (k + 1 < my_tiles) {
+                const int s1 = static_cast<int>((k + 1) % kTmaStages);
+                if (mbar_wait_bounded(&s_full[s1], static_cast<uint32_t>(((k + 1) / kTmaStages) & 1))) fetch(k + 1, g_next);
+                else s_abort = 1;   // seen by every thread at the next tile's barrier
+            }
+        }
 
         if (slot.kind == kTileBulk) {
             const GroupK k_ = unpack_group(s_group[slot.group]);
@@ -718,7 +743,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
         } else if (slot.kind == kTileRagged) {
             typename Lp<DT>::T* gp = static_cast<typename Lp<DT>::T*>(slot.lowp);
             const typename Lp<DT>::T* gin = static_cast<const typename Lp<DT>::T*>(slot.gsrc);
-            for (int64_t e = slot.e0 + threadIdx.x; e < slot.e1; e += blockDim.x) {
+            for (int64_t e = slot.e0 + threadIdx.x; e < slot.e1; e += kTmaThreads) {
                 float p = slot.master[e];
                 float g = 0.0f;
                 if (e < slot.n_valid) {
@@ -772,9 +797,31 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
             }
             nan_acc = 0.0f;
         }
-        __syncthreads();   // the stage is fully written (bulk) / fully consumed
-
-        if (threadIdx.x == 0) {
+        sync_computing();   // the stage is fully written (bulk) / fully consumed
+        if (threadIdx.x == 0) mbar_arrive(&s_done[s]);   // over to the data mover
+        if constexpr (MM) {
+#pragma unroll
+            for (int h = 0; h < kHalves; ++h) g_now[h] = g_next[h];
+        }
+    }
+    } else if (mover) {
+        // The data mover: for every tile, once the computing warps are through with its stage, the bulk stores
+        // of the stage and -- as soon as the stores of the tile before have read their stage -- the loads of the
+        // tile that will use that stage next.  None of this is on the computing warps' path.
+        for (; k < my_tiles; ++k) {
+            const int s = static_cast<int>(k % kTmaStages);
+            const uint32_t parity = static_cast<uint32_t>((k / kTmaStages) & 1);
+            bool handed_over = false;
+            for (uint32_t i = 0; i < kTmaSpinLimit && !handed_over; ++i) {
+                handed_over = mbar_try_wait(&s_done[s], parity);
+                if (!handed_over && *reinterpret_cast<volatile int*>(&s_abort)) break;   // the computing warps gave up
+            }
+            if (!handed_over) {
+                s_abort = 1;
+                break;
+            }
+            const TileSlot slot = s_slot[s];
+            unsigned char* base = s_dyn + static_cast<size_t>(s) * kStageBytes;
             if (slot.kind == kTileBulk || slot.kind == kTileRefresh) {
                 bulk_s2g(static_cast<char*>(slot.lowp) + slot.e0 * Lp<DT>::kBytes, base, Stage::kLowpBytes);
                 if (slot.kind == kTileBulk) {
@@ -800,12 +847,6 @@ __global__ void __launch_bounds__(kTmaThreads, 1) adam_tma_kernel(const __grid_c
                 produce(k + kTmaStages - 1);
             }
         }
-        if constexpr (MM) {
-#pragma unroll
-            for (int h = 0; h < kHalves; ++h) g_now[h] = g_next[h];
-        }
-    }
-    if (threadIdx.x == 0) {
         if (s_abort) {
             // gave up on tile k: the loads already issued for the tiles after it still target this CTA's
             // shared memory, so wait (bounded again) for them before the CTA may exit
@@ -883,7 +924,7 @@ int launch_adam_tma_ring(const AdamArgs& a, cudaStream_t s) {
     if (grid < 0) return grid;
     // fewer CTAs than SMs leave the other SMs to a kernel on another stream (the pull of the next chunk)
     if (g_tune.adam_tma_ctas > 0 && g_tune.adam_tma_ctas < grid) grid = g_tune.adam_tma_ctas;
-    adam_tma_kernel<DT, MATH, MM, PW, STAGES><<<grid, kTmaThreads, smem, s>>>(a);
+    adam_tma_kernel<DT, MATH, MM, PW, STAGES><<<grid, kTmaBlock, smem, s>>>(a);
     return record_cuda(cudaGetLastError());
 }
 
