@@ -78,6 +78,29 @@ def captured_traffic_per_element(step):
     return mbytes * 1e6 / elems, name
 
 
+def live_copy_gbs(device, nbytes=4 << 30, reps=5):
+    """Read + write rate of a device-to-device copy of ``nbytes`` (the runtime's own copy kernel) on ``device``: the best
+    of ``reps`` after two warm-up copies, CUDA events.  None if the memory for it is not there."""
+    try:
+        src = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        dst = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    except RuntimeError:
+        return None
+    src.zero_()
+    best = None
+    for i in range(reps + 2):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        dst.copy_(src)
+        b.record()
+        torch.cuda.synchronize(device)
+        if i >= 2:
+            ms = a.elapsed_time(b)
+            best = ms if best is None else min(best, ms)
+    del src, dst
+    return 2 * nbytes / (best * 1e-3) / 1e9
+
+
 def load_peaks():
     path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
     if os.path.exists(path):
@@ -668,6 +691,11 @@ def run_ours(args):
             'frac_of_8TBs_nominal': achieved / 8000.0,
         }
         result['adam_gparams_per_s'] = n_elems / (adam_ms * 1e-3) / 1e9
+        # the GPUs of the pool differ by several per cent: a device-to-device copy timed on THIS one, after the timed
+        # region, beside the pool-wide peak the fraction above refers to
+        live = live_copy_gbs(device)
+        result['roofline']['this_gpu_copy_gbs'] = live
+        result['roofline']['frac_of_this_gpu_copy'] = achieved / live if live else None
         if args.shards != 'device':
             per_dir = n_elems * (BYTES_PER_ELEM // 2) / (adam_ms * 1e-3) / 1e9
             result['roofline'] = {
