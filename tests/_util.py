@@ -75,3 +75,11 @@ def make_chunk(n, dtype, seed, scale=64.0, sigma=1e-3, device='cpu'):
     master = torch.randn(n, generator=gen) * 0.02
     grad = (torch.randn(n, generator=gen) * sigma * scale).to(dtype)
     return (master.to(device), torch.zeros(n, device=device), torch.zeros(n, device=device), grad.to(device))
+
+
+def free_port() -> int:
+    """A TCP port on 127.0.0.1 that nobody listens on right now (for a rendezvous of child processes)."""
+    import socket
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(('127.0.0.1', 0))
+        return s.getsockname()[1]

@@ -9,23 +9,24 @@ import torch
 import torch.multiprocessing as mp
 
 import _dist_workers as W
+from _util import free_port
 
 
 @pytest.mark.parametrize('world', [1, 2, 4])
 def test_chunk_geometry_gather_reduce_match_reference(world):
-    mp.spawn(W.chunk_worker, args=(world, 29700 + world), nprocs=world)
+    mp.spawn(W.chunk_worker, args=(world, free_port()), nprocs=world)
 
 
 @pytest.mark.parametrize('world', [1, 2, 4])
 def test_optimizer_trajectory_matches_reference_per_rank(world):
     """sync_overflow=False reproduces the reference decision rule (each rank looks at its own shards only),
     including the ranks drifting apart after an overflow that only one rank's shard holds."""
-    mp.spawn(W.optim_worker, args=(world, 29710 + world, False), nprocs=world)
+    mp.spawn(W.optim_worker, args=(world, free_port(), False), nprocs=world)
 
 
 @pytest.mark.parametrize('world', [2, 4])
 def test_overflow_agreement_keeps_ranks_in_lockstep(world):
-    mp.spawn(W.optim_worker, args=(world, 29720 + world, True), nprocs=world)
+    mp.spawn(W.optim_worker, args=(world, free_port(), True), nprocs=world)
 
 
 def test_oracle_replays_reference_steps(oracle):

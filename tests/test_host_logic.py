@@ -5,6 +5,7 @@ import torch
 import torch.distributed as dist
 
 import _dist_workers as W
+from _util import free_port
 
 
 @pytest.fixture(scope='module')
@@ -13,7 +14,7 @@ def host_backend():
     saved = (_lib._LIB, _lib._HOST_MEMORY)
     W.use_host_shim()
     if not dist.is_initialized():
-        dist.init_process_group('gloo', init_method='tcp://127.0.0.1:29790', rank=0, world_size=1)
+        dist.init_process_group('gloo', init_method=f'tcp://127.0.0.1:{free_port()}', rank=0, world_size=1)
     yield
     _lib._LIB, _lib._HOST_MEMORY = saved
 
@@ -208,7 +209,7 @@ def test_tensor_state_machine_equals_the_reference():
 @pytest.mark.parametrize('world', [1, 2])
 def test_chunk_group_and_memory_pool_bookkeeping(world):
     import torch.multiprocessing as mp
-    mp.spawn(W.group_worker, args=(world, 29730 + world), nprocs=world)
+    mp.spawn(W.group_worker, args=(world, free_port()), nprocs=world)
 
 
 def test_single_pass_step_bookkeeping_equals_the_two_phase_step(host_backend):

@@ -6,6 +6,7 @@ import torch
 import torch.multiprocessing as mp
 
 import _dist_workers as W
+from _util import free_port
 from elixir_b200.chunk import FIFOScheduler, PrefetchScheduler
 
 
@@ -122,29 +123,29 @@ def test_prefetch_scheduler_learns_the_trace_from_the_first_pass():
 @pytest.mark.parametrize('world', [1, 2])
 @pytest.mark.parametrize('prefetch', [False, True])
 def test_scheduled_residency_equals_everything_resident(world, prefetch):
-    mp.spawn(W.residency_worker, args=(world, 29740 + 2 * world + int(prefetch), prefetch, 'float32'), nprocs=world)
+    mp.spawn(W.residency_worker, args=(world, free_port(), prefetch, 'float32'), nprocs=world)
 
 
 def test_micro_gpt2_trains_identically_in_both_residency_modes_and_follows_plain_adamw():
     pytest.importorskip('transformers')
-    mp.spawn(W.gpt2_worker, args=(1, 29760), nprocs=1)
+    mp.spawn(W.gpt2_worker, args=(1, free_port()), nprocs=1)
 
 
 def test_an_abandoned_forward_gives_its_blocks_back():
-    mp.spawn(W.abandoned_pass_worker, args=(1, 29761), nprocs=1)
+    mp.spawn(W.abandoned_pass_worker, args=(1, free_port()), nprocs=1)
 
 
 def test_dropping_the_wrapper_frees_model_and_optimizer_state():
-    mp.spawn(W.lifetime_worker, args=(1, 29762), nprocs=1)
+    mp.spawn(W.lifetime_worker, args=(1, free_port()), nprocs=1)
 
 
 def test_fetcher_decisions_on_a_spelled_out_trace():
-    mp.spawn(W.fetcher_scenario_worker, args=(1, 29763), nprocs=1)
+    mp.spawn(W.fetcher_scenario_worker, args=(1, free_port()), nprocs=1)
 
 
 @pytest.mark.parametrize('world', [1, 2])
 def test_injected_gradients_land_identically_with_a_small_replica_cache(world):
-    mp.spawn(W.inject_worker, args=(world, 29764 + world), nprocs=world)
+    mp.spawn(W.inject_worker, args=(world, free_port()), nprocs=world)
 
 
 def _simulate(scheduler, trace, chunks, blocks, check_top=None):
