@@ -32,6 +32,7 @@ reference's CPU Adam path (torch.optim.AdamW on the host cores — ColossalAI's 
 offline — next to the C oracle with all threads) on a bounded sample of the same workload.
 """
 import argparse
+import contextlib
 import json
 import os
 import re
@@ -877,12 +878,15 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
     every rank's updated shard goes back after the update (the all-gather still runs on the device)."""
     pool = min(n_chunks, 8 if world == 1 else 4)
     in_elems = shard if world == 1 else chunk
+    from elixir_b200.numa import near_gpu
     host_in, host_out = [], []
     for b in range(pool):
         gen = torch.Generator().manual_seed(args.seed + 104729 * (b + 1) + rank)
         g = torch.empty(in_elems, dtype=torch.float32).normal_(0.0, sigma, generator=gen).mul_(scale).to(dtype)
-        host_in.append(g.pin_memory())
-        host_out.append(torch.empty(shard, dtype=dtype).pin_memory())
+        # pinned buffers on the GPU's own NUMA node where this process may run there (--no-numa: wherever it runs)
+        with (contextlib.nullcontext(set()) if args.no_numa else near_gpu(device)) as numa_cpus:
+            host_in.append(g.pin_memory())
+            host_out.append(torch.empty(shard, dtype=dtype).pin_memory())
     grads = [host_in[c % pool] for c in range(n_chunks)]
     outs = [host_out[c % pool] for c in range(n_chunks)]
     conservative_ms = None
@@ -932,6 +936,7 @@ def run_e2e(args, engine, world, rank, device, dtype, n_chunks, shard, chunk, sc
                 'H2D into the gradient slab + ChunkStepEngine.step_sharded_staged + D2H of the shards'
                 if args.collective == 'staged' else 'ChunkStepEngine.step_sharded(host_grads=, host_params=)'),
         'h2d_gbs_per_gpu': n_chunks * in_elems * 2 / (ms * 1e-3) / 1e9,
+        'pinned_on_gpu_numa_node': bool(numa_cpus),
         'note': ('pinned fp16 gradients in, updated fp16 parameters out; fp32 master and moments stay in HBM; the host '
                  f'side is a pool of {pool} pinned buffers per direction reused over the chunks (every byte is still moved '
                  'every step)' + ('' if world == 1 else '; every rank uploads its own full-size gradient block of every '
@@ -1257,6 +1262,8 @@ def main():
     ap.add_argument('--no-parity-check', action='store_true',
                     help='N > 1: skip the small sharded case that is checked against the CPU oracle before the warm-up')
     ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--no-numa', action='store_true',
+                    help='end-to-end leg: do not move to the CPUs of the GPU\'s NUMA node while the pinned buffers are allocated')
     ap.add_argument('--no-speculation', action='store_true',
                     help='N=1 end-to-end leg: only the step that updates nothing before the last gradient is probed')
     ap.add_argument('--shards', choices=['device', 'host', 'host-streamed'], default='device',

@@ -279,3 +279,22 @@ def test_single_pass_step_bookkeeping_equals_the_two_phase_step(host_backend):
     for sa, sb in zip(a.shards, b.shards):
         for x, y in zip(sa[:4], sb[:4]):
             assert torch.equal(x, y)
+
+
+def test_near_gpu_narrows_the_affinity_and_restores_it(monkeypatch):
+    """``numa.near_gpu``: inside the block the thread runs on the CPUs of the GPU's NUMA node, afterwards on those it
+    had before; with the node unknown nothing changes.  The sysfs lookup is replaced by a fake."""
+    import os
+    from elixir_b200 import numa
+    assert numa._parse_cpulist('0-3,8,10-11\n') == {0, 1, 2, 3, 8, 10, 11}
+    assert numa._parse_cpulist('') == set()
+    before = os.sched_getaffinity(0)
+    one = {min(before)}
+    monkeypatch.setattr(numa, 'gpu_numa_cpus', lambda device: one)
+    with numa.near_gpu(0) as cpus:
+        assert cpus == one and os.sched_getaffinity(0) == one
+    assert os.sched_getaffinity(0) == before
+    monkeypatch.setattr(numa, 'gpu_numa_cpus', lambda device: set())
+    with numa.near_gpu(0) as cpus:
+        assert cpus == set() and os.sched_getaffinity(0) == before
+    assert os.sched_getaffinity(0) == before
