@@ -43,6 +43,22 @@ __device__ __noinline__ GroupK derive_group(const ElxHyper& h, int step) {
     return k;
 }
 
+// IEEE division and square root whose zero operands never reach the instruction sequence: __fdiv_rn and
+// __fsqrt_rn handle a zero (like a denormal) on a slow path that a whole warp takes when one lane needs it, and
+// states with many exact zeros -- moments of parameters that never had a gradient -- made a launch take twice as
+// long (14.2 ms against 7.2 ms on an all-zero state).  For x = +-0 and y > 0 (inf included) the quotient is x itself,
+// and the square root of +-0 is itself: the same bits as the plain operations, for every input.
+__device__ __forceinline__ float div_or_zero(float x, float y) {
+    const bool zero = x == 0.0f && y > 0.0f;
+    const float q = __fdiv_rn(zero ? 1.0f : x, y);
+    return zero ? x : q;
+}
+__device__ __forceinline__ float sqrt_or_zero(float x) {
+    const bool zero = x == 0.0f;
+    const float r = __fsqrt_rn(zero ? 1.0f : x);
+    return zero ? x : r;
+}
+
 // How the gradient is unscaled in this launch.
 enum { kNoDiv = 0, kMulInv = 1, kTrueDiv = 2 };
 
@@ -50,16 +66,16 @@ template <int MATH>
 __device__ __forceinline__ void adam_elem(float& p, float& m, float& v, float g, const GroupK& k, int div_mode,
                                           float div, float inv_div) {
     if (div_mode == kMulInv) g *= inv_div;                    // exact: the divisor is a power of two
-    else if (div_mode == kTrueDiv) g = __fdiv_rn(g, div);
+    else if (div_mode == kTrueDiv) g = div_or_zero(g, div);
     g = fmaf(k.wd_l2, p, g);
     m = fmaf(k.beta1, m, k.omb1 * g);
     v = fmaf(k.beta2, v, (k.omb2 * g) * g);
     float upd;
     if constexpr (MATH == 1) {
-        float mhat = __fdiv_rn(m, k.bc1);
-        float vhat = __fdiv_rn(v, k.bc2);
-        float denom = __fsqrt_rn(vhat) + k.eps;
-        upd = __fdiv_rn(mhat, denom);
+        float mhat = div_or_zero(m, k.bc1);
+        float vhat = div_or_zero(v, k.bc2);
+        float denom = sqrt_or_zero(vhat) + k.eps;
+        upd = div_or_zero(mhat, denom);
     } else {
         float mhat = m * k.rbc1;
         float vhat = v * k.rbc2;

@@ -339,6 +339,51 @@ def test_adam_chunk_ill_conditioned_update_no_worse_than_strict_fp32(K, oracle, 
         assert (err_gpu[bad] <= 8 * err_f32[bad] + bound[bad]).all()
 
 
+@pytest.mark.parametrize('hyper_kw', [HYPERS[0], HYPERS[-1], dict(lr=1e-3, betas=(0.9, 0.999), eps=0.0, weight_decay=0.0)])
+def test_adam_elements_whose_state_and_gradient_are_zero(K, oracle, cuda, hyper_kw):
+    """Exact zeros (+0 and -0) in gradient and moments take a short cut around the IEEE division and square root
+    (whose zero operands cost a slow path): the results must be what the plain operations give -- zero moments stay
+    zero, everything within the tolerance of the double-precision oracle, and with eps = 0 the
+    0 / 0 of such an element is the NaN it is in the reference arithmetic."""
+    n = 3 * 4096 + 50
+    gen = torch.Generator().manual_seed(11)
+    p = torch.randn(n, generator=gen) * 0.05
+    m = torch.randn(n, generator=gen) * 1e-3
+    v = torch.rand(n, generator=gen) * 1e-6
+    g = (torch.randn(n, generator=gen) * 1e-3).to(torch.float16)
+    mask = torch.rand(n, generator=gen) < 0.5
+    neg = mask & (torch.rand(n, generator=gen) < 0.3)
+    m[mask], v[mask], g[mask] = 0.0, 0.0, 0.0
+    m[neg] = -0.0
+    g[neg] = -0.0
+    h = K.hyper(**hyper_kw)
+    cfg = K.scaler_cfg(False)
+    dp, dm, dv, dg = (t.to(cuda) for t in (p, m, v, g))
+    ref = [t.clone() for t in (p, m, v)]
+    f32 = [t.clone() for t in (p, m, v)]
+    dev_ctl, host_ctl = K.ControlBlock(cuda, 1.0), oracle.new_ctl(1.0)
+    # with eps = 0 the zero elements turn into NaN in the first step (and everything they touch in the second)
+    for _ in range(1 if hyper_kw['eps'] == 0.0 else 2):
+        K.step_begin(dev_ctl, cfg)
+        oracle.step_begin(host_ctl, cfg)
+        K.adam_chunk(dp, dm, dv, dg.clone(), h, dev_ctl)
+        oracle.adam(ref[0], ref[1], ref[2], g, h, host_ctl.step, host_ctl.div_scale, f64=True)
+        oracle.adam(f32[0], f32[1], f32[2], g, h, host_ctl.step, host_ctl.div_scale, f64=False)
+    got_p, got_m, got_v = dp.cpu(), dm.cpu(), dv.cpu()
+    # zero moments stay exact zeros, as in the strict fp32 evaluation
+    assert (got_m[mask] == 0).all() and (got_v[mask] == 0).all()
+    assert (f32[1][mask] == 0).all() and (f32[2][mask] == 0).all()
+    if hyper_kw['eps'] == 0.0:
+        # 0 / (sqrt(0) + 0): NaN in the reference arithmetic, NaN here
+        assert torch.isnan(got_p[mask]).all() and torch.isnan(f32[0][mask]).all()
+        keep = ~mask
+    else:
+        keep = torch.ones(n, dtype=torch.bool)
+    for name, got, want in (('master', got_p, ref[0]), ('exp_avg', got_m, ref[1]), ('exp_avg_sq', got_v, ref[2])):
+        ok, ratio = close_1e6(got[keep], want[keep])
+        assert ok, (name, ratio)
+
+
 @pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
 def test_adam_chunk_padding_is_only_refreshed(K, oracle, cuda, dtype):
     n, n_valid = 6 * 4096, 2 * 4096 + 33
