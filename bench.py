@@ -18,10 +18,14 @@ memory (``p2p-fused``), from 4 ranks on ONE kernel that reduces, updates and gat
 NVLink switch (``mm``); otherwise, and as fall-back, the pull reduce-scatter kernel and the update + push
 all-gather kernel (``p2p``).  Also: ``p2p-overlap``, copy-engine staged (``staged``), NCCL on side streams
 (``nccl``).  ``--workload opt66b_bf16``: the OPT-66B-shaped bf16 set; ``--workload residency``: one training
-iteration through the wrapper under three residency modes.
+iteration through the wrapper under three residency modes; ``--workload probe-rate``: the inf/nan probe alone, its
+load/store form against its bulk-copy ring.  ``--tune KNOB=VALUE`` sets a launch-shape knob of the library for the run
+(e.g. ``adam_tma_stages=3``, ``probe_variant=0``) and is named in ``config.tuning``.
 
 Prints ONE JSON line (rank 0).  ``value`` is whole-job parameters per second with all inputs resident
-in HBM; ``e2e`` is the same step through an engine method that takes pinned host buffers on both ends
+in HBM; ``roofline`` (N = 1) is the update launch against the pool-wide measured copy peak, with the DRAM traffic an
+ncu capture of a small case counted (scaled; the summary under ``profiles/`` is read at run time) and the rate of a
+device-to-device copy on the GPU of the run beside it; ``e2e`` is the same step through an engine method that takes pinned host buffers on both ends
 (gradients in, updated low-precision parameters out: ``step_from_host`` at N = 1, ``step_sharded_p2p`` /
 ``step_sharded_single_pass`` with ``host_grads=`` / ``host_params=`` at N > 1); at N = 1 it is the single-pass
 form (updates start while gradients still arrive and are dropped if an overflow turns up), with the plain
