@@ -533,6 +533,10 @@ __global__ void __launch_bounds__(kTmaBlock, 1) adam_tma_kernel(const __grid_con
     extern __shared__ __align__(128) unsigned char s_dyn[];
     __shared__ GroupStore s_group[kMaxGroups];
     __shared__ TileSlot s_slot[kTmaStages];
+    // the ring plus everything static has to fit the 227 KB a CTA may have (the four-stage ring leaves 3 KB)
+    static_assert(kTmaStages * kStageBytes + sizeof(GroupStore) * kMaxGroups + sizeof(TileSlot) * kTmaStages +
+                          2 * sizeof(uint64_t) * kTmaStages + 64 <= 227 * 1024,
+                  "ring and static shared memory exceed a CTA's shared memory");
     __shared__ __align__(8) uint64_t s_full[kTmaStages];   // the loads of a stage have landed (and its slot is published)
     __shared__ __align__(8) uint64_t s_done[kTmaStages];   // the computing warps are through with a stage
     __shared__ int s_abort;
